@@ -1,0 +1,278 @@
+"""Lower a transfer plan plus the converter's row maps into copy items.
+
+The planner speaks in *canonical* tensors: "send rows [a, b) of the training
+rank's converted tensor".  A converted tensor is never materialised here;
+:class:`awex_b200.converter.rows.Rows` says which physical training tensor and
+which of its rows each canonical row is.  Lowering intersects every planned
+box with those row runs and emits :class:`CopyItem` objects — plain N-d box
+copies from a *local training parameter* to a *named destination view* on an
+inference rank, with an optional value transform (cast, constant add, block
+fp8 quantisation).
+
+Re-homing: when a canonical tensor draws rows from tensor-parallel peers (the
+default fused-QKV regroup does), the plan's sender for a box may not hold the
+bytes.  Every training rank therefore also walks the plans of its TP peers for
+such tensors and keeps the pieces whose rows it physically owns.  The bytes
+that reach each destination element are exactly those the planned sender
+would have sent after an all-gather, so results are bit-identical to the
+gather-then-send pipeline of the reference (`awex/writer/nccl_writer.py:197-304`,
+`awex/converter/mcore_converter.py:1040-1052`) without the collective.
+
+Copy items are the common currency of all data planes: the CPU executor
+(:mod:`awex_b200.transfer.cpu_exec`) runs them with ``copy_``; the fused CUDA
+path encodes them into flat descriptors (:mod:`awex_b200.transfer.descriptors`).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+from awex_b200 import logging
+from awex_b200.converter.rows import IDENTITY, Rows, TensorSpec, ValueOp
+from awex_b200.converter.weights_converter import FP8_BLOCK, SCALE_SUFFIX
+from awex_b200.meta.weight_meta import ParameterMeta, ParameterShardMeta
+from awex_b200.sharding.rank_info import RankInfo
+from awex_b200.transfer.transfer_plan import CommunicationOperation, TransferPlanBuilder
+
+logger = logging.getLogger(__name__)
+
+
+@dataclass(slots=True)
+class CopyItem:
+    """Copy ``extent`` elements starting at ``src_start`` of local training
+    parameter ``src_param`` (chunk ``vp_stage``) to ``dst_start`` of the view
+    named ``dst_name`` on inference transfer rank ``dst_rank``."""
+
+    src_param: str
+    vp_stage: int
+    src_start: Tuple[int, ...]
+    extent: Tuple[int, ...]
+    dst_rank: int
+    dst_name: str
+    dst_start: Tuple[int, ...]
+    src_dtype: torch.dtype
+    dst_dtype: torch.dtype
+    value_op: ValueOp = IDENTITY
+    # fp8_block only: destination of the block scales and the block coordinates
+    # of this item's origin inside that scale tensor
+    scale_name: Optional[str] = None
+    scale_start: Tuple[int, int] = (0, 0)
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for e in self.extent:
+            n *= e
+        return n
+
+    @property
+    def dst_bytes(self) -> int:
+        return self.numel * self.dst_dtype.itemsize
+
+    def manifest_entry(self) -> tuple:
+        return (self.dst_name, self.dst_start, self.extent, str(self.dst_dtype), self.scale_name, self.scale_start)
+
+
+@dataclass
+class LocalParam:
+    name: str
+    vp_stage: int
+    shape: Tuple[int, ...]
+    dtype: torch.dtype
+
+
+def _tp_peers(my: RankInfo, all_ranks: Sequence[RankInfo]) -> List[RankInfo]:
+    """Training ranks that hold the other TP shards of what ``my`` holds."""
+    if my.tp_size <= 1:
+        return [my]
+    peers = [
+        r for r in all_ranks
+        if (r.pp_rank, r.dp_rank, r.cp_rank) == (my.pp_rank, my.dp_rank, my.cp_rank) and r.tp_size == my.tp_size
+    ]
+    if len({r.tp_rank for r in peers}) != my.tp_size or len(peers) != my.tp_size:
+        # EP-style layouts can give several ranks per (pp, dp, cp, tp); keep the
+        # ones that also share the expert coordinates, always including ``my``
+        peers = [r for r in peers if (r.ep_rank, r.ep_tp_rank) == (my.ep_rank, my.ep_tp_rank) or r.global_rank == my.global_rank]
+        by_tp: Dict[int, RankInfo] = {}
+        for r in sorted(peers, key=lambda x: x.global_rank != my.global_rank):
+            by_tp.setdefault(r.tp_rank, r)
+        peers = list(by_tp.values())
+    return sorted(peers, key=lambda r: r.tp_rank)
+
+
+class SendProgramCompiler:
+    """Builds the list of :class:`CopyItem` one training rank executes per update."""
+
+    def __init__(
+        self,
+        rank_info: RankInfo,
+        all_train_ranks: Sequence[RankInfo],
+        converter_factory: Callable[[RankInfo], object],
+        local_params: Sequence[LocalParam],
+        infer_meta: Sequence[ParameterMeta],
+        train_meta: Sequence[ParameterMeta],
+        builder: TransferPlanBuilder,
+    ):
+        self.rank_info = rank_info
+        self.peers = _tp_peers(rank_info, all_train_ranks)
+        self.converter_factory = converter_factory
+        self.local_params = list(local_params)
+        self.infer_meta = {m.name: m for m in infer_meta}
+        self.train_meta = {m.name: m for m in train_meta}
+        self.infer_meta_list = list(infer_meta)
+        self.train_meta_list = list(train_meta)
+        self.builder = builder
+        self.my_transfer_rank = rank_info.global_rank + builder.infer_world_size
+        self._param_by_key = {(p.name, p.vp_stage): p for p in self.local_params}
+
+    # ---- symbolic conversion for one (possibly virtual) sender ----------------------------
+    def _specs_for(self, sender: RankInfo) -> Dict[str, Tuple[TensorSpec, LocalParam]]:
+        converter = self.converter_factory(sender)
+        tied = bool(getattr(converter.hf_config, "tie_word_embeddings", False))
+        out: Dict[str, Tuple[TensorSpec, LocalParam]] = {}
+        for lp in self.local_params:
+            for spec in converter.plan_param(lp.name, lp.shape, lp.dtype, vp_stage=lp.vp_stage):
+                out[spec.name] = (spec, lp)
+        if tied and sender.pp_rank == sender.pp_size - 1 and "lm_head.weight" not in out and "model.embed_tokens.weight" in out:
+            spec, lp = out["model.embed_tokens.weight"]
+            out["lm_head.weight"] = (dataclasses.replace(spec, name="lm_head.weight"), lp)
+        return out
+
+    def compile(self) -> List[CopyItem]:
+        my_tp = self.rank_info.tp_rank
+        items: List[CopyItem] = []
+        own_plan = self.builder.build_local_transfer_plan(self.infer_meta_list, self.train_meta_list, self.my_transfer_rank)
+        for sender in self.peers:
+            specs = self._specs_for(sender)
+            is_me = sender.global_rank == self.rank_info.global_rank
+            if is_me:
+                ops = own_plan.all_operations()
+            else:
+                # only tensors that draw rows from this rank need the peer's plan
+                names = [
+                    n for n, (spec, _) in specs.items()
+                    if spec.rows is not None and any(src[1] == my_tp for src in spec.rows.sources() if isinstance(src, tuple) and src[0] != "__scale__")
+                    and n in self.train_meta and n in self.infer_meta
+                ]
+                virtual_rank = sender.global_rank + self.builder.infer_world_size
+                ops = []
+                for n in sorted(names):
+                    ops.extend(
+                        op for op in self.builder._build_parameter_communication_plan(
+                            n, self.infer_meta[n], self.train_meta[n], global_transfer_rank=virtual_rank
+                        ) if op.send_rank == virtual_rank
+                    )
+                ops.sort(key=lambda op: (op.recv_rank, op.send_shard_meta.name, op.send_offset, op.recv_offset))
+            for op in ops:
+                name = op.send_shard_meta.name
+                if name not in specs:
+                    if is_me:
+                        raise KeyError(f"plan asks rank {self.my_transfer_rank} for {name!r}, which its model does not produce")
+                    continue
+                items.extend(self._lower_op(op, *specs[name], my_tp))
+        items.sort(key=lambda it: (it.dst_rank, it.dst_name, it.dst_start, it.src_param, it.src_start))
+        return items
+
+    # ---- one planned box -> copy items ----------------------------------------------------------
+    def _lower_op(self, op: CommunicationOperation, spec: TensorSpec, lp: LocalParam, my_tp: int) -> List[CopyItem]:
+        if spec.scale_of is not None:
+            return []  # scales are produced together with their weight
+        dst_dtype = op.recv_shard_meta.dtype
+        if spec.rows is None:  # 0-d
+            return [CopyItem(lp.name, lp.vp_stage, (), (), op.recv_rank, spec.name, (), spec.src_dtype, dst_dtype, spec.value_op)]
+        row0 = op.train_slices[0].start
+        n_rows = op.overlap_shape[0]
+        tail_src = tuple(s.start for s in op.train_slices[1:])
+        tail_dst = tuple(s.start for s in op.inf_slices[1:])
+        tail_ext = tuple(op.overlap_shape[1:])
+        dst_row0 = op.inf_slices[0].start
+        out: List[CopyItem] = []
+        for rel, src, src_row, n in spec.rows.segments(row0, n_rows):
+            pname, tp_rank = src
+            if tp_rank != my_tp:
+                continue  # a TP peer owns these rows and sends them itself
+            if pname != lp.name:
+                lp_src = self._param_by_key[(pname, lp.vp_stage)]
+            else:
+                lp_src = lp
+            item = CopyItem(
+                src_param=lp_src.name, vp_stage=lp_src.vp_stage, src_start=(src_row,) + tail_src,
+                extent=(n,) + tail_ext, dst_rank=op.recv_rank, dst_name=spec.name,
+                dst_start=(dst_row0 + rel,) + tail_dst, src_dtype=spec.src_dtype, dst_dtype=dst_dtype,
+                value_op=spec.value_op,
+            )
+            if spec.value_op.kind == "fp8_block":
+                if len(item.extent) != 2:
+                    raise ValueError(f"{spec.name}: block fp8 needs a 2-D tensor, got extent {item.extent}")
+                if item.dst_start[0] % FP8_BLOCK or item.dst_start[1] % FP8_BLOCK:
+                    raise ValueError(
+                        f"{spec.name}: a piece starting at {item.dst_start} of the destination shard does not start on a "
+                        f"{FP8_BLOCK}x{FP8_BLOCK} block; its block would mix rows of several senders"
+                    )
+                shard = op.recv_shard_meta.shape
+                for d in (0, 1):
+                    end = item.dst_start[d] + item.extent[d]
+                    if end % FP8_BLOCK and end != shard[d]:
+                        raise ValueError(f"{spec.name}: piece ends inside a block at {end} (dim {d}, shard extent {shard[d]})")
+                item.scale_name = spec.name + SCALE_SUFFIX
+                item.scale_start = (item.dst_start[0] // FP8_BLOCK, item.dst_start[1] // FP8_BLOCK)
+            elif spec.value_op.kind == "l2norm_dim0":
+                raise NotImplementedError(f"{spec.name}: column-normalised tensors must be materialised before transfer")
+            out.append(item)
+        return out
+
+
+def manifest_by_destination(items: Iterable[CopyItem]) -> Dict[int, List[tuple]]:
+    """What each destination rank will receive from this sender, as plain
+    tuples that can be published through the MetaServer."""
+    out: Dict[int, List[tuple]] = {}
+    for it in items:
+        out.setdefault(it.dst_rank, []).append(it.manifest_entry())
+    return out
+
+
+def check_exactly_once(
+    manifests: Iterable[Sequence[tuple]],
+    views: Dict[str, Tuple[Tuple[int, ...], torch.dtype]],
+    required: Optional[Iterable[str]] = None,
+) -> List[str]:
+    """Host-side race/coverage check of everything that will be written into one
+    inference rank: every element of every required view is written exactly once
+    and nothing is written out of bounds.  Returns a list of problems."""
+    problems: List[str] = []
+    masks: Dict[str, torch.Tensor] = {}
+
+    def mark(name: str, start, extent, label: str) -> None:
+        if name not in views:
+            problems.append(f"{label}: write into unknown view {name!r}")
+            return
+        shape = views[name][0]
+        if len(start) != len(shape) or any(s < 0 or s + e > d for s, e, d in zip(start, extent, shape)):
+            problems.append(f"{label}: box start={start} extent={extent} exceeds {name!r} of shape {shape}")
+            return
+        mask = masks.setdefault(name, torch.zeros(shape if shape else (1,), dtype=torch.uint8))
+        region = mask[tuple(slice(s, s + e) for s, e in zip(start, extent))] if shape else mask
+        if bool(region.any()):
+            problems.append(f"{label}: box start={start} extent={extent} of {name!r} overlaps an earlier write")
+        region += 1
+
+    for sender, manifest in enumerate(manifests):
+        for name, start, extent, dtype, scale_name, scale_start in manifest:
+            if name in views and str(views[name][1]) != dtype:
+                problems.append(f"sender#{sender}: dtype {dtype} written into {name!r} of dtype {views[name][1]}")
+            mark(name, tuple(start), tuple(extent), f"sender#{sender}")
+            if scale_name is not None:
+                blocks = tuple(-(-e // FP8_BLOCK) for e in extent)
+                mark(scale_name, tuple(scale_start), blocks, f"sender#{sender}(scale)")
+    for name in required if required is not None else views:
+        mask = masks.get(name)
+        if mask is None:
+            problems.append(f"view {name!r} receives nothing")
+        elif not bool((mask == 1).all()):
+            missing = int((mask == 0).sum())
+            problems.append(f"view {name!r}: {missing} of {mask.numel()} elements are never written")
+    return problems
