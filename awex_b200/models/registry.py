@@ -7,10 +7,11 @@ entry is a class or a zero-argument factory returning a class.  Unknown
 architectures use the default strategy and converters
 (`awex/models/registry.py:49-172` in the reference).
 
-Unlike the reference, an architecture that registers only an SGLang-side
-converter gets the same canonical contract on vLLM: the SGLang converter is
-wrapped so that vLLM's ``self_attn.*`` names are normalised only when the
-training converter of that architecture emits ``attention.*`` names.
+Unlike the reference, every architecture has one canonical contract on both
+inference engines: an architecture that registers only an SGLang-side
+converter gets it on vLLM too (wrapped so that ``self_attn.*`` names are
+normalised only when that converter keeps QKV fused), and unregistered
+architectures use the name-normalising converter on SGLang as well.
 """
 
 from __future__ import annotations
@@ -148,7 +149,10 @@ class _Probe:
 def get_infer_weights_converter(engine_name: str, model_name: str, hf_config, rank_info, infer_engine_config):
     config = ModelRegistry.get_model_config(model_name)
     if engine_name == "sglang":
-        cls = _resolve_converter(_field(config, "sglang_converter"), SGlangToHFWeightConverter)
+        # unregistered architectures get the name-normalising converter on both
+        # engines, so "self_attn.qkv_proj" and "attention.query_key_value_proj"
+        # spellings meet the training side's default contract alike
+        cls = _resolve_converter(_field(config, "sglang_converter"), VLLMToHFWeightConverter)
     elif engine_name == "vllm":
         explicit = _field(config, "vllm_converter")
         sgl = _field(config, "sglang_converter")
