@@ -1,0 +1,517 @@
+// Fused resharding transfer for sm_100a.
+//
+// One persistent launch per (update, source GPU) walks a descriptor table
+// (xfer_desc.h).  Each CTA owns a contiguous range of tiles.  A tile is staged
+// from this GPU's HBM into shared memory with bulk-async copies
+// (cp.async.bulk global->shared, completion on an mbarrier) through a 6-deep
+// ring, then leaves either
+//   * unchanged, by bulk-async copies shared->global whose destination may be a
+//     peer GPU's memory mapped over NVLink (pure layout moves: slices, row
+//     permutations, column slabs), or
+//   * transformed in registers (dtype cast, constant add, 128x128 block-scaled
+//     fp8 e4m3 quantisation) and stored with 16-byte vector stores.
+// All loads read local memory; remote memory is only ever written.
+// When every CTA has drained its stores, the last one raises a per-destination
+// flag (release, system scope) carrying the update's epoch; receivers wait on
+// those flags with a bounded spin (wait_flags_kernel).  Every wait in this file
+// has a deadline after which the kernel records a status and returns.
+//
+// The reference does the same work with one ATen copy/cast kernel per slab,
+// an all-gather per fused QKV, and one NCCL send/recv pair per slab
+// (awex/transfer/nccl_comm.py:378-624, awex/converter/mcore_converter.py:1040-1052).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "xfer_desc.h"
+
+namespace awex {
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// global -> shared, completion counted in bytes on an mbarrier of this CTA
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
+               "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// shared -> global (local or peer-mapped), tracked by the thread's bulk group
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// ---------------------------------------------------------------- element helpers
+__device__ __forceinline__ uint32_t dtype_size(uint32_t dt) {
+  return dt == DT_F32 ? 4u : (dt == DT_BF16 || dt == DT_F16) ? 2u : 1u;
+}
+__device__ __forceinline__ float load_as_float(const unsigned char* p, uint32_t dt) {
+  switch (dt) {
+    case DT_BF16: return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+    case DT_F16: return __half2float(*reinterpret_cast<const __half*>(p));
+    case DT_F32: return *reinterpret_cast<const float*>(p);
+    case DT_FP8_E4M3: {
+      __half_raw h = __nv_cvt_fp8_to_halfraw(*p, __NV_E4M3);
+      return __half2float(*reinterpret_cast<__half*>(&h));
+    }
+    default: return static_cast<float>(*p);
+  }
+}
+__device__ __forceinline__ void store_from_float(unsigned char* p, uint32_t dt, float v) {
+  switch (dt) {
+    case DT_BF16: *reinterpret_cast<__nv_bfloat16*>(p) = __float2bfloat16_rn(v); break;
+    case DT_F16: *reinterpret_cast<__half*>(p) = __float2half_rn(v); break;
+    case DT_F32: *reinterpret_cast<float*>(p) = v; break;
+    case DT_FP8_E4M3: *p = static_cast<unsigned char>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3)); break;
+    default: *p = static_cast<unsigned char>(v); break;
+  }
+}
+
+// Position of a tile inside its slab.
+struct Tile {
+  uint64_t row0;
+  uint32_t rows;
+  uint64_t col0;  // elements
+  uint32_t cols;  // elements
+  uint32_t band, ct;
+};
+__device__ __forceinline__ Tile tile_of(const XferDesc& d, uint64_t k) {
+  Tile t;
+  t.band = static_cast<uint32_t>(k / d.col_tiles);
+  t.ct = static_cast<uint32_t>(k % d.col_tiles);
+  t.row0 = static_cast<uint64_t>(t.band) * d.tile_rows;
+  t.col0 = static_cast<uint64_t>(t.ct) * d.tile_cols;
+  uint64_t r = d.rows - t.row0;
+  uint64_t c = d.row_elems - t.col0;
+  t.rows = r < d.tile_rows ? static_cast<uint32_t>(r) : d.tile_rows;
+  t.cols = c < d.tile_cols ? static_cast<uint32_t>(c) : d.tile_cols;
+  return t;
+}
+__device__ __forceinline__ uint32_t stage_pitch(const XferDesc& d) {
+  return (d.tile_cols * dtype_size(d.src_dtype) + 15u) & ~15u;
+}
+
+// Descriptor cursor: tile number -> (descriptor, tile inside it), advanced monotonically.
+struct Cursor {
+  uint32_t di;
+  uint64_t begin, end;  // tile range of descs[di]
+};
+__device__ __forceinline__ void cursor_seek(Cursor& c, const XferParams& p, uint64_t tile) {
+  uint32_t lo = 0, hi = p.n_desc - 1;
+  while (lo < hi) {  // last descriptor whose tile_begin <= tile
+    uint32_t mid = (lo + hi + 1) >> 1;
+    if (p.descs[mid].tile_begin <= tile) lo = mid; else hi = mid - 1;
+  }
+  c.di = lo;
+  c.begin = p.descs[lo].tile_begin;
+  c.end = (lo + 1 < p.n_desc) ? p.descs[lo + 1].tile_begin : p.n_tiles;
+}
+__device__ __forceinline__ void cursor_advance_to(Cursor& c, const XferParams& p, uint64_t tile) {
+  while (tile >= c.end) {
+    ++c.di;
+    c.begin = c.end;
+    c.end = (c.di + 1 < p.n_desc) ? p.descs[c.di + 1].tile_begin : p.n_tiles;
+  }
+}
+
+// ---------------------------------------------------------------- tile bodies
+// Elementwise path straight from global memory (unaligned slabs, rare dtypes).
+__device__ void tile_elementwise_global(const XferDesc& d, const Tile& t) {
+  const uint32_t ses = dtype_size(d.src_dtype), des = dtype_size(d.dst_dtype);
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src);
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
+  const uint64_t n = static_cast<uint64_t>(t.rows) * t.cols;
+  const float addend = d.op == OP_ADD ? static_cast<float>(d.aux_f) : 0.f;
+  for (uint64_t e = threadIdx.x; e < n; e += blockDim.x) {
+    uint32_t r = static_cast<uint32_t>(e / t.cols), c = static_cast<uint32_t>(e % t.cols);
+    const unsigned char* s = src + (t.row0 + r) * d.src_stride + (t.col0 + c) * ses;
+    unsigned char* o = dst + (t.row0 + r) * d.dst_stride + (t.col0 + c) * des;
+    if (d.op == OP_COPY) *o = *s;
+    else store_from_float(o, d.dst_dtype, load_as_float(s, d.src_dtype) + addend);
+  }
+}
+
+// Elementwise path from a staged tile.
+__device__ void tile_elementwise_staged(const XferDesc& d, const Tile& t, const unsigned char* stage) {
+  const uint32_t ses = dtype_size(d.src_dtype), des = dtype_size(d.dst_dtype);
+  const uint32_t pitch = stage_pitch(d);
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
+  const uint32_t n = t.rows * t.cols;
+  const float addend = d.op == OP_ADD ? static_cast<float>(d.aux_f) : 0.f;
+  for (uint32_t e = threadIdx.x; e < n; e += blockDim.x) {
+    uint32_t r = e / t.cols, c = e % t.cols;
+    float v = load_as_float(stage + r * pitch + c * ses, d.src_dtype) + addend;
+    store_from_float(dst + (t.row0 + r) * d.dst_stride + (t.col0 + c) * des, d.dst_dtype, v);
+  }
+}
+
+// NaN-propagating |x| maximum, as torch.amax does.
+__device__ __forceinline__ float amax_step(float m, float x) {
+  float a = fabsf(x);
+  return (a > m || a != a) ? a : m;
+}
+
+// scale = max(amax, 1e-4) / 448, optionally rounded up to a power of two the
+// way fp32 log2 -> ceil -> exp2 does.
+__device__ __forceinline__ float block_scale(float amax, bool ue8m0) {
+  float s = (amax < 1e-4f ? 1e-4f : amax) / 448.0f;
+  if (ue8m0) {
+    float clamped = s < 1e-10f ? 1e-10f : s;
+    float l = static_cast<float>(log2(static_cast<double>(clamped)));
+    s = exp2f(ceilf(l));
+  }
+  return s;
+}
+
+// One 128x128 (or smaller edge) block: amax over the block, then q = x / scale.
+// `row_ptr(r)` gives the address of source row r of the block.
+template <typename RowPtr>
+__device__ void tile_fp8_block(const XferDesc& d, const Tile& t, RowPtr row_ptr, float* red /*[8]*/) {
+  const uint32_t ses = dtype_size(d.src_dtype);
+  const uint32_t row = threadIdx.x >> 1, half = threadIdx.x & 1;  // two threads per row, 64 columns each
+  const uint32_t c_begin = half * 64u;
+  const uint32_t c_end = min(c_begin + 64u, t.cols);
+  const bool active = row < t.rows && c_begin < t.cols;
+  float vals[64];
+  float m = 0.f;
+  if (active) {
+    const unsigned char* s = row_ptr(row) + c_begin * ses;
+    if (d.src_dtype == DT_BF16 && c_end - c_begin == 64u && (reinterpret_cast<uintptr_t>(s) & 15u) == 0) {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        uint4 raw = reinterpret_cast<const uint4*>(s)[v];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(h[j]);
+          vals[v * 8 + j * 2] = f.x;
+          vals[v * 8 + j * 2 + 1] = f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) vals[c] = (c_begin + c < c_end) ? load_as_float(s + c * ses, d.src_dtype) : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < 64; ++c) m = amax_step(m, vals[c]);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    float o = __shfl_xor_sync(0xffffffffu, m, off);
+    m = (o > m || o != o) ? o : m;
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  float amax = red[0];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) {
+    float o = red[w];
+    amax = (o > amax || o != o) ? o : amax;
+  }
+  const float scale = block_scale(amax, (d.flags & FLAG_UE8M0) != 0);
+  if (threadIdx.x == 0) {
+    float* sp = reinterpret_cast<float*>(d.aux_ptr) + static_cast<int64_t>(t.band) * d.aux_stride + t.ct;
+    *sp = scale;
+  }
+  if (active) {
+    unsigned char* o = reinterpret_cast<unsigned char*>(d.dst) + (t.row0 + row) * d.dst_stride + t.col0 + c_begin;
+    if ((d.flags & FLAG_DST_VEC16) && c_end - c_begin == 64u) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float* f = &vals[v * 16 + j * 4];
+          uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(f[0], scale), __fdiv_rn(f[1], scale)), __NV_SATFINITE, __NV_E4M3);
+          uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(f[2], scale), __fdiv_rn(f[3], scale)), __NV_SATFINITE, __NV_E4M3);
+          w[j] = lo | (hi << 16);
+        }
+        reinterpret_cast<uint4*>(o)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; ++c)
+        if (c_begin + c < c_end)
+          o[c] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(__fdiv_rn(vals[c], scale), __NV_SATFINITE, __NV_E4M3));
+    }
+  }
+  __syncthreads();  // `red` is reused by the next block
+}
+
+// ---------------------------------------------------------------- the kernel
+__device__ __forceinline__ bool wants_stage(const XferDesc& d) { return (d.flags & FLAG_BULK) != 0; }
+
+__global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __grid_constant__ XferParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ float red[kThreads / 32];
+  __shared__ volatile int abort_flag;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_addr(&full_bar[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // Wait until every destination has announced this epoch (its engine is paused
+  // and its parameters may be overwritten).
+  if (p.n_ready) {
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = threadIdx.x; i < p.n_ready; i += blockDim.x) {
+      const uint64_t* flag = p.ready_pad + p.ready_slots[i];
+      while (ld_acquire_sys(flag) < p.epoch) {
+        if (globaltimer_ns() - t0 > p.timeout_ns) {
+          if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_READY_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(p.ready_slots[i]);
+          abort_flag = 1;
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    __syncthreads();
+    if (abort_flag) return;  // nothing in flight yet
+  }
+
+  const uint64_t t_begin = p.n_tiles * blockIdx.x / gridDim.x;
+  const uint64_t t_end = p.n_tiles * (blockIdx.x + 1) / gridDim.x;
+  const uint64_t n = t_end - t_begin;
+
+  if (n > 0) {
+    Cursor load_cur, use_cur;
+    cursor_seek(load_cur, p, t_begin);
+    use_cur = load_cur;
+
+    // Stage tile j (relative number) of this CTA.  Executed by warp 0.
+    auto issue_load = [&](uint64_t j) {
+      cursor_advance_to(load_cur, p, t_begin + j);
+      const XferDesc d = p.descs[load_cur.di];
+      const uint32_t stage = static_cast<uint32_t>(j % kStages);
+      const uint32_t bar = smem_addr(&full_bar[stage]);
+      if (!wants_stage(d)) {
+        if (lane == 0) mbar_arrive(bar);  // keeps the ring's phases in step
+        return;
+      }
+      const Tile t = tile_of(d, t_begin + j - load_cur.begin);
+      const uint32_t ses = dtype_size(d.src_dtype);
+      const uint32_t pitch = stage_pitch(d);
+      const uint32_t bytes = t.cols * ses;
+      if (lane == 0) mbar_arrive_expect_tx(bar, bytes * t.rows);
+      __syncwarp();
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.row0 * d.src_stride + t.col0 * ses;
+      const uint32_t base = smem_addr(smem + static_cast<size_t>(stage) * kStageBytes);
+      for (uint32_t r = lane; r < t.rows; r += 32) bulk_load(base + r * pitch, src + static_cast<int64_t>(r) * d.src_stride, bytes, bar);
+    };
+
+    if (warp == 0)
+      for (uint64_t j = 0; j < kLookahead && j < n; ++j) issue_load(j);
+
+    for (uint64_t i = 0; i < n && !abort_flag; ++i) {
+      cursor_advance_to(use_cur, p, t_begin + i);
+      const XferDesc d = p.descs[use_cur.di];
+      const Tile t = tile_of(d, t_begin + i - use_cur.begin);
+      const uint32_t stage = static_cast<uint32_t>(i % kStages);
+      const uint32_t parity = static_cast<uint32_t>((i / kStages) & 1);
+      const uint32_t bar = smem_addr(&full_bar[stage]);
+      unsigned char* stage_ptr = smem + static_cast<size_t>(stage) * kStageBytes;
+
+      if (warp == 0) {
+        // The stage that tile i+lookahead will use was last read by the stores of
+        // tile i-2: allow only the most recent store group to be still reading.
+        bulk_wait_read_1();
+        __syncwarp();
+        if (i + kLookahead < n) issue_load(i + kLookahead);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar, parity)) {
+          if (globaltimer_ns() - t0 > p.timeout_ns) {
+            if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
+            abort_flag = 1;
+            break;
+          }
+        }
+      }
+
+      const bool staged = wants_stage(d);
+      if (d.op == OP_COPY && staged) {
+        if (warp == 0 && !abort_flag) {
+          const uint32_t pitch = stage_pitch(d);
+          const uint32_t bytes = t.cols;  // OP_COPY counts bytes
+          unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
+          const uint32_t base = smem_addr(stage_ptr);
+          for (uint32_t r = lane; r < t.rows; r += 32) bulk_store(dst + static_cast<int64_t>(r) * d.dst_stride, base + r * pitch, bytes);
+          bulk_commit();
+        }
+        continue;  // other warps have nothing to do for pure copies
+      }
+      if (warp == 0) bulk_commit();  // an empty group keeps "one group per tile"
+
+      __syncthreads();  // staged data (observed by warp 0) is ordered before everyone's reads
+      if (abort_flag) break;
+      if (d.op == OP_FP8_BLOCK) {
+        if (staged) {
+          const uint32_t pitch = stage_pitch(d);
+          tile_fp8_block(d, t, [&](uint32_t r) { return static_cast<const unsigned char*>(stage_ptr) + r * pitch; }, red);
+        } else {
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.row0 * d.src_stride + t.col0 * dtype_size(d.src_dtype);
+          tile_fp8_block(d, t, [&](uint32_t r) { return src + static_cast<int64_t>(r) * d.src_stride; }, red);
+        }
+      } else if (staged) {
+        tile_elementwise_staged(d, t, stage_ptr);
+      } else {
+        tile_elementwise_global(d, t);
+      }
+      __syncthreads();  // all reads of the stage are done before it is refilled
+    }
+  }
+
+  // Drain: make this CTA's writes visible system-wide, then count it in.
+  if (warp == 0) {
+    bulk_wait_all();
+    fence_proxy_async();
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int arrived = atomicAdd(p.cta_counter, 1u) + 1u;
+    if (arrived == gridDim.x) {
+      __threadfence_system();
+      const bool ok = *reinterpret_cast<volatile int32_t*>(p.status) == ST_OK;
+      // A failed launch raises no flag: receivers time out and report instead of
+      // consuming a partial update.
+      if (ok)
+        for (uint32_t i = 0; i < p.n_done; ++i) st_release_sys(p.done_flags[i], p.epoch);
+      *p.cta_counter = 0;  // ready for the next launch on this stream
+    }
+  }
+}
+
+// Receiver side: wait (bounded) until every listed sender has raised `epoch`.
+__global__ void wait_flags_kernel(const uint64_t* pad, const uint32_t* slots, uint32_t n, uint64_t epoch, uint64_t timeout_ns,
+                                  int32_t* status) {
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint64_t* flag = pad + slots[i];
+    while (ld_acquire_sys(flag) < epoch) {
+      if (globaltimer_ns() - t0 > timeout_ns) {
+        if (atomicCAS(reinterpret_cast<int*>(status), ST_OK, ST_FLAG_TIMEOUT) == ST_OK) {
+          status[1] = static_cast<int>(slots[i]);
+          status[2] = static_cast<int>(ld_acquire_sys(flag));
+        }
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+}
+
+// Raise flags at (possibly peer-mapped) addresses, after everything this
+// stream has written so far.
+__global__ void post_flags_kernel(uint64_t* const* addrs, uint32_t n, uint64_t epoch) {
+  __threadfence_system();
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) st_release_sys(addrs[i], epoch);
+}
+
+}  // namespace awex
+
+// ---------------------------------------------------------------- host launchers
+extern "C" {
+
+int awex_xfer_desc_size() { return static_cast<int>(sizeof(awex::XferDesc)); }
+int awex_xfer_smem_bytes() { return awex::kStages * awex::kStageBytes; }
+int awex_xfer_stage_bytes() { return awex::kStageBytes; }
+
+// Returns a cudaError_t.  `grid` == 0 picks one CTA per SM.
+int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_tiles, uint64_t epoch, uint64_t timeout_ns,
+                               const void* ready_pad, const void* ready_slots, uint32_t n_ready, const void* done_flags,
+                               uint32_t n_done, void* cta_counter, void* status, int grid, void* stream) {
+  static int configured_device = -1;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  const int smem = awex::kStages * awex::kStageBytes;
+  if (configured_device != dev) {
+    err = cudaFuncSetAttribute(awex::fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return err;
+    configured_device = dev;
+  }
+  if (grid <= 0) {
+    err = cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+  }
+  if (n_tiles > 0 && static_cast<uint64_t>(grid) > n_tiles) grid = static_cast<int>(n_tiles);
+  if (grid < 1) grid = 1;
+  awex::XferParams p;
+  p.descs = static_cast<const awex::XferDesc*>(descs);
+  p.n_desc = n_desc;
+  p.n_tiles = n_desc ? n_tiles : 0;
+  p.epoch = epoch;
+  p.timeout_ns = timeout_ns;
+  p.ready_pad = static_cast<const uint64_t*>(ready_pad);
+  p.ready_slots = static_cast<const uint32_t*>(ready_slots);
+  p.n_ready = n_ready;
+  p.done_flags = static_cast<uint64_t* const*>(done_flags);
+  p.n_done = n_done;
+  p.cta_counter = static_cast<unsigned int*>(cta_counter);
+  p.status = static_cast<int32_t*>(status);
+  awex::fused_transfer_kernel<<<grid, awex::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError();
+}
+
+int awex_launch_wait_flags(const void* pad, const void* slots, uint32_t n, uint64_t epoch, uint64_t timeout_ns, void* status,
+                           void* stream) {
+  if (n == 0) return cudaSuccess;
+  awex::wait_flags_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint64_t*>(pad), static_cast<const uint32_t*>(slots), n, epoch, timeout_ns, static_cast<int32_t*>(status));
+  return cudaGetLastError();
+}
+
+int awex_launch_post_flags(const void* addrs, uint32_t n, uint64_t epoch, void* stream) {
+  if (n == 0) return cudaSuccess;
+  awex::post_flags_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint64_t* const*>(addrs), n, epoch);
+  return cudaGetLastError();
+}
+
+}  // extern "C"

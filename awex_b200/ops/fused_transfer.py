@@ -1,0 +1,155 @@
+"""Python launcher of the fused transfer kernel (``csrc/fused_transfer.cu``).
+
+A :class:`TransferProgram` is one training rank's compiled update: a descriptor
+table resident on the device, the flags it must see before writing (one per
+destination, raised by the reader when its engine is paused) and the flags it
+raises when its writes are complete.  :meth:`TransferProgram.launch` is a single
+kernel launch on the current stream; nothing is allocated and nothing
+synchronises with the host.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from awex_b200.ops import native
+from awex_b200.transfer.descriptors import DESC_DTYPE
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "a destination did not announce readiness in time",
+    2: "a staged load did not complete in time",
+    3: "a sender's completion flag did not arrive in time",
+    4: "a descriptor failed a device-side check",
+}
+
+
+class TransferError(RuntimeError):
+    def __init__(self, code: int, detail: Sequence[int]):
+        self.code, self.detail = code, tuple(detail)
+        super().__init__(f"fused transfer failed: {STATUS_NAMES.get(code, code)} (detail={self.detail})")
+
+
+def _device_array(values, dtype, device) -> torch.Tensor:
+    return torch.from_numpy(np.asarray(values, dtype=dtype).view(np.uint8).copy()).to(device)
+
+
+class StatusWord:
+    """Four int32 on the device: code, detail0..2.  Kernels only ever move it
+    from OK to an error; the host reads it when it wants a verdict."""
+
+    def __init__(self, device):
+        self.t = torch.zeros(4, dtype=torch.int32, device=device)
+
+    @property
+    def ptr(self) -> int:
+        return self.t.data_ptr()
+
+    def reset(self) -> None:
+        self.t.zero_()
+
+    def read(self) -> List[int]:
+        return self.t.tolist()
+
+    def raise_if_failed(self) -> None:
+        code, *detail = self.read()
+        if code != 0:
+            self.reset()
+            raise TransferError(code, detail)
+
+
+class FlagPad:
+    """``n`` 64-bit flags in this GPU's memory, written by peers."""
+
+    def __init__(self, n_slots: int, device):
+        self.n = n_slots
+        self.t = torch.zeros(max(n_slots, 1), dtype=torch.int64, device=device)
+
+    @property
+    def ptr(self) -> int:
+        return self.t.data_ptr()
+
+    def slot_addr(self, slot: int, base: Optional[int] = None) -> int:
+        return (self.ptr if base is None else base) + 8 * slot
+
+
+class TransferProgram:
+    def __init__(self, table: np.ndarray, n_tiles: int, device, ready_pad: Optional[FlagPad] = None,
+                 ready_slots: Sequence[int] = (), done_flag_addrs: Sequence[int] = (), timeout_ms: int = 2000,
+                 grid: int = 0):
+        if table.dtype != DESC_DTYPE:
+            raise TypeError("descriptor table has the wrong dtype")
+        self.lib = native.load()
+        assert self.lib.awex_xfer_desc_size() == DESC_DTYPE.itemsize, "descriptor layout mismatch between Python and CUDA"
+        self.device = torch.device(device)
+        self.n_desc = int(table.shape[0])
+        self.n_tiles = int(n_tiles)
+        self.table_host = table
+        self.table_dev = torch.from_numpy(table.view(np.uint8).reshape(-1).copy()).to(self.device) if self.n_desc else torch.empty(0, dtype=torch.uint8, device=self.device)
+        self.ready_pad = ready_pad
+        self.ready_slots = _device_array(list(ready_slots), np.uint32, self.device) if len(ready_slots) else None
+        self.n_ready = len(ready_slots)
+        self.done_flags = _device_array(list(done_flag_addrs), np.uint64, self.device) if len(done_flag_addrs) else None
+        self.n_done = len(done_flag_addrs)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = StatusWord(self.device)
+        self.timeout_ns = int(timeout_ms) * 1_000_000
+        self.grid = grid
+        self.launches = 0
+
+    def launch(self, epoch: int, stream_ptr: Optional[int] = None) -> None:
+        stream = native.current_stream_ptr() if stream_ptr is None else stream_ptr
+        code = self.lib.awex_launch_fused_transfer(
+            self.table_dev.data_ptr() if self.n_desc else None, self.n_desc, self.n_tiles, epoch, self.timeout_ns,
+            self.ready_pad.ptr if (self.ready_pad is not None and self.n_ready) else None,
+            self.ready_slots.data_ptr() if self.n_ready else None, self.n_ready,
+            self.done_flags.data_ptr() if self.n_done else None, self.n_done,
+            self.counter.data_ptr(), self.status.ptr, self.grid, stream,
+        )
+        native.check(code, "fused_transfer launch")
+        self.launches += 1
+
+
+class FlagWaiter:
+    """Receiver side: one tiny kernel that returns when every listed slot of the
+    local pad has reached ``epoch`` or the deadline passed (status says which)."""
+
+    def __init__(self, pad: FlagPad, slots: Sequence[int], device, timeout_ms: int = 2000):
+        self.lib = native.load()
+        self.pad = pad
+        self.device = torch.device(device)
+        self.n = len(slots)
+        self.slots = _device_array(list(slots), np.uint32, self.device) if self.n else None
+        self.status = StatusWord(self.device)
+        self.timeout_ns = int(timeout_ms) * 1_000_000
+        self.launches = 0
+
+    def launch(self, epoch: int, stream_ptr: Optional[int] = None) -> None:
+        if not self.n:
+            return
+        stream = native.current_stream_ptr() if stream_ptr is None else stream_ptr
+        code = self.lib.awex_launch_wait_flags(self.pad.ptr, self.slots.data_ptr(), self.n, epoch, self.timeout_ns, self.status.ptr, stream)
+        native.check(code, "wait_flags launch")
+        self.launches += 1
+
+
+class FlagPoster:
+    """Raise ``epoch`` at a fixed list of (local or peer-mapped) flag addresses."""
+
+    def __init__(self, addrs: Sequence[int], device):
+        self.lib = native.load()
+        self.device = torch.device(device)
+        self.n = len(addrs)
+        self.addrs = _device_array(list(addrs), np.uint64, self.device) if self.n else None
+        self.launches = 0
+
+    def launch(self, epoch: int, stream_ptr: Optional[int] = None) -> None:
+        if not self.n:
+            return
+        stream = native.current_stream_ptr() if stream_ptr is None else stream_ptr
+        native.check(self.lib.awex_launch_post_flags(self.addrs.data_ptr(), self.n, epoch, stream), "post_flags launch")
+        self.launches += 1

@@ -208,6 +208,54 @@ class SimulatedJob:
             total += execute_items(items, local, views)
         return total
 
+    # ---- single-GPU emulation of all ranks ------------------------------------------------------------
+    def encode_all(self, validate: bool = True):
+        """Encode every rank's program against addresses in this process.
+        Returns ``{train_rank: (table, n_tiles, encoder)}``."""
+        from awex_b200.transfer.descriptors import TensorAddr, encode_items, validate_table
+
+        views = self.destination_views()
+        dst_addrs = {rank: {n: TensorAddr.of(v) for n, v in vs.items()} for rank, vs in views.items()}
+        dst_spans = [TensorAddr.of(p).byte_span() for models in self.infer_models for m in models for p in m.parameters()]
+        out = {}
+        for rank, items in self.programs.items():
+            src_addrs = {(n, 0): TensorAddr.of(t) for n, t in self.train_models[rank].named_parameters()}
+            table, n_tiles, enc = encode_items(items, src_addrs, dst_addrs)
+            if validate:
+                problems = validate_table(table, n_tiles, [a.byte_span() for a in src_addrs.values()], dst_spans)
+                if problems:
+                    raise ValueError(f"rank {rank}: descriptor table rejected: {problems[:5]}")
+            out[rank] = (table, n_tiles, enc)
+        self.encoded = out
+        return out
+
+    def build_gpu_programs(self, timeout_ms: int = 2000, grid: int = 0):
+        """One TransferProgram per training rank plus one done-flag pad and a
+        waiter, all on this job's device (every "rank" shares the GPU, so the
+        launches simply run in stream order and no wait ever spins)."""
+        from awex_b200.ops.fused_transfer import FlagPad, FlagWaiter, TransferProgram
+
+        if not hasattr(self, "encoded"):
+            self.encode_all()
+        self.done_pad = FlagPad(self.train.world, self.device)
+        self.gpu_programs = {
+            rank: TransferProgram(table, n_tiles, self.device, done_flag_addrs=[self.done_pad.slot_addr(rank)],
+                                  timeout_ms=timeout_ms, grid=grid)
+            for rank, (table, n_tiles, _) in self.encoded.items()
+        }
+        self.waiter = FlagWaiter(self.done_pad, list(range(self.train.world)), self.device, timeout_ms=timeout_ms)
+        return self.gpu_programs
+
+    def run_gpu(self, epoch: int) -> None:
+        for prog in self.gpu_programs.values():
+            prog.launch(epoch)
+        self.waiter.launch(epoch)
+
+    def gpu_status(self) -> None:
+        for prog in self.gpu_programs.values():
+            prog.status.raise_if_failed()
+        self.waiter.status.raise_if_failed()
+
     def mismatches(self) -> List[str]:
         """Names of inference parameters that differ from the layout built
         directly from the canonical weights."""
