@@ -1,0 +1,153 @@
+"""Publish device tensors to other processes and map theirs.
+
+An :class:`AddressBook` is plain data describing where named tensors (views of
+live inference parameters, flag pads) live: for each tensor the allocation
+("segment") that contains it, its byte offset inside the segment, shape,
+strides and dtype; for each segment a CUDA IPC handle.  The exporting process
+publishes the book through the MetaServer; an importing process opens every
+segment once (`cudaIpcOpenMemHandle` with lazy peer access, so the mapping
+works for the same GPU and for NVLink peers alike) and turns entries into
+:class:`TensorAddr` values it can write through.
+
+Processes recognise their own books by (host, pid) and use the raw addresses,
+because a process cannot open its own IPC handles.
+
+The reference pickles IPC tensors through the MetaServer on every update
+(`awex/util/tensor_util.py:35-183`, `awex/writer/nccl_writer.py:372-400`); a
+book is exchanged once and re-published only when a base address moves
+(:meth:`PeerMemoryExporter.changed`).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import socket
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from awex_b200 import logging
+from awex_b200.transfer.descriptors import TensorAddr
+
+logger = logging.getLogger(__name__)
+
+
+def process_identity() -> Tuple[str, int]:
+    return socket.gethostname(), os.getpid()
+
+
+@dataclass
+class AddressBook:
+    owner: Tuple[str, int]  # (host, pid) of the exporting process
+    device_index: int
+    device_uuid: str
+    epoch: int
+    # segment -> (ipc handle bytes, base address in the owner, size)
+    segments: List[Tuple[bytes, int, int]] = field(default_factory=list)
+    # name -> (segment index, byte offset of element 0, shape, strides, dtype name)
+    tensors: Dict[str, Tuple[int, int, Tuple[int, ...], Tuple[int, ...], str]] = field(default_factory=dict)
+
+    def dtype_of(self, name: str) -> torch.dtype:
+        return getattr(torch, self.tensors[name][4])
+
+
+def _device_uuid(index: int) -> str:
+    try:
+        return str(torch.cuda.get_device_properties(index).uuid)
+    except Exception:
+        return f"cuda:{index}"
+
+
+class PeerMemoryExporter:
+    def __init__(self, device_index: Optional[int] = None):
+        from awex_b200.ops import native
+
+        self.lib = native.load()
+        self.device_index = torch.cuda.current_device() if device_index is None else device_index
+        self.epoch = 0
+        self._last_bases: Dict[str, int] = {}
+
+    def _segment_of(self, ptr: int) -> Tuple[int, int]:
+        base, size = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        code = self.lib.awex_address_range(ptr, ctypes.byref(base), ctypes.byref(size))
+        if code != 0:
+            raise RuntimeError(f"cuMemGetAddressRange failed for {ptr:#x} (code {code})")
+        return base.value, size.value
+
+    def export(self, named: Iterable[Tuple[str, torch.Tensor]], with_handles: bool = True) -> AddressBook:
+        """Describe ``named`` tensors.  ``with_handles=False`` skips IPC export
+        (books that only this process will read)."""
+        self.epoch += 1
+        book = AddressBook(process_identity(), self.device_index, _device_uuid(self.device_index), self.epoch)
+        seg_index: Dict[int, int] = {}
+        hbytes = self.lib.awex_ipc_handle_bytes()
+        for name, t in named:
+            if not t.is_cuda:
+                raise ValueError(f"{name}: only CUDA tensors can be published")
+            if t.numel() == 0:
+                continue
+            lo, _hi = TensorAddr.of(t).byte_span()
+            base, size = self._segment_of(lo)
+            if base not in seg_index:
+                handle = b""
+                if with_handles:
+                    buf = ctypes.create_string_buffer(hbytes)
+                    code = self.lib.awex_ipc_export(base, buf)
+                    if code != 0:
+                        raise RuntimeError(
+                            f"cudaIpcGetMemHandle failed for the allocation of {name} (CUDA error {code}); allocations made "
+                            "with expandable segments / virtual memory cannot be exported this way"
+                        )
+                    handle = buf.raw
+                seg_index[base] = len(book.segments)
+                book.segments.append((handle, base, size))
+            book.tensors[name] = (seg_index[base], t.data_ptr() - base, tuple(t.shape), tuple(t.stride()), str(t.dtype).replace("torch.", ""))
+            self._last_bases[name] = t.data_ptr()
+        return book
+
+    def changed(self, named: Iterable[Tuple[str, torch.Tensor]]) -> bool:
+        """True when any tensor moved since the last export (engines that
+        re-map weights after a sleep/wake cycle): the book must be re-published."""
+        return any(self._last_bases.get(n) != t.data_ptr() for n, t in named if t.numel())
+
+
+class PeerMemoryImporter:
+    def __init__(self):
+        from awex_b200.ops import native
+
+        self.lib = native.load()
+        self._open: Dict[bytes, int] = {}
+        self._me = process_identity()
+
+    def resolve(self, book: AddressBook) -> Dict[str, TensorAddr]:
+        bases: List[int] = []
+        for handle, owner_base, _size in book.segments:
+            if tuple(book.owner) == self._me:
+                bases.append(owner_base)
+                continue
+            if not handle:
+                raise RuntimeError("address book of another process carries no IPC handles")
+            mapped = self._open.get(handle)
+            if mapped is None:
+                out = ctypes.c_uint64(0)
+                code = self.lib.awex_ipc_open(handle, ctypes.byref(out))
+                if code != 0:
+                    msg = self.lib.awex_cuda_error_string(code)
+                    raise RuntimeError(f"cudaIpcOpenMemHandle failed (CUDA error {code}: {msg.decode() if msg else '?'})")
+                mapped = self._open[handle] = out.value
+            bases.append(mapped)
+        out_addrs: Dict[str, TensorAddr] = {}
+        for name, (seg, offset, shape, strides, dtype) in book.tensors.items():
+            out_addrs[name] = TensorAddr(bases[seg] + offset, tuple(shape), tuple(strides), getattr(torch, dtype))
+        return out_addrs
+
+    def close_all(self) -> None:
+        """Unmap everything (must happen before the owner frees or re-maps the
+        memory)."""
+        for handle, mapped in list(self._open.items()):
+            code = self.lib.awex_ipc_close(mapped)
+            if code != 0:
+                logger.warning(f"cudaIpcCloseMemHandle returned {code}")
+            del self._open[handle]
