@@ -1,0 +1,164 @@
+"""Per-GPU reader that lives inside an inference model worker.
+
+``WorkerWeightsReader.initialize`` maps every parameter of the worker's model
+to canonical views (``self.parameters``: canonical name -> live tensor view);
+those views are what training ranks write into.  ``NCCLWorkerWeightsReader``
+keeps the reference's class name (`awex/reader/nccl_reader.py:49-493`) for the
+``nccl`` backend name; on CUDA its data plane is the fused NVLink peer-store
+path: it publishes an address book of the views, checks the senders' manifests
+for exactly-once coverage and afterwards only raises and waits on flags.
+"""
+
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional
+
+import torch
+
+from awex_b200 import logging
+from awex_b200.meta.infer_meta_resolver import canonical_named_views
+from awex_b200.meta.meta_server import MetaServerClient
+from awex_b200.models.registry import get_infer_weights_converter
+from awex_b200.sharding.param_sharding import get_rank_info_extractor
+from awex_b200.utils.common import compute_statistics
+
+logger = logging.getLogger(__name__)
+
+
+class WorkerWeightsReader:
+    def __init__(self, model, model_context: dict, infer_conf: dict, parameters_meta, training_params_meta,
+                 engine_rank: int, num_engines: int, meta_server_addr: str, enable_debug_mode: bool = False,
+                 debug_mode_config: Optional[dict] = None, enable_colocate_mode: bool = False,
+                 device_wait_timeout_ms: int = 2000, **_unused):
+        self.model = model
+        self.model_context = model_context
+        self.scheduler = model_context.get("scheduler")
+        self.infer_conf = infer_conf
+        self.engine_name = infer_conf["engine_name"]
+        self.infer_engine_config = infer_conf["infer_engine_config"]
+        self.parameters_meta = parameters_meta
+        self.training_params_meta = training_params_meta
+        self.engine_rank, self.num_engines = engine_rank, num_engines
+        self.meta_server_addr = meta_server_addr
+        self.meta_server_client = MetaServerClient(*meta_server_addr.rsplit(":", 1))
+        self.enable_debug_mode = enable_debug_mode
+        self.debug_mode_config = debug_mode_config or {}
+        self.enable_colocate_mode = enable_colocate_mode
+        self.device_wait_timeout_ms = device_wait_timeout_ms
+        self.rank_info = get_rank_info_extractor(self.engine_name)(model_context, engine_rank)
+        self.infer_world_size = int(infer_conf["infer_world_size"])
+        self.instance_world_size = self.infer_world_size // num_engines
+        self.transfer_rank = engine_rank * self.instance_world_size + self.rank_info.global_rank
+        self.training_world_size = training_params_meta[0].shards[0].world_size
+        self.timeout = 10000
+        self.parameters: Dict[str, torch.Tensor] = {}
+        self._history: Dict[str, List[float]] = {}
+        self._snapshot = None
+        self.epoch = 0
+
+    def initialize(self) -> None:
+        arch = type(self.model).__name__
+        converter = get_infer_weights_converter(
+            self.engine_name, arch, hf_config=self.model.config, infer_engine_config=self.infer_engine_config,
+            rank_info=self.rank_info,
+        )
+        self.parameters = dict(canonical_named_views(self.model, converter, self.model_context, convert_params=True))
+        train_names = {m.name for m in self.training_params_meta}
+        # what training will fill: its names, plus block scales that are produced
+        # together with their weights
+        self.required_names = [n for n in self.parameters if n in train_names]
+        self.device = next(iter(self.parameters.values())).device if self.parameters else torch.device("cpu")
+
+    # ---- update -----------------------------------------------------------------------------------
+    def begin_update(self, step_id) -> None:
+        raise NotImplementedError
+
+    def finish_update(self, step_id) -> None:
+        raise NotImplementedError
+
+    def update_weights(self, step_id) -> None:
+        t0 = time.time()
+        self.begin_update(step_id)
+        self.finish_update(step_id)
+        compute_statistics(self._history, step_id, time.time() - t0, "Receive weights")
+
+    def _after_update(self) -> None:
+        """Caches computed with the old weights are stale."""
+        if self.scheduler is not None and hasattr(self.scheduler, "flush_cache"):
+            self.scheduler.flush_cache()
+
+    # ---- validation: record, clear, compare ----------------------------------------------------------
+    def _validation_tensors(self):
+        names = sorted(self.required_names)
+        return names, [self.parameters[n] for n in names]
+
+    def snapshot_and_clear(self) -> int:
+        """Record what every parameter holds (device checksums on CUDA, host
+        copies on CPU), then zero it, so that an unwritten shard cannot pass."""
+        names, tensors = self._validation_tensors()
+        if self.device.type == "cuda":
+            from awex_b200.ops.checksum import ChecksumPlan
+
+            if getattr(self, "_sum_plan", None) is None:
+                self._sum_plan = ChecksumPlan(tensors, self.device)
+            self._snapshot = (names, self._sum_plan.run())
+        else:
+            self._snapshot = (names, [t.detach().clone() for t in tensors])
+        for t in tensors:
+            t.zero_()
+        return len(names)
+
+    def verify_against_snapshot(self) -> Dict[str, bool]:
+        if self._snapshot is None:
+            raise RuntimeError("verify_against_snapshot called without snapshot_and_clear")
+        names, before = self._snapshot
+        _, tensors = self._validation_tensors()
+        if self.device.type == "cuda":
+            sums, nans = self._sum_plan.run()
+            want_sums, _ = before
+            result = {n: (s == w and k == 0) for n, s, w, k in zip(names, sums, want_sums, nans)}
+        else:
+            from awex_b200.utils.tensor_util import check_and_log_nan_values, compare_and_log_tensor_differences
+
+            check_and_log_nan_values(dict(zip(names, tensors)), "infer")
+            result = {n: compare_and_log_tensor_differences(t, w, n, exact_match=True) for n, t, w in zip(names, tensors, before)}
+        self._snapshot = None
+        return result
+
+
+class NCCLWorkerWeightsReader(WorkerWeightsReader):
+    def initialize(self) -> None:
+        super().initialize()
+        t0 = time.time()
+        common = dict(
+            meta=self.meta_server_client, views=self.parameters, transfer_rank=self.transfer_rank,
+            infer_world=self.infer_world_size, train_world=self.training_world_size, required=self.required_names,
+            device=self.device, wait_timeout_s=self.timeout, strict=not self.enable_debug_mode,
+        )
+        if self.device.type == "cuda":
+            from awex_b200.transfer.transports import PeerStoreReceiver
+
+            self.transport = PeerStoreReceiver(timeout_ms=self.device_wait_timeout_ms, **common)
+        else:
+            from awex_b200.transfer.transports import GlooReceiver
+
+            self.transport = GlooReceiver(**common)
+        self.transport.connect()
+        logger.info(f"Rank[{self.transfer_rank}] reader ready in {time.time() - t0:.2f}s, {len(self.parameters)} canonical views")
+
+    def begin_update(self, step_id) -> None:
+        self.epoch += 1
+        if self.transport.republish_if_moved():
+            raise RuntimeError(
+                "inference parameters moved since they were published; senders hold stale addresses "
+                "(re-create the writer and reader after the engine re-maps its weights)"
+            )
+        self.transport.begin(self.epoch)
+
+    def finish_update(self, step_id, synchronize: bool = True) -> None:
+        self.transport.finish(self.epoch, synchronize=synchronize)
+        self._after_update()
+
+    def close(self) -> None:
+        self.transport.close()

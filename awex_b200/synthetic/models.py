@@ -89,6 +89,48 @@ class CanonicalWeights:
         return self.get("model.norm.weight", (self.arch.hidden,))
 
 
+class StoredCanonicalWeights(CanonicalWeights):
+    """Canonical tensors read from a name -> tensor mapping (a loaded HF
+    checkpoint) instead of being generated."""
+
+    def __init__(self, arch: Arch, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device):
+        super().__init__(arch, dtype, device)
+        self.tensors = tensors
+
+    def get(self, name: str, shape: Tuple[int, ...]) -> torch.Tensor:
+        t = self.tensors[name]
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != expected {tuple(shape)}")
+        return t.to(device=self.device, dtype=self.dtype)
+
+
+def canonical_state_dict(arch: Arch, weights: CanonicalWeights) -> "OrderedDict[str, torch.Tensor]":
+    """Every canonical (HF-layout) tensor of the model, by name."""
+    out: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+    out["model.embed_tokens.weight"] = weights.embed()
+    for l in range(arch.num_layers):
+        p = f"model.layers.{l}."
+        names = ["input_layernorm.weight", "self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+                 "self_attn.o_proj.weight", "post_attention_layernorm.weight"]
+        if arch.qkv_bias:
+            names += ["self_attn.q_proj.bias", "self_attn.k_proj.bias", "self_attn.v_proj.bias"]
+        if arch.qk_norm:
+            names += ["self_attn.q_norm.weight", "self_attn.k_norm.weight"]
+        if arch.is_moe:
+            names += ["mlp.gate.weight"]
+        else:
+            names += ["mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight"]
+        for n in names:
+            out[p + n] = weights.layer(l, n)
+        for e in range(arch.num_experts):
+            for what in ("gate_proj", "up_proj", "down_proj"):
+                out[f"{p}mlp.experts.{e}.{what}.weight"] = weights.expert(l, e, what)
+    out["model.norm.weight"] = weights.final_norm()
+    if not arch.tie_embeddings:
+        out["lm_head.weight"] = weights.lm_head()
+    return out
+
+
 class FlatModule:
     """Minimal stand-in for an ``nn.Module``: ordered named tensors (names may
     contain dots) plus a ``config``."""
@@ -128,8 +170,8 @@ def pp_layer_range(num_layers: int, pp_rank: int, pp_size: int) -> range:
 
 # ---- Megatron layout ---------------------------------------------------------------------------
 def build_megatron_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, device="cpu", seed: int = 0,
-                         step: int = 0, layers: Optional[range] = None) -> FlatModule:
-    w = CanonicalWeights(arch, dtype, device, seed, step)
+                         step: int = 0, layers: Optional[range] = None, weights: Optional[CanonicalWeights] = None) -> FlatModule:
+    w = weights or CanonicalWeights(arch, dtype, device, seed, step)
     tp, r = rank_info.tp_size, rank_info.tp_rank
     ep, er = rank_info.ep_size, rank_info.ep_rank
     etp, etr = rank_info.ep_tp_size, rank_info.ep_tp_rank
@@ -205,10 +247,11 @@ def _quant_parts(t2d: torch.Tensor, parts: int):
 
 
 def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, device="cpu", seed: int = 0,
-                     step: int = 0, fp8: bool = False, zero: bool = False, layers: Optional[range] = None) -> FlatModule:
+                     step: int = 0, fp8: bool = False, zero: bool = False, layers: Optional[range] = None,
+                     weights: Optional[CanonicalWeights] = None) -> FlatModule:
     """``zero=True`` allocates the same tensors filled with zeros (a freshly
     paused engine whose weights are about to be overwritten)."""
-    w = CanonicalWeights(arch, dtype, device, seed, step)
+    w = weights or CanonicalWeights(arch, dtype, device, seed, step)
     tp, r = rank_info.tp_size, rank_info.tp_rank
     ep, er = rank_info.ep_size, rank_info.ep_rank
     etp, etr = rank_info.ep_tp_size, rank_info.ep_tp_rank

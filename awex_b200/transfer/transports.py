@@ -1,0 +1,291 @@
+"""Data planes that execute a compiled send program.
+
+* :class:`PeerStoreSender` / :class:`PeerStoreReceiver` — the B200 path.  The
+  receiver publishes an address book of its live parameter views and a pad of
+  completion flags; the sender maps them (CUDA IPC, NVLink peer access),
+  encodes its copy items into a descriptor table once, and then every update
+  is ONE kernel launch per training rank that reads local shards, applies
+  layout / dtype / fp8 transforms and stores straight into the peers'
+  parameters.  No NCCL call, staging buffer or host synchronisation sits on
+  the path; ordering is carried by per-(sender, receiver) epoch flags in
+  device memory with bounded waits.
+* :class:`GlooSender` / :class:`GlooReceiver` — the same items moved as packed
+  byte messages over a Gloo exchange group; used on CPU-only hosts and as the
+  portable fallback.
+
+What both replace in the reference: per-operation ``isend``/``irecv`` lists
+inside one NCCL group, staging copies for strided views and a barrier per step
+(`awex/transfer/nccl_comm.py:378-624`, `awex/writer/nccl_writer.py:197-304`,
+`awex/reader/nccl_reader.py:329-398`).
+
+MetaServer keys used here: ``p2p_addr_<infer transfer rank>`` (address book),
+``p2p_manifest_<train transfer rank>`` (what that rank writes where, plus the
+address of its ready-flag pad), ``master_info`` (exchange group rendezvous).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from awex_b200 import logging
+from awex_b200.transfer.cpu_exec import entry_nbytes, pack_message, unpack_message
+from awex_b200.transfer.lowering import CopyItem, check_exactly_once, manifest_by_destination
+
+logger = logging.getLogger(__name__)
+
+DONE_PAD = "__done_flags__"
+READY_PAD = "__ready_flags__"
+
+
+def addr_key(infer_transfer_rank: int) -> str:
+    return f"p2p_addr_{infer_transfer_rank}"
+
+
+def manifest_key(train_transfer_rank: int) -> str:
+    return f"p2p_manifest_{train_transfer_rank}"
+
+
+class CoverageError(RuntimeError):
+    pass
+
+
+def _collect_manifests(meta, infer_world: int, train_world: int, my_rank: int, timeout: float):
+    """All training ranks' manifests; returns (senders, per-sender entries, per-sender record)."""
+    senders, entries, records = [], [], {}
+    for r in range(train_world):
+        rec = meta.get_object(manifest_key(infer_world + r), timeout=timeout)
+        mine = rec["manifest"].get(my_rank, [])
+        if mine:
+            senders.append(r)
+            entries.append(mine)
+            records[r] = rec
+    return senders, entries, records
+
+
+def _check_coverage(entries, views: Dict[str, torch.Tensor], required: Sequence[str], strict: bool, who: str) -> None:
+    shapes = {n: (tuple(v.shape), v.dtype) for n, v in views.items()}
+    problems = check_exactly_once(entries, shapes, required)
+    if problems:
+        msg = f"{who}: incoming writes do not tile the parameters exactly once: {problems[:6]}"
+        if strict:
+            raise CoverageError(msg)
+        logger.error(msg)
+
+
+# ------------------------------------------------------------------------------------ fused NVLink path
+class PeerStoreReceiver:
+    def __init__(self, meta, views: Dict[str, torch.Tensor], transfer_rank: int, infer_world: int, train_world: int,
+                 required: Sequence[str], device, timeout_ms: int = 2000, wait_timeout_s: float = 10000, strict: bool = True):
+        from awex_b200.ops.fused_transfer import FlagPad
+        from awex_b200.parallel.peer_memory import PeerMemoryExporter
+
+        self.meta, self.views, self.rank = meta, views, transfer_rank
+        self.infer_world, self.train_world = infer_world, train_world
+        self.required, self.device, self.strict = list(required), torch.device(device), strict
+        self.timeout_ms, self.wait_timeout_s = timeout_ms, wait_timeout_s
+        self.done_pad = FlagPad(train_world, self.device)
+        self.exporter = PeerMemoryExporter(self.device.index)
+        self.waiter = None
+        self.poster = None
+        self.publish()
+
+    def _named(self):
+        return list(self.views.items()) + [(DONE_PAD, self.done_pad.t)]
+
+    def publish(self) -> None:
+        self.meta.put_object(addr_key(self.rank), self.exporter.export(self._named()))
+
+    def republish_if_moved(self) -> bool:
+        if self.exporter.changed(self._named()):
+            self.publish()
+            return True
+        return False
+
+    def connect(self) -> None:
+        """Learn who writes here, check their manifests, map their ready pads."""
+        from awex_b200.ops.fused_transfer import FlagPoster, FlagWaiter
+        from awex_b200.parallel.peer_memory import PeerMemoryImporter
+
+        self.senders, entries, records = _collect_manifests(self.meta, self.infer_world, self.train_world, self.rank, self.wait_timeout_s)
+        _check_coverage(entries, self.views, self.required, self.strict, f"inference rank {self.rank}")
+        self.importer = PeerMemoryImporter()
+        ready_addrs = []
+        for r in self.senders:
+            pad = self.importer.resolve(records[r]["ready_pad"])[READY_PAD]
+            ready_addrs.append(pad.ptr + 8 * self.rank)
+        self.poster = FlagPoster(ready_addrs, self.device)
+        self.waiter = FlagWaiter(self.done_pad, self.senders, self.device, timeout_ms=self.timeout_ms)
+        self.bytes_in = sum(entry_nbytes(e) for es in entries for e in es)
+        logger.info(f"inference rank {self.rank}: {len(self.senders)} senders {self.senders}, {self.bytes_in} bytes per update")
+
+    def begin(self, epoch: int) -> None:
+        """Tell every sender that parameters may be overwritten now."""
+        self.poster.launch(epoch)
+
+    def finish(self, epoch: int, synchronize: bool = True) -> None:
+        self.waiter.launch(epoch)
+        if synchronize:
+            torch.cuda.current_stream(self.device).synchronize()
+            self.waiter.status.raise_if_failed()
+
+    def gpu_launches_per_update(self) -> int:
+        return (1 if self.poster and self.poster.n else 0) + (1 if self.waiter and self.waiter.n else 0)
+
+    def close(self) -> None:
+        if getattr(self, "importer", None) is not None:
+            self.importer.close_all()
+
+
+class PeerStoreSender:
+    def __init__(self, meta, items: Sequence[CopyItem], local: Dict[Tuple[str, int], torch.Tensor], train_rank: int,
+                 infer_world: int, device, timeout_ms: int = 2000, wait_timeout_s: float = 10000, validate: bool = True,
+                 grid: int = 0):
+        from awex_b200.ops.fused_transfer import FlagPad
+        from awex_b200.parallel.peer_memory import PeerMemoryExporter
+
+        self.meta, self.items, self.local = meta, list(items), local
+        self.train_rank, self.infer_world = train_rank, infer_world
+        self.transfer_rank = infer_world + train_rank
+        self.device = torch.device(device)
+        self.timeout_ms, self.wait_timeout_s, self.validate, self.grid = timeout_ms, wait_timeout_s, validate, grid
+        self.ready_pad = FlagPad(infer_world, self.device)
+        self.exporter = PeerMemoryExporter(self.device.index)
+        self.manifest = manifest_by_destination(self.items)
+        self.destinations = sorted(self.manifest)
+        self.meta.put_object(
+            manifest_key(self.transfer_rank),
+            {"manifest": self.manifest, "ready_pad": self.exporter.export([(READY_PAD, self.ready_pad.t)])},
+        )
+        self.program = None
+
+    def connect(self) -> None:
+        """Map every destination's address book and encode the descriptor table."""
+        from awex_b200.ops.fused_transfer import TransferProgram
+        from awex_b200.parallel.peer_memory import PeerMemoryImporter, process_identity
+        from awex_b200.transfer.descriptors import TensorAddr, encode_items, validate_table
+
+        self.importer = PeerMemoryImporter()
+        dst_addrs, done_flags, remote = {}, [], []
+        for d in self.destinations:
+            book = self.meta.get_object(addr_key(d), timeout=self.wait_timeout_s)
+            addrs = self.importer.resolve(book)
+            dst_addrs[d] = addrs
+            done_flags.append(addrs[DONE_PAD].ptr + 8 * self.train_rank)
+            if tuple(book.owner) != process_identity():
+                remote.append(d)
+        src_addrs = {key: TensorAddr.of(t) for key, t in self.local.items()}
+        table, n_tiles, enc = encode_items(self.items, src_addrs, dst_addrs)
+        if self.validate:
+            dst_spans = [a.byte_span() for book in dst_addrs.values() for n, a in book.items() if n != DONE_PAD]
+            problems = validate_table(table, n_tiles, [a.byte_span() for a in src_addrs.values()], dst_spans, check_overlap=False)
+            if problems:
+                raise ValueError(f"training rank {self.train_rank}: descriptor table rejected: {problems[:6]}")
+        # destinations in this very process are ordered by the stream; the others
+        # must announce readiness through a flag before they are overwritten
+        self.program = TransferProgram(
+            table, n_tiles, self.device, ready_pad=self.ready_pad, ready_slots=remote, done_flag_addrs=done_flags,
+            timeout_ms=self.timeout_ms, grid=self.grid,
+        )
+        self.bytes_out, self.bytes_in, self.n_desc = enc.bytes_out, enc.bytes_in, int(table.shape[0])
+        logger.info(
+            f"training rank {self.train_rank}: {len(self.items)} items -> {self.n_desc} descriptors, {n_tiles} tiles, "
+            f"{self.bytes_out} bytes to ranks {self.destinations}"
+        )
+
+    def send(self, epoch: int, synchronize: bool = True) -> None:
+        self.program.launch(epoch)
+        if synchronize:
+            torch.cuda.current_stream(self.device).synchronize()
+            self.program.status.raise_if_failed()
+
+    def gpu_launches_per_update(self) -> int:
+        return 1
+
+    def close(self) -> None:
+        if getattr(self, "importer", None) is not None:
+            self.importer.close_all()
+
+
+# ------------------------------------------------------------------------------------ CPU / portable path
+def _join_exchange_group(meta, transfer_rank: int, world: int, wait_timeout_s: float, device):
+    from awex_b200.parallel.process_group import init_weights_update_group
+    from awex_b200.utils.common import get_free_port, get_ip_address
+
+    if transfer_rank == 0:
+        info = (get_ip_address() if device.type == "cuda" else "127.0.0.1", get_free_port())
+        meta.put_object("master_info", info)
+    else:
+        info = meta.get_object("master_info", timeout=wait_timeout_s)
+    backend = "nccl" if device.type == "cuda" else "gloo"
+    return init_weights_update_group(info[0], info[1], transfer_rank, world, backend=backend, device=device)
+
+
+class GlooSender:
+    def __init__(self, meta, items, local, train_rank: int, infer_world: int, train_world: int, device="cpu",
+                 wait_timeout_s: float = 10000, **_unused):
+        self.meta, self.items, self.local = meta, list(items), local
+        self.train_rank, self.infer_world, self.train_world = train_rank, infer_world, train_world
+        self.transfer_rank = infer_world + train_rank
+        self.device, self.wait_timeout_s = torch.device(device), wait_timeout_s
+        self.manifest = manifest_by_destination(self.items)
+        self.destinations = sorted(self.manifest)
+        self.by_dst = {d: [it for it in self.items if it.dst_rank == d] for d in self.destinations}
+        self.meta.put_object(manifest_key(self.transfer_rank), {"manifest": self.manifest, "ready_pad": None})
+        self.bytes_out = sum(entry_nbytes(e) for es in self.manifest.values() for e in es)
+
+    def connect(self) -> None:
+        self.group = _join_exchange_group(self.meta, self.transfer_rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device)
+        self.group.barrier()
+
+    def send(self, epoch: int, synchronize: bool = True) -> None:
+        works = []
+        for d in self.destinations:
+            msg = pack_message(self.by_dst[d], self.local).to(self.device)
+            works.append((self.group.send(msg, d, tag=epoch & 0x7FFF), msg))
+        for w, _keepalive in works:
+            w.wait()
+
+    def gpu_launches_per_update(self) -> int:
+        return 0
+
+    def close(self) -> None:
+        pass
+
+
+class GlooReceiver:
+    def __init__(self, meta, views, transfer_rank: int, infer_world: int, train_world: int, required, device="cpu",
+                 wait_timeout_s: float = 10000, strict: bool = True, **_unused):
+        self.meta, self.views, self.rank = meta, views, transfer_rank
+        self.infer_world, self.train_world = infer_world, train_world
+        self.required, self.device, self.strict, self.wait_timeout_s = list(required), torch.device(device), strict, wait_timeout_s
+        self.group = None
+
+    def publish(self) -> None:
+        pass
+
+    def republish_if_moved(self) -> bool:
+        return False
+
+    def connect(self) -> None:
+        self.group = _join_exchange_group(self.meta, self.rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device)
+        self.senders, self.entries, _ = _collect_manifests(self.meta, self.infer_world, self.train_world, self.rank, self.wait_timeout_s)
+        _check_coverage(self.entries, self.views, self.required, self.strict, f"inference rank {self.rank}")
+        self.bytes_in = sum(entry_nbytes(e) for es in self.entries for e in es)
+        self.group.barrier()
+
+    def begin(self, epoch: int) -> None:
+        pass
+
+    def finish(self, epoch: int, synchronize: bool = True) -> None:
+        for r, entries in zip(self.senders, self.entries):
+            buf = torch.empty(sum(entry_nbytes(e) for e in entries), dtype=torch.uint8, device=self.device)
+            self.group.recv(buf, self.infer_world + r, tag=epoch & 0x7FFF).wait()
+            unpack_message(entries, buf, self.views)
+
+    def gpu_launches_per_update(self) -> int:
+        return 0
+
+    def close(self) -> None:
+        pass

@@ -1,0 +1,75 @@
+"""Writer for the ``nccl`` communication backend name.
+
+The class keeps the reference's name (`awex/writer/nccl_writer.py:43-427`) so
+user code is unchanged, but on CUDA devices the data plane is not NCCL: each
+``write_weights`` is one launch of the fused transfer kernel that stores this
+rank's shards, already converted, into the inference engines' live parameters
+over NVLink.  On CPU the same program travels over Gloo.
+
+Per update nothing is converted, sliced, cloned or packed on the host: the
+send program is compiled once, on the first update.
+"""
+
+from __future__ import annotations
+
+import time
+from typing import List
+
+import torch
+
+from awex_b200 import logging
+from awex_b200.transfer.lowering import LocalParam, SendProgramCompiler
+from awex_b200.transfer.transfer_plan import TransferPlanBuilder, compute_transfer_plan_stats
+from awex_b200.utils.common import compute_statistics
+from awex_b200.writer.weights_writer import WeightsExchangeShardingWriter
+
+logger = logging.getLogger(__name__)
+
+
+class NCCLWeightsWriter(WeightsExchangeShardingWriter):
+    def __init__(self, train_engine):
+        super().__init__(train_engine)
+        self.transport = None
+        self.epoch = 0
+        self.grid = int(self.config.get("transfer_grid", 0))
+
+    def _initialize(self) -> None:
+        super()._initialize()
+        t0 = time.time()
+        self.builder = TransferPlanBuilder(
+            self.infer_world_size, self.training_world_size, self.num_infer_engines, enable_debug_mode=self.enable_debug_mode
+        )
+        local = self.local_tensors()
+        params = [LocalParam(name, vp, tuple(t.shape), t.dtype) for (name, vp), t in local.items()]
+        compiler = SendProgramCompiler(
+            self.rank_info, self.all_train_ranks, self._make_converter, params, self.infer_params_meta,
+            self.parameters_meta, self.builder,
+        )
+        self.items = compiler.compile()
+        self.transfer_plan = self.builder.build_local_transfer_plan(self.infer_params_meta, self.parameters_meta, self.transfer_rank)
+        stats = compute_transfer_plan_stats(self.transfer_plan)
+        logger.info(f"Rank[{self.transfer_rank}] plan hash {stats['full_hash'][:16]} stats {stats['total']}; {len(self.items)} copy items")
+        self.required_param_names = sorted({it.dst_name for it in self.items})
+        device = next(iter(local.values())).device if local else torch.device("cpu")
+        common = dict(meta=self.meta_server_client, items=self.items, local=local, train_rank=self.rank_info.global_rank,
+                      infer_world=self.infer_world_size, device=device, wait_timeout_s=self.timeout)
+        if device.type == "cuda":
+            from awex_b200.transfer.transports import PeerStoreSender
+
+            self.transport = PeerStoreSender(timeout_ms=self.device_wait_timeout_ms, validate=True, grid=self.grid, **common)
+        else:
+            from awex_b200.transfer.transports import GlooSender
+
+            self.transport = GlooSender(train_world=self.training_world_size, **common)
+        self.transport.connect()
+        logger.info(f"Rank[{self.transfer_rank}] writer ready in {time.time() - t0:.2f}s")
+
+    def _write_weights(self, step_id, **kwargs) -> None:
+        t0 = time.time()
+        self.epoch += 1
+        self.transport.send(self.epoch, synchronize=kwargs.get("synchronize", True))
+        compute_statistics(self._history, step_id, time.time() - t0, "Send weights")
+
+    def close(self) -> None:
+        if self.transport is not None:
+            self.transport.close()
