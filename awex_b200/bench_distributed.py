@@ -1,0 +1,275 @@
+"""Multi-process weight-sync benchmark through the public API.
+
+One process per GPU (``torch.distributed.run``).  Rank 0 hosts the MetaServer.
+Ranks are split into training ranks (``NCCLWeightsWriter`` on a synthetic
+Megatron-layout model) and inference workers (``WeightsReader`` on a synthetic
+vLLM-layout model); with one GPU the single process plays both roles.
+
+Two measurements per configuration:
+
+* device time per update: CUDA events on every rank around that rank's share
+  of the update (readers: announce readiness + wait for every sender's flag;
+  writers: the fused transfer kernel), all ranks released by a barrier, maximum
+  over ranks;
+* end to end: wall clock of the blocking public calls
+  (``writer.write_weights`` / ``reader.update_weights``) plus, every step, a
+  host->device copy of the step's control record from pinned memory and a
+  device->host read of the verdict (status + checksums of every inference
+  parameter), maximum over ranks.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import threading
+import time
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+PUBLISHED_10B_SECONDS = 0.8
+
+
+def role_table(n: int):
+    """(train layout, infer layout, train ranks, [infer ranks per engine], label)"""
+    from awex_b200.synthetic.simulate import InferLayout, TrainLayout
+
+    if n == 1:
+        return TrainLayout(tp=1), InferLayout(tp=1), [0], [[0]], "colocated-tp1->tp1"
+    if n == 2:
+        return TrainLayout(tp=1), InferLayout(tp=1), [0], [[1]], "tp1->tp1"
+    if n == 4:
+        return TrainLayout(tp=2), InferLayout(tp=2), [0, 1], [[2, 3]], "tp2->tp2"
+    if n == 8:
+        return TrainLayout(tp=4), InferLayout(tp=2, num_engines=2), [0, 1, 2, 3], [[4, 5], [6, 7]], "tp4->2xtp2"
+    raise SystemExit("--gpus must be 1, 2, 4 or 8")
+
+
+def _max_over_ranks(value: float, group=None) -> float:
+    t = torch.tensor([value], dtype=torch.float64)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())
+
+
+def _sum_over_ranks(value: float, group=None) -> float:
+    t = torch.tensor([value], dtype=torch.float64)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return float(t.item())
+
+
+def run_distributed(args):
+    from awex_b200 import NCCLWeightsWriter, WeightsReader, logging
+    from awex_b200.meta.meta_server import MetaServer
+    from awex_b200.ops.checksum import ChecksumPlan
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticInferenceEngine, SyntheticTrainEngine
+    from awex_b200.synthetic.topology import infer_rank_infos, train_rank_infos
+    from awex_b200.utils.gpu import ClockSampler
+
+    logging.setLevel(os.environ.get("AWEX_LOG_LEVEL", "WARNING"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=device)
+    ctl = dist.new_group(list(range(world)), backend="gloo") if world > 1 else None  # host-side control traffic
+
+    train_layout, infer_layout, train_ranks, engines, label = role_table(world)
+    arch = get_arch(args.model)
+    if args.layers:
+        arch = arch.with_layers(args.layers)
+
+    # control plane
+    server = None
+    addr_box = [None]
+    if rank == 0:
+        server = MetaServer("127.0.0.1", 0)
+        server.start()
+        addr_box[0] = f"127.0.0.1:{server.port}"
+    if world > 1:
+        dist.broadcast_object_list(addr_box, src=0, group=ctl)
+    meta_addr = addr_box[0]
+
+    # process groups of each side (every rank must take part in every new_group call)
+    train_group = dist.new_group(train_ranks, backend="gloo") if world > 1 else None
+    instance_groups = [dist.new_group(r, backend="gloo") if world > 1 else None for r in engines]
+
+    is_train = rank in train_ranks
+    my_engine = next((e for e, ranks in enumerate(engines) if rank in ranks), None)
+    is_infer = my_engine is not None
+    t_setup = time.time()
+    writer = reader = train_engine = infer_engine = None
+    if is_train:
+        ri = train_rank_infos(tp=train_layout.tp)[train_ranks.index(rank)]
+        train_engine = SyntheticTrainEngine(arch, ri, meta_addr, dtype=torch.bfloat16, device=device,
+                                            process_group=train_group, transfer_grid=args.grid)
+        writer = NCCLWeightsWriter(train_engine)
+        writer.initialize()
+    if is_infer:
+        ri = infer_rank_infos(infer_layout.tp, infer_layout.ep, engine_rank=my_engine, first_local_rank=engines[my_engine][0])[
+            engines[my_engine].index(rank)
+        ]
+        infer_engine = SyntheticInferenceEngine(arch, infer_layout, ri, meta_addr, dtype=torch.bfloat16, device=device,
+                                                instance_group=instance_groups[my_engine])
+        reader = WeightsReader(infer_engine)
+        reader.initialize()
+
+    # one-time metadata exchange; both sides block on each other, so a process
+    # that plays both roles prepares them concurrently
+    errors: List[BaseException] = []
+
+    def _guard(fn):
+        def run():
+            try:
+                torch.cuda.set_device(device)  # the current device is per thread
+                fn()
+            except BaseException as exc:  # surfaced below
+                errors.append(exc)
+        return run
+
+    threads = []
+    if reader is not None:
+        threads.append(threading.Thread(target=_guard(reader.prepare)))
+    if writer is not None:
+        threads.append(threading.Thread(target=_guard(writer.prepare)))
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if errors:
+        raise errors[0]
+    torch.cuda.synchronize()
+    setup_s = time.time() - t_setup
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    step_no = [0]
+
+    def step_async():
+        """One update, launched without host synchronisation."""
+        step_no[0] += 1
+        s = step_no[0]
+        if reader is not None:
+            reader.begin_update(s)
+        if writer is not None:
+            writer.write_weights(step_id=s, synchronize=False)
+        if reader is not None:
+            reader.finish_update(s, synchronize=False)
+
+    def check_status():
+        torch.cuda.synchronize()
+        if writer is not None:
+            writer.transport.program.status.raise_if_failed()
+        if reader is not None:
+            infer_engine.schedulers[0].awes_weights_reader.transport.waiter.status.raise_if_failed()
+
+    for _ in range(args.warmup):
+        barrier()
+        step_async()
+    check_status()
+
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler([local_rank]) as clocks:
+        for i in range(args.steps):
+            barrier()
+            starts[i].record()
+            step_async()
+            stops[i].record()
+        torch.cuda.synchronize()
+    check_status()
+    per_step_ms = [_max_over_ranks(s.elapsed_time(e)) if world > 1 else s.elapsed_time(e) for s, e in zip(starts, stops)]
+    ms = sum(per_step_ms) / len(per_step_ms)
+
+    # ---- end to end through the blocking public API ------------------------------------------------
+    plan = None
+    if reader is not None:
+        worker = infer_engine.schedulers[0].awes_weights_reader
+        plan = ChecksumPlan([worker.parameters[n] for n in sorted(worker.required_names)], device)
+        verdict_host = torch.zeros(2, plan.n, dtype=torch.int64).pin_memory()
+    ctrl_host = torch.zeros(8, dtype=torch.int64).pin_memory()
+    ctrl_dev = torch.zeros(8, dtype=torch.int64, device=device)
+    e2e_ms = []
+    for i in range(args.warmup + args.steps):
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        step_no[0] += 1
+        s = step_no[0]
+        ctrl_host[0] = s
+        ctrl_dev.copy_(ctrl_host, non_blocking=True)
+        if world == 1:
+            reader.begin_update(s)
+            writer.write_weights(step_id=s)
+            reader.finish_update(s)
+        elif writer is not None:
+            writer.write_weights(step_id=s)
+        else:
+            reader.update_weights(step_id=s)
+        if plan is not None:
+            verdict_host.copy_(plan.launch(), non_blocking=True)
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) * 1e3
+        dt = _max_over_ranks(dt, ctl)
+        if i >= args.warmup:
+            e2e_ms.append(dt)
+    e2e = sum(e2e_ms) / len(e2e_ms)
+
+    # ---- validation and accounting ----------------------------------------------------------------------
+    valid = True
+    if not args.no_validate and reader is not None:
+        valid = infer_engine.mismatches(step=0) == []
+    valid = _max_over_ranks(0.0 if valid else 1.0, ctl) == 0.0
+    bytes_out = _sum_over_ranks(float(writer.transport.bytes_out) if writer is not None else 0.0, ctl)
+    egress = _max_over_ranks(float(writer.transport.bytes_out) if writer is not None else 0.0, ctl)
+    n_desc = _sum_over_ranks(float(writer.transport.n_desc) if writer is not None else 0.0, ctl)
+    launches = (1 if writer is not None else 0) + (infer_engine.schedulers[0].awes_weights_reader.transport.gpu_launches_per_update() if reader is not None else 0)
+    launches_total = _sum_over_ranks(float(launches), ctl)
+    clock_summary = clocks.summary()
+    d2h = (verdict_host.numel() * 8 + 16) if plan is not None else 16
+    seconds = ms / 1e3
+    if rank == 0:
+        if not valid:
+            raise SystemExit("validation failed: inference weights differ from the oracle")
+        remote = world > 1
+        result = {
+            "metric": "weight_sync_seconds_per_update", "value": seconds, "unit": "s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": seconds / PUBLISHED_10B_SECONDS, "dtype": "bf16",
+            "data": "synthetic random-init N(0,0.02) weights from per-name seeds", "impl": "ours",
+            "config": {
+                "model": arch.name, "params": arch.param_count(), "bytes_per_update": int(bytes_out), "parallelism": label,
+                "mode": "separated" if remote else "colocated", "l2": "inputs (>=8 GB per GPU) exceed L2; no flush needed",
+                "validated_bitwise": bool(valid),
+                "vs_baseline_note": "reference publishes only 10B/31GB in 0.8 s on an unnamed cluster; ratio is ours / 0.8 s",
+            },
+            "aggregate_GBps": bytes_out / seconds / 1e9,
+            "nvlink_GBps_per_gpu": (egress / seconds / 1e9) if remote else 0.0,
+            "nvlink_fraction_of_770GBps": (egress / seconds / 1e9 / 770.0) if remote else None,
+            "clocks": clock_summary,
+            "e2e": {"value": e2e / 1e3, "unit": "s", "h2d_bytes_per_step": ctrl_host.numel() * 8, "d2h_bytes_per_step": d2h,
+                    "what": "blocking write_weights/update_weights + control record H2D + checksums of all inference parameters + verdict D2H, max over ranks"},
+            "gpu_launches": int(launches_total) * args.steps,
+            "setup_seconds": setup_s, "descriptors": int(n_desc), "per_step_ms": per_step_ms,
+        }
+        print(json.dumps(result), flush=True)
+    barrier()
+    if writer is not None:
+        writer.close()
+    if reader is not None:
+        infer_engine.schedulers[0].awes_weights_reader.close()
+    if world > 1:
+        dist.destroy_process_group()
+    if server is not None:
+        server.stop()

@@ -74,7 +74,7 @@ class WorkerWeightsReader:
     def begin_update(self, step_id) -> None:
         raise NotImplementedError
 
-    def finish_update(self, step_id) -> None:
+    def finish_update(self, step_id, synchronize: bool = True) -> None:
         raise NotImplementedError
 
     def update_weights(self, step_id) -> None:

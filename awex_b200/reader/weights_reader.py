@@ -192,8 +192,8 @@ class WeightsReader(WeightExchangeReader):
         return True
 
     @staticmethod
-    def _finish_update_in_tp_worker(step_id, **kwargs):
-        _worker_reader(kwargs).finish_update(step_id)
+    def _finish_update_in_tp_worker(step_id, synchronize=True, **kwargs):
+        _worker_reader(kwargs).finish_update(step_id, synchronize=synchronize)
         return True
 
     @staticmethod
@@ -215,6 +215,12 @@ class WeightsReader(WeightExchangeReader):
             self._initialize()
             self.initialized = True
 
+    def prepare(self) -> None:
+        """Run the one-time metadata exchange and worker set-up now instead of
+        on the first update (blocks until the training side has published)."""
+        with self.lock:
+            self._ensure_initialized()
+
     def begin_update(self, step_id, **kwargs) -> None:
         """First half of an update: pause-side bookkeeping, validation snapshot,
         and the announcement that parameters may be overwritten."""
@@ -230,7 +236,9 @@ class WeightsReader(WeightExchangeReader):
     def finish_update(self, step_id, **kwargs) -> None:
         """Second half: wait until every sender has finished, flush caches,
         validate."""
-        self.inference_engine.execute_task_in_model_worker(self._finish_update_in_tp_worker, step_id=step_id)
+        self.inference_engine.execute_task_in_model_worker(
+            self._finish_update_in_tp_worker, step_id=step_id, synchronize=kwargs.get("synchronize", True)
+        )
         if self._validating:
             self._validate_weights(step_id)
         if self.enable_colocate_mode:

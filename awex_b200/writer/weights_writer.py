@@ -105,6 +105,15 @@ class WeightsExchangeShardingWriter(WeightExchangeWriter):
         """Nothing to do eagerly: the metadata exchange needs a reader that has
         loaded its model, so it happens on the first ``write_weights``."""
 
+    def prepare(self) -> None:
+        """Run the one-time metadata exchange and program compilation now
+        instead of on the first ``write_weights`` (blocks until a reader has
+        published its side)."""
+        with self.lock:
+            if not self.initialized:
+                self._initialize()
+                self.initialized = True
+
     def _initialize(self) -> None:
         meta = self.meta_server_client
         self.infer_conf = meta.get_object("infer_conf", timeout=self.timeout)

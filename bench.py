@@ -41,6 +41,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model to this many layers (result is then not a valid benchmark)")
     ap.add_argument("--no-validate", action="store_true")
     ap.add_argument("--grid", type=int, default=0)
+    ap.add_argument("--emulate", action="store_true", help="debug: run all ranks of the layout as launches on one GPU, without the writer/reader API")
     return ap.parse_args()
 
 
@@ -189,8 +190,7 @@ def main():
         from baseline.reference_bench import run_reference
 
         return run_reference(args)
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.gpus == 1 and world == 1:
+    if args.emulate:
         return run_single_gpu(args)
     from awex_b200.bench_distributed import run_distributed
 
