@@ -12,8 +12,8 @@ on inference ranks, its planner, converters, ``batch_send_recv`` and MetaServer.
 
 Process model: the launcher's ranks are split like ``bench.py`` does.  The
 reference gathers training metadata over the *default* process group, so the
-training ranks form their own default group; inference ranks have none and
-reach each other through the reference's MetaServer.
+training ranks form their own default group; the workers of each inference
+instance form theirs, and exchange worker metadata through the MetaServer.
 """
 
 from __future__ import annotations
@@ -126,6 +126,10 @@ def run_reference(args):
             )
         return
     train_tp, infer_tp, train_ranks, engines, label = layout
+    if os.environ.get("REFBENCH_DUMP_AFTER_S"):
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["REFBENCH_DUMP_AFTER_S"]), exit=True)
     sys.path.insert(0, STUBS)
     sys.path.insert(0, REF)
     os.environ.setdefault("AWEX_MASTER_ADDR", "127.0.0.1")
@@ -141,6 +145,11 @@ def run_reference(args):
     store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), int(os.environ["MASTER_PORT"]), world,
                           is_master=(rank == 0 and not agent_store), wait_for_workers=False)
     store = dist.PrefixStore("refbench", store)
+    # The launcher marks its store as agent-hosted, which makes every tcp://
+    # rendezvous in the process a pure client.  The reference creates its exchange
+    # group with such a rendezvous and expects rank 0 to host the store, as it
+    # does outside a launcher; drop the marker once our own store is connected.
+    os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
 
     import awex.logging as ref_logging
 
@@ -163,7 +172,7 @@ def run_reference(args):
 
     if is_train:
         tp_rank = train_ranks.index(rank)
-        dist.init_process_group("nccl", store=dist.PrefixStore("train_pg", store), rank=tp_rank, world_size=train_tp, device_id=device)
+        dist.init_process_group("nccl", store=dist.PrefixStore("train_pg", store), rank=tp_rank, world_size=train_tp)
         from awex.writer.nccl_writer import NCCLWeightsWriter
 
         model = synth.megatron_module(arch, train_tp, tp_rank, dtype, device)
@@ -173,6 +182,10 @@ def run_reference(args):
         local_bytes = 0
     else:
         tp_rank = engines[engine_rank].index(rank)
+        # an inference engine's workers have their own default group (the
+        # reference asserts that one exists before it builds the exchange group)
+        dist.init_process_group("nccl", store=dist.PrefixStore(f"infer_pg{engine_rank}", store), rank=tp_rank,
+                                world_size=infer_tp)
         from awex.config import InferenceConfig
         from awex.reader.weights_reader import WeightsReader
 
@@ -231,8 +244,7 @@ def run_reference(args):
         }
         print(json.dumps(out), flush=True)
     _store_barrier(store, "exit", world)
-    if is_train:
-        dist.destroy_process_group()
+    dist.destroy_process_group()
     if server is not None:
         server.stop()
     os._exit(0)
