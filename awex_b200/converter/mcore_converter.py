@@ -240,10 +240,6 @@ class McoreToHFWeightConverter:
             name = name.replace(old, new)
         return name.replace("query_key_value_proj_proj", "query_key_value_proj")
 
-    def _value_op_for(self, canonical_name: str, spec: TensorSpec) -> ValueOp:
-        """Hook for per-name value transforms added by model files (fp8 ...)."""
-        return spec.value_op
-
     # ---- symbolic sources -------------------------------------------------------------
     def _own(self, param_name: str, n_rows: int) -> Rows:
         return Rows.full((param_name, self.rank_info.tp_rank), n_rows)
@@ -385,24 +381,62 @@ class McoreToHFWeightConverter:
     def _infer_tp_size(self) -> int:
         return int(cfg_get(self.infer_conf.get("infer_engine_config"), "tp_size", None) or self.infer_atten_tp_size or 1)
 
+    def _dest_split(self, canonical_name: str) -> int:
+        """How many destination shards one of this rank's slices of
+        ``canonical_name`` covers along the sharded dim (>= 1)."""
+        engine_cfg = self.infer_conf.get("infer_engine_config")
+        tp_i = self._infer_tp_size()
+        if ".experts." in canonical_name:
+            ep_i = int(cfg_get(engine_cfg, "ep_size", None) or 1)
+            if ep_i > 1:
+                etp_i = tp_i // ep_i if self.infer_conf.get("engine_name") == "sglang" else 1
+            else:
+                etp_i = tp_i
+            return max(etp_i // max(int(self.rank_info.ep_tp_size), 1), 1)
+        if "attention" in canonical_name or "self_attn" in canonical_name:
+            tp_i = self.infer_atten_tp_size
+        return max(tp_i // max(int(self.rank_info.tp_size), 1), 1)
+
+    # ---- block fp8 serving -----------------------------------------------------------------
+    _FP8_SUFFIXES = (
+        "q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "dense.weight", "query_key_value_proj.weight",
+        "gate_proj.weight", "up_proj.weight", "down_proj.weight", "gate_up_proj.weight",
+    )
+
+    def _is_fp8_name(self, canonical_name: str) -> bool:
+        """Which tensors the inference engine serves quantised: the linear
+        layers inside decoder blocks; embeddings, output head, norms and router
+        weights stay in the training dtype."""
+        return ".layers." in canonical_name and canonical_name.endswith(self._FP8_SUFFIXES)
+
+    def _fp8_ue8m0(self, canonical_name: str) -> bool:
+        return False
+
+    def _value_op_for(self, canonical_name: str, spec: TensorSpec) -> ValueOp:
+        if (
+            self.infer_conf.get("fp8_block_quant")
+            and spec.value_op.kind == "none"
+            and len(spec.shape) == 2
+            and self._is_fp8_name(canonical_name)
+        ):
+            return ValueOp("fp8_block", dtype=torch.float8_e4m3fn, ue8m0=self._fp8_ue8m0(canonical_name))
+        return spec.value_op
+
     def _scale_spec(self, weight: TensorSpec) -> TensorSpec:
         """Scale tensor of a block-quantised weight.  Blocks are laid on the
         *destination* shard grid, so the scale extent along the sharded dim is
-        ``n_shards * ceil(shard_extent / 128)`` where the destination shards
-        are narrower than this rank's slice, else ``ceil(extent / 128)``."""
+        ``k * ceil(extent / k / 128)`` when this rank's slice covers ``k``
+        destination shards, else ``ceil(extent / 128)``."""
         from awex_b200.sharding.param_sharding import get_default_sharding_dim
 
-        rows, cols = weight.shape
+        extent = list(weight.shape)
         dim = get_default_sharding_dim(weight.name)
-        ratio = max(self._infer_tp_size() // max(int(self.rank_info.tp_size), 1), 1)
-        extent = [rows, cols]
-        if extent[dim] % ratio == 0:
-            per = extent[dim] // ratio
-            n = ratio * block_scale_shape(per, per)[0]
-        else:
-            n = block_scale_shape(extent[dim], extent[dim])[0]
+        k = self._dest_split(weight.name)
+        if extent[dim] % k != 0:
+            k = 1
+        along = k * block_scale_shape(extent[dim] // k, 1)[0]
         other = block_scale_shape(extent[1 - dim], 1)[0]
-        shape = (n, other) if dim == 0 else (other, n)
+        shape = (along, other) if dim == 0 else (other, along)
         return TensorSpec(
             weight.name + SCALE_SUFFIX, Rows.full(("__scale__", weight.name), shape[0]), (shape[1],),
             torch.float32, IDENTITY, scale_of=weight.name,
@@ -451,7 +485,7 @@ class McoreToHFWeightConverter:
         from awex_b200.sharding.param_sharding import get_default_sharding_dim
 
         dim = get_default_sharding_dim(spec.name)
-        ratio = max(self._infer_tp_size() // max(int(self.rank_info.tp_size), 1), 1)
+        ratio = self._dest_split(spec.name)
         if tensor.shape[dim] % ratio != 0:
             ratio = 1
         qs, ss = zip(*(per_block_cast_to_fp8(part.contiguous(), spec.value_op.ue8m0) for part in tensor.chunk(ratio, dim=dim)))

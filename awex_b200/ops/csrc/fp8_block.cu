@@ -1,0 +1,307 @@
+// Stand-alone block-scaled fp8 (e4m3) quantisation and dequantisation for sm_100a.
+//
+// Contract (the plain-PyTorch statement is per_block_cast_to_fp8 in
+// awex_b200/converter/weights_converter.py; reference: awex/converter/
+// weights_converter.py:42-61): 128x128 blocks over a zero-padded view of a 2-D
+// tensor, scale = max(amax, 1e-4) / 448 in fp32 (optionally rounded up to a power
+// of two), q = e4m3(x / scale) with a true division.
+//
+// Quantisation: persistent CTAs, one 128x128 block per iteration.  The block is
+// fetched with ONE tiled TMA load (cp.async.bulk.tensor.2d, completion on an
+// mbarrier) into a double-buffered stage; out-of-range rows/columns of edge
+// blocks are zero-filled by the TMA unit, which is exactly the reference's
+// zero padding.  Threads read the stage as consecutive 16-byte chunks (no bank
+// conflicts), reduce |x| through shuffles + shared memory, and write e4m3 with
+// coalesced 8-byte stores.  The reference spends ~10 ATen kernels and a padded
+// temporary on the same math.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <type_traits>
+
+namespace awex {
+
+constexpr int kBlk = 128;
+constexpr int kQThreads = 256;
+
+__device__ __forceinline__ uint32_t q_smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ float nan_max(float m, float a) { return (a > m || a != a) ? a : m; }
+
+__device__ __forceinline__ float scale_of(float amax, bool ue8m0) {
+  float s = (amax < 1e-4f ? 1e-4f : amax) / 448.0f;
+  if (ue8m0) {
+    float c = s < 1e-10f ? 1e-10f : s;
+    s = exp2f(ceilf(static_cast<float>(log2(static_cast<double>(c)))));
+  }
+  return s;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+
+// status: int32[4]; code 2 = a TMA load did not complete within the spin budget
+template <typename T>
+__global__ void __launch_bounds__(kQThreads, 1)
+fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char* __restrict__ q, float* __restrict__ scales,
+                       uint32_t rows, uint32_t cols, int64_t q_stride, int64_t scale_stride, uint32_t blocks_n,
+                       uint32_t n_blocks, int ue8m0, int32_t* status) {
+  extern __shared__ __align__(128) unsigned char stage_mem[];
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ float red[kQThreads / 32];
+  __shared__ int give_up;
+  constexpr uint32_t kStage = kBlk * kBlk * sizeof(T);
+  constexpr int kChunkElems = 16 / sizeof(T);          // elements per 16-byte chunk
+  constexpr int kChunksPerRow = kBlk / kChunkElems;    // 16 (2-byte types) or 32 (fp32)
+  constexpr int kRowsPerPass = kQThreads / kChunksPerRow;
+  constexpr int kPasses = kBlk / kRowsPerPass;
+  const uint32_t tid = threadIdx.x;
+  if (tid == 0) {
+    give_up = 0;
+    for (int s = 0; s < 2; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(q_smem_addr(&bars[s])), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](uint32_t blk, uint32_t stage) {  // thread 0 only
+    const uint32_t bar = q_smem_addr(&bars[stage]);
+    const int32_t x0 = static_cast<int32_t>((blk % blocks_n) * kBlk);  // element column: a multiple of 128, so 16-byte aligned
+    const int32_t y0 = static_cast<int32_t>((blk / blocks_n) * kBlk);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kStage) : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            q_smem_addr(stage_mem + stage * kStage)),
+        "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(x0), "r"(y0), "r"(bar)
+        : "memory");
+  };
+
+  uint32_t it = 0;
+  if (tid == 0 && blockIdx.x < n_blocks) issue(blockIdx.x, 0);
+  for (uint32_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x, ++it) {
+    const uint32_t stage = it & 1, parity = (it >> 1) & 1;
+    const uint32_t next = blk + gridDim.x;
+    if (tid == 0) {
+      if (next < n_blocks) issue(next, stage ^ 1);  // the other stage was released by the barrier ending the last iteration
+      const uint32_t bar = q_smem_addr(&bars[stage]);
+      uint32_t done = 0;
+      for (uint32_t spin = 0; !done; ++spin) {
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (!done && spin > (1u << 24)) {  // far beyond any real latency: report and stop
+          if (status && atomicCAS(status, 0, 2) == 0) status[1] = static_cast<int32_t>(blk);
+          give_up = 1;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (give_up) break;
+    const unsigned char* stage_ptr = stage_mem + stage * kStage;
+    const uint32_t chunk = tid % kChunksPerRow, row_in_pass = tid / kChunksPerRow;
+    float vals[kPasses][kChunkElems];
+    float m = 0.f;
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const uint32_t r = p * kRowsPerPass + row_in_pass;
+      const uint4 raw = *reinterpret_cast<const uint4*>(stage_ptr + (r * kChunksPerRow + chunk) * 16);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < kChunkElems; ++j) {
+        vals[p][j] = to_float<T>(e[j]);
+        m = nan_max(m, fabsf(vals[p][j]));
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((tid & 31) == 0) red[tid >> 5] = m;
+    __syncthreads();
+    float amax = red[0];
+#pragma unroll
+    for (int w = 1; w < kQThreads / 32; ++w) amax = nan_max(amax, red[w]);
+    const float scale = scale_of(amax, ue8m0 != 0);
+    const uint32_t brow = blk / blocks_n, bcol = blk % blocks_n;
+    if (tid == 0) scales[static_cast<int64_t>(brow) * scale_stride + bcol] = scale;
+    const uint32_t col0 = bcol * kBlk + chunk * kChunkElems;
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const uint32_t r = brow * kBlk + p * kRowsPerPass + row_in_pass;
+      if (r >= rows || col0 >= cols) continue;
+      unsigned char out[kChunkElems];
+#pragma unroll
+      for (int j = 0; j < kChunkElems; j += 2) {
+        const uint16_t pair = __nv_cvt_float2_to_fp8x2(
+            make_float2(__fdiv_rn(vals[p][j], scale), __fdiv_rn(vals[p][j + 1], scale)), __NV_SATFINITE, __NV_E4M3);
+        out[j] = static_cast<unsigned char>(pair & 0xFF);
+        out[j + 1] = static_cast<unsigned char>(pair >> 8);
+      }
+      unsigned char* o = q + static_cast<int64_t>(r) * q_stride + col0;
+      const bool whole = col0 + kChunkElems <= cols;
+      if (whole && kChunkElems == 8 && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
+        *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(out);
+      } else if (whole && kChunkElems == 4 && (reinterpret_cast<uintptr_t>(o) & 3) == 0) {
+        *reinterpret_cast<uint32_t*>(o) = *reinterpret_cast<const uint32_t*>(out);
+      } else {
+        for (int j = 0; j < kChunkElems; ++j)
+          if (col0 + j < cols) o[j] = out[j];
+      }
+    }
+    __syncthreads();  // stage and `red` may be reused
+  }
+}
+
+// x = float(q) * scale(block); 16 fp8 values per thread and iteration.
+template <typename T>
+__global__ void __launch_bounds__(256) fp8_block_dequant_kernel(const unsigned char* __restrict__ q, const float* __restrict__ scales,
+                                                                T* __restrict__ out, uint32_t rows, uint32_t cols, int64_t q_stride,
+                                                                int64_t scale_stride, int64_t out_stride) {
+  const uint32_t chunks_per_row = (cols + 15) / 16;
+  const uint64_t total = static_cast<uint64_t>(rows) * chunks_per_row;
+  for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t r = static_cast<uint32_t>(i / chunks_per_row), c0 = static_cast<uint32_t>(i % chunks_per_row) * 16;
+    const float s = scales[static_cast<int64_t>(r / kBlk) * scale_stride + c0 / kBlk];
+    const unsigned char* src = q + static_cast<int64_t>(r) * q_stride + c0;
+    T* dst = out + static_cast<int64_t>(r) * out_stride + c0;
+    unsigned char b[16];
+    const bool whole = c0 + 16 <= cols;
+    if (whole && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+      *reinterpret_cast<uint4*>(b) = __ldg(reinterpret_cast<const uint4*>(src));
+    } else {
+      for (int j = 0; j < 16; ++j) b[j] = (c0 + j < cols) ? src[j] : 0;
+    }
+    T vals[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      __half_raw h = __nv_cvt_fp8_to_halfraw(b[j], __NV_E4M3);
+      const float f = __half2float(*reinterpret_cast<__half*>(&h)) * s;
+      if constexpr (sizeof(T) == 4) vals[j] = f;
+      else if constexpr (std::is_same<T, __half>::value) vals[j] = __float2half_rn(f);
+      else vals[j] = __float2bfloat16_rn(f);
+    }
+    if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+      for (int v = 0; v < static_cast<int>(sizeof(T)); ++v) reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(vals)[v];
+    } else {
+      for (int j = 0; j < 16; ++j)
+        if (c0 + j < cols) dst[j] = vals[j];
+    }
+  }
+}
+
+}  // namespace awex
+
+// ---------------------------------------------------------------- host launchers
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+template <typename T>
+int launch_quant(const void* x, void* q, void* scales, uint64_t rows, uint64_t cols, int64_t x_stride, int64_t q_stride,
+                 int64_t scale_stride, CUtensorMapDataType dt, int ue8m0, void* status, cudaStream_t stream) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return -1;
+  // TMA rules: 16-byte aligned base, row pitch a multiple of 16 bytes
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || ((x_stride * sizeof(T)) & 15)) return -2;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(x_stride) * sizeof(T)};
+  const cuuint32_t box[2] = {awex::kBlk, awex::kBlk};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = encode(&map, dt, 2, const_cast<void*>(x), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 1000 + static_cast<int>(r);
+  const uint32_t blocks_m = static_cast<uint32_t>((rows + awex::kBlk - 1) / awex::kBlk);
+  const uint32_t blocks_n = static_cast<uint32_t>((cols + awex::kBlk - 1) / awex::kBlk);
+  const uint32_t n_blocks = blocks_m * blocks_n;
+  if (n_blocks == 0) return cudaSuccess;
+  const int smem = 2 * awex::kBlk * awex::kBlk * sizeof(T);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(awex::fp8_block_quant_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int per_sm = sizeof(T) == 4 ? 1 : 2;  // 64 KiB (2-byte types) or 128 KiB (fp32) of stages per CTA
+  uint32_t grid = static_cast<uint32_t>(sms * per_sm);
+  if (grid > n_blocks) grid = n_blocks;
+  awex::fp8_block_quant_kernel<T><<<grid, awex::kQThreads, smem, stream>>>(
+      map, static_cast<unsigned char*>(q), static_cast<float*>(scales), static_cast<uint32_t>(rows), static_cast<uint32_t>(cols),
+      q_stride, scale_stride, blocks_n, n_blocks, ue8m0, static_cast<int32_t*>(status));
+  return cudaGetLastError();
+}
+
+template <typename T>
+int launch_dequant(const void* q, const void* scales, void* out, uint64_t rows, uint64_t cols, int64_t q_stride, int64_t scale_stride,
+                   int64_t out_stride, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const uint64_t work = rows * ((cols + 15) / 16);
+  uint64_t grid = (work + 255) / 256;
+  if (grid > static_cast<uint64_t>(sms) * 16) grid = static_cast<uint64_t>(sms) * 16;
+  awex::fp8_block_dequant_kernel<T><<<static_cast<unsigned>(grid), 256, 0, stream>>>(
+      static_cast<const unsigned char*>(q), static_cast<const float*>(scales), static_cast<T*>(out), static_cast<uint32_t>(rows),
+      static_cast<uint32_t>(cols), q_stride, scale_stride, out_stride);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+// dtype codes as in xfer_desc.h: 1 bf16, 2 f16, 3 f32.  Strides in elements.
+// Returns 0, a cudaError_t, -1 (driver entry point missing) or -2 (input does
+// not meet the TMA alignment rules; callers then use the fused transfer kernel).
+int awex_launch_fp8_block_quant(const void* x, void* q, void* scales, uint64_t rows, uint64_t cols, int64_t x_stride,
+                                int64_t q_stride, int64_t scale_stride, int src_dtype, int ue8m0, void* status, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (src_dtype) {
+    case 1: return launch_quant<__nv_bfloat16>(x, q, scales, rows, cols, x_stride, q_stride, scale_stride, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ue8m0, status, s);
+    case 2: return launch_quant<__half>(x, q, scales, rows, cols, x_stride, q_stride, scale_stride, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, ue8m0, status, s);
+    case 3: return launch_quant<float>(x, q, scales, rows, cols, x_stride, q_stride, scale_stride, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, ue8m0, status, s);
+    default: return -3;
+  }
+}
+
+int awex_launch_fp8_block_dequant(const void* q, const void* scales, void* out, uint64_t rows, uint64_t cols, int64_t q_stride,
+                                  int64_t scale_stride, int64_t out_stride, int dst_dtype, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dst_dtype) {
+    case 1: return launch_dequant<__nv_bfloat16>(q, scales, out, rows, cols, q_stride, scale_stride, out_stride, s);
+    case 2: return launch_dequant<__half>(q, scales, out, rows, cols, q_stride, scale_stride, out_stride, s);
+    case 3: return launch_dequant<float>(q, scales, out, rows, cols, q_stride, scale_stride, out_stride, s);
+    default: return -3;
+  }
+}
+
+}  // extern "C"

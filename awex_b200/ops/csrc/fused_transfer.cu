@@ -133,6 +133,12 @@ __device__ __forceinline__ uint32_t stage_pitch(const XferDesc& d) {
   return (d.tile_cols * dtype_size(d.src_dtype) + 15u) & ~15u;
 }
 
+// Byte offset of source row `row` of a slab from its `src` address.
+__device__ __forceinline__ int64_t src_row_offset(const XferDesc& d, uint64_t row) {
+  if (d.row_table) return reinterpret_cast<const int64_t*>(d.row_table)[row];
+  return static_cast<int64_t>(row) * d.src_stride;
+}
+
 // Descriptor cursor: tile number -> (descriptor, tile inside it), advanced monotonically.
 struct Cursor {
   uint32_t di;
@@ -166,7 +172,7 @@ __device__ void tile_elementwise_global(const XferDesc& d, const Tile& t) {
   const float addend = d.op == OP_ADD ? static_cast<float>(d.aux_f) : 0.f;
   for (uint64_t e = threadIdx.x; e < n; e += blockDim.x) {
     uint32_t r = static_cast<uint32_t>(e / t.cols), c = static_cast<uint32_t>(e % t.cols);
-    const unsigned char* s = src + (t.row0 + r) * d.src_stride + (t.col0 + c) * ses;
+    const unsigned char* s = src + src_row_offset(d, t.row0 + r) + (t.col0 + c) * ses;
     unsigned char* o = dst + (t.row0 + r) * d.dst_stride + (t.col0 + c) * des;
     if (d.op == OP_COPY) *o = *s;
     else store_from_float(o, d.dst_dtype, load_as_float(s, d.src_dtype) + addend);
@@ -341,9 +347,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
       const uint32_t bytes = t.cols * ses;
       if (lane == 0) mbar_arrive_expect_tx(bar, bytes * t.rows);
       __syncwarp();
-      const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.row0 * d.src_stride + t.col0 * ses;
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.col0 * ses;
       const uint32_t base = smem_addr(smem + static_cast<size_t>(stage) * kStageBytes);
-      for (uint32_t r = lane; r < t.rows; r += 32) bulk_load(base + r * pitch, src + static_cast<int64_t>(r) * d.src_stride, bytes, bar);
+      for (uint32_t r = lane; r < t.rows; r += 32) bulk_load(base + r * pitch, src + src_row_offset(d, t.row0 + r), bytes, bar);
     };
 
     if (warp == 0)
@@ -395,8 +401,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
           const uint32_t pitch = stage_pitch(d);
           tile_fp8_block(d, t, [&](uint32_t r) { return static_cast<const unsigned char*>(stage_ptr) + r * pitch; }, red);
         } else {
-          const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.row0 * d.src_stride + t.col0 * dtype_size(d.src_dtype);
-          tile_fp8_block(d, t, [&](uint32_t r) { return src + static_cast<int64_t>(r) * d.src_stride; }, red);
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.col0 * dtype_size(d.src_dtype);
+          tile_fp8_block(d, t, [&](uint32_t r) { return src + src_row_offset(d, t.row0 + r); }, red);
         }
       } else if (staged) {
         tile_elementwise_staged(d, t, stage_ptr);

@@ -1,7 +1,9 @@
 // Descriptor table consumed by the fused transfer kernel.
 //
 // One descriptor is a 2-D slab: `rows` rows of `row_elems` elements, rows
-// `src_stride` / `dst_stride` bytes apart, read from this GPU's memory and
+// `src_stride` / `dst_stride` bytes apart (source rows may instead be gathered
+// through a per-row offset table, which is how a quantisation block collects
+// rows that a layout permutation scattered), read from this GPU's memory and
 // written to `dst`, which is either local or a peer-mapped address of another
 // GPU on the same NVLink domain.  The host cuts every slab into tiles of
 // `tile_rows` x `tile_cols` elements; tiles of all descriptors are numbered
@@ -49,8 +51,10 @@ struct alignas(16) XferDesc {
   uint32_t tile_cols;   // 100 elements
   uint32_t col_tiles;   // 104 tiles per band of tile_rows rows
   uint32_t reserved;    // 108
+  uint64_t row_table;   // 112 optional: address of int64 byte offsets, one per row, replacing row * src_stride
+  uint64_t reserved2;   // 120
 };
-static_assert(sizeof(XferDesc) == 112, "descriptor layout is shared with the Python encoder");
+static_assert(sizeof(XferDesc) == 128, "descriptor layout is shared with the Python encoder");
 
 // Status words written by kernels (int32[4]: code, detail0, detail1, detail2).
 enum XferStatus : int32_t {

@@ -80,7 +80,7 @@ class FlagPad:
 class TransferProgram:
     def __init__(self, table: np.ndarray, n_tiles: int, device, ready_pad: Optional[FlagPad] = None,
                  ready_slots: Sequence[int] = (), done_flag_addrs: Sequence[int] = (), timeout_ms: int = 2000,
-                 grid: int = 0):
+                 grid: int = 0, row_offsets: Sequence[int] = ()):
         if table.dtype != DESC_DTYPE:
             raise TypeError("descriptor table has the wrong dtype")
         self.lib = native.load()
@@ -88,6 +88,15 @@ class TransferProgram:
         self.device = torch.device(device)
         self.n_desc = int(table.shape[0])
         self.n_tiles = int(n_tiles)
+        self.row_table_dev = None
+        if len(row_offsets):
+            # descriptors refer to the gathered-row offsets by index + 1; give them addresses
+            self.row_table_dev = _device_array(list(row_offsets), np.int64, self.device)
+            table = table.copy()
+            has = table["row_table"] != 0
+            table["row_table"][has] = self.row_table_dev.data_ptr() + (table["row_table"][has] - 1) * 8
+        elif self.n_desc and bool((table["row_table"] != 0).any()):
+            raise ValueError("descriptor table uses gathered rows but no row offsets were given")
         self.table_host = table
         self.table_dev = torch.from_numpy(table.view(np.uint8).reshape(-1).copy()).to(self.device) if self.n_desc else torch.empty(0, dtype=torch.uint8, device=self.device)
         self.ready_pad = ready_pad

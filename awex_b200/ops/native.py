@@ -97,7 +97,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = argtypes, restype
     optional = {
-        "awex_launch_fp8_block_quant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, i32, vp], i32),
+        "awex_launch_fp8_block_quant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, i32, vp, vp], i32),
         "awex_launch_fp8_block_dequant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, vp], i32),
     }
     for name, (argtypes, restype) in optional.items():
@@ -132,6 +132,8 @@ def is_available() -> bool:
 
 
 def check(code: int, what: str) -> None:
+    if code < 0 or code >= 1000:
+        raise RuntimeError(f"{what} failed with code {code} (driver entry point missing, bad argument or tensor-map encode error)")
     if code != 0:
         msg = load().awex_cuda_error_string(code)
         raise RuntimeError(f"{what} failed: CUDA error {code} ({msg.decode() if msg else '?'})")

@@ -24,7 +24,11 @@ def _box(t: torch.Tensor, start: Sequence[int], extent: Sequence[int]) -> torch.
 
 def transformed_payload(item: CopyItem, src: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor | None]:
     """(values in destination dtype, block scales or None) for one item."""
-    piece = _box(src, item.src_start, item.extent)
+    if item.src_rows is not None:
+        rows = torch.cat([src.narrow(0, srow, n) for _rel, srow, n in item.src_rows], 0)
+        piece = _box(rows, (0,) + tuple(item.src_start[1:]), item.extent)
+    else:
+        piece = _box(src, item.src_start, item.extent)
     kind = item.value_op.kind
     if kind == "fp8_block":
         q, scale = per_block_cast_to_fp8(piece.contiguous(), item.value_op.ue8m0)

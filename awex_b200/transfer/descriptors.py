@@ -37,10 +37,10 @@ DESC_DTYPE = np.dtype(
         ("src", "<u8"), ("dst", "<u8"), ("rows", "<u8"), ("row_elems", "<u8"), ("src_stride", "<i8"),
         ("dst_stride", "<i8"), ("tile_begin", "<u8"), ("aux_ptr", "<u8"), ("aux_stride", "<i8"), ("aux_f", "<f8"),
         ("op", "<u4"), ("flags", "<u4"), ("src_dtype", "<u4"), ("dst_dtype", "<u4"), ("tile_rows", "<u4"),
-        ("tile_cols", "<u4"), ("col_tiles", "<u4"), ("reserved", "<u4"),
+        ("tile_cols", "<u4"), ("col_tiles", "<u4"), ("reserved", "<u4"), ("row_table", "<u8"), ("reserved2", "<u8"),
     ]
 )
-assert DESC_DTYPE.itemsize == 112
+assert DESC_DTYPE.itemsize == 128
 
 _DT_CODE = {torch.bfloat16: DT_BF16, torch.float16: DT_F16, torch.float32: DT_F32, torch.float8_e4m3fn: DT_FP8_E4M3}
 _DT_SIZE = {DT_BYTES: 1, DT_BF16: 2, DT_F16: 2, DT_F32: 4, DT_FP8_E4M3: 1}
@@ -126,6 +126,9 @@ def _tile_shape(rows: int, row_elems: int, ses: int, staged: bool) -> Tuple[int,
 class DescriptorEncoder:
     def __init__(self):
         self.rows: List[tuple] = []
+        # per-row source byte offsets of gathered slabs, concatenated; a descriptor's
+        # ``row_table`` holds 1 + its first index here until the table has a device address
+        self.row_offsets: List[int] = []
         self.n_tiles = 0
         self.bytes_out = 0
         self.bytes_in = 0
@@ -160,12 +163,18 @@ class DescriptorEncoder:
                        _DT_CODE[src.dtype], _DT_CODE[dst.dtype], aux_f=item.value_op.const if op == OP_ADD else 0.0)
 
     def _push(self, op, src, dst, rows, row_elems, src_stride, dst_stride, sdt, ddt, aux_ptr=0, aux_stride=0, aux_f=0.0, flags=0,
-              tile=None) -> None:
+              tile=None, row_offsets: Optional[Sequence[int]] = None) -> None:
         if op == OP_COPY:  # raw bytes
             row_elems *= _DT_SIZE[sdt]
             sdt = ddt = DT_BYTES
         ses, des = _DT_SIZE[sdt], _DT_SIZE[ddt]
         src_ok = _aligned16(src, row_elems * ses) and (rows == 1 or _aligned16(src_stride))
+        row_table = 0
+        if row_offsets is not None:
+            assert len(row_offsets) == rows
+            src_ok = _aligned16(src, row_elems * ses, *row_offsets)
+            row_table = 1 + len(self.row_offsets)
+            self.row_offsets.extend(int(o) for o in row_offsets)
         dst_ok = _aligned16(dst, row_elems * des) and (rows == 1 or _aligned16(dst_stride))
         staged = src_ok and (dst_ok or op != OP_COPY)
         if op == OP_FP8_BLOCK and sdt not in (DT_BF16, DT_F16):
@@ -184,7 +193,7 @@ class DescriptorEncoder:
         bands = -(-rows // tile_rows)
         self.rows.append(
             (src, dst, rows, row_elems, src_stride, dst_stride, self.n_tiles, aux_ptr, aux_stride, aux_f, op, flags, sdt, ddt,
-             tile_rows, tile_cols, col_tiles, 0)
+             tile_rows, tile_cols, col_tiles, 0, row_table, 0)
         )
         self.n_tiles += col_tiles * bands
 
@@ -198,9 +207,19 @@ class DescriptorEncoder:
         rows, cols = item.extent
         aux = scale.ptr + (item.scale_start[0] * scale.strides[0] + item.scale_start[1]) * 4
         flags = FLAG_UE8M0 if item.value_op.ue8m0 else 0
-        self._push(OP_FP8_BLOCK, src0, dst0, rows, cols, src.strides[0] * src.dtype.itemsize, dst.strides[0],
+        pitch = src.strides[0] * src.dtype.itemsize
+        row_offsets = None
+        if item.src_rows is not None:
+            # src0 was computed with src_start[0] as row 0; offsets are relative to it
+            row_offsets = [0] * rows
+            for rel, srow, n in item.src_rows:
+                if srow < 0 or srow + n > src.shape[0]:
+                    raise ValueError(f"{item.dst_name}: gathered rows [{srow}, {srow + n}) exceed the source tensor")
+                for i in range(n):
+                    row_offsets[rel + i] = (srow + i - item.src_start[0]) * pitch
+        self._push(OP_FP8_BLOCK, src0, dst0, rows, cols, pitch, dst.strides[0],
                    _DT_CODE[src.dtype], DT_FP8_E4M3, aux_ptr=aux, aux_stride=scale.strides[0], flags=flags,
-                   tile=(FP8_BLOCK, FP8_BLOCK))
+                   tile=(FP8_BLOCK, FP8_BLOCK), row_offsets=row_offsets)
         self.bytes_out += 4 * (-(-rows // FP8_BLOCK)) * (-(-cols // FP8_BLOCK))
 
     def table(self) -> np.ndarray:
@@ -256,7 +275,7 @@ def validate_table(table: np.ndarray, n_tiles: int, src_spans: Sequence[Tuple[in
             problems.append(f"{tag}: address or stride not aligned to the element size")
         s_lo, s_hi = src + min(0, (rows - 1) * s_stride), src + max(0, (rows - 1) * s_stride) + row_elems * ses
         d_lo, d_hi = dst + min(0, (rows - 1) * d_stride), dst + max(0, (rows - 1) * d_stride) + row_elems * des
-        if not inside(s_lo, s_hi, src_spans):
+        if int(d["row_table"]) == 0 and not inside(s_lo, s_hi, src_spans):
             problems.append(f"{tag}: reads [{s_lo:#x}, {s_hi:#x}) outside every source tensor")
         if not inside(d_lo, d_hi, dst_spans):
             problems.append(f"{tag}: writes [{d_lo:#x}, {d_hi:#x}) outside every destination tensor")

@@ -61,6 +61,9 @@ class CopyItem:
     # of this item's origin inside that scale tensor
     scale_name: Optional[str] = None
     scale_start: Tuple[int, int] = (0, 0)
+    # optional gather of dim-0 rows: ((row relative to the item, source row, n), ...)
+    # replacing the contiguous run that starts at src_start[0]
+    src_rows: Optional[Tuple[Tuple[int, int, int], ...]] = None
 
     @property
     def numel(self) -> int:
@@ -191,20 +194,37 @@ class SendProgramCompiler:
         tail_ext = tuple(op.overlap_shape[1:])
         dst_row0 = op.inf_slices[0].start
         out: List[CopyItem] = []
-        for rel, src, src_row, n in spec.rows.segments(row0, n_rows):
+        segments = spec.rows.segments(row0, n_rows)
+        if spec.value_op.kind == "fp8_block":
+            # a quantisation block needs all of its rows at once: keep the box whole
+            # and gather its rows, which must all be held by this rank
+            owners = {src[1] for _, src, _, _ in segments}
+            if owners != {my_tp}:
+                if my_tp not in owners:
+                    return []
+                raise NotImplementedError(
+                    f"{spec.name}: a block-quantised box draws rows from several training TP ranks {sorted(owners)}; "
+                    "quantising it needs those rows on one rank"
+                )
+            names = {src[0] for _, src, _, _ in segments}
+            if len(names) != 1:
+                raise NotImplementedError(f"{spec.name}: a block-quantised box draws rows from several tensors {sorted(names)}")
+            segments = [(0, segments[0][1], segments[0][2], n_rows, tuple((rel, srow, n) for rel, _, srow, n in segments))]
+        else:
+            segments = [(rel, src, src_row, n, None) for rel, src, src_row, n in segments]
+        for rel, src, src_row, n, gather in segments:
             pname, tp_rank = src
             if tp_rank != my_tp:
                 continue  # a TP peer owns these rows and sends them itself
-            if pname != lp.name:
-                lp_src = self._param_by_key[(pname, lp.vp_stage)]
-            else:
-                lp_src = lp
+            lp_src = lp if pname == lp.name else self._param_by_key[(pname, lp.vp_stage)]
             item = CopyItem(
                 src_param=lp_src.name, vp_stage=lp_src.vp_stage, src_start=(src_row,) + tail_src,
                 extent=(n,) + tail_ext, dst_rank=op.recv_rank, dst_name=spec.name,
                 dst_start=(dst_row0 + rel,) + tail_dst, src_dtype=spec.src_dtype, dst_dtype=dst_dtype,
                 value_op=spec.value_op,
             )
+            if gather is not None and len(gather) > 1:
+                item.src_rows = gather
             if spec.value_op.kind == "fp8_block":
                 if len(item.extent) != 2:
                     raise ValueError(f"{spec.name}: block fp8 needs a 2-D tensor, got extent {item.extent}")

@@ -73,3 +73,24 @@ def test_bf16_exchange_bitwise():
     job.compile_all()
     job.run_cpu()
     assert job.mismatches() == []
+
+
+@pytest.mark.parametrize("arch,train,infer", [
+    ("tiny-qwen3-moe", TrainLayout(tp=1, dp=2, ep=2), InferLayout(tp=1, fp8=True)),
+    ("tiny-llama", TrainLayout(tp=1), InferLayout(tp=2, fp8=True)),
+], ids=lambda v: v if isinstance(v, str) else v.label())
+def test_fp8_serving_exchange(arch, train, infer):
+    """bf16 training shards -> block-scaled fp8 inference shards: weights and
+    scales equal quantising the destination-layout shards directly."""
+    job = SimulatedJob(get_arch(arch), train, infer, dtype=torch.bfloat16)
+    job.compile_all()
+    assert job.check_coverage() == []
+    job.run_cpu()
+    assert job.mismatches() == []
+    assert any(it.src_rows for items in job.programs.values() for it in items) == (arch == "tiny-qwen3-moe")
+
+
+def test_fp8_block_that_spans_training_ranks_is_refused():
+    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=2), InferLayout(tp=1, fp8=True), dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError, match="several training TP ranks"):
+        job.compile_all()
