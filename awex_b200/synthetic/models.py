@@ -242,8 +242,11 @@ def _maybe_fp8(out, name: str, t: torch.Tensor, fp8: bool, parts: int = 1) -> No
 
 
 def _quant_parts(t2d: torch.Tensor, parts: int):
-    qs, ss = zip(*(per_block_cast_to_fp8(c.contiguous(), False) for c in t2d.chunk(parts, 0)))
-    return torch.cat(qs, 0), torch.cat(ss, 0)
+    # Quantise on the CPU: it is the stated oracle.  CUDA PyTorch divides by the
+    # scalar 448 as a multiplication by its reciprocal, which moves some scales by
+    # one ulp relative to the true division of the CPU path and of the kernels.
+    qs, ss = zip(*(per_block_cast_to_fp8(c.detach().cpu().contiguous(), False) for c in t2d.chunk(parts, 0)))
+    return torch.cat(qs, 0).to(t2d.device), torch.cat(ss, 0).to(t2d.device)
 
 
 def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, device="cpu", seed: int = 0,
