@@ -1,9 +1,9 @@
 """Device checksums of many tensors in one launch (``csrc/checksum.cu``) and
 the same function in numpy as its oracle.
 
-``checksum = sum_i mix64(word_i + GOLDEN * (i + 1)) mod 2**64`` over the
-8-byte words of each row (last word zero-padded), ``i = row * words_per_row +
-j``.  Contiguous tensors are hashed as one long row.
+``checksum = sum_i word_i * (GOLDEN * (2 i + 1)) mod 2**64`` over the 8-byte
+words of each row (last word zero-padded), ``i = row * words_per_row + j``.
+Contiguous tensors are hashed as one long row.
 """
 
 from __future__ import annotations
@@ -36,16 +36,6 @@ def _as_rows(t: torch.Tensor) -> Tuple[int, int, int]:
     raise ValueError("checksum needs a tensor whose rows are contiguous")
 
 
-def _mix64(x: np.ndarray) -> np.ndarray:
-    x = x.copy()
-    x ^= x >> np.uint64(33)
-    x *= np.uint64(0xFF51AFD7ED558CCD)
-    x ^= x >> np.uint64(33)
-    x *= np.uint64(0xC4CEB9FE1A85EC53)
-    x ^= x >> np.uint64(33)
-    return x
-
-
 def checksum_reference(t: torch.Tensor) -> int:
     """numpy statement of the checksum (CPU tensors or copies of GPU ones)."""
     rows, row_bytes, _ = _as_rows(t)
@@ -55,8 +45,9 @@ def checksum_reference(t: torch.Tensor) -> int:
     padded[:, :row_bytes] = raw
     words = padded.view("<u8").reshape(-1)
     with np.errstate(over="ignore"):
-        idx = np.arange(1, words.size + 1, dtype=np.uint64)
-        return int(_mix64(words + GOLDEN * idx).sum(dtype=np.uint64))
+        idx = np.arange(words.size, dtype=np.uint64)
+        keys = GOLDEN * (np.uint64(2) * idx + np.uint64(1))
+        return int((words * keys).sum(dtype=np.uint64))
 
 
 class ChecksumPlan:

@@ -4,10 +4,13 @@
 // A tensor is seen as `rows` rows of `row_bytes` bytes, `stride` bytes apart.
 // Each row is cut into 8-byte words (the last one zero-padded); word j of row r
 // has index i = r * words_per_row + j.  The checksum is
-//     sum_i mix64(word_i + GOLDEN * (i + 1))   (mod 2^64)
-// with mix64 the 64-bit murmur finaliser.  The sum is order-independent, so
-// CTAs combine partial sums with one atomic add each, while the index term
-// makes swapped rows, shifted shards and missing writes visible.
+//     sum_i word_i * K_i   (mod 2^64),   K_i = GOLDEN * (2 i + 1)
+// Every K_i is odd, so a flipped bit always changes the sum, and exchanging two
+// different words at i != j changes it by (w_i - w_j) * 2 (j - i) * GOLDEN, which is
+// non-zero modulo 2^64 for any tensor that fits in memory: swapped rows, shifted
+// shards and missing writes are all visible.  The sum is order-independent, so
+// CTAs combine partial sums with one atomic add each, and it costs one 64-bit
+// multiply-add per word, which keeps the kernel on the memory roofline.
 //
 // Used for weight validation: the reference copies every parameter to the host
 // and compares there (awex/reader/weights_reader.py:436-587); here only 16
@@ -35,16 +38,20 @@ static_assert(sizeof(SumDesc) == 56 + 8, "layout shared with the Python encoder"
 constexpr uint32_t kChunkWords = 4096;
 constexpr uint64_t kGolden = 0x9E3779B97F4A7C15ull;
 
-__device__ __forceinline__ uint64_t mix64(uint64_t x) {
-  x ^= x >> 33;
-  x *= 0xff51afd7ed558ccdull;
-  x ^= x >> 33;
-  x *= 0xc4ceb9fe1a85ec53ull;
-  x ^= x >> 33;
-  return x;
+__device__ __forceinline__ uint64_t key_of(uint64_t i) { return kGolden * (2 * i + 1); }
+
+// NaNs in a full 8-byte word, two SIMD compares per word.
+__device__ __forceinline__ uint32_t count_nans_full(uint64_t w, uint32_t dtype) {
+  const uint32_t lo = static_cast<uint32_t>(w), hi = static_cast<uint32_t>(w >> 32);
+  if (dtype == 1) return (__popc(__vcmpgtu2(lo & 0x7FFF7FFFu, 0x7F807F80u)) + __popc(__vcmpgtu2(hi & 0x7FFF7FFFu, 0x7F807F80u))) >> 4;
+  if (dtype == 2) return (__popc(__vcmpgtu2(lo & 0x7FFF7FFFu, 0x7C007C00u)) + __popc(__vcmpgtu2(hi & 0x7FFF7FFFu, 0x7C007C00u))) >> 4;
+  if (dtype == 3) return ((lo & 0x7FFFFFFFu) > 0x7F800000u) + ((hi & 0x7FFFFFFFu) > 0x7F800000u);
+  if (dtype == 4) return (__popc(__vcmpeq4(lo & 0x7F7F7F7Fu, 0x7F7F7F7Fu)) + __popc(__vcmpeq4(hi & 0x7F7F7F7Fu, 0x7F7F7F7Fu))) >> 3;
+  return 0;
 }
 
 __device__ __forceinline__ uint32_t count_nans(uint64_t w, uint32_t dtype, uint32_t valid_bytes) {
+  if (valid_bytes == 8) return count_nans_full(w, dtype);
   uint32_t n = 0;
   if (dtype == 1 || dtype == 2) {
     const uint32_t emask = dtype == 1 ? 0x7F80u : 0x7C00u, mmask = dtype == 1 ? 0x007Fu : 0x03FFu;
@@ -100,20 +107,31 @@ __global__ void __launch_bounds__(256) checksum_kernel(const SumDesc* descs, uin
       const unsigned char* row = base + static_cast<int64_t>(r) * d.stride;
       const uint64_t full_words = d.row_bytes / 8;  // words that need no padding
       const uint64_t jv1 = min(j1, full_words) & ~1ull;
-      const uint64_t idx0 = r * wpr + 1;
+      const uint64_t idx0 = r * wpr;
       uint64_t j = j0;
-      if (aligned && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {  // two words per 16-byte load
-        for (j = j0 + 2ull * threadIdx.x; j < jv1; j += 2ull * blockDim.x) {
-          const ulonglong2 w2 = __ldg(reinterpret_cast<const ulonglong2*>(row + j * 8));
-          acc += mix64(w2.x + kGolden * (idx0 + j)) + mix64(w2.y + kGolden * (idx0 + j + 1));
-          nan_acc += count_nans(w2.x, d.dtype, 8) + count_nans(w2.y, d.dtype, 8);
+      if (aligned && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {  // two words per 16-byte load, two loads in flight
+        const uint64_t step = 2ull * blockDim.x;
+        const uint64_t key_step = kGolden * 2 * step;
+        j = j0 + 2ull * threadIdx.x;
+        uint64_t key = key_of(idx0 + j);
+        for (; j + step < jv1; j += 2 * step, key += 2 * key_step) {
+          const ulonglong2 a = __ldg(reinterpret_cast<const ulonglong2*>(row + j * 8));
+          const ulonglong2 b = __ldg(reinterpret_cast<const ulonglong2*>(row + (j + step) * 8));
+          acc += a.x * key + a.y * (key + 2 * kGolden) + b.x * (key + key_step) + b.y * (key + key_step + 2 * kGolden);
+          nan_acc += count_nans_full(a.x, d.dtype) + count_nans_full(a.y, d.dtype) + count_nans_full(b.x, d.dtype) +
+                     count_nans_full(b.y, d.dtype);
+        }
+        for (; j < jv1; j += step, key += key_step) {
+          const ulonglong2 a = __ldg(reinterpret_cast<const ulonglong2*>(row + j * 8));
+          acc += a.x * key + a.y * (key + 2 * kGolden);
+          nan_acc += count_nans_full(a.x, d.dtype) + count_nans_full(a.y, d.dtype);
         }
         j = max(j0, jv1);
       }
       for (j += threadIdx.x; j < j1; j += blockDim.x) {
         uint32_t valid;
         uint64_t w = load_word(row, j, d.row_bytes, aligned, &valid);
-        acc += mix64(w + kGolden * (idx0 + j));
+        acc += w * key_of(idx0 + j);
         nan_acc += count_nans(w, d.dtype, valid);
       }
     } else {  // several whole (short) rows: one warp per row
@@ -124,7 +142,7 @@ __global__ void __launch_bounds__(256) checksum_kernel(const SumDesc* descs, uin
         for (uint64_t j = threadIdx.x & 31; j < wpr; j += 32) {
           uint32_t valid;
           uint64_t w = load_word(row, j, d.row_bytes, aligned, &valid);
-          acc += mix64(w + kGolden * (r * wpr + j + 1));
+          acc += w * key_of(r * wpr + j);
           nan_acc += count_nans(w, d.dtype, valid);
         }
       }

@@ -11,8 +11,9 @@
 // mbarrier) into a double-buffered stage; out-of-range rows/columns of edge
 // blocks are zero-filled by the TMA unit, which is exactly the reference's
 // zero padding.  Threads read the stage as consecutive 16-byte chunks (no bank
-// conflicts), reduce |x| through shuffles + shared memory, and write e4m3 with
-// coalesced 8-byte stores.  The reference spends ~10 ATen kernels and a padded
+// conflicts) twice: once for the block maximum (integer SIMD on magnitude bits),
+// once to quantise (exact without a division per element, see fp8_math.cuh) and
+// write e4m3 with coalesced 8-byte stores.  The reference spends ~10 ATen kernels and a padded
 // temporary on the same math.
 
 #include <cuda.h>
@@ -24,23 +25,14 @@
 #include <cstdint>
 #include <type_traits>
 
+#include "fp8_math.cuh"
+
 namespace awex {
 
 constexpr int kBlk = 128;
 constexpr int kQThreads = 256;
 
 __device__ __forceinline__ uint32_t q_smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ float nan_max(float m, float a) { return (a > m || a != a) ? a : m; }
-
-__device__ __forceinline__ float scale_of(float amax, bool ue8m0) {
-  float s = (amax < 1e-4f ? 1e-4f : amax) / 448.0f;
-  if (ue8m0) {
-    float c = s < 1e-10f ? 1e-10f : s;
-    s = exp2f(ceilf(static_cast<float>(log2(static_cast<double>(c)))));
-  }
-  return s;
-}
 
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
@@ -59,7 +51,7 @@ fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char*
                        uint32_t n_blocks, int ue8m0, int32_t* status) {
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t bars[2];
-  __shared__ float red[kQThreads / 32];
+  __shared__ uint32_t red[kQThreads / 32];
   __shared__ int give_up;
   constexpr uint32_t kStage = kBlk * kBlk * sizeof(T);
   constexpr int kChunkElems = 16 / sizeof(T);          // elements per 16-byte chunk
@@ -112,51 +104,60 @@ fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char*
     if (give_up) break;
     const unsigned char* stage_ptr = stage_mem + stage * kStage;
     const uint32_t chunk = tid % kChunksPerRow, row_in_pass = tid / kChunksPerRow;
-    float vals[kPasses][kChunkElems];
-    float m = 0.f;
+    // pass 1: amax as ordered magnitude bits (NaN sorts above infinity)
+    uint32_t m = 0;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
       const uint32_t r = p * kRowsPerPass + row_in_pass;
       const uint4 raw = *reinterpret_cast<const uint4*>(stage_ptr + (r * kChunksPerRow + chunk) * 16);
-      const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-      for (int j = 0; j < kChunkElems; ++j) {
-        vals[p][j] = to_float<T>(e[j]);
-        m = nan_max(m, fabsf(vals[p][j]));
+      if constexpr (sizeof(T) == 2) {
+        m = amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(m, raw.x), raw.y), raw.z), raw.w);
+      } else {
+        m = max(max(m, raw.x & 0x7FFFFFFFu), max(raw.y & 0x7FFFFFFFu, max(raw.z & 0x7FFFFFFFu, raw.w & 0x7FFFFFFFu)));
       }
     }
+    if constexpr (sizeof(T) == 2) m = max(m & 0xFFFFu, m >> 16);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m = nan_max(m, __shfl_xor_sync(0xffffffffu, m, off));
+    for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, off));
     if ((tid & 31) == 0) red[tid >> 5] = m;
     __syncthreads();
-    float amax = red[0];
+    uint32_t all = red[0];
 #pragma unroll
-    for (int w = 1; w < kQThreads / 32; ++w) amax = nan_max(amax, red[w]);
-    const float scale = scale_of(amax, ue8m0 != 0);
+    for (int w = 1; w < kQThreads / 32; ++w) all = max(all, red[w]);
+    float amax;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) amax = __uint_as_float(all << 16);
+    else if constexpr (std::is_same<T, __half>::value) amax = __half2float(__ushort_as_half(static_cast<unsigned short>(all)));
+    else amax = __uint_as_float(all);
+    const QuantScale qs = make_quant_scale(amax, ue8m0 != 0);
     const uint32_t brow = blk / blocks_n, bcol = blk % blocks_n;
-    if (tid == 0) scales[static_cast<int64_t>(brow) * scale_stride + bcol] = scale;
+    if (tid == 0) scales[static_cast<int64_t>(brow) * scale_stride + bcol] = qs.s;
+    // pass 2: re-read the stage, quantise, store
     const uint32_t col0 = bcol * kBlk + chunk * kChunkElems;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
       const uint32_t r = brow * kBlk + p * kRowsPerPass + row_in_pass;
       if (r >= rows || col0 >= cols) continue;
-      unsigned char out[kChunkElems];
-#pragma unroll
-      for (int j = 0; j < kChunkElems; j += 2) {
-        const uint16_t pair = __nv_cvt_float2_to_fp8x2(
-            make_float2(__fdiv_rn(vals[p][j], scale), __fdiv_rn(vals[p][j + 1], scale)), __NV_SATFINITE, __NV_E4M3);
-        out[j] = static_cast<unsigned char>(pair & 0xFF);
-        out[j + 1] = static_cast<unsigned char>(pair >> 8);
-      }
+      const uint4 raw = *reinterpret_cast<const uint4*>(stage_ptr + ((p * kRowsPerPass + row_in_pass) * kChunksPerRow + chunk) * 16);
       unsigned char* o = q + static_cast<int64_t>(r) * q_stride + col0;
       const bool whole = col0 + kChunkElems <= cols;
-      if (whole && kChunkElems == 8 && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
-        *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(out);
-      } else if (whole && kChunkElems == 4 && (reinterpret_cast<uintptr_t>(o) & 3) == 0) {
-        *reinterpret_cast<uint32_t*>(o) = *reinterpret_cast<const uint32_t*>(out);
+      if constexpr (sizeof(T) == 2) {
+        const uint2 out = quant_chunk16<std::is_same<T, __nv_bfloat16>::value>(raw, qs);
+        if (whole && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
+          *reinterpret_cast<uint2*>(o) = out;
+        } else {
+          const unsigned char* b = reinterpret_cast<const unsigned char*>(&out);
+          for (int j = 0; j < kChunkElems; ++j)
+            if (col0 + j < cols) o[j] = b[j];
+        }
       } else {
-        for (int j = 0; j < kChunkElems; ++j)
-          if (col0 + j < cols) o[j] = out[j];
+        const uint32_t out = quant_pair(__uint_as_float(raw.x), __uint_as_float(raw.y), qs) |
+                             (quant_pair(__uint_as_float(raw.z), __uint_as_float(raw.w), qs) << 16);
+        if (whole && (reinterpret_cast<uintptr_t>(o) & 3) == 0) {
+          *reinterpret_cast<uint32_t*>(o) = out;
+        } else {
+          for (int j = 0; j < kChunkElems; ++j)
+            if (col0 + j < cols) o[j] = static_cast<unsigned char>(out >> (8 * j));
+        }
       }
     }
     __syncthreads();  // stage and `red` may be reused
@@ -250,7 +251,7 @@ int launch_quant(const void* x, void* q, void* scales, uint64_t rows, uint64_t c
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int per_sm = sizeof(T) == 4 ? 1 : 2;  // 64 KiB (2-byte types) or 128 KiB (fp32) of stages per CTA
+  const int per_sm = sizeof(T) == 4 ? 1 : 3;  // 64 KiB (2-byte types) or 128 KiB (fp32) of stages per CTA
   uint32_t grid = static_cast<uint32_t>(sms * per_sm);
   if (grid > n_blocks) grid = n_blocks;
   awex::fp8_block_quant_kernel<T><<<grid, awex::kQThreads, smem, stream>>>(

@@ -27,6 +27,7 @@
 
 #include <cstdint>
 
+#include "fp8_math.cuh"
 #include "xfer_desc.h"
 
 namespace awex {
@@ -193,97 +194,92 @@ __device__ void tile_elementwise_staged(const XferDesc& d, const Tile& t, const 
   }
 }
 
-// NaN-propagating |x| maximum, as torch.amax does.
-__device__ __forceinline__ float amax_step(float m, float x) {
-  float a = fabsf(x);
-  return (a > m || a != a) ? a : m;
-}
+// ---- block fp8 tiles -------------------------------------------------------------------------
+// A tile is one 128x128 (or smaller edge) block.  Work is cut into items of one
+// row x 8 columns; two passes over the source: amax, then quantise and store.
+// Nothing is kept in registers between the passes, so the kernel's register
+// budget stays small and all warps of the CTA take part.
 
-// scale = max(amax, 1e-4) / 448, optionally rounded up to a power of two the
-// way fp32 log2 -> ceil -> exp2 does.
-__device__ __forceinline__ float block_scale(float amax, bool ue8m0) {
-  float s = (amax < 1e-4f ? 1e-4f : amax) / 448.0f;
-  if (ue8m0) {
-    float clamped = s < 1e-10f ? 1e-10f : s;
-    float l = static_cast<float>(log2(static_cast<double>(clamped)));
-    s = exp2f(ceilf(l));
-  }
-  return s;
-}
-
-// One 128x128 (or smaller edge) block: amax over the block, then q = x / scale.
-// `row_ptr(r)` gives the address of source row r of the block.
-template <typename RowPtr>
-__device__ void tile_fp8_block(const XferDesc& d, const Tile& t, RowPtr row_ptr, float* red /*[8]*/) {
-  const uint32_t ses = dtype_size(d.src_dtype);
-  const uint32_t row = threadIdx.x >> 1, half = threadIdx.x & 1;  // two threads per row, 64 columns each
-  const uint32_t c_begin = half * 64u;
-  const uint32_t c_end = min(c_begin + 64u, t.cols);
-  const bool active = row < t.rows && c_begin < t.cols;
-  float vals[64];
-  float m = 0.f;
-  if (active) {
-    const unsigned char* s = row_ptr(row) + c_begin * ses;
-    if (d.src_dtype == DT_BF16 && c_end - c_begin == 64u && (reinterpret_cast<uintptr_t>(s) & 15u) == 0) {
+// CTA-wide maximum of ordered magnitude bits (see fp8_math.cuh).
+__device__ __forceinline__ uint32_t cta_max_u32(uint32_t m, uint32_t* red) {
 #pragma unroll
-      for (int v = 0; v < 8; ++v) {
-        uint4 raw = reinterpret_cast<const uint4*>(s)[v];
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = __bfloat1622float2(h[j]);
-          vals[v * 8 + j * 2] = f.x;
-          vals[v * 8 + j * 2 + 1] = f.y;
-        }
-      }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 64; ++c) vals[c] = (c_begin + c < c_end) ? load_as_float(s + c * ses, d.src_dtype) : 0.f;
-    }
-#pragma unroll
-    for (int c = 0; c < 64; ++c) m = amax_step(m, vals[c]);
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    float o = __shfl_xor_sync(0xffffffffu, m, off);
-    m = (o > m || o != o) ? o : m;
-  }
+  for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, off));
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
   __syncthreads();
-  float amax = red[0];
-#pragma unroll
-  for (int w = 1; w < kThreads / 32; ++w) {
-    float o = red[w];
-    amax = (o > amax || o != o) ? o : amax;
+  uint32_t all = 0;
+  for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) all = max(all, red[w]);
+  __syncthreads();  // `red` may be rewritten by the next tile
+  return all;
+}
+
+__device__ __forceinline__ void store_scale(const XferDesc& d, const Tile& t, float scale) {
+  if (threadIdx.x == 0) reinterpret_cast<float*>(d.aux_ptr)[static_cast<int64_t>(t.band) * d.aux_stride + t.ct] = scale;
+}
+
+// Fast form: 2-byte source staged in shared memory with a 256-byte pitch
+// (tile_cols == 128), destination rows 8-byte aligned.
+template <bool kBf16>
+__device__ void tile_fp8_staged(const XferDesc& d, const Tile& t, const unsigned char* stage, uint32_t* red) {
+  const uint32_t chunks = t.cols >> 3;  // the bulk path guarantees cols % 8 == 0
+  const uint32_t items = t.rows * 16u;
+  uint32_t m = 0;
+  for (uint32_t it = threadIdx.x; it < items; it += blockDim.x) {
+    const uint32_t row = it >> 4, chunk = it & 15u;
+    if (chunk >= chunks) continue;
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + row * 256u + chunk * 16u);
+    m = amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(m, raw.x), raw.y), raw.z), raw.w);
   }
-  const float scale = block_scale(amax, (d.flags & FLAG_UE8M0) != 0);
-  if (threadIdx.x == 0) {
-    float* sp = reinterpret_cast<float*>(d.aux_ptr) + static_cast<int64_t>(t.band) * d.aux_stride + t.ct;
-    *sp = scale;
-  }
-  if (active) {
-    unsigned char* o = reinterpret_cast<unsigned char*>(d.dst) + (t.row0 + row) * d.dst_stride + t.col0 + c_begin;
-    if ((d.flags & FLAG_DST_VEC16) && c_end - c_begin == 64u) {
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float* f = &vals[v * 16 + j * 4];
-          uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(f[0], scale), __fdiv_rn(f[1], scale)), __NV_SATFINITE, __NV_E4M3);
-          uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(f[2], scale), __fdiv_rn(f[3], scale)), __NV_SATFINITE, __NV_E4M3);
-          w[j] = lo | (hi << 16);
-        }
-        reinterpret_cast<uint4*>(o)[v] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+  m = cta_max_u32(max(m & 0xFFFFu, m >> 16), red);
+  const float amax = kBf16 ? __uint_as_float(m << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(m)));
+  const QuantScale q = make_quant_scale(amax, (d.flags & FLAG_UE8M0) != 0);
+  store_scale(d, t, q.s);
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
+  const bool vec = (d.flags & FLAG_DST_VEC16) != 0;
+  for (uint32_t it = threadIdx.x; it < items; it += blockDim.x) {
+    const uint32_t row = it >> 4, chunk = it & 15u;
+    if (chunk >= chunks) continue;
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + row * 256u + chunk * 16u);
+    const uint2 out = quant_chunk16<kBf16>(raw, q);
+    unsigned char* o = dst + static_cast<int64_t>(row) * d.dst_stride + chunk * 8u;
+    if (vec) {
+      *reinterpret_cast<uint2*>(o) = out;
     } else {
-#pragma unroll
-      for (int c = 0; c < 64; ++c)
-        if (c_begin + c < c_end)
-          o[c] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(__fdiv_rn(vals[c], scale), __NV_SATFINITE, __NV_E4M3));
+      const unsigned char* b = reinterpret_cast<const unsigned char*>(&out);
+      for (int j = 0; j < 8; ++j) o[j] = b[j];
     }
   }
-  __syncthreads();  // `red` is reused by the next block
+}
+
+// General form: any source dtype and alignment, rows read from global memory
+// (directly or through the row table), columns masked at the edge.
+__device__ void tile_fp8_generic(const XferDesc& d, const Tile& t, uint32_t* red) {
+  const uint32_t ses = dtype_size(d.src_dtype);
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.col0 * ses;
+  const uint32_t chunks = (t.cols + 7u) >> 3;
+  const uint32_t items = t.rows * chunks;
+  uint32_t m = 0;
+  for (uint32_t it = threadIdx.x; it < items; it += blockDim.x) {
+    const uint32_t row = it / chunks, c0 = (it % chunks) * 8u;
+    const unsigned char* s = src + src_row_offset(d, t.row0 + row) + c0 * ses;
+    for (uint32_t j = 0; j < 8u && c0 + j < t.cols; ++j) m = amax_bits_f32(m, load_as_float(s + j * ses, d.src_dtype));
+  }
+  m = cta_max_u32(m, red);
+  const QuantScale q = make_quant_scale(__uint_as_float(m), (d.flags & FLAG_UE8M0) != 0);
+  store_scale(d, t, q.s);
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
+  for (uint32_t it = threadIdx.x; it < items; it += blockDim.x) {
+    const uint32_t row = it / chunks, c0 = (it % chunks) * 8u;
+    const unsigned char* s = src + src_row_offset(d, t.row0 + row) + c0 * ses;
+    unsigned char* o = dst + static_cast<int64_t>(row) * d.dst_stride + c0;
+    for (uint32_t j = 0; j < 8u && c0 + j < t.cols; j += 2) {
+      const float a = load_as_float(s + j * ses, d.src_dtype);
+      const bool pair = c0 + j + 1 < t.cols;
+      const float b = pair ? load_as_float(s + (j + 1) * ses, d.src_dtype) : 0.f;
+      const uint32_t out = quant_pair(a, b, q);
+      o[j] = static_cast<unsigned char>(out & 0xFFu);
+      if (pair) o[j + 1] = static_cast<unsigned char>(out >> 8);
+    }
+  }
 }
 
 // ---------------------------------------------------------------- the kernel
@@ -292,7 +288,7 @@ __device__ __forceinline__ bool wants_stage(const XferDesc& d) { return (d.flags
 __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __grid_constant__ XferParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ float red[kThreads / 32];
+  __shared__ uint32_t red[kThreads / 32];
   __shared__ volatile int abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -397,13 +393,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
       __syncthreads();  // staged data (observed by warp 0) is ordered before everyone's reads
       if (abort_flag) break;
       if (d.op == OP_FP8_BLOCK) {
-        if (staged) {
-          const uint32_t pitch = stage_pitch(d);
-          tile_fp8_block(d, t, [&](uint32_t r) { return static_cast<const unsigned char*>(stage_ptr) + r * pitch; }, red);
-        } else {
-          const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.col0 * dtype_size(d.src_dtype);
-          tile_fp8_block(d, t, [&](uint32_t r) { return src + src_row_offset(d, t.row0 + r); }, red);
-        }
+        if (staged && d.src_dtype == DT_BF16) tile_fp8_staged<true>(d, t, stage_ptr, red);
+        else if (staged && d.src_dtype == DT_F16) tile_fp8_staged<false>(d, t, stage_ptr, red);
+        else tile_fp8_generic(d, t, red);
       } else if (staged) {
         tile_elementwise_staged(d, t, stage_ptr);
       } else {

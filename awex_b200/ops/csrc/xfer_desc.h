@@ -68,7 +68,7 @@ enum XferStatus : int32_t {
 constexpr int kStageBytes = 32 * 1024;
 constexpr int kStages = 6;
 constexpr int kLookahead = 4;
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
 
 struct XferParams {
   const XferDesc* descs;
