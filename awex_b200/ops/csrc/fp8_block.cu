@@ -280,6 +280,25 @@ int launch_dequant(const void* q, const void* scales, void* out, uint64_t rows, 
 
 extern "C" {
 
+// Encode a 2-D tiled tensor map (no swizzle, zero fill) over a row-major slab.
+// `elem_bytes` is 1, 2 or 4.  Returns 0 on success.
+int awex_encode_tensor_map_2d(void* out_map128, int elem_bytes, uint64_t base, uint64_t cols, uint64_t rows,
+                              uint64_t row_pitch_bytes, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return -1;
+  if ((base & 15) || (row_pitch_bytes & 15) || box_cols > 256 || box_rows > 256) return -2;
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_pitch_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = encode(static_cast<CUtensorMap*>(out_map128), dt, 2, reinterpret_cast<void*>(base), dims, strides, box,
+                      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
+}
+
 // dtype codes as in xfer_desc.h: 1 bf16, 2 f16, 3 f32.  Strides in elements.
 // Returns 0, a cudaError_t, -1 (driver entry point missing) or -2 (input does
 // not meet the TMA alignment rules; callers then use the fused transfer kernel).

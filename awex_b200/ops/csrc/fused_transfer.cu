@@ -338,6 +338,20 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
         return;
       }
       const Tile t = tile_of(d, t_begin + j - load_cur.begin);
+      if (d.tensor_map) {
+        // one tiled TMA load for the whole tile; rows and columns past the slab's
+        // edge are zero-filled and still counted in the transaction bytes
+        if (lane == 0) {
+          const uint32_t box_bytes = d.tile_rows * stage_pitch(d);
+          mbar_arrive_expect_tx(bar, box_bytes);
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                  smem_addr(smem + static_cast<size_t>(stage) * kStageBytes)),
+              "l"(d.tensor_map), "r"(static_cast<int32_t>(t.col0)), "r"(static_cast<int32_t>(t.row0)), "r"(bar)
+              : "memory");
+        }
+        return;
+      }
       const uint32_t ses = dtype_size(d.src_dtype);
       const uint32_t pitch = stage_pitch(d);
       const uint32_t bytes = t.cols * ses;

@@ -52,7 +52,7 @@ struct alignas(16) XferDesc {
   uint32_t col_tiles;   // 104 tiles per band of tile_rows rows
   uint32_t reserved;    // 108
   uint64_t row_table;   // 112 optional: address of int64 byte offsets, one per row, replacing row * src_stride
-  uint64_t reserved2;   // 120
+  uint64_t tensor_map;  // 120 optional: address of a 128-byte CUtensorMap over this slab (2-D tiled loads)
 };
 static_assert(sizeof(XferDesc) == 128, "descriptor layout is shared with the Python encoder");
 

@@ -62,8 +62,8 @@ def _quant_via_transfer_kernel(x, q, s, ue8m0: bool) -> None:
 
     item = CopyItem("x", 0, (0, 0), tuple(x.shape), 0, "q", (0, 0), x.dtype, torch.float8_e4m3fn,
                     ValueOp("fp8_block", dtype=torch.float8_e4m3fn, ue8m0=ue8m0), scale_name="s", scale_start=(0, 0))
-    table, n_tiles, _ = encode_items([item], {("x", 0): TensorAddr.of(x)}, {0: {"q": TensorAddr.of(q), "s": TensorAddr.of(s)}})
-    TransferProgram(table, n_tiles, x.device).launch(1)
+    table, n_tiles, enc = encode_items([item], {("x", 0): TensorAddr.of(x)}, {0: {"q": TensorAddr.of(q), "s": TensorAddr.of(s)}})
+    TransferProgram(table, n_tiles, x.device, encoder=enc).launch(1)
 
 
 def block_dequant(q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:

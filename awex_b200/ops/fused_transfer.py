@@ -80,7 +80,9 @@ class FlagPad:
 class TransferProgram:
     def __init__(self, table: np.ndarray, n_tiles: int, device, ready_pad: Optional[FlagPad] = None,
                  ready_slots: Sequence[int] = (), done_flag_addrs: Sequence[int] = (), timeout_ms: int = 2000,
-                 grid: int = 0, row_offsets: Sequence[int] = ()):
+                 grid: int = 0, row_offsets: Sequence[int] = (), tensor_map_descs: Sequence[int] = (), encoder=None):
+        if encoder is not None:  # side tables produced while encoding
+            row_offsets, tensor_map_descs = encoder.row_offsets, encoder.tensor_map_descs
         if table.dtype != DESC_DTYPE:
             raise TypeError("descriptor table has the wrong dtype")
         self.lib = native.load()
@@ -97,6 +99,9 @@ class TransferProgram:
             table["row_table"][has] = self.row_table_dev.data_ptr() + (table["row_table"][has] - 1) * 8
         elif self.n_desc and bool((table["row_table"] != 0).any()):
             raise ValueError("descriptor table uses gathered rows but no row offsets were given")
+        self.tensor_maps_dev = None
+        if len(tensor_map_descs):
+            table = self._attach_tensor_maps(table, tensor_map_descs)
         self.table_host = table
         self.table_dev = torch.from_numpy(table.view(np.uint8).reshape(-1).copy()).to(self.device) if self.n_desc else torch.empty(0, dtype=torch.uint8, device=self.device)
         self.ready_pad = ready_pad
@@ -109,6 +114,31 @@ class TransferProgram:
         self.timeout_ns = int(timeout_ms) * 1_000_000
         self.grid = grid
         self.launches = 0
+
+    def _attach_tensor_maps(self, table: np.ndarray, indices: Sequence[int]) -> np.ndarray:
+        """Encode one CUtensorMap per listed descriptor (its tiles are then fetched
+        with a single tiled TMA load each) and store their device addresses."""
+        import ctypes
+
+        from awex_b200.transfer.descriptors import _DT_SIZE
+
+        table = table.copy()
+        maps = np.zeros((len(indices), 128), dtype=np.uint8)
+        for slot, i in enumerate(indices):
+            d = table[i]
+            es = _DT_SIZE[int(d["src_dtype"])]
+            code = self.lib.awex_encode_tensor_map_2d(
+                maps[slot].ctypes.data_as(ctypes.c_void_p), es, int(d["src"]), int(d["row_elems"]), int(d["rows"]),
+                int(d["src_stride"]) if int(d["rows"]) > 1 else int(d["row_elems"]) * es, int(d["tile_cols"]), int(d["tile_rows"]),
+            )
+            if code != 0:
+                raise RuntimeError(f"cuTensorMapEncodeTiled failed for descriptor {i} (code {code})")
+        self.tensor_maps_dev = torch.from_numpy(maps.reshape(-1)).to(self.device)
+        base = self.tensor_maps_dev.data_ptr()
+        assert base % 128 == 0
+        for slot, i in enumerate(indices):
+            table["tensor_map"][i] = base + 128 * slot
+        return table
 
     def launch(self, epoch: int, stream_ptr: Optional[int] = None) -> None:
         stream = native.current_stream_ptr() if stream_ptr is None else stream_ptr

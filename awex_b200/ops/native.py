@@ -97,6 +97,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = argtypes, restype
     optional = {
+        "awex_encode_tensor_map_2d": ([vp, i32, u64, u64, u64, u64, u32, u32], i32),
         "awex_launch_fp8_block_quant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, i32, vp, vp], i32),
         "awex_launch_fp8_block_dequant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, vp], i32),
     }

@@ -69,10 +69,10 @@ def _transfer_case(kind: str, mb: int):
         raise SystemExit(f"unknown case {kind}")
     srcs = {("w", 0): TensorAddr.of(src)}
     dsts = {0: {n: TensorAddr.of(t) for n, t in views.items()}}
-    table, n_tiles, _ = encode_items(items, srcs, dsts)
+    table, n_tiles, enc = encode_items(items, srcs, dsts)
     problems = validate_table(table, n_tiles, [a.byte_span() for a in srcs.values()], [a.byte_span() for a in dsts[0].values()])
     assert not problems, problems
-    prog = TransferProgram(table, n_tiles, "cuda")
+    prog = TransferProgram(table, n_tiles, "cuda", encoder=enc)
     epoch = [0]
 
     def run():

@@ -240,7 +240,7 @@ class SimulatedJob:
         self.done_pad = FlagPad(self.train.world, self.device)
         self.gpu_programs = {
             rank: TransferProgram(table, n_tiles, self.device, done_flag_addrs=[self.done_pad.slot_addr(rank)],
-                                  timeout_ms=timeout_ms, grid=grid, row_offsets=enc.row_offsets)
+                                  timeout_ms=timeout_ms, grid=grid, encoder=enc)
             for rank, (table, n_tiles, enc) in self.encoded.items()
         }
         self.waiter = FlagWaiter(self.done_pad, list(range(self.train.world)), self.device, timeout_ms=timeout_ms)

@@ -37,7 +37,7 @@ DESC_DTYPE = np.dtype(
         ("src", "<u8"), ("dst", "<u8"), ("rows", "<u8"), ("row_elems", "<u8"), ("src_stride", "<i8"),
         ("dst_stride", "<i8"), ("tile_begin", "<u8"), ("aux_ptr", "<u8"), ("aux_stride", "<i8"), ("aux_f", "<f8"),
         ("op", "<u4"), ("flags", "<u4"), ("src_dtype", "<u4"), ("dst_dtype", "<u4"), ("tile_rows", "<u4"),
-        ("tile_cols", "<u4"), ("col_tiles", "<u4"), ("reserved", "<u4"), ("row_table", "<u8"), ("reserved2", "<u8"),
+        ("tile_cols", "<u4"), ("col_tiles", "<u4"), ("reserved", "<u4"), ("row_table", "<u8"), ("tensor_map", "<u8"),
     ]
 )
 assert DESC_DTYPE.itemsize == 128
@@ -129,6 +129,8 @@ class DescriptorEncoder:
         # per-row source byte offsets of gathered slabs, concatenated; a descriptor's
         # ``row_table`` holds 1 + its first index here until the table has a device address
         self.row_offsets: List[int] = []
+        # descriptors (by index) whose tiles are fetched with one tiled TMA load each
+        self.tensor_map_descs: List[int] = []
         self.n_tiles = 0
         self.bytes_out = 0
         self.bytes_in = 0
@@ -191,6 +193,8 @@ class DescriptorEncoder:
             flags |= FLAG_DST_VEC16
         col_tiles = -(-row_elems // tile_cols)
         bands = -(-rows // tile_rows)
+        if op == OP_FP8_BLOCK and staged and row_offsets is None:
+            self.tensor_map_descs.append(len(self.rows))
         self.rows.append(
             (src, dst, rows, row_elems, src_stride, dst_stride, self.n_tiles, aux_ptr, aux_stride, aux_f, op, flags, sdt, ddt,
              tile_rows, tile_cols, col_tiles, 0, row_table, 0)

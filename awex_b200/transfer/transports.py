@@ -186,7 +186,7 @@ class PeerStoreSender:
         # must announce readiness through a flag before they are overwritten
         self.program = TransferProgram(
             table, n_tiles, self.device, ready_pad=self.ready_pad, ready_slots=remote, done_flag_addrs=done_flags,
-            timeout_ms=self.timeout_ms, grid=self.grid, row_offsets=enc.row_offsets,
+            timeout_ms=self.timeout_ms, grid=self.grid, encoder=enc,
         )
         self.bytes_out, self.bytes_in, self.n_desc = enc.bytes_out, enc.bytes_in, int(table.shape[0])
         logger.info(
