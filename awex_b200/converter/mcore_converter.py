@@ -360,18 +360,25 @@ class McoreToHFWeightConverter:
         )
 
     # ---- public API --------------------------------------------------------------------------
-    def plan_param(self, name: str, shape: Sequence[int], dtype: torch.dtype, vp_stage: Optional[int] = None) -> List[TensorSpec]:
+    def plan_param(self, name: str, shape: Sequence[int], dtype: torch.dtype, vp_stage: Optional[int] = None,
+                   source_name: Optional[str] = None) -> List[TensorSpec]:
         """Describe the canonical tensors produced from training parameter
         ``name`` without touching data.  Sources in the returned row maps are
-        ``(name, tp_rank)`` with ``name`` exactly as passed in."""
+        ``(source_name or name, tp_rank)``; ``source_name`` lets a subclass
+        route a rewritten name while still pointing at the real parameter."""
         shape = tuple(int(d) for d in shape)
+        src = source_name or name
+        routed = self._canonical_source_name(name, vp_stage)
         if not shape:
-            out = self._route(self._canonical_source_name(name, vp_stage), name, Rows.full((name, self.rank_info.tp_rank), 1))
+            out = self._route(routed, src, Rows.full((src, self.rank_info.tp_rank), 1))
             return [TensorSpec(n, None, (), dtype, op) for n, _, op in out]
-        rows = self._own(name, shape[0])
+        rows = self._own(src, shape[0])
+        return self._finish_specs(self._route(routed, src, rows), shape, dtype)
+
+    def _finish_specs(self, routed, shape, dtype) -> List[TensorSpec]:
         specs: List[TensorSpec] = []
-        for cname, crow, op in self._route(self._canonical_source_name(name, vp_stage), name, rows):
-            spec = TensorSpec(cname, crow, shape[1:], dtype, op)
+        for cname, crow, op in routed:
+            spec = TensorSpec(cname, crow, tuple(shape[1:]), dtype, op)
             spec.value_op = self._value_op_for(cname, spec)
             specs.append(spec)
             if spec.value_op.kind == "fp8_block":
