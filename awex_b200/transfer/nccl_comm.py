@@ -1,0 +1,213 @@
+"""Library send/recv transport: the portable data plane for links that peer
+stores cannot reach (another node, or a CPU run over gloo).
+
+Where the fused kernel writes straight into a peer's parameters, this path ships
+one packed message per (sender, destination) pair with ``torch.distributed``
+point-to-point calls.  It keeps the host-side pieces the reference's NCCL
+transports are made of (`awex/transfer/nccl_comm.py:53-624`): consistency check
+of the train<->inference device maps, the ring-stage schedule of the co-located
+exchange with its two-phase colouring, round-robin interleaving across peers,
+and a watchdog that reports what was in flight when an exchange stalls.
+"""
+
+from __future__ import annotations
+
+import faulthandler
+import math
+import tempfile
+import threading
+import time
+from dataclasses import dataclass
+from typing import Callable, Dict, Iterable, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from awex_b200 import logging
+
+logger = logging.getLogger(__name__)
+
+
+# ------------------------------------------------------------------------------------ rank maps
+def validate_rank_mappings(train_to_infer: Dict[int, int], infer_to_train: Dict[int, int]) -> None:
+    """The two device maps of co-located mode must be inverse bijections."""
+    for a, b, fwd, back in ((train_to_infer, infer_to_train, "train", "infer"), (infer_to_train, train_to_infer, "infer", "train")):
+        for src, dst in a.items():
+            if b.get(dst) != src:
+                raise ValueError(f"Inconsistent rank mapping: {fwd}_rank {src} -> {back}_rank {dst} but the inverse map returns {b.get(dst)}")
+
+
+# ------------------------------------------------------------------------------------ ring stages
+def ring_peers(rank: int, stage: int, world: int) -> Tuple[int, int]:
+    """At ring stage ``stage`` a rank sends to ``rank + stage`` and receives from
+    ``rank - stage`` (mod world); stage 0 is the local copy."""
+    return (rank + stage) % world, (rank - stage) % world
+
+
+def compute_two_phase_partition(rank: int, stage_idx: int, world_size: int) -> int:
+    """Colour (0 or 1) of ``rank`` at a ring stage.  The edges ``r -> r+stage``
+    split the ranks into ``gcd(world, stage)`` cycles; walking a cycle, colours
+    alternate, so on even cycles every edge joins a colour-0 rank (sends first)
+    to a colour-1 rank (receives first) and blocking calls cannot deadlock."""
+    if stage_idx % world_size == 0:
+        return 0
+    g = math.gcd(world_size, stage_idx)
+    cycle_len, step = world_size // g, stage_idx // g
+    position = ((rank // g) * pow(step, -1, cycle_len)) % cycle_len
+    return position % 2
+
+
+def interleave_by_peer(ops: Sequence, peer_of: Callable = lambda op: op.peer) -> list:
+    """Round-robin over peers so that consecutive operations target different
+    links."""
+    lanes: Dict[int, list] = {}
+    for op in ops:
+        lanes.setdefault(peer_of(op), []).append(op)
+    order = sorted(lanes)
+    out = []
+    depth = max((len(v) for v in lanes.values()), default=0)
+    for i in range(depth):
+        out.extend(lanes[p][i] for p in order if i < len(lanes[p]))
+    return out
+
+
+# ------------------------------------------------------------------------------------ watchdog
+class ExchangeWatchdog:
+    """Context manager: if the body has not finished after ``timeout_s``, log
+    ``describe()`` and the Python stacks of all threads (the reference shells
+    out to py-spy, `nccl_comm.py:299-330`; ``faulthandler`` needs no tool)."""
+
+    def __init__(self, what: str, describe: Callable[[], object] = lambda: None, timeout_s: float = 30.0, sink: Optional[Callable[[str], None]] = None):
+        self.what, self.describe, self.timeout_s = what, describe, timeout_s
+        self.sink = sink or logger.error
+        self.fired = False
+        self._done = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+
+    def _watch(self):
+        if self._done.wait(self.timeout_s):
+            return
+        self.fired = True
+        with tempfile.TemporaryFile(mode="w+") as f:
+            faulthandler.dump_traceback(file=f, all_threads=True)
+            f.seek(0)
+            stacks = f.read()
+        self.sink(f"[{self.what}] still running after {self.timeout_s:.1f}s; in flight: {self.describe()}\n{stacks}")
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._watch, name=f"awex-watchdog-{self.what}", daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._done.set()
+        self._thread.join()
+        return False
+
+
+# ------------------------------------------------------------------------------------ send / recv
+@dataclass
+class P2PRequest:
+    """One message: ``send=True`` ships ``tensor`` to ``peer``, else receives
+    into it.  ``label`` is what the watchdog prints."""
+
+    send: bool
+    tensor: torch.Tensor
+    peer: int
+    label: str = ""
+
+
+def summarize_requests(reqs: Iterable[P2PRequest]) -> list:
+    return [("send" if r.send else "recv", r.label, str(r.tensor.dtype), list(r.tensor.shape), r.tensor.is_contiguous(), r.peer) for r in reqs]
+
+
+def batch_send_recv(requests: Sequence[P2PRequest], group=None, blocking: bool = True, use_group: bool = True,
+                    watchdog_s: Optional[float] = 30.0, what: str = "batch_send_recv") -> list:
+    """Issue all requests, interleaved across peers.
+
+    ``use_group=True`` coalesces them in one ``batch_isend_irecv`` (one NCCL
+    group call: no ordering constraint between peers).  Otherwise they are posted
+    one by one as non-blocking calls in interleaved order.  Returns the pending
+    ``Work`` handles when ``blocking`` is false, else waits for all of them."""
+    reqs = interleave_by_peer(list(requests))
+    if not reqs:
+        return []
+    if use_group:
+        ops = [dist.P2POp(dist.isend if r.send else dist.irecv, r.tensor, r.peer, group=group) for r in reqs]
+        works = dist.batch_isend_irecv(ops)
+    else:
+        works = [(dist.isend if r.send else dist.irecv)(r.tensor, r.peer, group=group) for r in reqs]
+    if not blocking:
+        return works
+    if watchdog_s is None:
+        for w in works:
+            w.wait()
+    else:
+        with ExchangeWatchdog(what, lambda: summarize_requests(reqs), watchdog_s):
+            for w in works:
+                w.wait()
+    if any(r.tensor.is_cuda for r in reqs):
+        torch.cuda.current_stream().synchronize()
+    return []
+
+
+def two_phase_send_recv(rank: int, stage: int, world: int, sends: Sequence[P2PRequest], recvs: Sequence[P2PRequest], group=None, **kw) -> None:
+    """Blocking exchange of one ring stage without a grouped call: colour-0 ranks
+    send then receive, colour-1 ranks receive then send."""
+    first, second = (sends, recvs) if compute_two_phase_partition(rank, stage, world) == 0 else (recvs, sends)
+    batch_send_recv(first, group=group, use_group=False, **kw)
+    batch_send_recv(second, group=group, use_group=False, **kw)
+
+
+# ------------------------------------------------------------------------------------ co-located exchange
+class NcclColocateTransport:
+    """Exchange over ONE communicator whose ranks each hold a training shard and
+    an inference shard on the same device (`nccl_comm.py:53-224` in the
+    reference).  Messages are the packed per-destination payloads of the lowered
+    copy items; the walk over ring stages bounds the staging memory to one
+    outgoing and one incoming message at a time, and stage 0 is a local copy.
+
+    ``items`` are this rank's copy items (destination = inference transfer
+    rank), ``local`` its training tensors, ``views`` its inference views,
+    ``incoming`` maps a sending transfer rank to the manifest entries it will
+    deliver here.
+    """
+
+    def __init__(self, transfer_rank: int, world_size: int, group=None, device="cpu"):
+        self.transfer_rank, self.world_size, self.group = transfer_rank, world_size, group
+        self.device = torch.device(device)
+
+    def update_weights_in_colocate_mode(self, train_to_infer: Dict[int, int], infer_to_train: Dict[int, int], items, local,
+                                        views, incoming: Dict[int, Sequence[tuple]], use_group: bool = True) -> Dict[str, float]:
+        from awex_b200.transfer.cpu_exec import entry_nbytes, execute_items, pack_message, unpack_message
+
+        validate_rank_mappings(train_to_infer, infer_to_train)
+        me, world = self.transfer_rank, self.world_size
+        by_dst: Dict[int, list] = {}
+        for it in items:
+            by_dst.setdefault(it.dst_rank, []).append(it)
+        started = time.time()
+        moved = 0
+        for stage in range(world):
+            to, frm = ring_peers(me, stage, world)
+            if stage == 0:
+                if me in by_dst:
+                    moved += execute_items(by_dst[me], local, {me: views})
+                continue
+            sends, recvs = [], []
+            if to in by_dst:
+                msg = pack_message(by_dst[to], local).to(self.device)
+                sends.append(P2PRequest(True, msg, to, f"stage{stage}->{to}"))
+                moved += msg.numel()
+            entries = incoming.get(frm)
+            buf = None
+            if entries:
+                buf = torch.empty(sum(entry_nbytes(e) for e in entries), dtype=torch.uint8, device=self.device)
+                recvs.append(P2PRequest(False, buf, frm, f"stage{stage}<-{frm}"))
+            if use_group:
+                batch_send_recv(sends + recvs, group=self.group, what=f"colocate stage {stage}")
+            else:
+                two_phase_send_recv(me, stage, world, sends, recvs, group=self.group, what=f"colocate stage {stage}")
+            if buf is not None:
+                unpack_message(entries, buf, views)
+        return {"seconds": time.time() - started, "bytes": float(moved)}

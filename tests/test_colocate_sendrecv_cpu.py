@@ -1,0 +1,56 @@
+"""Co-located exchange over library send/recv on CPU: four gloo ranks, each
+holding one Megatron-layout training shard (TP=2 x PP=2) and one vLLM-layout
+inference shard (two engines of TP=2), walk the ring stages and end with
+inference weights bit-identical to the layout built from the canonical weights."""
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+WORLD = 4
+
+
+def _rank_main(rank, port, use_group, result_q):
+    import torch.distributed as dist
+
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+    from awex_b200.transfer.lowering import manifest_by_destination
+    from awex_b200.transfer.nccl_comm import NcclColocateTransport
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=WORLD)
+    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=2, pp=2), InferLayout(tp=2, num_engines=2), dtype=torch.float32)
+    programs = job.compile_all()
+    assert not job.check_coverage()
+    local = {(n, 0): t for n, t in job.train_models[rank].named_parameters()}
+    views = job.destination_views()[rank]
+    incoming = {src: manifest_by_destination(items).get(rank, []) for src, items in programs.items()}
+    identity = {r: r for r in range(WORLD)}
+    transport = NcclColocateTransport(rank, WORLD)
+    stats = transport.update_weights_in_colocate_mode(identity, identity, programs[rank], local, views, incoming, use_group=use_group)
+    mine = f"engine{rank // 2}/rank{rank % 2}/"
+    bad = [m for m in job.mismatches() if m.startswith(mine)]
+    result_q.put((rank, bad, stats["bytes"]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("use_group", [True, False])
+def test_ring_staged_colocated_exchange(use_group):
+    from awex_b200.utils.common import get_free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = get_free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, port, use_group, q)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r for r, _, _ in results) == list(range(WORLD))
+    for rank, bad, moved in results:
+        assert not bad, (rank, bad[:5])
+        assert moved > 0
