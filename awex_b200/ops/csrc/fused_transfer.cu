@@ -527,3 +527,104 @@ int awex_launch_post_flags(const void* addrs, uint32_t n, uint64_t epoch, void* 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- allocation-free launch
+// See awex_no_alloc.h for who calls this and under which rules.
+#include <cstdio>
+#include <mutex>
+
+#include "awex_no_alloc.h"
+
+namespace awex {
+
+// Scratch of the allocation-free launch: [0, 4) CTA arrival counter, [16, 32)
+// status words, [256, ...) descriptor table.  In host code this name is only a
+// handle for the runtime's symbol calls; its device address is looked up once
+// per device below.
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[AWEX_NO_ALLOC_SCRATCH_BYTES];
+
+static_assert(AWEX_NO_ALLOC_HEADER_BYTES % alignof(XferDesc) == 0, "table must start aligned");
+static_assert(sizeof(XferDesc) == 128, "scratch size is stated in 128-byte descriptors");
+
+constexpr int kNoAllocMaxDevices = 64;
+static unsigned char* g_no_alloc_ptr[kNoAllocMaxDevices] = {};
+static std::mutex g_no_alloc_mutex;
+
+static int no_alloc_fail(cudaError_t code, char* err, size_t cap, const char* what) {
+  if (err != nullptr && cap > 0) std::snprintf(err, cap, "awex_fused_transfer_no_alloc: %s (%s)", what, cudaGetErrorString(code));
+  return static_cast<int>(code);
+}
+
+}  // namespace awex
+
+extern "C" int awex_fused_transfer_no_alloc(const void* host_descs, uint32_t n_desc, uint64_t n_tiles, uint64_t timeout_ns,
+                                            int grid, void* stream, int32_t* status_out, char* err, size_t err_cap) {
+  using namespace awex;
+  if (err != nullptr && err_cap > 0) err[0] = '\0';
+  if (n_desc > AWEX_NO_ALLOC_MAX_DESCS) {
+    if (err != nullptr && err_cap > 0)
+      std::snprintf(err, err_cap,
+                    "awex_fused_transfer_no_alloc: %u descriptors exceed the built-in scratch of %u descriptors; split the table",
+                    n_desc, AWEX_NO_ALLOC_MAX_DESCS);
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (n_desc > 0 && host_descs == nullptr) return no_alloc_fail(cudaErrorInvalidValue, err, err_cap, "null descriptor table");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "cudaGetDevice");
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return no_alloc_fail(cudaErrorInvalidDevice, err, err_cap, "device index beyond the per-device table");
+  const int smem = kStages * kStageBytes;
+  unsigned char* scratch = nullptr;
+  {
+    // once per device, with that device current
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (g_no_alloc_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
+      if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "cudaGetSymbolAddress of the scratch array");
+      e = cudaFuncSetAttribute(fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "cudaFuncSetAttribute");
+      g_no_alloc_ptr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    scratch = g_no_alloc_ptr[dev];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps the previous call's contents: counter and status start at zero.
+  e = cudaMemsetAsync(scratch, 0, AWEX_NO_ALLOC_HEADER_BYTES, s);
+  if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "clearing the scratch header");
+  int32_t* status = reinterpret_cast<int32_t*>(scratch + 16);
+  if (n_desc > 0 && n_tiles > 0) {
+    e = cudaMemcpyAsync(scratch + AWEX_NO_ALLOC_HEADER_BYTES, host_descs, static_cast<size_t>(n_desc) * sizeof(XferDesc),
+                        cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "copying the descriptor table");
+    if (grid <= 0) {
+      e = cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "cudaDeviceGetAttribute");
+    }
+    if (static_cast<uint64_t>(grid) > n_tiles) grid = static_cast<int>(n_tiles);
+    if (grid < 1) grid = 1;
+    XferParams p;
+    p.descs = reinterpret_cast<const XferDesc*>(scratch + AWEX_NO_ALLOC_HEADER_BYTES);
+    p.n_desc = n_desc;
+    p.n_tiles = n_tiles;
+    p.epoch = 0;
+    p.timeout_ns = timeout_ns;
+    p.ready_pad = nullptr;
+    p.ready_slots = nullptr;
+    p.n_ready = 0;
+    p.done_flags = nullptr;
+    p.n_done = 0;
+    p.cta_counter = reinterpret_cast<unsigned int*>(scratch);
+    p.status = status;
+    fused_transfer_kernel<<<grid, kThreads, smem, s>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "kernel launch");
+  }
+  if (status_out != nullptr) {
+    e = cudaMemcpyAsync(status_out, status, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "reading the status words");
+    e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "cudaStreamSynchronize");
+  }
+  return static_cast<int>(cudaSuccess);
+}
