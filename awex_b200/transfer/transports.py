@@ -18,6 +18,12 @@ inside one NCCL group, staging copies for strided views and a barrier per step
 (`awex/transfer/nccl_comm.py:378-624`, `awex/writer/nccl_writer.py:197-304`,
 `awex/reader/nccl_reader.py:329-398`).
 
+A sender and a receiver that are different processes on the SAME GPU (the
+reference's co-located deployment) never wait for each other on the device: two
+kernels of different processes are time-sliced, and one that spins on a flag the
+other has yet to write can starve it.  Such pairs shake hands on the host
+instead (``p2p_host_ready_<dst>_<epoch>`` / ``p2p_host_done_<src>_<epoch>``).
+
 MetaServer keys used here: ``p2p_addr_<infer transfer rank>`` (address book),
 ``p2p_manifest_<train transfer rank>`` (what that rank writes where, plus the
 address of its ready-flag pad), ``master_info`` (exchange group rendezvous).
@@ -26,6 +32,8 @@ address of its ready-flag pad), ``master_info`` (exchange group rendezvous).
 from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
+
+import time
 
 import torch
 
@@ -47,8 +55,37 @@ def manifest_key(train_transfer_rank: int) -> str:
     return f"p2p_manifest_{train_transfer_rank}"
 
 
+def host_ready_key(infer_transfer_rank: int, epoch: int) -> str:
+    return f"p2p_host_ready_{infer_transfer_rank}_{epoch}"
+
+
+def host_done_key(train_transfer_rank: int, epoch: int) -> str:
+    return f"p2p_host_done_{train_transfer_rank}_{epoch}"
+
+
 class CoverageError(RuntimeError):
     pass
+
+
+class HostHandshakeTimeout(TimeoutError):
+    pass
+
+
+def poll_key(meta, key: str, timeout_s: float, poll_s: float = 0.002) -> None:
+    """Tight poll for a key that the other side of a same-GPU pair posts once per
+    update (the client's own ``wait_key`` backs off from 0.2 s)."""
+    deadline = time.time() + timeout_s
+    while not meta.has_key(key):
+        if time.time() > deadline:
+            raise HostHandshakeTimeout(f"no '{key}' on the meta server after {timeout_s:.1f}s")
+        time.sleep(poll_s)
+
+
+def shares_gpu(book_or_record, my_uuid: str, me: Tuple[str, int]) -> bool:
+    """Another process on this very GPU?"""
+    owner = tuple(book_or_record["owner"] if isinstance(book_or_record, dict) else book_or_record.owner)
+    uuid = book_or_record["device_uuid"] if isinstance(book_or_record, dict) else book_or_record.device_uuid
+    return owner != tuple(me) and owner[0] == me[0] and uuid == my_uuid
 
 
 def _collect_manifests(meta, infer_world: int, train_world: int, my_rank: int, timeout: float):
@@ -77,7 +114,8 @@ def _check_coverage(entries, views: Dict[str, torch.Tensor], required: Sequence[
 # ------------------------------------------------------------------------------------ fused NVLink path
 class PeerStoreReceiver:
     def __init__(self, meta, views: Dict[str, torch.Tensor], transfer_rank: int, infer_world: int, train_world: int,
-                 required: Sequence[str], device, timeout_ms: int = 2000, wait_timeout_s: float = 10000, strict: bool = True):
+                 required: Sequence[str], device, timeout_ms: int = 2000, wait_timeout_s: float = 10000, strict: bool = True,
+                 host_wait_timeout_s: Optional[float] = None):
         from awex_b200.ops.fused_transfer import FlagPad
         from awex_b200.parallel.peer_memory import PeerMemoryExporter
 
@@ -85,6 +123,9 @@ class PeerStoreReceiver:
         self.infer_world, self.train_world = infer_world, train_world
         self.required, self.device, self.strict = list(required), torch.device(device), strict
         self.timeout_ms, self.wait_timeout_s = timeout_ms, wait_timeout_s
+        self.host_wait_timeout_s = wait_timeout_s if host_wait_timeout_s is None else host_wait_timeout_s
+        self.host_senders: List[int] = []
+        self._last_host_epoch: Optional[int] = None
         self.done_pad = FlagPad(train_world, self.device)
         self.exporter = PeerMemoryExporter(self.device.index)
         self.waiter = None
@@ -106,26 +147,38 @@ class PeerStoreReceiver:
     def connect(self) -> None:
         """Learn who writes here, check their manifests, map their ready pads."""
         from awex_b200.ops.fused_transfer import FlagPoster, FlagWaiter
-        from awex_b200.parallel.peer_memory import PeerMemoryImporter
+        from awex_b200.parallel.peer_memory import PeerMemoryImporter, _device_uuid, process_identity
 
         self.senders, entries, records = _collect_manifests(self.meta, self.infer_world, self.train_world, self.rank, self.wait_timeout_s)
         _check_coverage(entries, self.views, self.required, self.strict, f"inference rank {self.rank}")
         self.importer = PeerMemoryImporter()
+        my_uuid, me = _device_uuid(self.exporter.device_index), process_identity()
+        self.host_senders = [r for r in self.senders if "owner" in records[r] and shares_gpu(records[r], my_uuid, me)]
+        device_senders = [r for r in self.senders if r not in self.host_senders]
         ready_addrs = []
-        for r in self.senders:
+        for r in device_senders:
             pad = self.importer.resolve(records[r]["ready_pad"])[READY_PAD]
             ready_addrs.append(pad.ptr + 8 * self.rank)
         self.poster = FlagPoster(ready_addrs, self.device)
-        self.waiter = FlagWaiter(self.done_pad, self.senders, self.device, timeout_ms=self.timeout_ms)
+        self.waiter = FlagWaiter(self.done_pad, device_senders, self.device, timeout_ms=self.timeout_ms)
         self.bytes_in = sum(entry_nbytes(e) for es in entries for e in es)
         logger.info(f"inference rank {self.rank}: {len(self.senders)} senders {self.senders}, {self.bytes_in} bytes per update")
 
     def begin(self, epoch: int) -> None:
         """Tell every sender that parameters may be overwritten now."""
         self.poster.launch(epoch)
+        if self.host_senders:
+            # work queued on this GPU before the update must not read half-written weights
+            torch.cuda.current_stream(self.device).synchronize()
+            self.meta.put_object(host_ready_key(self.rank, epoch), 1)
+            if self._last_host_epoch is not None and self._last_host_epoch != epoch:
+                self.meta.delete_if_exists(host_ready_key(self.rank, self._last_host_epoch))
+            self._last_host_epoch = epoch
 
     def finish(self, epoch: int, synchronize: bool = True) -> None:
         self.waiter.launch(epoch)
+        for r in self.host_senders:
+            poll_key(self.meta, host_done_key(self.infer_world + r, epoch), self.host_wait_timeout_s)
         if synchronize:
             torch.cuda.current_stream(self.device).synchronize()
             self.waiter.status.raise_if_failed()
@@ -141,39 +194,46 @@ class PeerStoreReceiver:
 class PeerStoreSender:
     def __init__(self, meta, items: Sequence[CopyItem], local: Dict[Tuple[str, int], torch.Tensor], train_rank: int,
                  infer_world: int, device, timeout_ms: int = 2000, wait_timeout_s: float = 10000, validate: bool = True,
-                 grid: int = 0):
+                 grid: int = 0, host_wait_timeout_s: Optional[float] = None):
         from awex_b200.ops.fused_transfer import FlagPad
-        from awex_b200.parallel.peer_memory import PeerMemoryExporter
+        from awex_b200.parallel.peer_memory import PeerMemoryExporter, _device_uuid, process_identity
 
         self.meta, self.items, self.local = meta, list(items), local
         self.train_rank, self.infer_world = train_rank, infer_world
         self.transfer_rank = infer_world + train_rank
         self.device = torch.device(device)
         self.timeout_ms, self.wait_timeout_s, self.validate, self.grid = timeout_ms, wait_timeout_s, validate, grid
+        self.host_wait_timeout_s = wait_timeout_s if host_wait_timeout_s is None else host_wait_timeout_s
+        self.host_destinations: List[int] = []
+        self._last_host_epoch: Optional[int] = None
         self.ready_pad = FlagPad(infer_world, self.device)
         self.exporter = PeerMemoryExporter(self.device.index)
         self.manifest = manifest_by_destination(self.items)
         self.destinations = sorted(self.manifest)
         self.meta.put_object(
             manifest_key(self.transfer_rank),
-            {"manifest": self.manifest, "ready_pad": self.exporter.export([(READY_PAD, self.ready_pad.t)])},
+            {"manifest": self.manifest, "ready_pad": self.exporter.export([(READY_PAD, self.ready_pad.t)]),
+             "owner": process_identity(), "device_uuid": _device_uuid(self.exporter.device_index)},
         )
         self.program = None
 
     def connect(self) -> None:
         """Map every destination's address book and encode the descriptor table."""
         from awex_b200.ops.fused_transfer import TransferProgram
-        from awex_b200.parallel.peer_memory import PeerMemoryImporter, process_identity
+        from awex_b200.parallel.peer_memory import PeerMemoryImporter, _device_uuid, process_identity
         from awex_b200.transfer.descriptors import TensorAddr, encode_items, validate_table
 
         self.importer = PeerMemoryImporter()
+        my_uuid, me = _device_uuid(self.exporter.device_index), process_identity()
         dst_addrs, done_flags, remote = {}, [], []
         for d in self.destinations:
             book = self.meta.get_object(addr_key(d), timeout=self.wait_timeout_s)
             addrs = self.importer.resolve(book)
             dst_addrs[d] = addrs
             done_flags.append(addrs[DONE_PAD].ptr + 8 * self.train_rank)
-            if tuple(book.owner) != process_identity():
+            if shares_gpu(book, my_uuid, me):
+                self.host_destinations.append(d)  # same GPU, other process: host handshake
+            elif tuple(book.owner) != me:
                 remote.append(d)
         src_addrs = {key: TensorAddr.of(t) for key, t in self.local.items()}
         table, n_tiles, enc = encode_items(self.items, src_addrs, dst_addrs)
@@ -195,10 +255,17 @@ class PeerStoreSender:
         )
 
     def send(self, epoch: int, synchronize: bool = True) -> None:
+        for d in self.host_destinations:
+            poll_key(self.meta, host_ready_key(d, epoch), self.host_wait_timeout_s)
         self.program.launch(epoch)
-        if synchronize:
+        if synchronize or self.host_destinations:
             torch.cuda.current_stream(self.device).synchronize()
             self.program.status.raise_if_failed()
+        if self.host_destinations:
+            self.meta.put_object(host_done_key(self.transfer_rank, epoch), 1)
+            if self._last_host_epoch is not None and self._last_host_epoch != epoch:
+                self.meta.delete_if_exists(host_done_key(self.transfer_rank, self._last_host_epoch))
+            self._last_host_epoch = epoch
 
     def gpu_launches_per_update(self) -> int:
         return 1
