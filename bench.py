@@ -37,7 +37,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--config", default="separated", choices=["separated", "colocated", "moe", "fp8"],
+                    help="separated: Llama-3-8B, training and inference on disjoint GPUs; colocated: Qwen2.5-32B TP n -> TP n on the same GPUs; "
+                         "moe: Qwen3-30B-A3B EP n -> 2 x (TP n/2, EP n/2); fp8: Qwen3-235B-A22B EP n -> TP n block-fp8")
+    ap.add_argument("--model", default=None, help="architecture preset; default is the one the configuration names")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model to this many layers (result is then not a valid benchmark)")
     ap.add_argument("--no-validate", action="store_true")
     ap.add_argument("--grid", type=int, default=0)
@@ -187,10 +190,18 @@ def run_single_gpu(args):
 def main():
     args = parse_args()
     if args.impl == "reference":
+        if args.config != "separated":
+            # the reference's co-located writer reads attributes nothing assigns
+            # (`awex/writer/nccl_writer.py:175,182`): only its separated mode runs unmodified
+            if int(os.environ.get("RANK", "0")) != 0:
+                return None
+            return emit({"impl": "reference", "unavailable": "the unmodified reference cannot run its co-located mode (nccl_writer.py:175,182 read unset attributes)"})
+        args.model = args.model or "llama3-8b"
         from baseline.reference_bench import run_reference
 
         return run_reference(args)
     if args.emulate:
+        args.model = args.model or "llama3-8b"
         return run_single_gpu(args)
     from awex_b200.bench_distributed import run_distributed
 
