@@ -202,9 +202,17 @@ def run_reference(args):
         step_fn = lambda s: actor.update_weights(step_id=s)  # noqa: E731
         local_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
 
+    # clock record of the timed region (a sampler of this repository: it only reads nvidia-smi)
+    sys.path.insert(0, os.path.dirname(HERE))
+    from awex_b200.utils.gpu import ClockSampler
+
+    sampler = None
     times_ms, wall_ms = [], []
     total = args.warmup + args.steps
     for s in range(1, total + 1):
+        if s == args.warmup + 1 and rank == 0:
+            sampler = ClockSampler([local_rank])
+            sampler.__enter__()
         _store_barrier(store, f"step{s}", world)
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -215,6 +223,8 @@ def run_reference(args):
         torch.cuda.synchronize()
         wall_ms.append((time.perf_counter() - t0) * 1e3)
         times_ms.append(start.elapsed_time(stop))
+    if sampler is not None:
+        sampler.__exit__(None, None, None)
     valid = True
     if not is_train and not args.no_validate:
         want = synth.vllm_module(arch, infer_tp, tp_rank, dtype, device, hf_config)
@@ -240,7 +250,7 @@ def run_reference(args):
             "aggregate_GBps": total_bytes / (ms / 1e3) / 1e9, "nvlink_GBps_per_gpu": egress / (ms / 1e3) / 1e9,
             "e2e": {"value": wall / 1e3, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "what": "wall clock of the blocking reference calls, max over ranks"},
-            "gpu_launches": 0, "per_step_ms": per_step,
+            "gpu_launches": 0, "per_step_ms": per_step, "clocks": sampler.summary() if sampler is not None else None,
         }
         print(json.dumps(out), flush=True)
     _store_barrier(store, "exit", world)
