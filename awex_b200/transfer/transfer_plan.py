@@ -8,7 +8,9 @@ contract is the reference's (`awex/transfer/transfer_plan.py:158-813`):
 * transfer ranks: inference shard -> ``global_rank + engine * instance_world``;
   training shard -> ``global_rank + infer_world_size``;
 * inference replica *i* (engines outermost) is fed by training replica
-  ``i mod n_train_replicas``;
+  ``i mod n_train_replicas`` (``replica_pairing="spread"`` instead hands each
+  inference replica the least-loaded training replica, walking the parameters
+  in sorted order, to balance the senders);
 * an operation is the N-d box intersection of one inference shard with one
   training shard, with offsets and slices relative to each shard;
 * a rank's plan maps peer -> operations sorted by (name, send offset, recv
@@ -142,7 +144,12 @@ class TransferPlanBuilder:
         num_infer_engines: int = 1,
         enable_debug_mode: bool = False,
         strict_param_key_match: bool = False,
+        replica_pairing: str = "round_robin",
     ):
+        if replica_pairing not in ("round_robin", "spread"):
+            raise ValueError(f"unknown replica_pairing {replica_pairing!r}")
+        self.replica_pairing = replica_pairing
+        self._replica_load: Dict[int, List[int]] = {}
         if num_infer_engines <= 0:
             raise ValueError("num_infer_engines must be positive")
         self.train_world_size = train_world_size
@@ -298,12 +305,30 @@ class TransferPlanBuilder:
         only_train = global_transfer_rank if (global_transfer_rank is not None and global_transfer_rank >= self.infer_world_size) else None
         ops: List[CommunicationOperation] = []
         for i, (engine, inf_replica) in enumerate(infer_replicas):
-            trn_replica = train_replicas[i % len(train_replicas)]
+            trn_replica = train_replicas[self._pick_train_replica(i, training_meta)]
             inf_boxes = self._create_shard_offset_for_replica(inf_replica, engine, True, only_infer)
             trn_boxes = self._create_shard_offset_for_replica(trn_replica, 0, False, only_train)
             for region in self._find_overlapping_regions(inf_boxes, trn_boxes):
                 ops.extend(self._build_region_communication_plan(region))
         return ops
+
+    def _pick_train_replica(self, i: int, training_meta: ParameterMeta) -> int:
+        """Index of the training replica that feeds inference replica ``i``.
+        ``spread`` gives each inference replica the training replica that has
+        been handed the fewest bytes so far (ties: lowest index), so parameters
+        replicated over many data-parallel ranks are served by all of them; the
+        choice depends only on the metadata and the sorted parameter order, hence
+        every rank computes the same one."""
+        n = len(training_meta.replicas)
+        if self.replica_pairing != "spread" or n == 1:
+            return i % n
+        loads = self._replica_load.setdefault(n, [0] * n)
+        k = min(range(n), key=lambda j: (loads[j], j))
+        nbytes = 1
+        for d in training_meta.global_shape:
+            nbytes *= int(d)
+        loads[k] += nbytes
+        return k
 
     def build_weights_mapping_operations(
         self,
@@ -317,6 +342,7 @@ class TransferPlanBuilder:
         infer = {m.name: m for m in inference_weights_meta}
         train = {m.name: m for m in training_weights_meta}
         ops: List[CommunicationOperation] = []
+        self._replica_load = {}
         for name in self._common_names(infer, train):
             ops.extend(self._build_parameter_communication_plan(name, infer[name], train[name], global_transfer_rank))
         return ops

@@ -37,7 +37,8 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
         super()._initialize()
         t0 = time.time()
         self.builder = TransferPlanBuilder(
-            self.infer_world_size, self.training_world_size, self.num_infer_engines, enable_debug_mode=self.enable_debug_mode
+            self.infer_world_size, self.training_world_size, self.num_infer_engines, enable_debug_mode=self.enable_debug_mode,
+            replica_pairing=str(self.config.get("replica_pairing", "spread")),
         )
         local = self.local_tensors()
         params = [LocalParam(name, vp, tuple(t.shape), t.dtype) for (name, vp), t in local.items()]

@@ -94,3 +94,29 @@ def test_fp8_block_that_spans_training_ranks_is_refused():
     job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=2), InferLayout(tp=1, fp8=True), dtype=torch.bfloat16)
     with pytest.raises(NotImplementedError, match="several training TP ranks"):
         job.compile_all()
+
+
+def test_spread_replica_pairing_balances_data_parallel_senders():
+    """Dense parameters replicated over four data-parallel training ranks: the
+    reference's round-robin lets the first replicas send all of them, the
+    least-loaded pairing spreads them; both tile every destination exactly once
+    and give bit-identical weights."""
+    from awex_b200.transfer.transfer_plan import TransferPlanBuilder
+
+    job = SimulatedJob(get_arch("tiny-qwen3-moe"), TrainLayout(tp=1, dp=4, ep=4), InferLayout(tp=2, ep=2, num_engines=2), dtype=torch.float32)
+    spans = {}
+    for mode in ("round_robin", "spread"):
+        job.builder = TransferPlanBuilder(job.infer_world_size, job.train.world, job.infer.num_engines, replica_pairing=mode)
+        programs = job.compile_all()
+        assert job.check_coverage() == []
+        for models in job.infer_models:
+            for m in models:
+                for p in m.parameters():
+                    p.zero_()
+        job.run_cpu()
+        assert job.mismatches() == []
+        sent = [sum(it.dst_bytes for it in items) for items in programs.values()]
+        spans[mode] = max(sent) / min(sent)
+    assert spans["round_robin"] > 1.5 and spans["spread"] < 1.05
+    with pytest.raises(ValueError):
+        TransferPlanBuilder(2, 2, 1, replica_pairing="nearest")
