@@ -72,6 +72,10 @@ class SGlangToHFWeightConverter:
                 return [(name, parameter)]
             heads = int(self.total_num_heads)
             kv = int(self.total_kv_heads or heads)
+            tp = int(self.tp_size or 1)
+            if tp > kv and tp % kv == 0 and heads % tp == 0:
+                # every rank stores one whole (replicated) KV head beside its query heads
+                heads, kv = heads // tp, 1
             units, rows = heads + 2 * kv, parameter.shape[0]
             if (rows * heads) % units or (rows * kv) % units:
                 raise ValueError(

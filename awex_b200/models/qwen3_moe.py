@@ -10,7 +10,7 @@ is cut in the ratio ``n_heads : n_kv : n_kv``
 
 from __future__ import annotations
 
-from awex_b200.converter.rows import IDENTITY
+from awex_b200.converter.rows import IDENTITY, Rows
 from awex_b200.converter.sglang_converter import SGlangToHFWeightConverter
 
 
@@ -60,7 +60,19 @@ def _build_mcore_converter_qwen3_moe():
                     f"Unexpected linear_qkv rows for GQA split: got {len(rows)}, expected {expected} "
                     f"(kv_heads={hf.num_key_value_heads}, attn_tp={attn_tp}, q_per_group={q_per_group}, head_dim={head})"
                 )
-            return split_interleaved_qkv(rows, groups, q_per_group * head, head)
+            q, k, v = split_interleaved_qkv(rows, groups, q_per_group * head, head)
+            # More attention-TP ranks on the inference side than KV heads: every
+            # inference rank stores a whole KV head, so each head appears
+            # infer_tp / n_kv times in the canonical K and V (the reference
+            # refuses this layout, `awex/converter/sglang_converter.py:127-136`).
+            infer_tp = int(self.infer_atten_tp_size or 1)
+            if infer_tp > hf.num_key_value_heads:
+                if infer_tp % hf.num_key_value_heads:
+                    raise ValueError(f"inference attention TP {infer_tp} is not a multiple of num_key_value_heads {hf.num_key_value_heads}")
+                repeat = infer_tp // hf.num_key_value_heads
+                k = Rows.cat([part for part in k.chunk(groups) for _ in range(repeat)])
+                v = Rows.cat([part for part in v.chunk(groups) for _ in range(repeat)])
+            return q, k, v
 
         def _convert_attention_param(self, name, src, rows, layer_number):
             for kind in ("weight", "bias"):

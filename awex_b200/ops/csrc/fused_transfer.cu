@@ -155,6 +155,12 @@ __device__ __forceinline__ void cursor_seek(Cursor& c, const XferParams& p, uint
   c.begin = p.descs[lo].tile_begin;
   c.end = (lo + 1 < p.n_desc) ? p.descs[lo + 1].tile_begin : p.n_tiles;
 }
+// Jump to the descriptor that holds the first tile of a chunk (host-built index).
+__device__ __forceinline__ void cursor_jump(Cursor& c, const XferParams& p, uint64_t chunk) {
+  c.di = p.chunk_desc[chunk];
+  c.begin = p.descs[c.di].tile_begin;
+  c.end = (c.di + 1 < p.n_desc) ? p.descs[c.di + 1].tile_begin : p.n_tiles;
+}
 __device__ __forceinline__ void cursor_advance_to(Cursor& c, const XferParams& p, uint64_t tile) {
   while (tile >= c.end) {
     ++c.di;
@@ -318,18 +324,47 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
     if (abort_flag) return;  // nothing in flight yet
   }
 
-  const uint64_t t_begin = p.n_tiles * blockIdx.x / gridDim.x;
-  const uint64_t t_end = p.n_tiles * (blockIdx.x + 1) / gridDim.x;
-  const uint64_t n = t_end - t_begin;
+  // Which tiles this CTA owns.  Without a chunk index: one contiguous range.
+  // With one: chunks of 2^chunk_shift tiles dealt round-robin to the CTAs, so
+  // that cheap and expensive tiles (plain copies, quantised blocks, gathered
+  // rows, local and remote destinations) are spread over all of them.
+  const bool chunked = p.chunk_desc != nullptr;
+  const uint32_t cs = p.chunk_shift;
+  const uint64_t cmask = (uint64_t{1} << cs) - 1;
+  uint64_t t_begin = 0, n = 0;
+  if (!chunked) {
+    t_begin = p.n_tiles * blockIdx.x / gridDim.x;
+    n = p.n_tiles * (blockIdx.x + 1) / gridDim.x - t_begin;
+  } else {
+    const uint64_t n_chunks = (p.n_tiles + cmask) >> cs;
+    if (blockIdx.x < n_chunks) {
+      const uint64_t mine = (n_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x;
+      const uint64_t last_chunk = blockIdx.x + (mine - 1) * gridDim.x;
+      n = mine << cs;
+      if (last_chunk == n_chunks - 1) n -= (n_chunks << cs) - p.n_tiles;  // the table's last chunk may be short
+    }
+  }
+  // relative tile number of this CTA -> tile number in the table
+  auto tile_at = [&](uint64_t j) -> uint64_t {
+    if (!chunked) return t_begin + j;
+    return ((((j >> cs) * gridDim.x) + blockIdx.x) << cs) + (j & cmask);
+  };
+  auto cursor_to = [&](Cursor& c, uint64_t j) -> uint64_t {
+    const uint64_t tile = tile_at(j);
+    if (chunked && (j & cmask) == 0) cursor_jump(c, p, tile >> cs);
+    cursor_advance_to(c, p, tile);
+    return tile;
+  };
 
   if (n > 0) {
     Cursor load_cur, use_cur;
-    cursor_seek(load_cur, p, t_begin);
+    if (chunked) cursor_jump(load_cur, p, blockIdx.x);
+    else cursor_seek(load_cur, p, t_begin);
     use_cur = load_cur;
 
     // Stage tile j (relative number) of this CTA.  Executed by warp 0.
     auto issue_load = [&](uint64_t j) {
-      cursor_advance_to(load_cur, p, t_begin + j);
+      const uint64_t tile_no = cursor_to(load_cur, j);
       const XferDesc d = p.descs[load_cur.di];
       const uint32_t stage = static_cast<uint32_t>(j % kStages);
       const uint32_t bar = smem_addr(&full_bar[stage]);
@@ -337,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
         if (lane == 0) mbar_arrive(bar);  // keeps the ring's phases in step
         return;
       }
-      const Tile t = tile_of(d, t_begin + j - load_cur.begin);
+      const Tile t = tile_of(d, tile_no - load_cur.begin);
       if (d.tensor_map) {
         // one tiled TMA load for the whole tile; rows and columns past the slab's
         // edge are zero-filled and still counted in the transaction bytes
@@ -366,9 +401,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
       for (uint64_t j = 0; j < kLookahead && j < n; ++j) issue_load(j);
 
     for (uint64_t i = 0; i < n && !abort_flag; ++i) {
-      cursor_advance_to(use_cur, p, t_begin + i);
+      const uint64_t tile_no = cursor_to(use_cur, i);
       const XferDesc d = p.descs[use_cur.di];
-      const Tile t = tile_of(d, t_begin + i - use_cur.begin);
+      const Tile t = tile_of(d, tile_no - use_cur.begin);
       const uint32_t stage = static_cast<uint32_t>(i % kStages);
       const uint32_t parity = static_cast<uint32_t>((i / kStages) & 1);
       const uint32_t bar = smem_addr(&full_bar[stage]);
@@ -478,7 +513,8 @@ int awex_xfer_stage_bytes() { return awex::kStageBytes; }
 // Returns a cudaError_t.  `grid` == 0 picks one CTA per SM.
 int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_tiles, uint64_t epoch, uint64_t timeout_ns,
                                const void* ready_pad, const void* ready_slots, uint32_t n_ready, const void* done_flags,
-                               uint32_t n_done, void* cta_counter, void* status, int grid, void* stream) {
+                               uint32_t n_done, void* cta_counter, void* status, int grid, void* stream,
+                               const void* chunk_desc, uint32_t chunk_shift) {
   static int configured_device = -1;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
@@ -508,6 +544,8 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
   p.n_done = n_done;
   p.cta_counter = static_cast<unsigned int*>(cta_counter);
   p.status = static_cast<int32_t*>(status);
+  p.chunk_desc = static_cast<const uint32_t*>(chunk_desc);
+  p.chunk_shift = chunk_desc ? chunk_shift : 0;
   awex::fused_transfer_kernel<<<grid, awex::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError();
 }
@@ -616,6 +654,8 @@ extern "C" int awex_fused_transfer_no_alloc(const void* host_descs, uint32_t n_d
     p.n_done = 0;
     p.cta_counter = reinterpret_cast<unsigned int*>(scratch);
     p.status = status;
+    p.chunk_desc = nullptr;  // contiguous tile ranges
+    p.chunk_shift = 0;
     fused_transfer_kernel<<<grid, kThreads, smem, s>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "kernel launch");

@@ -87,6 +87,10 @@ struct XferParams {
   // scratch: CTA arrival counter (self-resetting) and status words
   unsigned int* cta_counter;
   int32_t* status;
+  // optional: descriptor index of the first tile of every chunk of 2^chunk_shift
+  // tiles; when given, chunks are dealt round-robin to the CTAs
+  const uint32_t* chunk_desc;
+  uint32_t chunk_shift;
 };
 
 }  // namespace awex

@@ -38,6 +38,30 @@ def _device_array(values, dtype, device) -> torch.Tensor:
     return torch.from_numpy(np.asarray(values, dtype=dtype).view(np.uint8).copy()).to(device)
 
 
+def _max_chunk_shift(table: np.ndarray, n_tiles: int) -> int:
+    """log2 of the largest chunk in tiles.  Measured on B200: tables of plain
+    copies run fastest with chunks of 4 tiles (the depth of the load pipeline),
+    tables dominated by quantised blocks with 16.  ``AWEX_CHUNK_MB`` (the
+    reference's knob for its chunked co-located mode,
+    `awex/transfer/nccl_stream_batch.py:438-470`) overrides the choice with a
+    chunk size in MiB of staged source data."""
+    import os
+
+    from awex_b200.transfer.descriptors import OP_FP8_BLOCK, STAGE_BYTES
+
+    override = os.environ.get("AWEX_CHUNK_MB")
+    if override:
+        try:
+            tiles = max(1, int(float(override) * 1024 * 1024) // STAGE_BYTES)
+            return min(tiles.bit_length() - 1, 12)
+        except ValueError:
+            pass
+    begins = table["tile_begin"].astype(np.int64)
+    counts = np.diff(np.append(begins, n_tiles))
+    fp8_tiles = int(counts[table["op"] == OP_FP8_BLOCK].sum())
+    return 4 if 2 * fp8_tiles > n_tiles else 2
+
+
 class StatusWord:
     """Four int32 on the device: code, detail0..2.  Kernels only ever move it
     from OK to an error; the host reads it when it wants a verdict."""
@@ -80,7 +104,8 @@ class FlagPad:
 class TransferProgram:
     def __init__(self, table: np.ndarray, n_tiles: int, device, ready_pad: Optional[FlagPad] = None,
                  ready_slots: Sequence[int] = (), done_flag_addrs: Sequence[int] = (), timeout_ms: int = 2000,
-                 grid: int = 0, row_offsets: Sequence[int] = (), tensor_map_descs: Sequence[int] = (), encoder=None):
+                 grid: int = 0, row_offsets: Sequence[int] = (), tensor_map_descs: Sequence[int] = (), encoder=None,
+                 interleave: bool = True):
         if encoder is not None:  # side tables produced while encoding
             row_offsets, tensor_map_descs = encoder.row_offsets, encoder.tensor_map_descs
         if table.dtype != DESC_DTYPE:
@@ -109,6 +134,18 @@ class TransferProgram:
         self.n_ready = len(ready_slots)
         self.done_flags = _device_array(list(done_flag_addrs), np.uint64, self.device) if len(done_flag_addrs) else None
         self.n_done = len(done_flag_addrs)
+        # chunk index for the round-robin deal of tiles to CTAs: chunks of up to 16
+        # tiles, smaller when the table is short so that every CTA still gets work
+        self.chunk_desc, self.chunk_shift = None, 0
+        if interleave and self.n_desc and self.n_tiles:
+            ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count
+            shift = _max_chunk_shift(table, self.n_tiles)
+            while shift > 0 and (self.n_tiles >> shift) < 4 * ctas:
+                shift -= 1
+            starts = np.arange(0, self.n_tiles, 1 << shift, dtype=np.uint64)
+            index = np.searchsorted(table["tile_begin"].astype(np.uint64), starts, side="right") - 1
+            self.chunk_desc = _device_array(index, np.uint32, self.device)
+            self.chunk_shift = shift
         self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.status = StatusWord(self.device)
         self.timeout_ns = int(timeout_ms) * 1_000_000
@@ -148,6 +185,7 @@ class TransferProgram:
             self.ready_slots.data_ptr() if self.n_ready else None, self.n_ready,
             self.done_flags.data_ptr() if self.n_done else None, self.n_done,
             self.counter.data_ptr(), self.status.ptr, self.grid, stream,
+            self.chunk_desc.data_ptr() if self.chunk_desc is not None else None, self.chunk_shift,
         )
         native.check(code, "fused_transfer launch")
         self.launches += 1

@@ -18,6 +18,7 @@ tensors is the oracle a transfer result is compared with.
 from __future__ import annotations
 
 import hashlib
+import os
 from collections import OrderedDict
 from types import SimpleNamespace
 from typing import Callable, Dict, Iterator, List, Optional, Tuple
@@ -87,6 +88,13 @@ class CanonicalWeights:
 
     def final_norm(self) -> torch.Tensor:
         return self.get("model.norm.weight", (self.arch.hidden,))
+
+
+class ZeroWeights(CanonicalWeights):
+    """Right shapes, no values: for models that are only allocated."""
+
+    def get(self, name: str, shape: Tuple[int, ...]) -> torch.Tensor:
+        return torch.zeros(shape, dtype=self.dtype, device=self.device)
 
 
 class StoredCanonicalWeights(CanonicalWeights):
@@ -226,12 +234,18 @@ def build_megatron_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, 
 
 
 # ---- vLLM layout ----------------------------------------------------------------------------------
-def _maybe_fp8(out, name: str, t: torch.Tensor, fp8: bool, parts: int = 1) -> None:
+def _maybe_fp8(out, name: str, t: torch.Tensor, fp8: bool, parts: int = 1, zero: bool = False) -> None:
     """Store ``t`` under ``name``; with ``fp8`` as e4m3 + ``_scale_inv``, each of
     the ``parts`` equal dim-0 sub-tensors (gate/up, q/k/v are quantised as a
-    whole: parts=1) carrying its own block grid."""
+    whole: parts=1) carrying its own block grid.  ``zero`` only allocates."""
     if not fp8 or t.dim() < 2:
         out[name] = t.contiguous()
+        return
+    if zero:
+        rows, cols = t.shape[-2], t.shape[-1]
+        grid = (parts * -(-(rows // parts) // 128), -(-cols // 128))
+        out[name] = torch.zeros(t.shape, dtype=torch.float8_e4m3fn, device=t.device)
+        out[name + "_scale_inv"] = torch.zeros(tuple(t.shape[:-2]) + grid, dtype=torch.float32, device=t.device)
         return
     if t.dim() == 3:  # fused experts: quantise every expert slot separately
         qs, ss = zip(*(_quant_parts(t[e], parts) for e in range(t.shape[0])))
@@ -245,6 +259,14 @@ def _quant_parts(t2d: torch.Tensor, parts: int):
     # Quantise on the CPU: it is the stated oracle.  CUDA PyTorch divides by the
     # scalar 448 as a multiplication by its reciprocal, which moves some scales by
     # one ulp relative to the true division of the CPU path and of the kernels.
+    # For models of hundreds of GB the CPU is too slow; AWEX_SYNTH_FP8_ORACLE=kernel
+    # switches to the stand-alone quantisation kernel, which the GPU tests hold
+    # bit-identical to the CPU path.
+    if t2d.is_cuda and os.environ.get("AWEX_SYNTH_FP8_ORACLE", "cpu") == "kernel":
+        from awex_b200.ops.fp8 import block_quant
+
+        qs, ss = zip(*(block_quant(c.contiguous()) for c in t2d.chunk(parts, 0)))
+        return torch.cat(qs, 0), torch.cat(ss, 0)
     qs, ss = zip(*(per_block_cast_to_fp8(c.detach().cpu().contiguous(), False) for c in t2d.chunk(parts, 0)))
     return torch.cat(qs, 0).to(t2d.device), torch.cat(ss, 0).to(t2d.device)
 
@@ -254,7 +276,7 @@ def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, devi
                      weights: Optional[CanonicalWeights] = None) -> FlatModule:
     """``zero=True`` allocates the same tensors filled with zeros (a freshly
     paused engine whose weights are about to be overwritten)."""
-    w = weights or CanonicalWeights(arch, dtype, device, seed, step)
+    w = weights or (ZeroWeights(arch, dtype, device) if zero else CanonicalWeights(arch, dtype, device, seed, step))
     tp, r = rank_info.tp_size, rank_info.tp_rank
     ep, er = rank_info.ep_size, rank_info.ep_rank
     etp, etr = rank_info.ep_tp_size, rank_info.ep_tp_rank
@@ -279,13 +301,13 @@ def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, devi
             )
 
         out[p + "input_layernorm.weight"] = w.layer(l, "input_layernorm.weight")
-        _maybe_fp8(out, p + "self_attn.qkv_proj.weight", fused("weight"), fp8)
+        _maybe_fp8(out, p + "self_attn.qkv_proj.weight", fused("weight"), fp8, zero=zero)
         if arch.qkv_bias:
             out[p + "self_attn.qkv_proj.bias"] = fused("bias")
         if arch.qk_norm:
             out[p + "self_attn.q_norm.weight"] = w.layer(l, "self_attn.q_norm.weight")
             out[p + "self_attn.k_norm.weight"] = w.layer(l, "self_attn.k_norm.weight")
-        _maybe_fp8(out, p + "self_attn.o_proj.weight", _chunk(w.layer(l, "self_attn.o_proj.weight"), tp, r, 1), fp8)
+        _maybe_fp8(out, p + "self_attn.o_proj.weight", _chunk(w.layer(l, "self_attn.o_proj.weight"), tp, r, 1), fp8, zero=zero)
         out[p + "post_attention_layernorm.weight"] = w.layer(l, "post_attention_layernorm.weight")
         if arch.is_moe:
             out[p + "mlp.gate.weight"] = w.layer(l, "mlp.gate.weight")
@@ -295,12 +317,12 @@ def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, devi
                 e = er * n_local + le
                 w13.append(torch.cat([_chunk(w.expert(l, e, "gate_proj"), etp, etr), _chunk(w.expert(l, e, "up_proj"), etp, etr)], 0))
                 w2.append(_chunk(w.expert(l, e, "down_proj"), etp, etr, 1))
-            _maybe_fp8(out, p + "mlp.experts.w13_weight", torch.stack(w13), fp8, parts=2)
-            _maybe_fp8(out, p + "mlp.experts.w2_weight", torch.stack(w2), fp8)
+            _maybe_fp8(out, p + "mlp.experts.w13_weight", torch.stack(w13), fp8, parts=2, zero=zero)
+            _maybe_fp8(out, p + "mlp.experts.w2_weight", torch.stack(w2), fp8, zero=zero)
         else:
             gate_up = torch.cat([_chunk(w.layer(l, "mlp.gate_proj.weight"), tp, r), _chunk(w.layer(l, "mlp.up_proj.weight"), tp, r)], 0)
-            _maybe_fp8(out, p + "mlp.gate_up_proj.weight", gate_up, fp8, parts=2)
-            _maybe_fp8(out, p + "mlp.down_proj.weight", _chunk(w.layer(l, "mlp.down_proj.weight"), tp, r, 1), fp8)
+            _maybe_fp8(out, p + "mlp.gate_up_proj.weight", gate_up, fp8, parts=2, zero=zero)
+            _maybe_fp8(out, p + "mlp.down_proj.weight", _chunk(w.layer(l, "mlp.down_proj.weight"), tp, r, 1), fp8, zero=zero)
     if last_stage:
         out["model.norm.weight"] = w.final_norm()
         if not arch.tie_embeddings:
