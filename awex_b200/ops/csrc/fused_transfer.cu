@@ -291,16 +291,20 @@ __device__ void tile_fp8_generic(const XferDesc& d, const Tile& t, uint32_t* red
 // ---------------------------------------------------------------- the kernel
 __device__ __forceinline__ bool wants_stage(const XferDesc& d) { return (d.flags & FLAG_BULK) != 0; }
 
-__global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __grid_constant__ XferParams p) {
+template <int kT, int kS, int kL>
+__device__ __forceinline__ void transfer_body(const XferParams& p) {
+  // the stage that tile i + kL loads into was last used by tile i - 2, whose
+  // store group is the one `wait_group.read 1` has retired
+  static_assert(kL == kS - 2, "ring depth and lookahead must keep two store groups apart");
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ uint32_t red[kThreads / 32];
+  __shared__ __align__(8) uint64_t full_bar[kS];
+  __shared__ uint32_t red[kT / 32];
   __shared__ volatile int abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) mbar_init(smem_addr(&full_bar[s]), 1);
+    for (int s = 0; s < kS; ++s) mbar_init(smem_addr(&full_bar[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -366,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
     auto issue_load = [&](uint64_t j) {
       const uint64_t tile_no = cursor_to(load_cur, j);
       const XferDesc d = p.descs[load_cur.di];
-      const uint32_t stage = static_cast<uint32_t>(j % kStages);
+      const uint32_t stage = static_cast<uint32_t>(j % kS);
       const uint32_t bar = smem_addr(&full_bar[stage]);
       if (!wants_stage(d)) {
         if (lane == 0) mbar_arrive(bar);  // keeps the ring's phases in step
@@ -398,14 +402,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
     };
 
     if (warp == 0)
-      for (uint64_t j = 0; j < kLookahead && j < n; ++j) issue_load(j);
+      for (uint64_t j = 0; j < kL && j < n; ++j) issue_load(j);
 
     for (uint64_t i = 0; i < n && !abort_flag; ++i) {
       const uint64_t tile_no = cursor_to(use_cur, i);
       const XferDesc d = p.descs[use_cur.di];
       const Tile t = tile_of(d, tile_no - use_cur.begin);
-      const uint32_t stage = static_cast<uint32_t>(i % kStages);
-      const uint32_t parity = static_cast<uint32_t>((i / kStages) & 1);
+      const uint32_t stage = static_cast<uint32_t>(i % kS);
+      const uint32_t parity = static_cast<uint32_t>((i / kS) & 1);
       const uint32_t bar = smem_addr(&full_bar[stage]);
       unsigned char* stage_ptr = smem + static_cast<size_t>(stage) * kStageBytes;
 
@@ -414,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
         // tile i-2: allow only the most recent store group to be still reading.
         bulk_wait_read_1();
         __syncwarp();
-        if (i + kLookahead < n) issue_load(i + kLookahead);
+        if (i + kL < n) issue_load(i + kL);
         const uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait(bar, parity)) {
           if (globaltimer_ns() - t0 > p.timeout_ns) {
@@ -475,6 +479,23 @@ __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __gri
   }
 }
 
+// One CTA of 512 threads per SM with a 6-stage ring: the variant for tables of
+// plain copies, where one warp moves the data and depth matters.
+__global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __grid_constant__ XferParams p) {
+  transfer_body<kThreads, kStages, kLookahead>(p);
+}
+
+// Two CTAs of 256 threads per SM with a 3-stage ring each: the variant for
+// tables dominated by tiles that every warp works on (block quantisation,
+// casts).  A tile's barriers and reductions are exposed latency inside one CTA;
+// a second resident CTA fills those gaps with another tile.
+constexpr int kThreadsX2 = 256;
+constexpr int kStagesX2 = 3;
+constexpr int kLookaheadX2 = 1;
+__global__ void __launch_bounds__(kThreadsX2, 2) fused_transfer_kernel_x2(const __grid_constant__ XferParams p) {
+  transfer_body<kThreadsX2, kStagesX2, kLookaheadX2>(p);
+}
+
 // Receiver side: wait (bounded) until every listed sender has raised `epoch`.
 __global__ void wait_flags_kernel(const uint64_t* pad, const uint32_t* slots, uint32_t n, uint64_t epoch, uint64_t timeout_ns,
                                   int32_t* status) {
@@ -510,24 +531,28 @@ int awex_xfer_desc_size() { return static_cast<int>(sizeof(awex::XferDesc)); }
 int awex_xfer_smem_bytes() { return awex::kStages * awex::kStageBytes; }
 int awex_xfer_stage_bytes() { return awex::kStageBytes; }
 
-// Returns a cudaError_t.  `grid` == 0 picks one CTA per SM.
+// Returns a cudaError_t.  `variant` 0: one CTA of 512 threads per SM; 1: two
+// CTAs of 256 threads per SM.  `grid` == 0 fills the device for the variant.
 int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_tiles, uint64_t epoch, uint64_t timeout_ns,
                                const void* ready_pad, const void* ready_slots, uint32_t n_ready, const void* done_flags,
                                uint32_t n_done, void* cta_counter, void* status, int grid, void* stream,
-                               const void* chunk_desc, uint32_t chunk_shift) {
-  static int configured_device = -1;
+                               const void* chunk_desc, uint32_t chunk_shift, uint32_t variant) {
+  static int configured_device[2] = {-1, -1};
+  if (variant > 1) return cudaErrorInvalidValue;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  const int smem = awex::kStages * awex::kStageBytes;
-  if (configured_device != dev) {
-    err = cudaFuncSetAttribute(awex::fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  const int smem = (variant ? awex::kStagesX2 : awex::kStages) * awex::kStageBytes;
+  if (configured_device[variant] != dev) {
+    err = variant ? cudaFuncSetAttribute(awex::fused_transfer_kernel_x2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                  : cudaFuncSetAttribute(awex::fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
-    configured_device = dev;
+    configured_device[variant] = dev;
   }
   if (grid <= 0) {
     err = cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
+    if (variant) grid *= 2;
   }
   if (n_tiles > 0 && static_cast<uint64_t>(grid) > n_tiles) grid = static_cast<int>(n_tiles);
   if (grid < 1) grid = 1;
@@ -546,7 +571,10 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
   p.status = static_cast<int32_t*>(status);
   p.chunk_desc = static_cast<const uint32_t*>(chunk_desc);
   p.chunk_shift = chunk_desc ? chunk_shift : 0;
-  awex::fused_transfer_kernel<<<grid, awex::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  if (variant)
+    awex::fused_transfer_kernel_x2<<<grid, awex::kThreadsX2, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    awex::fused_transfer_kernel<<<grid, awex::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError();
 }
 

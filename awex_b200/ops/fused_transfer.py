@@ -62,6 +62,25 @@ def _max_chunk_shift(table: np.ndarray, n_tiles: int) -> int:
     return 4 if 2 * fp8_tiles > n_tiles else 2
 
 
+def _pick_variant(table: np.ndarray, n_tiles: int) -> int:
+    """0: one 512-thread CTA per SM, deep ring (copy-dominated tables); 1: two
+    256-thread CTAs per SM (tables dominated by tiles all warps compute on).
+    ``AWEX_XFER_VARIANT`` overrides."""
+    import os
+
+    from awex_b200.transfer.descriptors import OP_COPY
+
+    forced = os.environ.get("AWEX_XFER_VARIANT")
+    if forced in ("0", "1"):
+        return int(forced)
+    if not len(table) or not n_tiles:
+        return 0
+    begins = table["tile_begin"].astype(np.int64)
+    counts = np.diff(np.append(begins, n_tiles))
+    computed = int(counts[table["op"] != OP_COPY].sum())
+    return 1 if 2 * computed > n_tiles else 0
+
+
 class StatusWord:
     """Four int32 on the device: code, detail0..2.  Kernels only ever move it
     from OK to an error; the host reads it when it wants a verdict."""
@@ -105,7 +124,7 @@ class TransferProgram:
     def __init__(self, table: np.ndarray, n_tiles: int, device, ready_pad: Optional[FlagPad] = None,
                  ready_slots: Sequence[int] = (), done_flag_addrs: Sequence[int] = (), timeout_ms: int = 2000,
                  grid: int = 0, row_offsets: Sequence[int] = (), tensor_map_descs: Sequence[int] = (), encoder=None,
-                 interleave: bool = True):
+                 interleave: bool = True, variant: Optional[int] = None):
         if encoder is not None:  # side tables produced while encoding
             row_offsets, tensor_map_descs = encoder.row_offsets, encoder.tensor_map_descs
         if table.dtype != DESC_DTYPE:
@@ -136,9 +155,10 @@ class TransferProgram:
         self.n_done = len(done_flag_addrs)
         # chunk index for the round-robin deal of tiles to CTAs: chunks of up to 16
         # tiles, smaller when the table is short so that every CTA still gets work
+        self.variant = _pick_variant(table, self.n_tiles) if variant is None else int(variant)
         self.chunk_desc, self.chunk_shift = None, 0
         if interleave and self.n_desc and self.n_tiles:
-            ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count
+            ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count * (2 if self.variant else 1)
             shift = _max_chunk_shift(table, self.n_tiles)
             while shift > 0 and (self.n_tiles >> shift) < 4 * ctas:
                 shift -= 1
@@ -185,7 +205,7 @@ class TransferProgram:
             self.ready_slots.data_ptr() if self.n_ready else None, self.n_ready,
             self.done_flags.data_ptr() if self.n_done else None, self.n_done,
             self.counter.data_ptr(), self.status.ptr, self.grid, stream,
-            self.chunk_desc.data_ptr() if self.chunk_desc is not None else None, self.chunk_shift,
+            self.chunk_desc.data_ptr() if self.chunk_desc is not None else None, self.chunk_shift, self.variant,
         )
         native.check(code, "fused_transfer launch")
         self.launches += 1

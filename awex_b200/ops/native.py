@@ -79,7 +79,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "awex_xfer_desc_size": ([], i32),
         "awex_xfer_smem_bytes": ([], i32),
         "awex_xfer_stage_bytes": ([], i32),
-        "awex_launch_fused_transfer": ([vp, u32, u64, u64, u64, vp, vp, u32, vp, u32, vp, vp, i32, vp, vp, u32], i32),
+        "awex_launch_fused_transfer": ([vp, u32, u64, u64, u64, vp, vp, u32, vp, u32, vp, vp, i32, vp, vp, u32, u32], i32),
         "awex_launch_wait_flags": ([vp, vp, u32, u64, u64, vp, vp], i32),
         "awex_launch_post_flags": ([vp, u32, u64, vp], i32),
         "awex_sum_desc_size": ([], i32),
