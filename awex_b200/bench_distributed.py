@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import json
 import os
+import sys
 import threading
 import time
 from typing import List, Optional
@@ -132,6 +133,11 @@ def run_distributed(args):
     my_engine = next((e for e, ranks in enumerate(engines) if rank in ranks), None)
     is_infer = my_engine is not None
     t_setup = time.time()
+
+    def note(what: str) -> None:
+        if rank == 0 or os.environ.get("AWEX_BENCH_VERBOSE"):
+            print(f"[bench] rank {rank} +{time.time() - t_setup:7.1f}s {what}", file=sys.stderr, flush=True)
+
     writer = reader = train_engine = infer_engine = None
     if is_train:
         ri = train_rank_infos(train_layout.tp, train_layout.pp, train_layout.dp, train_layout.ep, train_layout.etp)[train_ranks.index(rank)]
@@ -139,6 +145,7 @@ def run_distributed(args):
                                             process_group=train_group, transfer_grid=args.grid)
         writer = NCCLWeightsWriter(train_engine)
         writer.initialize()
+        note("training shard built")
     if is_infer:
         ri = infer_rank_infos(infer_layout.tp, infer_layout.ep, engine_rank=my_engine, first_local_rank=engines[my_engine][0])[
             engines[my_engine].index(rank)
@@ -147,6 +154,7 @@ def run_distributed(args):
                                                 instance_group=instance_groups[my_engine])
         reader = WeightsReader(infer_engine)
         reader.initialize()
+        note("inference shard built")
 
     # one-time metadata exchange; both sides block on each other, so a process
     # that plays both roles prepares them concurrently
@@ -157,8 +165,16 @@ def run_distributed(args):
             try:
                 torch.cuda.set_device(device)  # the current device is per thread
                 fn()
-            except BaseException as exc:  # surfaced below
+            except BaseException as exc:
+                # The other role (and the other ranks) block on what this role was
+                # about to publish: end the whole job now instead of waiting out
+                # their timeouts.
+                import traceback
+
                 errors.append(exc)
+                traceback.print_exc()
+                print(f"[bench] rank {rank}: set-up failed: {exc!r}", file=sys.stderr, flush=True)
+                os._exit(3)
         return run
 
     threads = []
@@ -174,6 +190,7 @@ def run_distributed(args):
         raise errors[0]
     torch.cuda.synchronize()
     setup_s = time.time() - t_setup
+    note("metadata exchanged, plans compiled, peers mapped")
 
     def barrier():
         if world > 1:
@@ -203,6 +220,7 @@ def run_distributed(args):
         barrier()
         step_async()
     check_status()
+    note("warm-up done")
 
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -250,6 +268,7 @@ def run_distributed(args):
         if i >= args.warmup:
             e2e_ms.append(dt)
     e2e = sum(e2e_ms) / len(e2e_ms)
+    note("timed loops done; validating")
 
     # ---- validation and accounting ----------------------------------------------------------------------
     valid = True

@@ -41,6 +41,8 @@ class CanonicalWeights:
         return int.from_bytes(digest[:7], "little")
 
     def get(self, name: str, shape: Tuple[int, ...]) -> torch.Tensor:
+        if self.device.type == "meta":  # shapes only: planning studies of models too large to hold
+            return torch.empty(shape, dtype=self.dtype, device=self.device)
         gen = torch.Generator(device=self.device)
         gen.manual_seed(self._seed_of(name))
         if name.endswith("norm.weight"):

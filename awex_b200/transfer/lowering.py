@@ -262,37 +262,104 @@ def check_exactly_once(
 ) -> List[str]:
     """Host-side race/coverage check of everything that will be written into one
     inference rank: every element of every required view is written exactly once
-    and nothing is written out of bounds.  Returns a list of problems."""
-    problems: List[str] = []
-    masks: Dict[str, torch.Tensor] = {}
+    and nothing is written out of bounds.  Returns a list of problems.
 
-    def mark(name: str, start, extent, label: str) -> None:
+    Cost depends on the number of boxes, not on the size of the tensors: per
+    view the box boundaries cut the index space into a coarse grid whose cells
+    are counted (a few cells per box for the regular shardings that occur)."""
+    problems: List[str] = []
+    boxes: Dict[str, List[Tuple[Tuple[int, ...], Tuple[int, ...], str]]] = {}
+
+    def note(name: str, start, extent, label: str) -> None:
         if name not in views:
             problems.append(f"{label}: write into unknown view {name!r}")
             return
         shape = views[name][0]
-        if len(start) != len(shape) or any(s < 0 or s + e > d for s, e, d in zip(start, extent, shape)):
+        if len(start) != len(shape) or any(s < 0 or e < 0 or s + e > d for s, e, d in zip(start, extent, shape)):
             problems.append(f"{label}: box start={start} extent={extent} exceeds {name!r} of shape {shape}")
             return
-        mask = masks.setdefault(name, torch.zeros(shape if shape else (1,), dtype=torch.uint8))
-        region = mask[tuple(slice(s, s + e) for s, e in zip(start, extent))] if shape else mask
-        if bool(region.any()):
-            problems.append(f"{label}: box start={start} extent={extent} of {name!r} overlaps an earlier write")
-        region += 1
+        boxes.setdefault(name, []).append((tuple(start), tuple(extent), label))
 
     for sender, manifest in enumerate(manifests):
         for name, start, extent, dtype, scale_name, scale_start in manifest:
             if name in views and str(views[name][1]) != dtype:
                 problems.append(f"sender#{sender}: dtype {dtype} written into {name!r} of dtype {views[name][1]}")
-            mark(name, tuple(start), tuple(extent), f"sender#{sender}")
+            note(name, tuple(start), tuple(extent), f"sender#{sender}")
             if scale_name is not None:
                 blocks = tuple(-(-e // FP8_BLOCK) for e in extent)
-                mark(scale_name, tuple(scale_start), blocks, f"sender#{sender}(scale)")
+                note(scale_name, tuple(scale_start), blocks, f"sender#{sender}(scale)")
+    for name, written in boxes.items():
+        problems.extend(_cover_problems(name, views[name][0], written))
     for name in required if required is not None else views:
-        mask = masks.get(name)
-        if mask is None:
+        if name not in boxes and not any(name in p for p in problems):
             problems.append(f"view {name!r} receives nothing")
-        elif not bool((mask == 1).all()):
-            missing = int((mask == 0).sum())
-            problems.append(f"view {name!r}: {missing} of {mask.numel()} elements are never written")
     return problems
+
+
+_MAX_GRID_CELLS = 20_000_000
+
+
+def _cover_problems(name: str, shape: Tuple[int, ...], written) -> List[str]:
+    """Overlaps and gaps of in-bounds boxes inside ``shape``."""
+    import numpy as np
+
+    if not shape:  # scalar view
+        return [] if len(written) == 1 else [f"view {name!r}: scalar written {len(written)} times"]
+    nd = len(shape)
+    cuts = []
+    for d in range(nd):
+        edge = {0, shape[d]}
+        for start, extent, _ in written:
+            edge.add(start[d])
+            edge.add(start[d] + extent[d])
+        cuts.append(np.array(sorted(edge), dtype=np.int64))
+    cells = 1
+    for c in cuts:
+        cells *= max(len(c) - 1, 1)
+    if cells > _MAX_GRID_CELLS:
+        return _cover_problems_pairwise(name, shape, written)
+    grid = np.zeros([max(len(c) - 1, 1) for c in cuts], dtype=np.int32)
+    out: List[str] = []
+    for start, extent, label in written:
+        if any(e == 0 for e in extent):
+            continue
+        sl = tuple(slice(int(np.searchsorted(cuts[d], start[d])), int(np.searchsorted(cuts[d], start[d] + extent[d]))) for d in range(nd))
+        if grid[sl].any() and len(out) < 8:
+            out.append(f"{label}: box start={start} extent={extent} of {name!r} overlaps an earlier write")
+        grid[sl] += 1
+    if (grid != 1).any():
+        volume = np.ones(grid.shape, dtype=np.int64)
+        for d, c in enumerate(cuts):
+            widths = np.diff(c) if len(c) > 1 else np.array([0])
+            volume = volume * widths.reshape([-1 if i == d else 1 for i in range(nd)])
+        missing = int(volume[grid == 0].sum())
+        if missing:
+            total = 1
+            for n in shape:
+                total *= n
+            out.append(f"view {name!r}: {missing} of {total} elements are never written")
+    return out
+
+
+def _cover_problems_pairwise(name: str, shape: Tuple[int, ...], written) -> List[str]:
+    """Irregular box sets: disjointness by pairs (sorted by first coordinate) and
+    coverage by total volume."""
+    out: List[str] = []
+    order = sorted(written, key=lambda b: b[0])
+    volume = 0
+    for i, (s_i, e_i, label) in enumerate(order):
+        v = 1
+        for e in e_i:
+            v *= e
+        volume += v
+        for s_j, e_j, _ in order[i + 1 :]:
+            if s_j[0] >= s_i[0] + e_i[0]:
+                break
+            if all(a < b + eb and b < a + ea for a, ea, b, eb in zip(s_i, e_i, s_j, e_j)) and len(out) < 8:
+                out.append(f"{label}: box start={s_i} extent={e_i} of {name!r} overlaps another write")
+    total = 1
+    for n in shape:
+        total *= n
+    if not out and volume != total:
+        out.append(f"view {name!r}: {total - volume} of {total} elements are never written")
+    return out

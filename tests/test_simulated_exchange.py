@@ -122,3 +122,28 @@ def test_spread_replica_pairing_balances_data_parallel_senders():
     assert spans["round_robin"] > 1.5 and spans["spread"] < 1.05
     with pytest.raises(ValueError):
         TransferPlanBuilder(2, 2, 1, replica_pairing="nearest")
+
+
+def test_exactly_once_check_finds_gaps_overlaps_and_strays():
+    from awex_b200.transfer.lowering import _cover_problems_pairwise, check_exactly_once
+
+    views = {"w": ((8, 6), torch.float32), "s": ((), torch.float32), "w_scale_inv": ((1, 1), torch.float32)}
+    entry = lambda name, start, extent, dtype="torch.float32": (name, start, extent, dtype, None, None)  # noqa: E731
+    good = [[entry("w", (0, 0), (4, 6)), entry("s", (), ())], [entry("w", (4, 0), (4, 3)), entry("w", (4, 3), (4, 3))]]
+    assert check_exactly_once(good, views, ["w", "s"]) == []
+    gap = [[entry("w", (0, 0), (4, 6))], [entry("w", (4, 0), (4, 3))]]
+    assert any("12 of 48 elements are never written" in p for p in check_exactly_once(gap, views, ["w"]))
+    twice = [good[0], good[1] + [entry("w", (3, 2), (2, 2))]]
+    assert any("overlaps" in p for p in check_exactly_once(twice, views, ["w"]))
+    stray = [[entry("w", (6, 0), (4, 6))]]
+    assert any("exceeds" in p for p in check_exactly_once(stray, views, ["w"]))
+    assert any("unknown view" in p for p in check_exactly_once([[entry("x", (0,), (1,))]], views, []))
+    assert any("dtype" in p for p in check_exactly_once([[entry("w", (0, 0), (8, 6), "torch.bfloat16")]], views, ["w"]))
+    assert any("receives nothing" in p for p in check_exactly_once([[entry("s", (), ())]], views, ["w", "s"]))
+    with_scale = [[("w", (0, 0), (8, 6), "torch.float32", "w_scale_inv", (0, 0))]]
+    assert check_exactly_once(with_scale, views, ["w", "w_scale_inv"]) == []
+    # the pairwise fallback agrees
+    boxes = [((0, 0), (4, 6), "a"), ((4, 0), (4, 3), "b"), ((4, 3), (4, 3), "c")]
+    assert _cover_problems_pairwise("w", (8, 6), boxes) == []
+    assert any("overlaps" in p for p in _cover_problems_pairwise("w", (8, 6), boxes + [((3, 2), (2, 2), "d")]))
+    assert any("never written" in p for p in _cover_problems_pairwise("w", (8, 6), boxes[:2]))
