@@ -22,7 +22,6 @@ SUM_DTYPE = np.dtype(
 )
 assert SUM_DTYPE.itemsize == 64
 GOLDEN = np.uint64(0x9E3779B97F4A7C15)
-CHUNK_WORDS = 4096
 
 
 def _as_rows(t: torch.Tensor) -> Tuple[int, int, int]:
@@ -58,6 +57,7 @@ class ChecksumPlan:
         assert self.lib.awex_sum_desc_size() == SUM_DTYPE.itemsize
         self.device = torch.device(device) if device is not None else tensors[0].device
         self.n = len(tensors)
+        CHUNK_WORDS = int(self.lib.awex_sum_chunk_words())  # words one CTA sums per step; fixed by the kernel
         table = np.zeros(self.n, dtype=SUM_DTYPE)
         chunks = 0
         for i, t in enumerate(tensors):

@@ -35,7 +35,9 @@ struct alignas(16) SumDesc {
 };
 static_assert(sizeof(SumDesc) == 56 + 8, "layout shared with the Python encoder");
 
-constexpr uint32_t kChunkWords = 4096;
+// A chunk is what one CTA sums between two lookups in the descriptor table and
+// two atomics: large enough (128 KiB) that those fixed costs stay small.
+constexpr uint32_t kChunkWords = 16384;
 constexpr uint64_t kGolden = 0x9E3779B97F4A7C15ull;
 
 __device__ __forceinline__ uint64_t key_of(uint64_t i) { return kGolden * (2 * i + 1); }
