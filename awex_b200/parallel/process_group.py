@@ -52,14 +52,7 @@ class ExchangeGroup:
         self._store = None
 
 
-def init_weights_update_group(master_address: str, master_port: int, rank: int, world_size: int,
-                              group_name: str = "weights_exchange", backend: Optional[str] = None,
-                              timeout_s: float = 1800.0, device: Optional[torch.device] = None) -> ExchangeGroup:
-    backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
-    timeout = timedelta(seconds=timeout_s)
-    store = dist.TCPStore(master_address, int(master_port), world_size, is_master=(rank == 0), timeout=timeout,
-                          wait_for_workers=False)
-    prefixed = dist.PrefixStore(group_name, store)
+def _backend_over_store(prefixed, rank: int, world_size: int, backend: str, timeout: timedelta, device, keep_alive, name: str) -> ExchangeGroup:
     if backend == "gloo":
         pg = dist.ProcessGroupGloo(prefixed, rank, world_size, timeout)
     elif backend == "nccl":
@@ -70,8 +63,55 @@ def init_weights_update_group(master_address: str, master_port: int, rank: int, 
             pg.eager_connect_single_device(device)
     else:
         raise ValueError(f"unsupported exchange group backend {backend!r}")
-    logger.info(f"joined exchange group {group_name!r}: rank {rank}/{world_size} via {backend} at {master_address}:{master_port}")
-    return ExchangeGroup(pg, rank, world_size, backend, store)
+    logger.info(f"joined group {name!r}: rank {rank}/{world_size} via {backend}")
+    return ExchangeGroup(pg, rank, world_size, backend, keep_alive)
+
+
+def init_weights_update_group(master_address: str, master_port: int, rank: int, world_size: int,
+                              group_name: str = "weights_exchange", backend: Optional[str] = None,
+                              timeout_s: float = 1800.0, device: Optional[torch.device] = None) -> ExchangeGroup:
+    backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
+    timeout = timedelta(seconds=timeout_s)
+    store = dist.TCPStore(master_address, int(master_port), world_size, is_master=(rank == 0), timeout=timeout,
+                          wait_for_workers=False)
+    return _backend_over_store(dist.PrefixStore(group_name, store), rank, world_size, backend, timeout, device, store, group_name)
+
+
+def init_custom_process_group(backend: Optional[str] = None, init_method: Optional[str] = None, timeout_s: float = 1800.0,
+                              world_size: int = -1, rank: int = -1, store=None, group_name: str = "main",
+                              device: Optional[torch.device] = None) -> ExchangeGroup:
+    """A group beside whatever default group the process already has
+    (`awex/util/process_group.py:34-98` in the reference, which reaches into
+    torch's private group constructor for this).  Give either a ``store`` or a
+    ``tcp://host:port`` ``init_method``; rank 0 hosts the store of the latter."""
+    if world_size <= 0 or rank < 0:
+        raise ValueError("world_size and rank must be given")
+    backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
+    timeout = timedelta(seconds=timeout_s)
+    if store is None:
+        if not init_method or not init_method.startswith("tcp://"):
+            raise ValueError("init_custom_process_group needs a store or a tcp://host:port init_method")
+        host, _, port = init_method[len("tcp://"):].partition(":")
+        store = dist.TCPStore(host, int(port), world_size, is_master=(rank == 0), timeout=timeout, wait_for_workers=False)
+    return _backend_over_store(dist.PrefixStore(group_name, store), rank, world_size, backend, timeout, device, store, group_name)
+
+
+def create_pair_subgroups_from_parent(store, rank: int, pairs: Sequence[Sequence[int]], backend: Optional[str] = None,
+                                      timeout_s: float = 1800.0, device: Optional[torch.device] = None) -> dict:
+    """Two-rank groups over the parent's store, one per listed pair that
+    contains ``rank``; returns ``{(a, b): ExchangeGroup}`` where the group rank
+    of ``a`` is 0 (`awex/util/process_group.py:101-196` in the reference)."""
+    backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
+    timeout = timedelta(seconds=timeout_s)
+    out = {}
+    for a, b in pairs:
+        if a == b:
+            raise ValueError(f"a pair needs two different ranks, got ({a}, {b})")
+        if rank not in (a, b):
+            continue
+        name = f"pair_{a}_{b}"
+        out[(a, b)] = _backend_over_store(dist.PrefixStore(name, store), 0 if rank == a else 1, 2, backend, timeout, device, store, name)
+    return out
 
 
 def setup_batch_isend_irecv(group: ExchangeGroup, device: torch.device, n_elems: int = 100) -> None:

@@ -1,0 +1,150 @@
+"""MetaServer and its client against a real aiohttp server on an ephemeral port:
+every route, objects, sets, barriers, waits and their timeouts, keys with
+slashes, the id allocator, and failure behaviour (dropped keys, a server that is
+gone, a rank that never joins)."""
+
+import threading
+import time
+
+import pytest
+import requests
+
+from awex_b200.meta.meta_server import MetaServer, MetaServerClient
+from awex_b200.utils.common import from_binary, to_binary
+
+
+@pytest.fixture()
+def served():
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    client = MetaServerClient("127.0.0.1", server.port, max_retries=2)
+    yield server, client
+    client.close()
+    server.stop()
+
+
+def test_store_api_without_http():
+    server = MetaServer("127.0.0.1", 0)
+    server.put_object("a", {"x": 1})
+    assert server.get_object("a") == {"x": 1}
+    server.put_binary("b", b"raw")
+    assert server.get_binary("b") == b"raw"
+    server.put_json("j", [1, 2])
+    assert server.get_json("j") == [1, 2]
+    server.delete("a")
+    with pytest.raises(Exception):
+        server.get_binary("a")
+
+
+def test_raw_routes(served):
+    server, _ = served
+    base = f"http://127.0.0.1:{server.port}/v1"
+    assert requests.get(f"{base}/health").json()["success"]
+    assert requests.get(f"{base}/get_binary/missing").status_code == 404
+    assert requests.put(f"{base}/put_binary/k", data=b"\x00\x01").json()["success"]
+    assert requests.get(f"{base}/get_binary/k").content == b"\x00\x01"
+    assert requests.get(f"{base}/has_key/k").json()["has_key"] is True
+    assert requests.get(f"{base}/has_key/other").json()["has_key"] is False
+    assert "k" in requests.get(f"{base}/keys").json()["keys"]
+    assert requests.put(f"{base}/put_json/doc", json={"a": [1, 2]}).json()["success"]
+    assert requests.get(f"{base}/get_json/doc").json()["data"] == {"a": [1, 2]}
+    assert requests.get(f"{base}/get_json/nodoc").status_code == 404
+    assert requests.put(f"{base}/add_object_to_set/s", data=to_binary(3)).json()["success"]
+    assert requests.put(f"{base}/add_object_to_set/s", data=to_binary(3)).json()["success"]
+    assert from_binary(requests.get(f"{base}/get_binary/s").content) == {3}
+    assert requests.delete(f"{base}/delete/k").json()["success"]
+    assert requests.delete(f"{base}/delete/k").status_code == 404
+    first = requests.post(f"{base}/allocate_auto_grow_id").json()["id"]
+    assert requests.post(f"{base}/allocate_auto_grow_id").json()["id"] == first + 1
+
+
+def test_client_objects_sets_and_slash_keys(served):
+    _, c = served
+    c.put_object("step/1/meta", {"names": ["a", "b"], "n": 2})
+    assert c.get_object("step/1/meta") == {"names": ["a", "b"], "n": 2}
+    assert c.has_key("step/1/meta") and "step/1/meta" in c.list_keys()
+    assert c.get_object("absent") is None
+    assert c.get_object("absent", default_value=7) == 7
+    with pytest.raises(ValueError):
+        c.get_binary("absent")
+    c.put_binary("blob", b"abc")
+    assert c.get_binary("blob") == b"abc"
+    c.put_json("cfg", {"tp": 2})
+    assert c.get_json("cfg") == {"tp": 2}
+    with pytest.raises(ValueError):
+        c.get_json("nocfg")
+    for r in (0, 1, 1, 2):
+        c.add_object_to_set("joined", r)
+    assert c.get_set("joined") == {0, 1, 2} and c.get_set("nobody") == set()
+    c.put_object("once", (1, 2))
+    assert c.get_object_then_delete("once", timeout=1) == (1, 2) and not c.has_key("once")
+    c.delete_if_exists("once")  # absent keys are fine
+    a, b = c.allocate_auto_grow_id(), c.allocate_auto_grow_id()
+    assert b == a + 1
+    assert c.health_check()["success"]
+
+
+def test_waits_return_when_posted_and_time_out_when_not(served):
+    _, c = served
+    threading.Timer(0.3, lambda: MetaServerClient("127.0.0.1", c._port).put_object("late", 5)).start()
+    started = time.time()
+    assert c.get_object("late", timeout=10) == 5
+    assert time.time() - started < 5
+    started = time.time()
+    with pytest.raises(TimeoutError):
+        c.wait_key("never", timeout=0.5)
+    assert time.time() - started < 3
+    assert c.get_object("never", timeout=0.3, default_value="fallback") == "fallback"
+    with pytest.raises(TimeoutError):
+        c.get_object("never", timeout=0.3)
+
+
+def test_barrier_completes_and_a_missing_rank_times_out(served):
+    _, c = served
+    port = c._port
+    done = []
+
+    def member(rank):
+        MetaServerClient("127.0.0.1", port).barrier("b1", rank, 3, timeout=20)
+        done.append(rank)
+
+    threads = [threading.Thread(target=member, args=(r,)) for r in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=30)
+    assert sorted(done) == [0, 1, 2]
+    # rank 2 never joins: the others give up after their timeout instead of hanging
+    with pytest.raises(TimeoutError):
+        c.barrier("b2", 0, 3, timeout=0.6)
+    c.add_object_to_set("grow", 1)
+    with pytest.raises(TimeoutError):
+        c.wait_set_until_size("grow", 2, timeout=0.5)
+    c.add_object_to_set("grow", 2)
+    c.wait_set_until_size("grow", 2, timeout=5, delete_after_wait=True)
+    assert not c.has_key("grow")
+
+
+def test_client_gives_up_when_the_server_is_gone():
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    port = server.port
+    c = MetaServerClient("127.0.0.1", port, max_retries=1)
+    c.put_object("x", 1)
+    server.stop()
+    with pytest.raises(Exception):
+        c.put_object("y", 2)
+    c.delete_if_exists("x")  # swallowed
+
+
+def test_host_handshake_poll_times_out_quickly(served):
+    from awex_b200.transfer.transports import HostHandshakeTimeout, host_done_key, host_ready_key, poll_key
+
+    _, c = served
+    assert host_ready_key(3, 7) == "p2p_host_ready_3_7" and host_done_key(9, 7) == "p2p_host_done_9_7"
+    started = time.time()
+    with pytest.raises(HostHandshakeTimeout):
+        poll_key(c, host_ready_key(0, 1), timeout_s=0.2)
+    assert time.time() - started < 2
+    c.put_object(host_ready_key(0, 1), 1)
+    poll_key(c, host_ready_key(0, 1), timeout_s=0.2)
