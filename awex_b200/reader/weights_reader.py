@@ -169,9 +169,13 @@ class WeightsReader(WeightExchangeReader):
 
         ctx = kwargs["model_context"]
         backend = kwargs.get("weights_comm_backend", "nccl")
-        if backend not in ("nccl", "p2p", "gloo"):
+        if backend == "astate":
+            from awex_b200.reader.astate_reader import AStateWorkerWeightsReader as worker_cls
+        elif backend in ("nccl", "p2p", "gloo"):
+            worker_cls = NCCLWorkerWeightsReader
+        else:
             raise NotImplementedError(f"worker reader for comm_backend {backend!r} is not available")
-        reader = NCCLWorkerWeightsReader(
+        reader = worker_cls(
             model=kwargs["model"], model_context=ctx,
             infer_conf=pickle.loads(kwargs["infer_conf_bytes"]),
             parameters_meta=pickle.loads(kwargs["parameters_meta_bytes"]),
