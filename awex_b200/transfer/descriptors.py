@@ -244,14 +244,37 @@ def encode_items(items: Iterable[CopyItem], src_addrs: Dict[Tuple[str, int], Ten
 
 
 # ---- host-side checks ------------------------------------------------------------------------------
+class _SpanIndex:
+    """``[low, high)`` ranges with an O(log n) "is this range inside one of
+    them" query: ranges sorted by start, with the running maximum of their ends
+    (the range that attains it starts at or before the query and ends at or after it)."""
+
+    def __init__(self, spans: Sequence[Tuple[int, int]]):
+        import bisect
+
+        self._bisect = bisect.bisect_right
+        ordered = sorted((int(a), int(b)) for a, b in spans)
+        self.starts = [a for a, _ in ordered]
+        self.reach: List[int] = []
+        best = -1
+        for _, b in ordered:
+            best = max(best, b)
+            self.reach.append(best)
+
+    def contains(self, lo: int, hi: int) -> bool:
+        i = self._bisect(self.starts, lo) - 1
+        return i >= 0 and self.reach[i] >= hi
+
+
 def validate_table(table: np.ndarray, n_tiles: int, src_spans: Sequence[Tuple[int, int]],
                    dst_spans: Sequence[Tuple[int, int]], check_overlap: bool = True) -> List[str]:
     """Return every violated rule.  ``src_spans`` / ``dst_spans`` are the
     ``[low, high)`` address ranges of the tensors the table may read / write."""
     problems: List[str] = []
+    src_spans, dst_spans = _SpanIndex(src_spans), _SpanIndex(dst_spans)
 
-    def inside(lo: int, hi: int, spans) -> bool:
-        return any(a <= lo and hi <= b for a, b in spans)
+    def inside(lo: int, hi: int, spans: "_SpanIndex") -> bool:
+        return spans.contains(lo, hi)
 
     expect_begin = 0
     written: List[Tuple[int, int, int]] = []

@@ -229,3 +229,21 @@ def test_descriptor_validator_rejects_seeded_bad_tables():
     assert broken(op=99)                                            # unknown operation
     assert broken(tile_rows=0)
     assert validate_table(table, n_tiles + 1, src_spans, dst_spans)  # tile count does not match
+
+
+def test_span_index_agrees_with_a_linear_scan():
+    import random
+
+    from awex_b200.transfer.descriptors import _SpanIndex
+
+    rng = random.Random(5)
+    spans = []
+    for _ in range(200):
+        lo = rng.randrange(0, 10_000)
+        spans.append((lo, lo + rng.randrange(1, 400)))  # overlapping and nested ranges included
+    index = _SpanIndex(spans)
+    for _ in range(5000):
+        lo = rng.randrange(0, 10_500)
+        hi = lo + rng.randrange(1, 300)
+        assert index.contains(lo, hi) == any(a <= lo and hi <= b for a, b in spans), (lo, hi)
+    assert not _SpanIndex([]).contains(0, 1)
