@@ -33,11 +33,13 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import os
 import time
 
 import torch
 
 from awex_b200 import logging
+from awex_b200.utils import env
 from awex_b200.transfer.cpu_exec import entry_nbytes, pack_message, unpack_message
 from awex_b200.transfer.lowering import CopyItem, check_exactly_once, manifest_by_destination
 
@@ -271,6 +273,10 @@ class PeerStoreSender:
     def send(self, epoch: int, synchronize: bool = True) -> None:
         for d in self.host_destinations:
             poll_key(self.meta, host_ready_key(d, epoch), self.host_wait_timeout_s)
+        if env.flag("AWEX_P2P_TRACE"):
+            per_dst = {d: sum(entry_nbytes(e) for e in es) for d, es in self.manifest.items()}
+            logger.info(f"[p2p] train rank {self.train_rank} epoch {epoch}: {self.n_desc} descriptors, {self.program.n_tiles} tiles, "
+                        f"bytes per destination {per_dst}, host-synchronised {self.host_destinations}")
         self.program.launch(epoch)
         if synchronize or self.host_destinations:
             torch.cuda.current_stream(self.device).synchronize()
@@ -319,12 +325,20 @@ class GlooSender:
     def connect(self) -> None:
         self.group = _join_exchange_group(self.meta, self.transfer_rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device)
         self.group.barrier()
+        env.warn_about_ignored(logger)
 
     def send(self, epoch: int, synchronize: bool = True) -> None:
+        one_by_one = os.environ.get("AWEX_USE_BATCH_SEND_RECV", "1") == "0"
         works = []
         for d in self.destinations:
             msg = pack_message(self.by_dst[d], self.local).to(self.device)
-            works.append((self.group.send(msg, d, tag=epoch & 0x7FFF), msg))
+            if env.flag("AWEX_P2P_TRACE"):
+                logger.info(f"[p2p] train rank {self.train_rank} epoch {epoch}: {msg.numel()} bytes in {len(self.by_dst[d])} items to rank {d}")
+            work = self.group.send(msg, d, tag=epoch & 0x7FFF)
+            if one_by_one:
+                work.wait()
+            else:
+                works.append((work, msg))
         for w, _keepalive in works:
             w.wait()
 

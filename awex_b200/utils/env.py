@@ -1,0 +1,59 @@
+"""Every environment variable the framework reads, in one table, with what it
+does here.  Variables of the reference that steer machinery this framework does
+not have (per-operation NCCL batching, chunked co-located exchange, HCCL
+buffers) are still accepted, and :func:`describe_env` says so, so that a launch
+script written for the reference keeps working and nobody wonders why a knob
+has no effect."""
+
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Tuple
+
+# name -> (default, effect)
+KNOBS: Dict[str, Tuple[str, str]] = {
+    "AWEX_DEVICE_TYPE": ("", "force the device type: cuda or cpu (npu is not supported)"),
+    "AWEX_MASTER_ADDR": ("", "address other processes should use to reach this host (else the outbound interface's)"),
+    "AWEX_META_SERVER_ADDR": ("", "ip:port of the MetaServer; exported by the Megatron engine for child processes"),
+    "AWEX_META_SERVER_IP": ("", "set together with AWEX_META_SERVER_ADDR"),
+    "AWEX_META_SERVER_PORT": ("", "set together with AWEX_META_SERVER_ADDR"),
+    "AWEX_COMM_BACKEND": ("file", "default comm_backend of vLLM workers that were not handed a configuration"),
+    "AWEX_CP_MODE": ("", "label of the context-parallel scheme (ring | ulysses | none) recorded in rank infos"),
+    "AWEX_LOG_LEVEL": ("INFO", "log level of the framework's logger"),
+    "AWEX_MEM_DEBUG": ("0", "1: log device memory around the phases of an update"),
+    "AWEX_DEBUG_INFER_META": ("0", "1: log every inference parameter while metadata is collected"),
+    "AWEX_P2P_TRACE": ("0", "1: log, per update, what each sender writes to each destination (bytes, descriptors, tiles)"),
+    "AWEX_CHUNK_MB": ("", "size in MiB of the chunks of tiles dealt to CTAs by the fused transfer kernel (default by op mix)"),
+    "AWEX_XFER_VARIANT": ("", "0 | 1: force the launch shape of the fused transfer kernel (one 512-thread or two 256-thread CTAs per SM)"),
+    "AWEX_XFER_INTERLEAVE": ("", "0 | 1: force contiguous tile ranges or round-robin chunks"),
+    "AWEX_USE_BATCH_SEND_RECV": ("1", "message transport only: 0 sends one message at a time and waits for each"),
+    "AWEX_SYNTH_FP8_ORACLE": ("cpu", "synthetic models: 'kernel' builds fp8 oracles with the quantisation kernel instead of the CPU"),
+    # accepted, no effect here
+    "AWEX_CHUNK_OPS": ("", "no effect: the reference's cap on operations per chunk of its chunked co-located exchange"),
+    "AWEX_DESTROY_PG_AFTER_UPDATE": ("0", "no effect on the fused path (it holds no communicator); the message transport keeps its group"),
+    "AWEX_P2P_HCCL_BUFFER_SIZE": ("", "no effect: Ascend HCCL is not supported"),
+    "AWEX_USE_MINDSPEED": ("0", "no effect: the Ascend MindSpeed patch is not applied on CUDA"),
+}
+
+NO_EFFECT = ("AWEX_CHUNK_OPS", "AWEX_DESTROY_PG_AFTER_UPDATE", "AWEX_P2P_HCCL_BUFFER_SIZE", "AWEX_USE_MINDSPEED")
+
+
+def flag(name: str) -> bool:
+    return os.environ.get(name, KNOBS.get(name, ("0", ""))[0]) == "1"
+
+
+def describe_env() -> List[str]:
+    """One line per variable that is set in this process."""
+    lines = []
+    for name, (_default, effect) in KNOBS.items():
+        if name in os.environ:
+            lines.append(f"{name}={os.environ[name]}: {effect}")
+    unknown = sorted(k for k in os.environ if k.startswith("AWEX_") and k not in KNOBS and not k.startswith("AWEX_BENCH"))
+    lines.extend(f"{name}={os.environ[name]}: not a variable this framework knows" for name in unknown)
+    return lines
+
+
+def warn_about_ignored(logger) -> None:
+    for name in NO_EFFECT:
+        if os.environ.get(name) not in (None, "", "0"):
+            logger.warning(f"{name} is set but has {KNOBS[name][1]}")

@@ -247,3 +247,30 @@ def test_span_index_agrees_with_a_linear_scan():
         hi = lo + rng.randrange(1, 300)
         assert index.contains(lo, hi) == any(a <= lo and hi <= b for a, b in spans), (lo, hi)
     assert not _SpanIndex([]).contains(0, 1)
+
+
+def test_environment_table(monkeypatch):
+    from awex_b200.utils import env
+
+    monkeypatch.setenv("AWEX_CHUNK_OPS", "64")
+    monkeypatch.setenv("AWEX_P2P_TRACE", "1")
+    monkeypatch.setenv("AWEX_TYPO", "x")
+    lines = env.describe_env()
+    assert any(line.startswith("AWEX_CHUNK_OPS=64: no effect") for line in lines)
+    assert any(line.startswith("AWEX_TYPO=x: not a variable") for line in lines)
+    assert env.flag("AWEX_P2P_TRACE") and not env.flag("AWEX_MEM_DEBUG")
+    warned = []
+    env.warn_about_ignored(SimpleNamespace(warning=warned.append))
+    assert len(warned) == 1 and "AWEX_CHUNK_OPS" in warned[0]
+    # every variable the package reads is in the table
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(env.__file__)))
+    used = set()
+    for folder, _dirs, files in os.walk(root):
+        for name in files:
+            if name.endswith(".py"):
+                with open(os.path.join(folder, name)) as f:
+                    used |= set(re.findall(r'''environ(?:\.get)?[(\[]\s*["'](AWEX_[A-Z0-9_]+)''', f.read()))
+    assert used and used - set(env.KNOBS) - {"AWEX_BENCH_VERBOSE"} == set(), used - set(env.KNOBS)
