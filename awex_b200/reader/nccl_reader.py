@@ -22,6 +22,7 @@ from awex_b200.meta.meta_server import MetaServerClient
 from awex_b200.models.registry import get_infer_weights_converter
 from awex_b200.sharding.param_sharding import get_rank_info_extractor
 from awex_b200.utils.common import compute_statistics
+from awex_b200.utils.trace import phase
 
 logger = logging.getLogger(__name__)
 
@@ -51,7 +52,8 @@ class WorkerWeightsReader:
         self.instance_world_size = self.infer_world_size // num_engines
         self.transfer_rank = engine_rank * self.instance_world_size + self.rank_info.global_rank
         self.training_world_size = training_params_meta[0].shards[0].world_size
-        self.timeout = 10000
+        self.timeout = float(self.debug_mode_config.get("host_wait_timeout_s", 10000))
+        self.exchange_timeout_s = float(self.debug_mode_config.get("exchange_timeout_s", 1800))
         self.parameters: Dict[str, torch.Tensor] = {}
         self._history: Dict[str, List[float]] = {}
         self._snapshot = None
@@ -143,7 +145,7 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
         else:
             from awex_b200.transfer.transports import GlooReceiver
 
-            self.transport = GlooReceiver(**common)
+            self.transport = GlooReceiver(exchange_timeout_s=self.exchange_timeout_s, **common)
         self.transport.connect()
         logger.info(f"Rank[{self.transfer_rank}] reader ready in {time.time() - t0:.2f}s, {len(self.parameters)} canonical views")
 
@@ -154,10 +156,12 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
                 "inference parameters moved since they were published; senders hold stale addresses "
                 "(re-create the writer and reader after the engine re-maps its weights)"
             )
-        self.transport.begin(self.epoch)
+        with phase("announce_ready"):
+            self.transport.begin(self.epoch)
 
     def finish_update(self, step_id, synchronize: bool = True) -> None:
-        self.transport.finish(self.epoch, synchronize=synchronize)
+        with phase("receive_weights"):
+            self.transport.finish(self.epoch, synchronize=synchronize)
         self._after_update()
 
     def close(self) -> None:

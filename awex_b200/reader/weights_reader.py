@@ -107,7 +107,7 @@ class WeightsReader(WeightExchangeReader):
         self.debug_mode_config = config.debug_mode_config or {}
         self.raise_on_validation_fail = self.debug_mode_config.get("raise_on_validation_fail", False)
         self.ipc_backend = config.weights_exchange_ipc_backend
-        self.timeout = 10000
+        self.timeout = float(self.debug_mode_config.get("host_wait_timeout_s", 10000))
         self.lock = threading.Lock()
         self.initialized = False
         self.expected_pp_ranks: List[int] = []

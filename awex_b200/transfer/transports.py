@@ -296,7 +296,7 @@ class PeerStoreSender:
 
 
 # ------------------------------------------------------------------------------------ CPU / portable path
-def _join_exchange_group(meta, transfer_rank: int, world: int, wait_timeout_s: float, device):
+def _join_exchange_group(meta, transfer_rank: int, world: int, wait_timeout_s: float, device, exchange_timeout_s: float = 1800.0):
     from awex_b200.parallel.process_group import init_weights_update_group
     from awex_b200.utils.common import get_free_port, get_ip_address
 
@@ -306,12 +306,13 @@ def _join_exchange_group(meta, transfer_rank: int, world: int, wait_timeout_s: f
     else:
         info = meta.get_object("master_info", timeout=wait_timeout_s)
     backend = "nccl" if device.type == "cuda" else "gloo"
-    return init_weights_update_group(info[0], info[1], transfer_rank, world, backend=backend, device=device)
+    return init_weights_update_group(info[0], info[1], transfer_rank, world, backend=backend, device=device, timeout_s=exchange_timeout_s)
 
 
 class GlooSender:
     def __init__(self, meta, items, local, train_rank: int, infer_world: int, train_world: int, device="cpu",
-                 wait_timeout_s: float = 10000, **_unused):
+                 wait_timeout_s: float = 10000, exchange_timeout_s: float = 1800.0, **_unused):
+        self.exchange_timeout_s = exchange_timeout_s
         self.meta, self.items, self.local = meta, list(items), local
         self.train_rank, self.infer_world, self.train_world = train_rank, infer_world, train_world
         self.transfer_rank = infer_world + train_rank
@@ -323,7 +324,8 @@ class GlooSender:
         self.bytes_out = sum(entry_nbytes(e) for es in self.manifest.values() for e in es)
 
     def connect(self) -> None:
-        self.group = _join_exchange_group(self.meta, self.transfer_rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device)
+        self.group = _join_exchange_group(self.meta, self.transfer_rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device,
+                                          self.exchange_timeout_s)
         self.group.barrier()
         env.warn_about_ignored(logger)
 
@@ -351,7 +353,8 @@ class GlooSender:
 
 class GlooReceiver:
     def __init__(self, meta, views, transfer_rank: int, infer_world: int, train_world: int, required, device="cpu",
-                 wait_timeout_s: float = 10000, strict: bool = True, **_unused):
+                 wait_timeout_s: float = 10000, strict: bool = True, exchange_timeout_s: float = 1800.0, **_unused):
+        self.exchange_timeout_s = exchange_timeout_s
         self.meta, self.views, self.rank = meta, views, transfer_rank
         self.infer_world, self.train_world = infer_world, train_world
         self.required, self.device, self.strict, self.wait_timeout_s = list(required), torch.device(device), strict, wait_timeout_s
@@ -364,7 +367,8 @@ class GlooReceiver:
         return False
 
     def connect(self) -> None:
-        self.group = _join_exchange_group(self.meta, self.rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device)
+        self.group = _join_exchange_group(self.meta, self.rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device,
+                                          self.exchange_timeout_s)
         self.senders, self.entries, _ = _collect_manifests(self.meta, self.infer_world, self.train_world, self.rank, self.wait_timeout_s)
         _check_coverage(self.entries, self.views, self.required, self.strict, f"inference rank {self.rank}")
         self.bytes_in = sum(entry_nbytes(e) for es in self.entries for e in es)

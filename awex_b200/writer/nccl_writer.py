@@ -20,6 +20,7 @@ import torch
 from awex_b200 import logging
 from awex_b200.transfer.lowering import LocalParam, SendProgramCompiler
 from awex_b200.transfer.transfer_plan import TransferPlanBuilder, compute_transfer_plan_stats
+from awex_b200.utils.trace import phase
 from awex_b200.utils.common import compute_statistics
 from awex_b200.writer.weights_writer import WeightsExchangeShardingWriter
 
@@ -61,14 +62,15 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
         else:
             from awex_b200.transfer.transports import GlooSender
 
-            self.transport = GlooSender(train_world=self.training_world_size, **common)
+            self.transport = GlooSender(train_world=self.training_world_size, exchange_timeout_s=self.exchange_timeout_s, **common)
         self.transport.connect()
         logger.info(f"Rank[{self.transfer_rank}] writer ready in {time.time() - t0:.2f}s")
 
     def _write_weights(self, step_id, **kwargs) -> None:
         t0 = time.time()
         self.epoch += 1
-        self.transport.send(self.epoch, synchronize=kwargs.get("synchronize", True))
+        with phase("send_weights"):
+            self.transport.send(self.epoch, synchronize=kwargs.get("synchronize", True))
         compute_statistics(self._history, step_id, time.time() - t0, "Send weights")
 
     def close(self) -> None:

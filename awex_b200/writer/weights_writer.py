@@ -83,7 +83,10 @@ class WeightsExchangeShardingWriter(WeightExchangeWriter):
         self.validated_steps = 0
         self.start_step = -1
         self.lock = threading.Lock()
-        self.timeout = 10000
+        # how long host-side waits for the other side last (metadata, address books, co-located hand-off)
+        self.timeout = float(get("host_wait_timeout_s", 10000))
+        # timeout of collectives and messages of the exchange group (message transport)
+        self.exchange_timeout_s = float(get("exchange_timeout_s", 1800))
         self.initialized = False
         self.num_infer_engines = None
         self.engine_name = train_engine.engine_name

@@ -59,3 +59,52 @@ def test_interpreter_refuses_accesses_outside_the_given_tensors():
     bad["col_tiles"][0] = -(-10_000 // int(bad["tile_cols"][0]))
     with pytest.raises(IndexError):
         run_table(bad, int(bad["col_tiles"][0]), HostMemory([src, dst]))
+
+
+def _random_case(rng, case):
+    """One random copy item between two 2-D or 3-D tensors with odd sizes,
+    offsets and (sometimes) non-contiguous destinations."""
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.transfer.lowering import CopyItem
+
+    nd = rng.choice([1, 2, 2, 3])
+    extent = tuple(rng.choice([1, 2, 3, 5, 7, 8, 16, 33, 64, 130]) for _ in range(nd))
+    src_pad = tuple(rng.randrange(0, 4) for _ in range(nd))
+    dst_pad = tuple(rng.randrange(0, 4) for _ in range(nd))
+    src_shape = tuple(e + p + rng.randrange(0, 3) for e, p in zip(extent, src_pad))
+    dst_shape = tuple(e + p + rng.randrange(0, 3) for e, p in zip(extent, dst_pad))
+    kind = rng.choice(["copy", "copy", "cast", "add"])
+    src_dtype = rng.choice([torch.bfloat16, torch.float16, torch.float32])
+    dst_dtype = src_dtype if kind == "copy" else rng.choice([torch.bfloat16, torch.float32])
+    g = torch.Generator().manual_seed(case)
+    src = torch.randn(src_shape, generator=g).to(src_dtype)
+    dst = torch.full(dst_shape, -7.0, dtype=dst_dtype)
+    if nd >= 2 and rng.random() < 0.3:  # a destination view with a non-unit outer stride
+        dst = torch.full((dst_shape[0], 2) + dst_shape[1:], -7.0, dtype=dst_dtype)[:, 1]
+    op = {"copy": ValueOp("none") if src_dtype == dst_dtype else ValueOp("cast", dtype=dst_dtype),
+          "cast": ValueOp("cast", dtype=dst_dtype), "add": ValueOp("add", dtype=dst_dtype, const=1.0)}[kind]
+    item = CopyItem("w", 0, src_pad, extent, 0, "w", dst_pad, src_dtype, dst_dtype, op)
+    return item, src, dst
+
+
+def test_random_odd_shaped_items_encode_to_equivalent_tables():
+    import random
+
+    from awex_b200.transfer.cpu_exec import execute_items
+    from awex_b200.transfer.descriptors import TensorAddr, encode_items, validate_table
+
+    rng = random.Random(11)
+    for case in range(150):
+        item, src, dst = _random_case(rng, case)
+        want = dst.clone()
+        execute_items([item], {("w", 0): src}, {0: {"w": want}})
+        table, n_tiles, enc = encode_items([item], {("w", 0): TensorAddr.of(src)}, {0: {"w": TensorAddr.of(dst)}})
+        problems = validate_table(table, n_tiles, [TensorAddr.of(src).byte_span()], [TensorAddr.of(dst).byte_span()])
+        assert problems == [], (case, item, problems)
+        base = dst._base if dst._base is not None else dst
+        run_table(table, n_tiles, HostMemory([src, base]), enc.row_offsets)
+        assert torch.equal(dst.float(), want.float()), (case, item)
+        # and in the order round-robin chunks would visit the tiles
+        dst.fill_(-7.0)
+        run_chunked(table, n_tiles, HostMemory([src, base]), grid=3, chunk_shift=1, row_offsets=enc.row_offsets)
+        assert torch.equal(dst.float(), want.float()), (case, item)

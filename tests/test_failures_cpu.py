@@ -1,0 +1,129 @@
+"""Failure detection on the host, among CPU ranks: a side that never shows up, a
+sender whose manifest is missing, a training rank that leaves between two
+updates.  Every wait involved is bounded, so each case ends with an exception
+within seconds instead of a hang."""
+
+import os
+import time
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+
+def test_writer_gives_up_when_no_inference_side_appears():
+    from awex_b200 import NCCLWeightsWriter
+    from awex_b200.meta.meta_server import MetaServer
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticTrainEngine
+    from awex_b200.synthetic.topology import train_rank_infos
+
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    try:
+        engine = SyntheticTrainEngine(get_arch("tiny-llama"), train_rank_infos()[0], f"127.0.0.1:{server.port}", dtype=torch.float32,
+                                      host_wait_timeout_s=0.5)
+        writer = NCCLWeightsWriter(engine)
+        writer.initialize()
+        started = time.time()
+        with pytest.raises(TimeoutError, match="infer_conf"):
+            writer.write_weights(step_id=1)
+        assert time.time() - started < 10
+    finally:
+        server.stop()
+
+
+def test_reader_gives_up_when_a_sender_never_publishes_its_manifest():
+    from awex_b200.meta.meta_server import MetaServer, MetaServerClient
+    from awex_b200.transfer.transports import GlooReceiver, _collect_manifests, manifest_key
+
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    try:
+        meta = MetaServerClient("127.0.0.1", server.port)
+        meta.put_object(manifest_key(1), {"manifest": {0: [("w", (0,), (4,), "torch.float32", None, None)]}, "ready_pad": None})
+        started = time.time()
+        with pytest.raises(TimeoutError, match="p2p_manifest_2"):
+            _collect_manifests(meta, infer_world=1, train_world=2, my_rank=0, timeout=0.5)  # sender 2 is absent
+        assert time.time() - started < 10
+        receiver = GlooReceiver(meta, {"w": torch.zeros(4)}, 0, 1, 2, ["w"], wait_timeout_s=0.5)
+        assert receiver.group is None
+    finally:
+        server.stop()
+
+
+def test_missing_or_doubled_writes_are_refused_before_any_transfer():
+    from awex_b200.transfer.transports import CoverageError, _check_coverage
+
+    views = {"w": torch.zeros(8, 4)}
+    half = [("w", (0, 0), (4, 4), "torch.float32", None, None)]
+    with pytest.raises(CoverageError, match="never written"):
+        _check_coverage([half], views, ["w"], strict=True, who="rank 0")
+    both = half + [("w", (2, 0), (6, 4), "torch.float32", None, None)]
+    with pytest.raises(CoverageError, match="overlaps"):
+        _check_coverage([both], views, ["w"], strict=True, who="rank 0")
+    _check_coverage([half], views, ["w"], strict=False, who="rank 0")  # debug mode only logs
+
+
+# ------------------------------------------------------------------------------------------ a rank leaves between steps
+def _writer_that_leaves(meta_addr, q):
+    from awex_b200 import NCCLWeightsWriter
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticTrainEngine
+    from awex_b200.synthetic.topology import train_rank_infos
+
+    os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+    engine = SyntheticTrainEngine(get_arch("tiny-llama"), train_rank_infos()[0], meta_addr, dtype=torch.float32, device="cpu",
+                                  exchange_timeout_s=5)
+    writer = NCCLWeightsWriter(engine)
+    writer.initialize()
+    writer.write_weights(step_id=1)
+    q.put(("writer", "left after step 1"))
+    # leaves between steps, nothing in flight
+
+
+def _reader_that_stays(meta_addr, q):
+    from awex_b200 import WeightsReader
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticInferenceEngine
+    from awex_b200.synthetic.simulate import InferLayout
+    from awex_b200.synthetic.topology import infer_rank_infos
+
+    os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+    engine = SyntheticInferenceEngine(get_arch("tiny-llama"), InferLayout(tp=1), infer_rank_infos()[0], meta_addr, dtype=torch.float32,
+                                      device="cpu", debug_mode_config={"exchange_timeout_s": 5})
+    reader = WeightsReader(engine)
+    reader.initialize()
+    reader.update_weights(step_id=1)
+    ok_first = engine.mismatches(step=0) == []
+    started = time.time()
+    try:
+        reader.update_weights(step_id=2)  # nobody sends
+        q.put(("reader", ok_first, "no error", time.time() - started))
+    except Exception as exc:
+        q.put(("reader", ok_first, type(exc).__name__, time.time() - started))
+
+
+@pytest.mark.timeout(180)
+def test_reader_learns_that_the_sender_left_between_steps():
+    from awex_b200.meta.meta_server import MetaServer
+
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    addr = f"127.0.0.1:{server.port}"
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_reader_that_stays, args=(addr, q)), ctx.Process(target=_writer_that_leaves, args=(addr, q))]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in procs:
+        item = q.get(timeout=150)
+        got[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=30)
+    server.stop()
+    ok_first, outcome, seconds = got["reader"]
+    assert ok_first, "the first update must have landed"
+    assert outcome != "no error", "an update nobody sends must not be reported as done"
+    assert seconds < 60
