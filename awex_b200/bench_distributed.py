@@ -224,7 +224,7 @@ def run_distributed(args):
 
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    with ClockSampler([local_rank]) as clocks:
+    with ClockSampler([local_rank], period_ms=50) as clocks:
         for i in range(args.steps):
             barrier()
             starts[i].record()

@@ -211,7 +211,7 @@ def run_reference(args):
     total = args.warmup + args.steps
     for s in range(1, total + 1):
         if s == args.warmup + 1 and rank == 0:
-            sampler = ClockSampler([local_rank])
+            sampler = ClockSampler([local_rank], period_ms=50)
             sampler.__enter__()
         _store_barrier(store, f"step{s}", world)
         torch.cuda.synchronize()

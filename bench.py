@@ -34,8 +34,8 @@ PUBLISHED_10B_SECONDS = 0.8  # the reference's published NCCL-mode time for a 10
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="separated", choices=["separated", "colocated", "moe", "fp8"],
                     help="separated: Llama-3-8B, training and inference on disjoint GPUs; colocated: Qwen2.5-32B TP n -> TP n on the same GPUs; "
