@@ -238,7 +238,7 @@ class PeerStoreSender:
             elif tuple(book.owner) != me:
                 remote.append(d)
         src_addrs = {key: TensorAddr.of(t) for key, t in self.local.items()}
-        table, n_tiles, enc = encode_items(self.items, src_addrs, dst_addrs)
+        table, n_tiles, enc = encode_items(self._ordered_items(), src_addrs, dst_addrs)
         if self.validate:
             dst_spans = [a.byte_span() for book in dst_addrs.values() for n, a in book.items() if n != DONE_PAD]
             problems = validate_table(table, n_tiles, [a.byte_span() for a in src_addrs.values()], dst_spans, check_overlap=False)
@@ -260,6 +260,18 @@ class PeerStoreSender:
             f"training rank {self.train_rank}: {len(self.items)} items -> {self.n_desc} descriptors, {n_tiles} tiles, "
             f"{self.bytes_out} bytes to ranks {self.destinations}"
         )
+
+    def _ordered_items(self) -> List[CopyItem]:
+        """Items arrive grouped by destination in ascending rank order.  With
+        ``AWEX_XFER_DEST_ROTATE=1`` every sender starts its walk at a different
+        destination (rotation by its own rank), so that senders which work on one
+        destination at a time (round-robin chunks) take turns at each receiver
+        instead of meeting there.  Experimental: off by default."""
+        if os.environ.get("AWEX_XFER_DEST_ROTATE", "0") != "1" or len(self.destinations) < 2:
+            return self.items
+        shift = self.train_rank % len(self.destinations)
+        order = {d: (i - shift) % len(self.destinations) for i, d in enumerate(self.destinations)}
+        return sorted(self.items, key=lambda it: order[it.dst_rank])  # stable: keeps the order inside a destination
 
     @staticmethod
     def _interleave(remote) -> bool:
