@@ -57,6 +57,25 @@ def compute_two_phase_partition(rank: int, stage_idx: int, world_size: int) -> i
     return position % 2
 
 
+def recursive_partition_rounds(rank: int, world: int):
+    """Rounds of the recursive-partition ("butterfly") schedule of the reference's
+    stream-batch transport (`awex/transfer/nccl_stream_batch.py:261-357`): in
+    round k the ranks are cut into partitions of ``world / 2^k``; a rank talks
+    to ALL ranks in the other half of its partition, the first half sending
+    first.  After ``log2(world)`` rounds every pair has met exactly once.
+    Yields ``(peers, send_first)``; ``world`` must be a power of two."""
+    if world < 1 or world & (world - 1):
+        raise ValueError(f"the recursive-partition schedule needs a power-of-two world, got {world}")
+    size = world
+    while size >= 2:
+        half = size // 2
+        base = (rank // size) * size
+        first = rank - base < half
+        other = range(base + half, base + size) if first else range(base, base + half)
+        yield list(other), first
+        size = half
+
+
 def interleave_by_peer(ops: Sequence, peer_of: Callable = lambda op: op.peer) -> list:
     """Round-robin over peers so that consecutive operations target different
     links."""
@@ -178,7 +197,8 @@ class NcclColocateTransport:
         self.device = torch.device(device)
 
     def update_weights_in_colocate_mode(self, train_to_infer: Dict[int, int], infer_to_train: Dict[int, int], items, local,
-                                        views, incoming: Dict[int, Sequence[tuple]], use_group: bool = True) -> Dict[str, float]:
+                                        views, incoming: Dict[int, Sequence[tuple]], use_group: bool = True,
+                                        schedule: str = "ring") -> Dict[str, float]:
         from awex_b200.transfer.cpu_exec import entry_nbytes, execute_items, pack_message, unpack_message
 
         validate_rank_mappings(train_to_infer, infer_to_train)
@@ -188,6 +208,10 @@ class NcclColocateTransport:
             by_dst.setdefault(it.dst_rank, []).append(it)
         started = time.time()
         moved = 0
+        if schedule == "recursive":
+            return self._recursive(by_dst, local, views, incoming, started)
+        if schedule != "ring":
+            raise ValueError(f"unknown schedule {schedule!r}")
         for stage in range(world):
             to, frm = ring_peers(me, stage, world)
             if stage == 0:
@@ -209,5 +233,32 @@ class NcclColocateTransport:
             else:
                 two_phase_send_recv(me, stage, world, sends, recvs, group=self.group, what=f"colocate stage {stage}")
             if buf is not None:
+                unpack_message(entries, buf, views)
+        return {"seconds": time.time() - started, "bytes": float(moved)}
+
+    def _recursive(self, by_dst, local, views, incoming, started) -> Dict[str, float]:
+        """log2(world) rounds of two phases; in each phase all messages of one
+        direction between the two halves are in flight together."""
+        from awex_b200.transfer.cpu_exec import entry_nbytes, execute_items, pack_message, unpack_message
+
+        me = self.transfer_rank
+        moved = execute_items(by_dst[me], local, {me: views}) if me in by_dst else 0
+        for round_idx, (peers, send_first) in enumerate(recursive_partition_rounds(me, self.world_size)):
+            sends = []
+            for peer in peers:
+                if peer in by_dst:
+                    msg = pack_message(by_dst[peer], local).to(self.device)
+                    sends.append(P2PRequest(True, msg, peer, f"round{round_idx}->{peer}"))
+                    moved += msg.numel()
+            recvs, landing = [], []
+            for peer in peers:
+                entries = incoming.get(peer)
+                if entries:
+                    buf = torch.empty(sum(entry_nbytes(e) for e in entries), dtype=torch.uint8, device=self.device)
+                    recvs.append(P2PRequest(False, buf, peer, f"round{round_idx}<-{peer}"))
+                    landing.append((entries, buf))
+            for phase_reqs in ((sends, recvs) if send_first else (recvs, sends)):
+                batch_send_recv(phase_reqs, group=self.group, what=f"recursive round {round_idx}")
+            for entries, buf in landing:
                 unpack_message(entries, buf, views)
         return {"seconds": time.time() - started, "bytes": float(moved)}

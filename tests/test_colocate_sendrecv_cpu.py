@@ -10,7 +10,7 @@ import torch.multiprocessing as mp
 WORLD = 4
 
 
-def _rank_main(rank, port, use_group, result_q):
+def _rank_main(rank, port, use_group, schedule, result_q):
     import torch.distributed as dist
 
     from awex_b200.synthetic.arch import get_arch
@@ -27,7 +27,7 @@ def _rank_main(rank, port, use_group, result_q):
     incoming = {src: manifest_by_destination(items).get(rank, []) for src, items in programs.items()}
     identity = {r: r for r in range(WORLD)}
     transport = NcclColocateTransport(rank, WORLD)
-    stats = transport.update_weights_in_colocate_mode(identity, identity, programs[rank], local, views, incoming, use_group=use_group)
+    stats = transport.update_weights_in_colocate_mode(identity, identity, programs[rank], local, views, incoming, use_group=use_group, schedule=schedule)
     mine = f"engine{rank // 2}/rank{rank % 2}/"
     bad = [m for m in job.mismatches() if m.startswith(mine)]
     result_q.put((rank, bad, stats["bytes"]))
@@ -36,14 +36,14 @@ def _rank_main(rank, port, use_group, result_q):
 
 
 @pytest.mark.timeout(300)
-@pytest.mark.parametrize("use_group", [True, False])
-def test_ring_staged_colocated_exchange(use_group):
+@pytest.mark.parametrize("use_group,schedule", [(True, "ring"), (False, "ring"), (True, "recursive")])
+def test_staged_colocated_exchange(use_group, schedule):
     from awex_b200.utils.common import get_free_port
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = get_free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, port, use_group, q)) for r in range(WORLD)]
+    procs = [ctx.Process(target=_rank_main, args=(r, port, use_group, schedule, q)) for r in range(WORLD)]
     for p in procs:
         p.start()
     results = [q.get(timeout=240) for _ in procs]
@@ -54,3 +54,20 @@ def test_ring_staged_colocated_exchange(use_group):
     for rank, bad, moved in results:
         assert not bad, (rank, bad[:5])
         assert moved > 0
+
+
+def test_recursive_partition_schedule_meets_every_pair_once():
+    from awex_b200.transfer.nccl_comm import recursive_partition_rounds
+
+    for world in (2, 4, 8, 16):
+        met = {r: [] for r in range(world)}
+        for r in range(world):
+            for peers, send_first in recursive_partition_rounds(r, world):
+                met[r].extend(peers)
+                for p in peers:  # the two sides of a pair agree on who sends first
+                    theirs = [sf for ps, sf in recursive_partition_rounds(p, world) if r in ps]
+                    assert theirs == [not send_first]
+        for r in range(world):
+            assert sorted(met[r]) == [p for p in range(world) if p != r]
+    with pytest.raises(ValueError):
+        list(recursive_partition_rounds(0, 6))
