@@ -262,3 +262,4 @@ class NcclColocateTransport:
             for entries, buf in landing:
                 unpack_message(entries, buf, views)
         return {"seconds": time.time() - started, "bytes": float(moved)}
+
