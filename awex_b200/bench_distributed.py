@@ -212,7 +212,7 @@ def run_distributed(args):
     def check_status():
         torch.cuda.synchronize()
         if writer is not None:
-            writer.transport.program.status.raise_if_failed()
+            writer.transport.program.check()
         if reader is not None:
             infer_engine.schedulers[0].awes_weights_reader.transport.waiter.status.raise_if_failed()
 

@@ -197,6 +197,17 @@ class TransferProgram:
             table["tensor_map"][i] = base + 128 * slot
         return table
 
+    def check(self) -> None:
+        """Raise :class:`TransferError` if the last launches reported a failure.
+        A failed launch may have counted only some of its CTAs in, so the arrival
+        counter is cleared together with the status: the program can be launched
+        again (a retried update writes the same bytes to the same addresses)."""
+        try:
+            self.status.raise_if_failed()
+        except TransferError:
+            self.counter.zero_()
+            raise
+
     def launch(self, epoch: int, stream_ptr: Optional[int] = None) -> None:
         stream = native.current_stream_ptr() if stream_ptr is None else stream_ptr
         code = self.lib.awex_launch_fused_transfer(

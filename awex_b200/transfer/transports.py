@@ -292,7 +292,7 @@ class PeerStoreSender:
         self.program.launch(epoch)
         if synchronize or self.host_destinations:
             torch.cuda.current_stream(self.device).synchronize()
-            self.program.status.raise_if_failed()
+            self.program.check()
         if self.host_destinations:
             self.meta.put_object(host_done_key(self.transfer_rank, epoch), 1)
             if self._last_host_epoch is not None and self._last_host_epoch != epoch:
