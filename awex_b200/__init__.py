@@ -4,7 +4,7 @@ Public names match the reference package (`awex/__init__.py:18-28`); they are
 resolved lazily so that importing the package does not pull in CUDA code.
 """
 
-__version__ = "0.1.0"
+from awex_b200.version import __version__  # noqa: F401
 
 _LAZY = {
     "InferenceConfig": ("awex_b200.config", "InferenceConfig"),
