@@ -71,6 +71,17 @@ class WorkerWeightsReader:
         # together with their weights
         self.required_names = [n for n in self.parameters if n in train_names]
         self.device = next(iter(self.parameters.values())).device if self.parameters else torch.device("cpu")
+        self._published_ptrs = self._model_ptrs()
+
+    def _model_ptrs(self) -> Dict[str, int]:
+        """Address of every parameter of the model as it is now.  The canonical
+        views keep the storages alive that they were cut from, so only the model
+        itself shows whether the engine has re-allocated or re-mapped its weights."""
+        return {name: p.data_ptr() for name, p in self.model.named_parameters()}
+
+    def parameters_moved(self) -> List[str]:
+        now = self._model_ptrs()
+        return [n for n, ptr in self._published_ptrs.items() if now.get(n) != ptr] + [n for n in now if n not in self._published_ptrs]
 
     # ---- update -----------------------------------------------------------------------------------
     def begin_update(self, step_id) -> None:
@@ -151,10 +162,11 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
 
     def begin_update(self, step_id) -> None:
         self.epoch += 1
-        if self.transport.republish_if_moved():
+        moved = self.parameters_moved()
+        if moved:
             raise RuntimeError(
-                "inference parameters moved since they were published; senders hold stale addresses "
-                "(re-create the writer and reader after the engine re-maps its weights)"
+                f"{len(moved)} inference parameters (e.g. {moved[:3]}) moved since they were published; senders hold "
+                "stale addresses (re-create the writer and reader after the engine re-maps its weights)"
             )
         with phase("announce_ready"):
             self.transport.begin(self.epoch)

@@ -127,3 +127,26 @@ def test_reader_learns_that_the_sender_left_between_steps():
     assert ok_first, "the first update must have landed"
     assert outcome != "no error", "an update nobody sends must not be reported as done"
     assert seconds < 60
+
+
+def test_reader_notices_reallocated_parameters():
+    """An engine that replaces a parameter's storage after publishing would be
+    written through stale addresses: the worker reader refuses the update."""
+    from awex_b200.config import InferenceConfig
+    from awex_b200.reader.nccl_reader import WorkerWeightsReader
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.models import build_vllm_model, vllm_model_context
+    from awex_b200.synthetic.topology import infer_rank_infos
+
+    arch, ri = get_arch("tiny-llama"), infer_rank_infos(tp=1)[0]
+    model = build_vllm_model(arch, ri, torch.float32, "cpu")
+    cfg = InferenceConfig(tp_size=1, pp_size=1, dp_size=1, ep_size=1)
+    fake_meta = [type("M", (), {"name": n, "shards": [type("S", (), {"world_size": 1})()]})() for n in ("model.norm.weight",)]
+    reader = WorkerWeightsReader(model, vllm_model_context(ri, infer_engine_config=cfg),
+                                 {"engine_name": "vllm", "infer_engine_config": cfg, "infer_world_size": 1}, [], fake_meta,
+                                 engine_rank=0, num_engines=1, meta_server_addr="127.0.0.1:1")
+    reader.initialize()
+    assert reader.parameters_moved() == []
+    name, old = next(iter(model.named_parameters()))
+    model._tensors[name] = old.clone()  # what a reload or a re-mapping allocator does
+    assert reader.parameters_moved() == [name]
