@@ -263,3 +263,82 @@ class NcclColocateTransport:
                 unpack_message(entries, buf, views)
         return {"seconds": time.time() - started, "bytes": float(moved)}
 
+
+
+# ------------------------------------------------------------------------------------ per-operation send / recv
+def clone_p2p_send_tensor(tensor: torch.Tensor) -> torch.Tensor:
+    """A dense copy fit for a point-to-point send (the source may change after
+    the call returns)."""
+    return tensor.clone(memory_format=torch.contiguous_format)
+
+
+class RecvStaging:
+    """Point-to-point receives need dense buffers; views that are not dense get a
+    staging buffer and are filled when :meth:`finish` copies back
+    (`awex/transfer/nccl_stream_batch.py:44-66` in the reference)."""
+
+    def __init__(self):
+        self.pairs: list = []
+
+    def prepare(self, view: torch.Tensor) -> torch.Tensor:
+        if view.is_contiguous():
+            return view
+        buffer = torch.empty(tuple(view.shape), dtype=view.dtype, device=view.device)
+        self.pairs.append((view, buffer))
+        return buffer
+
+    @torch.no_grad()
+    def finish(self) -> int:
+        n = len(self.pairs)
+        for view, buffer in self.pairs:
+            view.copy_(buffer)
+        self.pairs.clear()
+        return n
+
+
+def _round_robin(per_peer: Dict[int, list]) -> list:
+    out, depth = [], max((len(v) for v in per_peer.values()), default=0)
+    for i in range(depth):
+        out.extend(per_peer[p][i] for p in sorted(per_peer) if i < len(per_peer[p]))
+    return out
+
+
+def build_send_requests(plan, tensors: Dict[str, torch.Tensor], slice_context: Optional[dict] = None) -> list:
+    """One send per planned operation, from materialised canonical tensors, in
+    round-robin order over the peers: the data path of the reference
+    (`awex/transfer/nccl_comm.py:378-445`), kept as the in-repo baseline and for
+    links the fused kernel cannot reach.  Strided slices are made dense once per
+    (name, slice) through ``slice_context``."""
+    from awex_b200.transfer.transfer_plan import slice_tensor
+
+    cache = {} if slice_context is None else slice_context
+    per_peer: Dict[int, list] = {}
+    for peer, ops in plan.operations.items():
+        for op in ops:
+            piece = slice_tensor(tensors[op.send_shard_meta.name], op, True, slice_context=cache)
+            per_peer.setdefault(peer, []).append(P2PRequest(True, piece, peer, op.send_shard_meta.name))
+    return _round_robin(per_peer)
+
+
+def build_recv_requests(plan, tensors: Dict[str, torch.Tensor], staging: RecvStaging) -> list:
+    """The receiving mirror of :func:`build_send_requests` (`nccl_comm.py:448-488`):
+    the same operations in the same order, into views of the live parameters or
+    staging buffers for strided views."""
+    from awex_b200.transfer.transfer_plan import slice_tensor
+
+    per_peer: Dict[int, list] = {}
+    for peer, ops in plan.operations.items():
+        for op in ops:
+            view = slice_tensor(tensors[op.recv_shard_meta.name], op, False)
+            per_peer.setdefault(peer, []).append(P2PRequest(False, staging.prepare(view), peer, op.recv_shard_meta.name))
+    return _round_robin(per_peer)
+
+
+def execute_p2p_requests(requests: Sequence[P2PRequest], stage: str, group=None, use_group: bool = True,
+                         watchdog_s: Optional[float] = 30.0) -> float:
+    """Run the requests and return the seconds it took (`nccl_comm.py:333-375`)."""
+    started = time.time()
+    batch_send_recv(requests, group=group, use_group=use_group, watchdog_s=watchdog_s, what=stage)
+    took = time.time() - started
+    logger.info(f"Finished executing {len(requests)} p2p operations for {stage}, took {took:.4f} seconds")
+    return took
