@@ -382,3 +382,13 @@ def test_handle_counts():
     counts = get_handle_counts()
     assert counts["open_fds"] > 0 and counts["soft_limit"] <= counts["hard_limit"] or counts["hard_limit"] == -1
     assert counts["total_ipc"] == counts["sysv_ipc"] + counts["posix_ipc"]
+
+
+def test_server_wrapper_separates_its_own_flags():
+    from awex_b200.awex_vllm_server import split_own_arguments
+
+    rest, own = split_own_arguments(["--model", "m", "--awex-comm-backend", "nccl", "--tp", "2", "--awex-meta-server-addr=10.0.0.1:80"])
+    assert rest == ["--model", "m", "--tp", "2"]
+    assert own == {"AWEX_COMM_BACKEND": "nccl", "AWEX_META_SERVER_ADDR": "10.0.0.1:80"}
+    with pytest.raises(SystemExit):
+        split_own_arguments(["--awex-comm-backend"])
