@@ -82,6 +82,48 @@ def _sum_over_ranks(value: float, group=None) -> float:
     return float(t.item())
 
 
+NVLINK_GBPS = 770.0  # measured peer copy per direction per GPU on this kind of box
+HBM_FALLBACK_GBPS = 6650.0
+
+
+def _measured_hbm_gbps() -> float:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except Exception:
+        return HBM_FALLBACK_GBPS
+
+
+def _roofline(writer, reader, infer_engine, measured_ms: float, ctl) -> dict:
+    """Lower bound of one update from the bytes each GPU must move: what leaves
+    it over NVLink, what arrives over NVLink, and what it reads and writes in its
+    own memory, each at the measured peak; the slowest GPU and resource set the
+    bound.  (Quantisation arithmetic is far below its peak and never the bound.)
+    Every rank takes part in the three reductions, whatever its own numbers are."""
+    hbm = _measured_hbm_gbps()
+    egress = read = local_written = ingress = 0.0
+    try:
+        if writer is not None:
+            egress = float(getattr(writer.transport, "bytes_remote", 0))
+            read = float(getattr(writer.transport, "bytes_in", 0))
+            local_written = float(getattr(writer.transport, "bytes_local", 0))
+        if reader is not None:
+            ingress = float(getattr(infer_engine.schedulers[0].awes_weights_reader.transport, "bytes_in_remote", 0))
+    except Exception:
+        pass
+    bounds = {
+        "nvlink_egress": egress / (NVLINK_GBPS * 1e9) * 1e3,
+        "nvlink_ingress": ingress / (NVLINK_GBPS * 1e9) * 1e3,
+        "hbm": (read + local_written + ingress) / (hbm * 1e9) * 1e3,  # source reads + writes that land in this GPU's memory
+    }
+    worst = {k: _max_over_ranks(bounds[k], ctl) for k in ("nvlink_egress", "nvlink_ingress", "hbm")}
+    bound = max(worst, key=worst.get)
+    return {"ms": worst[bound], "bound": bound, "per_resource_ms": worst,
+            "fraction_of_roofline": (worst[bound] / measured_ms) if measured_ms else None,
+            "peaks": {"hbm_GBps_measured": hbm, "nvlink_GBps_measured": NVLINK_GBPS}}
+
+
 def run_distributed(args):
     from awex_b200 import NCCLWeightsWriter, WeightsReader, logging
     from awex_b200.meta.meta_server import MetaServer
@@ -276,10 +318,12 @@ def run_distributed(args):
         valid = infer_engine.mismatches(step=0) == []
     valid = _max_over_ranks(0.0 if valid else 1.0, ctl) == 0.0
     bytes_out = _sum_over_ranks(float(writer.transport.bytes_out) if writer is not None else 0.0, ctl)
-    egress = _max_over_ranks(float(writer.transport.bytes_out) if writer is not None else 0.0, ctl)
+    # the busiest sender's bytes that cross NVLink (destinations on its own GPU do not)
+    egress = _max_over_ranks(float(getattr(writer.transport, "bytes_remote", writer.transport.bytes_out)) if writer is not None else 0.0, ctl)
     n_desc = _sum_over_ranks(float(writer.transport.n_desc) if writer is not None else 0.0, ctl)
     launches = (1 if writer is not None else 0) + (infer_engine.schedulers[0].awes_weights_reader.transport.gpu_launches_per_update() if reader is not None else 0)
     launches_total = _sum_over_ranks(float(launches), ctl)
+    roofline = _roofline(writer, reader, infer_engine, ms, ctl)
     clock_summary = clocks.summary()
     d2h = int(_max_over_ranks(float((verdict_host.numel() * 8 + 16) if plan is not None else 16), ctl))
     seconds = ms / 1e3
@@ -304,6 +348,7 @@ def run_distributed(args):
             "aggregate_GBps": bytes_out / seconds / 1e9,
             "nvlink_GBps_per_gpu": (egress / seconds / 1e9) if remote else 0.0,
             "nvlink_fraction_of_770GBps": (egress / seconds / 1e9 / 770.0) if remote else None,
+            "roofline": roofline,
             "clocks": clock_summary,
             "e2e": {"value": e2e / 1e3, "unit": "s", "h2d_bytes_per_step": ctrl_host.numel() * 8, "d2h_bytes_per_step": d2h,
                     "what": "blocking write_weights/update_weights + control record H2D + checksums of all inference parameters + verdict D2H, max over ranks"},

@@ -164,6 +164,9 @@ class PeerStoreReceiver:
         self.poster = FlagPoster(ready_addrs, self.device)
         self.waiter = FlagWaiter(self.done_pad, device_senders, self.device, timeout_ms=self.timeout_ms)
         self.bytes_in = sum(entry_nbytes(e) for es in entries for e in es)
+        on_this_gpu = {r for r in self.senders if "owner" in records[r] and
+                       (tuple(records[r]["owner"]) == tuple(me) or r in self.host_senders)}
+        self.bytes_in_remote = sum(entry_nbytes(e) for r, es in zip(self.senders, entries) if r not in on_this_gpu for e in es)
         logger.info(f"inference rank {self.rank}: {len(self.senders)} senders {self.senders}, {self.bytes_in} bytes per update")
 
     def begin(self, epoch: int) -> None:
@@ -256,6 +259,9 @@ class PeerStoreSender:
             timeout_ms=self.timeout_ms, grid=self.grid, encoder=enc, interleave=self._interleave(remote),
         )
         self.bytes_out, self.bytes_in, self.n_desc = enc.bytes_out, enc.bytes_in, int(table.shape[0])
+        # bytes that cross NVLink (destinations on other GPUs) and bytes that stay in this GPU's memory
+        self.bytes_remote = sum(entry_nbytes(e) for d in remote for e in self.manifest[d])
+        self.bytes_local = self.bytes_out - self.bytes_remote
         logger.info(
             f"training rank {self.train_rank}: {len(self.items)} items -> {self.n_desc} descriptors, {n_tiles} tiles, "
             f"{self.bytes_out} bytes to ranks {self.destinations}"
