@@ -274,3 +274,22 @@ def test_environment_table(monkeypatch):
                 with open(os.path.join(folder, name)) as f:
                     used |= set(re.findall(r'''environ(?:\.get)?[(\[]\s*["'](AWEX_[A-Z0-9_]+)''', f.read()))
     assert used and used - set(env.KNOBS) - {"AWEX_BENCH_VERBOSE"} == set(), used - set(env.KNOBS)
+
+
+def test_bench_roofline_arithmetic():
+    from awex_b200 import bench_distributed as bd
+
+    writer = SimpleNamespace(transport=SimpleNamespace(bytes_remote=7.7e9, bytes_in=8.0e9, bytes_local=0.3e9, bytes_out=8.0e9))
+    worker = SimpleNamespace(transport=SimpleNamespace(bytes_in_remote=3.85e9))
+    engine = SimpleNamespace(schedulers=[SimpleNamespace(awes_weights_reader=worker)])
+    r = bd._roofline(writer, object(), engine, measured_ms=12.5, ctl=None)
+    assert r["bound"] == "nvlink_egress" and abs(r["ms"] - 10.0) < 1e-6 and abs(r["fraction_of_roofline"] - 0.8) < 1e-6
+    assert abs(r["per_resource_ms"]["nvlink_ingress"] - 5.0) < 1e-6
+    local = bd._roofline(SimpleNamespace(transport=SimpleNamespace(bytes_remote=0, bytes_in=8e9, bytes_local=8e9)), None, None, 5.0, None)
+    assert local["bound"] == "hbm" and 2.0 < local["ms"] < 3.0
+    bare = bd._roofline(SimpleNamespace(transport=object()), None, None, 1.0, None)  # a transport without byte accounting
+    assert bare["ms"] == 0.0
+    layouts = {cfg: bd.role_table(8, cfg)[4] for cfg in ("separated", "colocated", "moe", "fp8")}
+    assert layouts == {"separated": "tp4->2xtp2", "colocated": "colocated-tp8->tp8", "moe": "colocated-ep8->2xtp4ep4", "fp8": "colocated-ep8->tp8-fp8"}
+    with pytest.raises(SystemExit):
+        bd.role_table(3)
