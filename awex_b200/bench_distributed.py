@@ -82,6 +82,21 @@ def _sum_over_ranks(value: float, group=None) -> float:
     return float(t.item())
 
 
+class _HostChecksums:
+    """CPU stand-in of ChecksumPlan for the functional check."""
+
+    def __init__(self, tensors):
+        self.tensors, self.n = list(tensors), len(tensors)
+
+    def launch(self):
+        from awex_b200.ops.checksum import checksum_reference
+
+        sums = [checksum_reference(t) for t in self.tensors]
+        out = torch.zeros(2, self.n, dtype=torch.int64)
+        out[0] = torch.tensor([s - (1 << 64) if s >= (1 << 63) else s for s in sums], dtype=torch.int64)
+        return out
+
+
 NVLINK_GBPS = 770.0  # measured peer copy per direction per GPU on this kind of box
 HBM_FALLBACK_GBPS = 6650.0
 
@@ -139,11 +154,26 @@ def run_distributed(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=device)
+    # "--device cpu" runs the same flow over gloo on CPU tensors: a functional check of
+    # this harness and of the public API, not a measurement
+    cpu = getattr(args, "device", "cuda") == "cpu"
+    if cpu and (world == 1 or getattr(args, "config", "separated") != "separated"):
+        raise SystemExit("--device cpu runs the separated layouts with 2, 4 or 8 processes: the message transport blocks a "
+                         "process that plays both roles")
+    if cpu:
+        os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        device = torch.device("cpu")
+        sync = lambda: None  # noqa: E731
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    else:
+        torch.cuda.set_device(local_rank)
+        device = torch.device("cuda", local_rank)
+        sync = torch.cuda.synchronize
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=device)
     ctl = dist.new_group(list(range(world)), backend="gloo") if world > 1 else None  # host-side control traffic
 
     config = getattr(args, "config", "separated")
@@ -205,7 +235,8 @@ def run_distributed(args):
     def _guard(fn):
         def run():
             try:
-                torch.cuda.set_device(device)  # the current device is per thread
+                if not cpu:
+                    torch.cuda.set_device(device)  # the current device is per thread
                 fn()
             except BaseException as exc:
                 # The other role (and the other ranks) block on what this role was
@@ -230,7 +261,7 @@ def run_distributed(args):
         t.join()
     if errors:
         raise errors[0]
-    torch.cuda.synchronize()
+    sync()
     setup_s = time.time() - t_setup
     note("metadata exchanged, plans compiled, peers mapped")
 
@@ -252,7 +283,9 @@ def run_distributed(args):
             reader.finish_update(s, synchronize=False)
 
     def check_status():
-        torch.cuda.synchronize()
+        sync()
+        if cpu:
+            return  # the message transport raises on the host
         if writer is not None:
             writer.transport.program.check()
         if reader is not None:
@@ -264,31 +297,46 @@ def run_distributed(args):
     check_status()
     note("warm-up done")
 
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    with ClockSampler([local_rank], period_ms=50) as clocks:
+    if cpu:
+        clocks = None
+        local_ms = []
         for i in range(args.steps):
             barrier()
-            starts[i].record()
+            t0 = time.perf_counter()
             step_async()
-            stops[i].record()
-        torch.cuda.synchronize()
+            local_ms.append((time.perf_counter() - t0) * 1e3)
+    else:
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        with ClockSampler([local_rank], period_ms=50) as clocks:
+            for i in range(args.steps):
+                barrier()
+                starts[i].record()
+                step_async()
+                stops[i].record()
+            torch.cuda.synchronize()
+        local_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
     check_status()
-    per_step_ms = [_max_over_ranks(s.elapsed_time(e)) if world > 1 else s.elapsed_time(e) for s, e in zip(starts, stops)]
+    per_step_ms = [_max_over_ranks(v, ctl) if world > 1 else v for v in local_ms]
     ms = sum(per_step_ms) / len(per_step_ms)
 
     # ---- end to end through the blocking public API ------------------------------------------------
     plan = None
     if reader is not None:
         worker = infer_engine.schedulers[0].awes_weights_reader
-        plan = ChecksumPlan([worker.parameters[n] for n in sorted(worker.required_names)], device)
-        verdict_host = torch.zeros(2, plan.n, dtype=torch.int64).pin_memory()
-    ctrl_host = torch.zeros(8, dtype=torch.int64).pin_memory()
+        verdict_tensors = [worker.parameters[n] for n in sorted(worker.required_names)]
+        plan = _HostChecksums(verdict_tensors) if cpu else ChecksumPlan(verdict_tensors, device)
+        verdict_host = torch.zeros(2, plan.n, dtype=torch.int64)
+    ctrl_host = torch.zeros(8, dtype=torch.int64)
+    if not cpu:
+        ctrl_host = ctrl_host.pin_memory()
+        if plan is not None:
+            verdict_host = verdict_host.pin_memory()
     ctrl_dev = torch.zeros(8, dtype=torch.int64, device=device)
     e2e_ms = []
     for i in range(args.warmup + args.steps):
         barrier()
-        torch.cuda.synchronize()
+        sync()
         t0 = time.perf_counter()
         step_no[0] += 1
         s = step_no[0]
@@ -304,7 +352,7 @@ def run_distributed(args):
             reader.update_weights(step_id=s)
         if plan is not None:
             verdict_host.copy_(plan.launch(), non_blocking=True)
-        torch.cuda.synchronize()
+        sync()
         dt = (time.perf_counter() - t0) * 1e3
         dt = _max_over_ranks(dt, ctl)
         if i >= args.warmup:
@@ -320,11 +368,11 @@ def run_distributed(args):
     bytes_out = _sum_over_ranks(float(writer.transport.bytes_out) if writer is not None else 0.0, ctl)
     # the busiest sender's bytes that cross NVLink (destinations on its own GPU do not)
     egress = _max_over_ranks(float(getattr(writer.transport, "bytes_remote", writer.transport.bytes_out)) if writer is not None else 0.0, ctl)
-    n_desc = _sum_over_ranks(float(writer.transport.n_desc) if writer is not None else 0.0, ctl)
+    n_desc = _sum_over_ranks(float(getattr(writer.transport, "n_desc", 0)) if writer is not None else 0.0, ctl)
     launches = (1 if writer is not None else 0) + (infer_engine.schedulers[0].awes_weights_reader.transport.gpu_launches_per_update() if reader is not None else 0)
     launches_total = _sum_over_ranks(float(launches), ctl)
     roofline = _roofline(writer, reader, infer_engine, ms, ctl)
-    clock_summary = clocks.summary()
+    clock_summary = clocks.summary() if clocks is not None else {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["cpu run"], "samples": 0}
     d2h = int(_max_over_ranks(float((verdict_host.numel() * 8 + 16) if plan is not None else 16), ctl))
     seconds = ms / 1e3
     if rank == 0:
@@ -336,6 +384,7 @@ def run_distributed(args):
             "metric": "weight_sync_seconds_per_update", "value": seconds, "unit": "s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": seconds / PUBLISHED_10B_SECONDS, "dtype": "bf16",
+            "device": "cpu (functional check, not a measurement)" if cpu else "cuda",
             "data": "synthetic random-init N(0,0.02) weights from per-name seeds", "impl": "ours",
             "config": {
                 "model": arch.name, "params": arch.param_count(), "bytes_per_update": int(bytes_out), "parallelism": label,

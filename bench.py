@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model to this many layers (result is then not a valid benchmark)")
     ap.add_argument("--no-validate", action="store_true")
     ap.add_argument("--grid", type=int, default=0)
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu: run the same flow over gloo on CPU tensors (a functional check of the harness; use a tiny --model)")
     ap.add_argument("--emulate", action="store_true", help="debug: run all ranks of the layout as launches on one GPU, without the writer/reader API")
     return ap.parse_args()
 
