@@ -124,3 +124,21 @@ def test_canonical_names_exist_in_the_checkpoint(job, tmp_path):
     assert report["ok"] and report["checked"] == len(names), report["missing"][:3]
     assert not verify_names(names + ["model.layers.0.mlp.ghost.weight"], checkpoint_weight_map(str(tmp_path)))["ok"]
     assert checkpoint_equivalents("model.layers.3.mlp.gate_up_proj.weight") == ["model.layers.3.mlp.gate_proj.weight", "model.layers.3.mlp.up_proj.weight"]
+
+
+def test_plan_study_reports_bytes_and_bounds():
+    from awex_b200.debug.plan_study import main, parse_layout, study
+
+    assert parse_layout("tp1,dp4,ep4") == {"tp": 1, "dp": 4, "ep": 4} and parse_layout("tp2,engines2") == {"tp": 2, "engines": 2}
+    with pytest.raises(SystemExit):
+        parse_layout("tp")
+    spread = study("tiny-qwen3-moe", {"tp": 1, "dp": 4, "ep": 4}, {"tp": 2, "ep": 2, "engines": 2}, placement="colocated")
+    rr = study("tiny-qwen3-moe", {"tp": 1, "dp": 4, "ep": 4}, {"tp": 2, "ep": 2, "engines": 2}, placement="colocated", pairing="round_robin")
+    assert spread["coverage_problems"] == [] and len(spread["senders"]) == 4
+    total = lambda rep: sum(x["remote_egress"] + x["local_written"] for x in rep["senders"])  # noqa: E731
+    assert total(spread) == total(rr)  # the same bytes, differently shared
+    assert max(x["read"] for x in spread["senders"]) < max(x["read"] for x in rr["senders"])
+    separated = study("tiny-qwen3-moe", {"tp": 1, "dp": 4, "ep": 4}, {"tp": 2, "ep": 2, "engines": 2}, placement="separated")
+    assert all(x["local_written"] == 0 for x in separated["senders"]) and separated["lower_bound_ms"] > 0
+    assert sum(separated["ingress_per_inference_rank"]) == total(separated)
+    assert main(["--model", "tiny-llama", "--train", "tp2", "--infer", "tp1", "--placement", "separated"]) == 0
