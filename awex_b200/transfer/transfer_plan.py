@@ -149,7 +149,7 @@ class TransferPlanBuilder:
         if replica_pairing not in ("round_robin", "spread"):
             raise ValueError(f"unknown replica_pairing {replica_pairing!r}")
         self.replica_pairing = replica_pairing
-        self._replica_load: Dict[int, List[int]] = {}
+        self._replica_choice: Dict[Tuple[str, int], int] = {}
         if num_infer_engines <= 0:
             raise ValueError("num_infer_engines must be positive")
         self.train_world_size = train_world_size
@@ -314,21 +314,37 @@ class TransferPlanBuilder:
 
     def _pick_train_replica(self, i: int, training_meta: ParameterMeta) -> int:
         """Index of the training replica that feeds inference replica ``i``.
-        ``spread`` gives each inference replica the training replica that has
-        been handed the fewest bytes so far (ties: lowest index), so parameters
-        replicated over many data-parallel ranks are served by all of them; the
-        choice depends only on the metadata and the sorted parameter order, hence
-        every rank computes the same one."""
+        ``spread`` looks the answer up in the table made by
+        :meth:`_assign_replicas`; a parameter the table does not know (a direct
+        call before any plan was built) falls back to the reference's modulo."""
         n = len(training_meta.replicas)
         if self.replica_pairing != "spread" or n == 1:
             return i % n
-        loads = self._replica_load.setdefault(n, [0] * n)
-        k = min(range(n), key=lambda j: (loads[j], j))
-        nbytes = 1
-        for d in training_meta.global_shape:
-            nbytes *= int(d)
-        loads[k] += nbytes
-        return k
+        return self._replica_choice.get((training_meta.name, i), i % n)
+
+    def _assign_replicas(self, names: Sequence[str], infer: Dict[str, ParameterMeta], train: Dict[str, ParameterMeta]) -> None:
+        """``spread``: walk the parameters in sorted order and hand each inference
+        replica the training replica that has been given the fewest bytes so far
+        (ties: lowest index), so parameters replicated over many data-parallel
+        ranks are served by all of them.  The table depends only on the metadata,
+        hence every rank computes the same one, and it is kept so that later
+        per-parameter calls (plans made on behalf of a TP peer) agree with it."""
+        self._replica_choice = {}
+        if self.replica_pairing != "spread":
+            return
+        loads: Dict[int, List[int]] = {}
+        for name in names:
+            n = len(train[name].replicas)
+            if n <= 1:
+                continue
+            nbytes = 1
+            for d in train[name].global_shape:
+                nbytes *= int(d)
+            per_group = loads.setdefault(n, [0] * n)
+            for i in range(self.num_infer_engines * len(infer[name].replicas)):
+                k = min(range(n), key=lambda j: (per_group[j], j))
+                per_group[k] += nbytes
+                self._replica_choice[(name, i)] = k
 
     def build_weights_mapping_operations(
         self,
@@ -342,8 +358,9 @@ class TransferPlanBuilder:
         infer = {m.name: m for m in inference_weights_meta}
         train = {m.name: m for m in training_weights_meta}
         ops: List[CommunicationOperation] = []
-        self._replica_load = {}
-        for name in self._common_names(infer, train):
+        names = self._common_names(infer, train)
+        self._assign_replicas(names, infer, train)
+        for name in names:
             ops.extend(self._build_parameter_communication_plan(name, infer[name], train[name], global_transfer_rank))
         return ops
 

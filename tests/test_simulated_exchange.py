@@ -147,3 +147,35 @@ def test_exactly_once_check_finds_gaps_overlaps_and_strays():
     assert _cover_problems_pairwise("w", (8, 6), boxes) == []
     assert any("overlaps" in p for p in _cover_problems_pairwise("w", (8, 6), boxes + [((3, 2), (2, 2), "d")]))
     assert any("never written" in p for p in _cover_problems_pairwise("w", (8, 6), boxes[:2]))
+
+
+@pytest.mark.parametrize("arch,train,infer", [
+    ("tiny-qwen2", TrainLayout(tp=4, dp=2), InferLayout(tp=2, num_engines=2)),
+    ("tiny-qwen2", TrainLayout(tp=4, dp=2), InferLayout(tp=2)),
+    ("tiny-llama", TrainLayout(tp=2, dp=3), InferLayout(tp=1, num_engines=2)),
+    ("tiny-qwen3-moe", TrainLayout(tp=2, dp=4, ep=4), InferLayout(tp=2, ep=2, num_engines=2)),
+], ids=lambda v: v if isinstance(v, str) else v.label())
+def test_spread_pairing_agrees_between_a_rank_and_the_plans_it_makes_for_its_peers(arch, train, infer):
+    """Rows that a TP peer owns are sent by that peer, which plans them with
+    per-parameter calls after its own plan: those calls must choose the same
+    training replica as the full pass did."""
+    from awex_b200.transfer.transfer_plan import TransferPlanBuilder
+
+    job = SimulatedJob(get_arch(arch), train, infer, dtype=torch.float32)
+    builder = TransferPlanBuilder(job.infer_world_size, job.train.world, job.infer.num_engines, replica_pairing="spread")
+    job.builder = builder
+    seen, clashes = {}, []
+    pick = builder._pick_train_replica
+
+    def spy(i, meta):
+        k = pick(i, meta)
+        if seen.setdefault((meta.name, i), k) != k:
+            clashes.append((meta.name, i, seen[(meta.name, i)], k))
+        return k
+
+    builder._pick_train_replica = spy
+    job.compile_all()
+    assert clashes == []
+    assert job.check_coverage() == []
+    job.run_cpu()
+    assert job.mismatches() == []
