@@ -17,6 +17,8 @@ from awex_b200.sharding.rank_info import RankInfo
 
 def train_rank_infos(tp: int = 1, pp: int = 1, dp: int = 1, ep: int = 1, etp: int = 1, gpus_per_node: int = 8) -> List[RankInfo]:
     world = tp * pp * dp
+    if ep == 1:
+        etp = tp  # Megatron's default: without expert parallelism the experts are cut over the TP group
     assert (tp * dp) % (ep * etp) == 0, "expert grid must tile the tp*dp ranks of a stage"
     out = []
     for rank in range(world):

@@ -1,0 +1,52 @@
+"""Seeded random layouts: architecture dimensions (heads, KV heads, head size,
+tied embeddings), training grids (TP / PP / DP / EP), inference grids (TP / EP /
+several engines, vLLM or SGLang flavour) and both replica pairings.  Every case
+must tile every destination exactly once and reproduce the oracle bit for bit."""
+
+import dataclasses
+import random
+
+import pytest
+import torch
+
+from awex_b200.synthetic.arch import get_arch
+from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+from awex_b200.transfer.transfer_plan import TransferPlanBuilder
+
+
+def _draw(rng):
+    base = rng.choice(["tiny-llama", "tiny-qwen2", "tiny-qwen3-moe"])
+    arch = get_arch(base)
+    heads = rng.choice([4, 8, 16])
+    kv = rng.choice([k for k in (1, 2, 4, 8, 16) if heads % k == 0])
+    arch = dataclasses.replace(arch, num_heads=heads, num_kv_heads=kv, head_dim=rng.choice([16, 32]), hidden=rng.choice([128, 256]),
+                               num_layers=rng.choice([2, 4]), tie_embeddings=rng.random() < 0.3)
+    ttp, tpp, tdp = rng.choice([1, 2, 4]), rng.choice([1, 1, 2]), rng.choice([1, 1, 2, 4])
+    itp, engines = rng.choice([1, 2, 4, 8]), rng.choice([1, 1, 2])
+    tep = iep = 1
+    if arch.is_moe:
+        tep = rng.choice([e for e in (1, 2, 4, 8) if (ttp * tdp) % e == 0 and arch.num_experts % e == 0])
+        iep = rng.choice([e for e in (1, 2, 4, 8) if itp % e == 0 and arch.num_experts % e == 0])
+    ok = (heads % ttp == 0 and heads % itp == 0 and kv % ttp == 0 and (itp <= kv or itp % kv == 0) and arch.num_layers % tpp == 0
+          and ttp * tpp * tdp <= 16 and itp * engines <= 16)
+    train = TrainLayout(tp=ttp, pp=tpp, dp=tdp, ep=tep)
+    infer = InferLayout(tp=itp, ep=iep, num_engines=engines, engine_name=rng.choice(["vllm", "vllm", "sglang"]))
+    return ok, arch, train, infer, rng.choice(["round_robin", "spread"])
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_layouts_are_exact(seed):
+    rng = random.Random(1000 + seed)
+    done = 0
+    while done < 12:
+        ok, arch, train, infer, pairing = _draw(rng)
+        if not ok:
+            continue
+        label = f"{arch.architecture} h{arch.num_heads}/kv{arch.num_kv_heads} {train.label()} -> {infer.label()} {infer.engine_name} {pairing}"
+        job = SimulatedJob(arch, train, infer, dtype=torch.float32)
+        job.builder = TransferPlanBuilder(job.infer_world_size, train.world, infer.num_engines, replica_pairing=pairing)
+        job.compile_all()
+        assert job.check_coverage() == [], label
+        job.run_cpu()
+        assert job.mismatches() == [], label
+        done += 1
