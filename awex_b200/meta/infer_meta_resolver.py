@@ -50,6 +50,23 @@ def canonical_named_views(model, converter, model_context: dict | None = None, c
     return out
 
 
+def find_aliases(views) -> Dict[str, str]:
+    """Canonical names that are second names of the very same memory in this
+    worker (tied ``lm_head.weight`` served by the embedding tensor): alias ->
+    first name.  Writing the first name fills the alias too."""
+    first: Dict[tuple, str] = {}
+    out: Dict[str, str] = {}
+    for name, t in views:
+        if t.numel() == 0:
+            continue
+        key = (t.data_ptr(), tuple(t.shape), tuple(t.stride()), str(t.dtype))
+        if key in first:
+            out[name] = first[key]
+        else:
+            first[key] = name
+    return out
+
+
 def collect_worker_param_info(engine_name, infer_engine_config, convert_params=False, engine_rank=0, **kwargs):
     """Runs inside a model worker; ``kwargs`` carries ``model`` and
     ``model_context``.  dtypes are sent as strings without the ``torch.``
@@ -75,6 +92,7 @@ def collect_worker_param_info(engine_name, infer_engine_config, convert_params=F
     return {
         "rank_info": rank_info,
         "model_arch_name": arch,
+        "aliases": find_aliases(views),
         "params_meta": [
             {"name": n, "numel": t.numel(), "shape": tuple(t.shape), "dtype": str(t.dtype).replace("torch.", "")}
             for n, t in views
@@ -108,6 +126,14 @@ class InferParamMetaResolver(ParamMetaResolver):
                 info["rank_info"] = RankInfo(**info["rank_info"])
         if debug:
             self._dump(f"infer_params_raw_meta_{suffix}", to_dict(self._params_raw_meta))
+        # a name is an alias for the job only if every worker that reports it holds it as one
+        reported, aliased = {}, {}
+        for info in self._params_raw_meta:
+            for pm in info["params_meta"]:
+                reported[pm["name"]] = reported.get(pm["name"], 0) + 1
+            for alias, target in (info.get("aliases") or {}).items():
+                aliased.setdefault(alias, []).append(target)
+        self.aliases: Dict[str, str] = {a: ts[0] for a, ts in aliased.items() if len(ts) == reported.get(a) and len(set(ts)) == 1}
         self._rank0_meta = self._select_canonical_rank0_meta(self._params_raw_meta)
         self.rank0_info = self._rank0_meta["rank_info"]
         self._world_size = self.rank0_info.world_size

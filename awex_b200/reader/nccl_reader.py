@@ -69,7 +69,8 @@ class WorkerWeightsReader:
         train_names = {m.name for m in self.training_params_meta}
         # what training will fill: its names, plus block scales that are produced
         # together with their weights
-        self.required_names = [n for n in self.parameters if n in train_names]
+        aliases = set((self.infer_conf.get("aliased_parameters") or {}))
+        self.required_names = [n for n in self.parameters if n in train_names and n not in aliases]
         self.device = next(iter(self.parameters.values())).device if self.parameters else torch.device("cpu")
         self._published_ptrs = self._model_ptrs()
 

@@ -136,6 +136,8 @@ class WeightsReader(WeightExchangeReader):
             "expected_pp_ranks": self.expected_pp_ranks,
             "device_backend": device_util.get_device_type(),
             "fp8_block_quant": bool(getattr(config, "fp8_block_quant", False)),
+            # second names of memory that another name already covers: nobody sends them
+            "aliased_parameters": dict(getattr(self.meta_resolver, "aliases", {}) or {}),
         }
         meta.put_object("infer_conf", self.infer_conf)
         if self.engine_rank == 0:

@@ -140,6 +140,8 @@ class SimulatedJob:
     def _resolve_metadata(self) -> None:
         resolver = InferParamMetaResolver(self.engines[0], convert_params=True, num_engines=self.infer.num_engines, engine_rank=0)
         self.infer_meta: List[ParameterMeta] = resolver.get_parameters_meta()
+        self.aliases = dict(getattr(resolver, "aliases", {}) or {})
+        self.builder.skip_names = frozenset(self.aliases)
         self.infer_conf = {
             "engine_name": self.infer.engine_name,
             "infer_atten_tp_size": self.infer.tp,
@@ -148,6 +150,7 @@ class SimulatedJob:
             "hf_config": self.hf_config,
             "infer_world_size": self.infer_world_size,
             "fp8_block_quant": self.infer.fp8,
+            "aliased_parameters": self.aliases,
         }
         raw = [
             list_local_train_params([m], self._train_converter(ri, with_pp_map=False), ri, self.hf_config, self.arch.architecture)
@@ -196,7 +199,7 @@ class SimulatedJob:
         for rank, rank_views in views.items():
             manifests = [manifest_by_destination(items).get(rank, []) for items in self.programs.values()]
             shapes = {n: (tuple(v.shape), v.dtype) for n, v in rank_views.items()}
-            required = [n for n in shapes if n in {m.name for m in self.train_meta} or n.endswith("_scale_inv")]
+            required = [n for n in shapes if (n in {m.name for m in self.train_meta} or n.endswith("_scale_inv")) and n not in self.aliases]
             problems += [f"rank {rank}: {p}" for p in check_exactly_once(manifests, shapes, required)]
         return problems
 

@@ -159,7 +159,7 @@ class SendProgramCompiler:
                 names = [
                     n for n, (spec, _) in specs.items()
                     if spec.rows is not None and any(src[1] == my_tp for src in spec.rows.sources() if isinstance(src, tuple) and src[0] != "__scale__")
-                    and n in self.train_meta and n in self.infer_meta
+                    and n in self.train_meta and n in self.infer_meta and n not in self.builder.skip_names
                 ]
                 virtual_rank = sender.global_rank + self.builder.infer_world_size
                 ops = []

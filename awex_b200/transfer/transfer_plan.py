@@ -145,7 +145,10 @@ class TransferPlanBuilder:
         enable_debug_mode: bool = False,
         strict_param_key_match: bool = False,
         replica_pairing: str = "round_robin",
+        skip_names: Iterable[str] = (),
     ):
+        # names that are planned for nobody (aliases of memory another name covers)
+        self.skip_names = frozenset(skip_names)
         if replica_pairing not in ("round_robin", "spread"):
             raise ValueError(f"unknown replica_pairing {replica_pairing!r}")
         self.replica_pairing = replica_pairing
@@ -176,7 +179,7 @@ class TransferPlanBuilder:
             raise ValueError(msg)
         if extra:
             logger.info(f"Infer metadata has extra keys ignored by the plan: count={len(extra)} sample={sorted(extra)[:8]}")
-        return sorted(ik & tk)
+        return sorted((ik & tk) - self.skip_names)
 
     # ---- per-shard helpers ----------------------------------------------
     def _compute_shard_transfer_rank(self, shard: ParameterShardMeta, engine_rank: int, is_infer: bool) -> int:

@@ -179,3 +179,24 @@ def test_spread_pairing_agrees_between_a_rank_and_the_plans_it_makes_for_its_pee
     assert job.check_coverage() == []
     job.run_cpu()
     assert job.mismatches() == []
+
+
+def test_tied_lm_head_is_an_alias_that_nobody_sends():
+    """With tied embeddings the inference worker answers for ``lm_head.weight``
+    through the embedding tensor: one memory, two names.  The alias is
+    published, the planner leaves it out, and the embedding is written once."""
+    import dataclasses
+
+    arch = dataclasses.replace(get_arch("tiny-llama"), tie_embeddings=True)
+    job = SimulatedJob(arch, TrainLayout(tp=2, pp=2), InferLayout(tp=2), dtype=torch.float32)
+    assert job.aliases == {"lm_head.weight": "model.embed_tokens.weight"}
+    assert job.infer_conf["aliased_parameters"] == job.aliases
+    programs = job.compile_all()
+    assert not any(it.dst_name == "lm_head.weight" for items in programs.values() for it in items)
+    assert any(it.dst_name == "model.embed_tokens.weight" for items in programs.values() for it in items)
+    assert job.check_coverage() == []
+    job.encode_all(validate=True)  # includes the no-two-descriptors-overlap rule
+    job.run_cpu()
+    assert job.mismatches() == []
+    untied = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=2), InferLayout(tp=2), dtype=torch.float32)
+    assert untied.aliases == {} and any(it.dst_name == "lm_head.weight" for items in untied.compile_all().values() for it in items)
