@@ -129,7 +129,7 @@ class WeightsReader(WeightExchangeReader):
         self.infer_conf = {
             "engine_name": self.inference_engine.engine_name,
             "infer_atten_tp_size": self.meta_resolver.rank0_info.attn_tp_size,
-            "router_dtype": getattr(self.hf_config, "router_dtype", "bf16"),
+            "router_dtype": self._router_dtype(),
             "infer_engine_config": self.infer_engine_config,
             "hf_config": simple_hf_config(self.hf_config) if hasattr(self.hf_config, "to_dict") else self.hf_config,
             "infer_world_size": self.infer_world_size,
@@ -162,6 +162,18 @@ class WeightsReader(WeightExchangeReader):
             weights_comm_nccl_group_size=self.weights_comm_nccl_group_size,
             device_wait_timeout_ms=getattr(config, "device_wait_timeout_ms", 2000),
         )
+
+    def _router_dtype(self) -> str:
+        """Dtype the training side casts MoE router weights to: the model
+        config's ``router_dtype`` if it names one (as the reference reads it),
+        else whatever dtype the engine actually holds its router weights in."""
+        named = getattr(self.hf_config, "router_dtype", None)
+        if named:
+            return named
+        for meta in self.parameters_meta:
+            if meta.name.endswith(("mlp.gate.weight", "mlp.router.weight")):
+                return {torch.float32: "fp32", torch.float16: "fp16"}.get(meta.dtype, "bf16")
+        return "bf16"
 
     @staticmethod
     def _init_in_tp_worker(**kwargs):
