@@ -1,0 +1,110 @@
+"""More layouts through the public API across real CPU processes (gloo):
+pipeline-parallel writers feeding one engine of two workers (whose metadata is
+gathered over the instance group), and block-fp8 serving, where the message
+transport carries quantised payloads and their scales."""
+
+import os
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+
+def _layouts(case):
+    from awex_b200.synthetic.simulate import InferLayout
+
+    if case == "pp2_to_tp2":
+        return "tiny-llama", dict(tp=1, pp=2), InferLayout(tp=2), torch.float32
+    if case == "tp1_to_tp2_fp8":
+        return "tiny-llama", dict(tp=1), InferLayout(tp=2, fp8=True), torch.bfloat16
+    raise ValueError(case)
+
+
+def _train_world(spec):
+    return spec.get("tp", 1) * spec.get("pp", 1) * spec.get("dp", 1)
+
+
+def _writer(case, rank, meta_addr, store_port, q):
+    import torch.distributed as dist
+
+    from awex_b200 import NCCLWeightsWriter
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticTrainEngine
+    from awex_b200.synthetic.topology import train_rank_infos
+
+    try:
+        os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        arch, train, _infer, dtype = _layouts(case)
+        world = _train_world(train)
+        group = None
+        if world > 1:
+            dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=rank, world_size=world)
+        ri = train_rank_infos(**train)[rank]
+        engine = SyntheticTrainEngine(get_arch(arch), ri, meta_addr, dtype=dtype, device="cpu", process_group=group, exchange_timeout_s=120)
+        writer = NCCLWeightsWriter(engine)
+        writer.initialize()
+        writer.write_weights(step_id=1)
+        q.put(("writer", rank, writer.transport.bytes_out))
+        if world > 1:
+            dist.destroy_process_group()
+    except BaseException as exc:
+        q.put(("error", f"writer {rank}: {exc!r}", 0))
+        raise
+
+
+def _reader(case, worker_rank, meta_addr, store_port, q):
+    import torch.distributed as dist
+
+    from awex_b200 import WeightsReader
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticInferenceEngine
+    from awex_b200.synthetic.topology import infer_rank_infos
+
+    try:
+        os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        arch, _train, layout, dtype = _layouts(case)
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=worker_rank, world_size=layout.tp)
+        ri = infer_rank_infos(tp=layout.tp)[worker_rank]
+        engine = SyntheticInferenceEngine(get_arch(arch), layout, ri, meta_addr, dtype=dtype, device="cpu", instance_group=dist.group.WORLD,
+                                          debug_mode_config={"exchange_timeout_s": 120})
+        reader = WeightsReader(engine)
+        reader.initialize()
+        reader.update_weights(step_id=1)
+        q.put(("reader", worker_rank, engine.mismatches(step=0)))
+        dist.destroy_process_group()
+    except BaseException as exc:
+        q.put(("error", f"reader {worker_rank}: {exc!r}", 0))
+        raise
+
+
+@pytest.mark.timeout(400)
+@pytest.mark.parametrize("case", ["pp2_to_tp2", "tp1_to_tp2_fp8"])
+def test_layout_over_gloo(case):
+    from awex_b200.meta.meta_server import MetaServer
+    from awex_b200.utils.common import get_free_port
+
+    _arch, train, layout, _dtype = _layouts(case)
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    addr = f"127.0.0.1:{server.port}"
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    train_port, infer_port = get_free_port(), get_free_port()
+    procs = [ctx.Process(target=_writer, args=(case, r, addr, train_port, q)) for r in range(_train_world(train))]
+    procs += [ctx.Process(target=_reader, args=(case, w, addr, infer_port, q)) for w in range(layout.tp)]
+    for p in procs:
+        p.start()
+    results = []
+    for _ in procs:
+        item = q.get(timeout=300)
+        assert item[0] != "error", item[1]
+        results.append(item)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    server.stop()
+    for kind, rank, payload in results:
+        if kind == "reader":
+            assert payload == [], (case, rank, payload[:3])
+        else:
+            assert payload > 0
