@@ -179,14 +179,32 @@ def pp_layer_range(num_layers: int, pp_rank: int, pp_size: int) -> range:
 
 
 # ---- Megatron layout ---------------------------------------------------------------------------
+def vpp_layer_range(num_layers: int, pp_rank: int, pp_size: int, vp_stage: int, vp_size: int) -> range:
+    """Layers of model chunk ``vp_stage`` on pipeline rank ``pp_rank`` with
+    interleaved (virtual) pipelining: chunks are numbered virtual stage
+    outermost, pipeline rank innermost."""
+    per_chunk = num_layers // (pp_size * vp_size)
+    first = (vp_stage * pp_size + pp_rank) * per_chunk
+    return range(first, first + per_chunk)
+
+
 def build_megatron_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, device="cpu", seed: int = 0,
-                         step: int = 0, layers: Optional[range] = None, weights: Optional[CanonicalWeights] = None) -> FlatModule:
+                         step: int = 0, layers: Optional[range] = None, weights: Optional[CanonicalWeights] = None,
+                         virtual_stage: Optional[Tuple[int, int]] = None) -> FlatModule:
+    """``virtual_stage=(vp_stage, vp_size)`` builds one chunk of an interleaved
+    pipeline: its layers, the embedding only in the very first chunk and the
+    output layer only in the very last."""
     w = weights or CanonicalWeights(arch, dtype, device, seed, step)
     tp, r = rank_info.tp_size, rank_info.tp_rank
     ep, er = rank_info.ep_size, rank_info.ep_rank
     etp, etr = rank_info.ep_tp_size, rank_info.ep_tp_rank
     out: "OrderedDict[str, torch.Tensor]" = OrderedDict()
     first_stage, last_stage = rank_info.pp_rank == 0, rank_info.pp_rank == rank_info.pp_size - 1
+    if virtual_stage is not None:
+        vp_stage, vp_size = virtual_stage
+        first_stage, last_stage = first_stage and vp_stage == 0, last_stage and vp_stage == vp_size - 1
+        if layers is None:
+            layers = vpp_layer_range(arch.num_layers, rank_info.pp_rank, rank_info.pp_size, vp_stage, vp_size)
     if first_stage:
         out["embedding.word_embeddings.weight"] = _chunk(w.embed(), tp, r).contiguous()
     global_layers = layers if layers is not None else pp_layer_range(arch.num_layers, rank_info.pp_rank, rank_info.pp_size)

@@ -108,3 +108,85 @@ def test_layout_over_gloo(case):
             assert payload == [], (case, rank, payload[:3])
         else:
             assert payload > 0
+
+
+# ------------------------------------------------------------------------------------------ interleaved pipeline
+def _vpp_writer(rank, meta_addr, store_port, q):
+    import dataclasses
+
+    import torch.distributed as dist
+
+    from awex_b200 import NCCLWeightsWriter
+    from awex_b200.engine.mcore import MegatronEngine
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.models import build_megatron_model
+    from awex_b200.synthetic.topology import train_rank_infos
+
+    try:
+        os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=rank, world_size=2)
+        arch = dataclasses.replace(get_arch("tiny-llama"), num_layers=4)
+        ri = train_rank_infos(tp=1, pp=2)[rank]
+        chunks = [build_megatron_model(arch, ri, torch.float32, "cpu", virtual_stage=(vp, 2)) for vp in range(2)]
+        engine = MegatronEngine({"meta_server_addr": meta_addr, "comm_backend": "nccl", "exchange_timeout_s": 120}, arch.hf_config(), chunks, rank_info=ri)
+        writer = NCCLWeightsWriter(engine)
+        writer.initialize()
+        writer.write_weights(step_id=1)
+        q.put(("writer", rank, sorted({it.dst_name.split(".")[2] for it in writer.items if it.dst_name.startswith("model.layers.")})))
+        dist.destroy_process_group()
+    except BaseException as exc:
+        q.put(("error", f"writer {rank}: {exc!r}", 0))
+        raise
+
+
+def _vpp_reader(meta_addr, q):
+    import dataclasses
+
+    from awex_b200 import WeightsReader
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticInferenceEngine
+    from awex_b200.synthetic.simulate import InferLayout
+    from awex_b200.synthetic.topology import infer_rank_infos
+
+    try:
+        os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        arch = dataclasses.replace(get_arch("tiny-llama"), num_layers=4)
+        engine = SyntheticInferenceEngine(arch, InferLayout(tp=1), infer_rank_infos()[0], meta_addr, dtype=torch.float32, device="cpu",
+                                          debug_mode_config={"exchange_timeout_s": 120})
+        reader = WeightsReader(engine)
+        reader.initialize()
+        reader.update_weights(step_id=1)
+        q.put(("reader", 0, engine.mismatches(step=0)))
+    except BaseException as exc:
+        q.put(("error", f"reader: {exc!r}", 0))
+        raise
+
+
+@pytest.mark.timeout(400)
+def test_interleaved_pipeline_chunks_are_renumbered_to_global_layers():
+    """Two pipeline ranks with two model chunks each (virtual pipeline): chunk
+    (pp, vp) holds global layer vp * 2 + pp under the local id 0."""
+    from awex_b200.meta.meta_server import MetaServer
+    from awex_b200.utils.common import get_free_port
+
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    addr = f"127.0.0.1:{server.port}"
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = get_free_port()
+    procs = [ctx.Process(target=_vpp_writer, args=(r, addr, port, q)) for r in range(2)] + [ctx.Process(target=_vpp_reader, args=(addr, q))]
+    for p in procs:
+        p.start()
+    results = []
+    for _ in procs:
+        item = q.get(timeout=300)
+        assert item[0] != "error", item[1]
+        results.append(item)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    server.stop()
+    layers = {rank: payload for kind, rank, payload in results if kind == "writer"}
+    assert layers == {0: ["0", "2"], 1: ["1", "3"]}
+    assert [payload for kind, _, payload in results if kind == "reader"] == [[]]
