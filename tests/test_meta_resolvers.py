@@ -203,3 +203,31 @@ def test_control_reader_publishes_engine_name_and_layout_facts():
     assert name == "_init_in_tp_worker" and kwargs["weights_comm_backend"] == "nccl" and kwargs["num_engines"] == 1
     assert pickle.loads(kwargs["infer_conf_bytes"])["engine_name"] == "sglang"
     assert len(pickle.loads(kwargs["training_params_meta_bytes"])) == 4
+
+
+def test_uneven_pipeline_splits_and_explicit_layouts():
+    from awex_b200.converter.pp_layout import resolve_pp_stage_global_layer_ids, stage_counts_from_layout, stage_counts_from_split_config
+
+    assert stage_counts_from_split_config(10, 4, {"num_layers_in_first_pipeline_stage": 2, "num_layers_in_last_pipeline_stage": 2}) == [[2], [3], [3], [2]]
+    assert stage_counts_from_split_config(7, 2, {"num_layers_in_first_pipeline_stage": 3}) == [[3], [4]]
+    # the embedding and the loss each count as a layer when the split is made, then give their slot back
+    assert stage_counts_from_split_config(6, 4, {"account_for_embedding_in_pipeline_split": True, "account_for_loss_in_pipeline_split": True}) == [[1], [2], [2], [1]]
+    assert stage_counts_from_split_config(8, 2, {"virtual_pipeline_model_parallel_size": 2}) == [[2, 2], [2, 2]]
+    for bad in ({"num_layers_in_first_pipeline_stage": 2, "account_for_loss_in_pipeline_split": True}, {"num_layers_in_first_pipeline_stage": 0},
+                {"num_layers_in_first_pipeline_stage": 9, "num_layers_in_last_pipeline_stage": 9}, {"virtual_pipeline_model_parallel_size": 3}):
+        with pytest.raises(ValueError):
+            stage_counts_from_split_config(8, 2, bad)
+    with pytest.raises(ValueError):
+        stage_counts_from_split_config(7, 2, {})
+    flat = [["embedding", "decoder"], ["decoder", "decoder"], ["decoder"], ["decoder", "loss"]]  # stage = vp * pp + pp_rank
+    assert stage_counts_from_layout(flat, 2) == [[1, 1], [2, 1]]
+    nested = [[["embedding", "decoder"], ["decoder"]], [["decoder", "decoder"], ["decoder", "loss"]]]
+    assert stage_counts_from_layout(nested, 2) == [[1, 1], [2, 1]]
+    for bad, pp in (([], 2), ("decoder", 2), ([["decoder"]] * 3, 2), ([[["decoder"]], [["decoder"], ["decoder"]]], 2)):
+        with pytest.raises(ValueError):
+            stage_counts_from_layout(bad, pp)
+    hf = SimpleNamespace(num_hidden_layers=5)
+    ids = lambda pp, vp: resolve_pp_stage_global_layer_ids(SimpleNamespace(pp_rank=pp, pp_size=2), hf, {"pipeline_model_parallel_layout": flat}, vp)  # noqa: E731
+    assert [ids(0, 0), ids(1, 0), ids(0, 1), ids(1, 1)] == [[0], [1, 2], [3], [4]]
+    with pytest.raises(ValueError, match="do not match num_hidden_layers"):
+        resolve_pp_stage_global_layer_ids(SimpleNamespace(pp_rank=0, pp_size=2), SimpleNamespace(num_hidden_layers=6), {"pipeline_model_parallel_layout": flat}, 0)
