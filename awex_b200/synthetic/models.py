@@ -246,7 +246,9 @@ def build_megatron_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, 
             out[p + "mlp.linear_fc2.weight"] = _chunk(w.layer(l, "mlp.down_proj.weight"), tp, r, 1).contiguous()
     if last_stage:
         out["decoder.final_layernorm.weight"] = w.final_norm()
-        if not arch.tie_embeddings:
+        # tied embeddings: one tensor when this stage also holds the embedding; with
+        # pipeline stages apart, the last stage keeps its own (synchronised) copy
+        if not arch.tie_embeddings or not first_stage:
             out["output_layer.weight"] = _chunk(w.lm_head(), tp, r).contiguous()
     model = FlatModule(out, arch.tf_config())
     model.transformer_config = model.config
@@ -345,7 +347,7 @@ def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, devi
             _maybe_fp8(out, p + "mlp.down_proj.weight", _chunk(w.layer(l, "mlp.down_proj.weight"), tp, r, 1), fp8, zero=zero)
     if last_stage:
         out["model.norm.weight"] = w.final_norm()
-        if not arch.tie_embeddings:
+        if not arch.tie_embeddings or not first_stage:  # as on the training side
             out["lm_head.weight"] = _chunk(w.lm_head(), tp, r).contiguous()
     if zero:
         for t in out.values():

@@ -54,17 +54,18 @@ class InferLayout:
     num_engines: int = 1
     engine_name: str = "vllm"
     fp8: bool = False
+    pp: int = 1
 
     @property
     def instance_world(self) -> int:
-        return self.tp
+        return self.tp * self.pp
 
     @property
     def world(self) -> int:
-        return self.tp * self.num_engines
+        return self.tp * self.pp * self.num_engines
 
     def label(self) -> str:
-        base = f"tp{self.tp}" + (f"ep{self.ep}" if self.ep > 1 else "") + ("-fp8" if self.fp8 else "")
+        base = f"tp{self.tp}" + (f"pp{self.pp}" if self.pp > 1 else "") + (f"ep{self.ep}" if self.ep > 1 else "") + ("-fp8" if self.fp8 else "")
         return f"{self.num_engines}x{base}" if self.num_engines > 1 else base
 
 
@@ -88,7 +89,7 @@ class LocalInferenceEngine:
         self.engine_name = layout.engine_name
         self.hf_config = models[0].config
         cfg = dict(
-            tp_size=layout.tp, pp_size=1, dp_size=1, ep_size=layout.ep, enable_dp_attention=False,
+            tp_size=layout.tp, pp_size=layout.pp, dp_size=1, ep_size=layout.ep, enable_dp_attention=False,
             enable_dp_lm_head=False, moe_dense_tp_size=None, num_engines=layout.num_engines, engine_rank=engine_rank,
             comm_backend="nccl", fp8_block_quant=layout.fp8,
         )
@@ -121,7 +122,7 @@ class SimulatedJob:
         self.arch, self.train, self.infer, self.dtype, self.device, self.seed = arch, train, infer, dtype, device, seed
         self.hf_config = arch.hf_config()
         self.train_ranks = train_rank_infos(train.tp, train.pp, train.dp, train.ep, train.etp)
-        self.infer_ranks = [infer_rank_infos(infer.tp, infer.ep, engine_rank=e, flavour=infer.engine_name) for e in range(infer.num_engines)]
+        self.infer_ranks = [infer_rank_infos(infer.tp, infer.ep, engine_rank=e, pp=infer.pp, flavour=infer.engine_name) for e in range(infer.num_engines)]
         self.train_models: List[FlatModule] = []
         self.infer_models: List[List[FlatModule]] = []
         if build_models:

@@ -1,5 +1,5 @@
 """Seeded random layouts: architecture dimensions (heads, KV heads, head size,
-tied embeddings), training grids (TP / PP / DP / EP), inference grids (TP / EP /
+tied embeddings), training grids (TP / PP / DP / EP), inference grids (TP / PP / EP /
 several engines, vLLM or SGLang flavour) and both replica pairings.  Every case
 must tile every destination exactly once and reproduce the oracle bit for bit."""
 
@@ -22,15 +22,15 @@ def _draw(rng):
     arch = dataclasses.replace(arch, num_heads=heads, num_kv_heads=kv, head_dim=rng.choice([16, 32]), hidden=rng.choice([128, 256]),
                                num_layers=rng.choice([2, 4]), tie_embeddings=rng.random() < 0.3)
     ttp, tpp, tdp = rng.choice([1, 2, 4]), rng.choice([1, 1, 2]), rng.choice([1, 1, 2, 4])
-    itp, engines = rng.choice([1, 2, 4, 8]), rng.choice([1, 1, 2])
+    itp, engines, ipp = rng.choice([1, 2, 4, 8]), rng.choice([1, 1, 2]), rng.choice([1, 1, 1, 2])
     tep = iep = 1
     if arch.is_moe:
         tep = rng.choice([e for e in (1, 2, 4, 8) if (ttp * tdp) % e == 0 and arch.num_experts % e == 0])
         iep = rng.choice([e for e in (1, 2, 4, 8) if itp % e == 0 and arch.num_experts % e == 0])
     ok = (heads % ttp == 0 and heads % itp == 0 and kv % ttp == 0 and (itp <= kv or itp % kv == 0) and arch.num_layers % tpp == 0
-          and ttp * tpp * tdp <= 16 and itp * engines <= 16)
+          and arch.num_layers % ipp == 0 and ttp * tpp * tdp <= 16 and itp * ipp * engines <= 16)
     train = TrainLayout(tp=ttp, pp=tpp, dp=tdp, ep=tep)
-    infer = InferLayout(tp=itp, ep=iep, num_engines=engines, engine_name=rng.choice(["vllm", "vllm", "sglang"]))
+    infer = InferLayout(tp=itp, ep=iep, num_engines=engines, engine_name=rng.choice(["vllm", "vllm", "sglang"]), pp=ipp)
     return ok, arch, train, infer, rng.choice(["round_robin", "spread"])
 
 
