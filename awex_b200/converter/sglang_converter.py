@@ -72,7 +72,8 @@ class SGlangToHFWeightConverter:
                 return [(name, parameter)]
             heads = int(self.total_num_heads)
             kv = int(self.total_kv_heads or heads)
-            tp = int(self.tp_size or 1)
+            # attention is cut over attention TP, which is smaller than TP under DP attention
+            tp = int(getattr(self.rank_info, "attn_tp_size", 0) or self.tp_size or 1)
             if tp > kv and tp % kv == 0 and heads % tp == 0:
                 # every rank stores one whole (replicated) KV head beside its query heads
                 heads, kv = heads // tp, 1

@@ -144,7 +144,9 @@ class ShardingStrategy:
             (has("expert"), self.get_expert_sharding_strategy),
             (has("gate.weight", "router.weight"), whole),
             (has("mlp"), self.get_mlp_sharding_strategy),
-            (has("attention"), self.get_attention_sharding_strategy),
+            # "self_attn" names (architectures whose converters keep Hugging Face attention names) follow the
+            # attention rule too: under DP attention they are cut over attention TP, not TP
+            (has("attention", "self_attn"), self.get_attention_sharding_strategy),
         ]
 
     def get_sharding_strategy(self, parameter_name, **kwargs) -> Decision:

@@ -295,30 +295,34 @@ def _quant_parts(t2d: torch.Tensor, parts: int):
 
 def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, device="cpu", seed: int = 0,
                      step: int = 0, fp8: bool = False, zero: bool = False, layers: Optional[range] = None,
-                     weights: Optional[CanonicalWeights] = None) -> FlatModule:
+                     weights: Optional[CanonicalWeights] = None, dp_lm_head: bool = False) -> FlatModule:
     """``zero=True`` allocates the same tensors filled with zeros (a freshly
     paused engine whose weights are about to be overwritten)."""
     w = weights or (ZeroWeights(arch, dtype, device) if zero else CanonicalWeights(arch, dtype, device, seed, step))
     tp, r = rank_info.tp_size, rank_info.tp_rank
+    # attention, embeddings and (with ``dp_lm_head``) the head follow attention TP, which
+    # equals TP unless the engine runs DP attention
+    atp, ar = rank_info.attn_tp_size, rank_info.attn_tp_rank
+    htp, hr = (atp, ar) if dp_lm_head else (tp, r)
     ep, er = rank_info.ep_size, rank_info.ep_rank
     etp, etr = rank_info.ep_tp_size, rank_info.ep_tp_rank
     if ep == 1:  # no expert parallelism: experts are TP-sliced
         etp, etr = tp, r
     out: "OrderedDict[str, torch.Tensor]" = OrderedDict()
     hd = arch.head_dim
-    heads_local = arch.num_heads // tp
-    kv_local = max(arch.num_kv_heads // tp, 1)
-    kv_first = (r * arch.num_kv_heads) // tp  # index of this rank's first KV head
+    heads_local = arch.num_heads // atp
+    kv_local = max(arch.num_kv_heads // atp, 1)
+    kv_first = (ar * arch.num_kv_heads) // atp  # index of this rank's first KV head
     first_stage, last_stage = rank_info.pp_rank == 0, rank_info.pp_rank == rank_info.pp_size - 1
     if first_stage:
-        out["model.embed_tokens.weight"] = _chunk(w.embed(), tp, r).contiguous()
+        out["model.embed_tokens.weight"] = _chunk(w.embed(), atp, ar).contiguous()
     for l in layers if layers is not None else pp_layer_range(arch.num_layers, rank_info.pp_rank, rank_info.pp_size):
         p = f"model.layers.{l}."
 
         def fused(kind: str) -> torch.Tensor:
             q, k, v = (w.layer(l, f"self_attn.{x}_proj.{kind}") for x in "qkv")
             return torch.cat(
-                [q.narrow(0, r * heads_local * hd, heads_local * hd), k.narrow(0, kv_first * hd, kv_local * hd),
+                [q.narrow(0, ar * heads_local * hd, heads_local * hd), k.narrow(0, kv_first * hd, kv_local * hd),
                  v.narrow(0, kv_first * hd, kv_local * hd)], 0,
             )
 
@@ -329,7 +333,7 @@ def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, devi
         if arch.qk_norm:
             out[p + "self_attn.q_norm.weight"] = w.layer(l, "self_attn.q_norm.weight")
             out[p + "self_attn.k_norm.weight"] = w.layer(l, "self_attn.k_norm.weight")
-        _maybe_fp8(out, p + "self_attn.o_proj.weight", _chunk(w.layer(l, "self_attn.o_proj.weight"), tp, r, 1), fp8, zero=zero)
+        _maybe_fp8(out, p + "self_attn.o_proj.weight", _chunk(w.layer(l, "self_attn.o_proj.weight"), atp, ar, 1), fp8, zero=zero)
         out[p + "post_attention_layernorm.weight"] = w.layer(l, "post_attention_layernorm.weight")
         if arch.is_moe:
             out[p + "mlp.gate.weight"] = w.layer(l, "mlp.gate.weight")
@@ -348,7 +352,7 @@ def build_vllm_model(arch: Arch, rank_info: RankInfo, dtype=torch.bfloat16, devi
     if last_stage:
         out["model.norm.weight"] = w.final_norm()
         if not arch.tie_embeddings or not first_stage:  # as on the training side
-            out["lm_head.weight"] = _chunk(w.lm_head(), tp, r).contiguous()
+            out["lm_head.weight"] = _chunk(w.lm_head(), htp, hr).contiguous()
     if zero:
         for t in out.values():
             t.zero_()

@@ -55,6 +55,12 @@ class InferLayout:
     engine_name: str = "vllm"
     fp8: bool = False
     pp: int = 1
+    attn_tp: int = 0  # SGLang DP attention: attention TP inside TP (0: same as tp)
+    dp_lm_head: bool = False
+
+    @property
+    def attention_tp(self) -> int:
+        return self.attn_tp or self.tp
 
     @property
     def instance_world(self) -> int:
@@ -65,7 +71,7 @@ class InferLayout:
         return self.tp * self.pp * self.num_engines
 
     def label(self) -> str:
-        base = f"tp{self.tp}" + (f"pp{self.pp}" if self.pp > 1 else "") + (f"ep{self.ep}" if self.ep > 1 else "") + ("-fp8" if self.fp8 else "")
+        base = f"tp{self.tp}" + (f"attn{self.attn_tp}" if self.attn_tp not in (0, self.tp) else "") + (f"pp{self.pp}" if self.pp > 1 else "") + (f"ep{self.ep}" if self.ep > 1 else "") + ("-fp8" if self.fp8 else "")
         return f"{self.num_engines}x{base}" if self.num_engines > 1 else base
 
 
@@ -89,8 +95,8 @@ class LocalInferenceEngine:
         self.engine_name = layout.engine_name
         self.hf_config = models[0].config
         cfg = dict(
-            tp_size=layout.tp, pp_size=layout.pp, dp_size=1, ep_size=layout.ep, enable_dp_attention=False,
-            enable_dp_lm_head=False, moe_dense_tp_size=None, num_engines=layout.num_engines, engine_rank=engine_rank,
+            tp_size=layout.tp, pp_size=layout.pp, dp_size=layout.tp // layout.attention_tp, ep_size=layout.ep,
+            enable_dp_attention=layout.attention_tp != layout.tp, enable_dp_lm_head=layout.dp_lm_head, moe_dense_tp_size=None, num_engines=layout.num_engines, engine_rank=engine_rank,
             comm_backend="nccl", fp8_block_quant=layout.fp8,
         )
         cfg.update(config_overrides)
@@ -122,13 +128,13 @@ class SimulatedJob:
         self.arch, self.train, self.infer, self.dtype, self.device, self.seed = arch, train, infer, dtype, device, seed
         self.hf_config = arch.hf_config()
         self.train_ranks = train_rank_infos(train.tp, train.pp, train.dp, train.ep, train.etp)
-        self.infer_ranks = [infer_rank_infos(infer.tp, infer.ep, engine_rank=e, pp=infer.pp, flavour=infer.engine_name) for e in range(infer.num_engines)]
+        self.infer_ranks = [infer_rank_infos(infer.tp, infer.ep, engine_rank=e, pp=infer.pp, flavour=infer.engine_name, attn_tp=infer.attn_tp) for e in range(infer.num_engines)]
         self.train_models: List[FlatModule] = []
         self.infer_models: List[List[FlatModule]] = []
         if build_models:
             self.train_models = [build_megatron_model(arch, ri, dtype, device, seed) for ri in self.train_ranks]
             self.infer_models = [
-                [build_vllm_model(arch, ri, dtype, device, seed, fp8=infer.fp8, zero=True) for ri in ranks] for ranks in self.infer_ranks
+                [build_vllm_model(arch, ri, dtype, device, seed, fp8=infer.fp8, zero=True, dp_lm_head=infer.dp_lm_head) for ri in ranks] for ranks in self.infer_ranks
             ]
         self.engines = [
             LocalInferenceEngine(arch, infer, self.infer_ranks[e], self.infer_models[e], engine_rank=e) for e in range(infer.num_engines)
@@ -145,7 +151,7 @@ class SimulatedJob:
         self.builder.skip_names = frozenset(self.aliases)
         self.infer_conf = {
             "engine_name": self.infer.engine_name,
-            "infer_atten_tp_size": self.infer.tp,
+            "infer_atten_tp_size": self.infer.attention_tp,
             "router_dtype": "bf16" if self.dtype == torch.bfloat16 else ("fp16" if self.dtype == torch.float16 else "fp32"),
             "infer_engine_config": self.engines[0].config,
             "hf_config": self.hf_config,
@@ -266,7 +272,7 @@ class SimulatedJob:
         bad = []
         for e, (ranks, models) in enumerate(zip(self.infer_ranks, self.infer_models)):
             for ri, model in zip(ranks, models):
-                oracle = build_vllm_model(self.arch, ri, self.dtype, self.device, self.seed, fp8=self.infer.fp8)
+                oracle = build_vllm_model(self.arch, ri, self.dtype, self.device, self.seed, fp8=self.infer.fp8, dp_lm_head=self.infer.dp_lm_head)
                 for (name, got), (_, want) in zip(model.named_parameters(), oracle.named_parameters()):
                     same = torch.equal(got.view(torch.uint8), want.view(torch.uint8)) if got.dtype == torch.float8_e4m3fn else torch.equal(got, want)
                     if not same:

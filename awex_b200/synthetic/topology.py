@@ -38,9 +38,14 @@ def train_rank_infos(tp: int = 1, pp: int = 1, dp: int = 1, ep: int = 1, etp: in
 
 
 def infer_rank_infos(tp: int = 1, ep: int = 1, engine_rank: int = 0, pp: int = 1, flavour: str = "vllm",
-                     first_local_rank: int = 0) -> List[RankInfo]:
-    """Ranks of ONE inference instance (``global_rank`` is instance-local)."""
+                     first_local_rank: int = 0, attn_tp: int = 0) -> List[RankInfo]:
+    """Ranks of ONE inference instance (``global_rank`` is instance-local).
+    ``attn_tp`` (SGLang's DP attention): attention, embeddings and, optionally,
+    the head are cut over ``attn_tp`` ranks and replicated over ``tp / attn_tp``
+    attention-DP groups; everything else is cut over ``tp``."""
     world = tp * pp
+    attn_tp = attn_tp or tp
+    assert tp % attn_tp == 0, "attention TP must divide TP"
     out = []
     for rank in range(world):
         tp_rank, pp_rank = rank % tp, rank // tp
@@ -54,7 +59,7 @@ def infer_rank_infos(tp: int = 1, ep: int = 1, engine_rank: int = 0, pp: int = 1
             RankInfo(
                 tp_rank=tp_rank, tp_size=tp, pp_rank=pp_rank, pp_size=pp, dp_size=1, dp_rank=0,
                 ep_rank=ep_rank, ep_size=ep, ep_tp_rank=ep_tp_rank, ep_tp_size=ep_tp,
-                attn_tp_rank=tp_rank, attn_tp_size=tp, attn_dp_rank=0, world_size=world,
+                attn_tp_rank=tp_rank % attn_tp, attn_tp_size=attn_tp, attn_dp_rank=tp_rank // attn_tp, world_size=world,
                 global_rank=rank, local_rank=first_local_rank + rank, engine_rank=engine_rank, is_infer=True,
             )
         )

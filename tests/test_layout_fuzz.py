@@ -30,7 +30,12 @@ def _draw(rng):
     ok = (heads % ttp == 0 and heads % itp == 0 and kv % ttp == 0 and (itp <= kv or itp % kv == 0) and arch.num_layers % tpp == 0
           and arch.num_layers % ipp == 0 and ttp * tpp * tdp <= 16 and itp * ipp * engines <= 16)
     train = TrainLayout(tp=ttp, pp=tpp, dp=tdp, ep=tep)
-    infer = InferLayout(tp=itp, ep=iep, num_engines=engines, engine_name=rng.choice(["vllm", "vllm", "sglang"]), pp=ipp)
+    flavour = rng.choice(["vllm", "vllm", "sglang"])
+    attn_tp = rng.choice([a for a in (1, 2, 4, 8) if itp % a == 0]) if flavour == "sglang" and rng.random() < 0.4 else 0
+    ok = ok and (attn_tp == 0 or (heads % attn_tp == 0 and (attn_tp <= kv or attn_tp % kv == 0)))
+    infer = InferLayout(tp=itp, ep=iep, num_engines=engines, engine_name=flavour, pp=ipp, attn_tp=attn_tp, 
+                        # a tied head is the embedding tensor, so it is cut the way the embedding is
+                        dp_lm_head=bool(attn_tp) and (arch.tie_embeddings or rng.random() < 0.5))
     return ok, arch, train, infer, rng.choice(["round_robin", "spread"])
 
 

@@ -29,6 +29,11 @@ LAYOUTS = [
     ("tiny-qwen3-moe", TrainLayout(tp=1, dp=2, ep=2), InferLayout(tp=2, ep=2, engine_name="sglang")),
     ("tiny-qwen3-moe", TrainLayout(tp=2, dp=2, ep=4), InferLayout(tp=8)),  # split Q/K/V with replicated KV heads
     ("tiny-qwen3-moe", TrainLayout(tp=1, dp=8, ep=8), InferLayout(tp=8)),
+    # SGLang DP attention: attention / embeddings cut over attention TP and replicated over attention-DP groups
+    ("tiny-qwen2", TrainLayout(tp=2), InferLayout(tp=4, attn_tp=2, engine_name="sglang")),
+    ("tiny-qwen2", TrainLayout(tp=4), InferLayout(tp=4, attn_tp=1, engine_name="sglang", dp_lm_head=True)),
+    ("tiny-qwen3-moe", TrainLayout(tp=1, dp=2, ep=2), InferLayout(tp=4, ep=4, attn_tp=2, engine_name="sglang")),
+    ("tiny-llama", TrainLayout(tp=2, pp=2), InferLayout(tp=2, attn_tp=1, engine_name="sglang", num_engines=2)),
     ("tiny-llama", TrainLayout(tp=2), InferLayout(tp=1, pp=2)),  # pipeline-parallel inference
     ("tiny-qwen2", TrainLayout(tp=2, pp=2), InferLayout(tp=2, pp=2)),
     ("tiny-qwen3-moe", TrainLayout(tp=1, dp=2, ep=2), InferLayout(tp=2, pp=2, num_engines=2)),
