@@ -38,7 +38,7 @@ from awex_b200.converter.pp_layout import (  # noqa: F401  (re-exported helpers)
     stage_counts_from_split_config,
 )
 from awex_b200.converter.rows import IDENTITY, Rows, TensorSpec, ValueOp
-from awex_b200.converter.weights_converter import SCALE_SUFFIX, block_scale_shape, per_block_cast_to_fp8
+from awex_b200.converter.weights_converter import FP8_BLOCK, SCALE_SUFFIX, block_scale_shape, per_block_cast_to_fp8
 from awex_b200.sharding.rank_info import RankInfo
 from awex_b200.utils.common import cfg_get, divide
 
@@ -404,6 +404,23 @@ class McoreToHFWeightConverter:
             tp_i = self.infer_atten_tp_size
         return max(tp_i // max(int(self.rank_info.tp_size), 1), 1)
 
+    def _source_split(self, canonical_name: str) -> int:
+        """How many of this side's slices share one destination shard of
+        ``canonical_name`` along the sharded dim (>= 1): the mirror of
+        :meth:`_dest_split`."""
+        engine_cfg = self.infer_conf.get("infer_engine_config")
+        tp_i = self._infer_tp_size()
+        if ".experts." in canonical_name:
+            ep_i = int(cfg_get(engine_cfg, "ep_size", None) or 1)
+            if ep_i > 1:
+                etp_i = tp_i // ep_i if self.infer_conf.get("engine_name") == "sglang" else 1
+            else:
+                etp_i = tp_i
+            return max(max(int(self.rank_info.ep_tp_size), 1) // max(etp_i, 1), 1)
+        if "attention" in canonical_name or "self_attn" in canonical_name:
+            tp_i = self.infer_atten_tp_size
+        return max(max(int(self.rank_info.tp_size), 1) // max(tp_i, 1), 1)
+
     # ---- block fp8 serving -----------------------------------------------------------------
     _FP8_SUFFIXES = (
         "q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "dense.weight", "query_key_value_proj.weight",
@@ -441,6 +458,14 @@ class McoreToHFWeightConverter:
         k = self._dest_split(weight.name)
         if extent[dim] % k != 0:
             k = 1
+        if self._source_split(weight.name) > 1 and extent[dim] % FP8_BLOCK:
+            # several training ranks share one destination shard and this rank's slice ends inside a
+            # quantisation block: that block would need rows (or columns) from two ranks on one
+            raise NotImplementedError(
+                f"{weight.name}: this rank's slice ({extent[dim]} along dim {dim}) is not a whole number of {FP8_BLOCK}-wide "
+                "quantisation blocks while several training ranks feed one inference shard; quantising those blocks needs "
+                "their data on one rank (use a training TP that keeps slices block aligned, or an inference TP >= training TP)"
+            )
         along = k * block_scale_shape(extent[dim] // k, 1)[0]
         other = block_scale_shape(extent[1 - dim], 1)[0]
         shape = (along, other) if dim == 0 else (other, along)

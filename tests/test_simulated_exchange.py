@@ -208,3 +208,20 @@ def test_tied_lm_head_is_an_alias_that_nobody_sends():
     assert job.mismatches() == []
     untied = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=2), InferLayout(tp=2), dtype=torch.float32)
     assert untied.aliases == {} and any(it.dst_name == "lm_head.weight" for items in untied.compile_all().values() for it in items)
+
+
+def test_fp8_slices_that_end_inside_a_block_are_refused_with_a_reason():
+    """Two training TP ranks feed one inference shard and each holds half of a
+    128-row quantisation block: no rank can compute that block's scale."""
+    import dataclasses
+
+    arch = dataclasses.replace(get_arch("tiny-qwen3-moe"), num_heads=4, num_kv_heads=4, head_dim=128, hidden=512, num_layers=1,
+                               vocab=512, num_experts=4, expert_ffn=128)
+    with pytest.raises(NotImplementedError, match="not a whole number of 128-wide quantisation blocks"):
+        SimulatedJob(arch, TrainLayout(tp=2), InferLayout(tp=1, fp8=True), dtype=torch.bfloat16)
+    aligned = dataclasses.replace(arch, expert_ffn=256)
+    job = SimulatedJob(aligned, TrainLayout(tp=2), InferLayout(tp=1, fp8=True), dtype=torch.bfloat16)
+    job.compile_all()
+    assert job.check_coverage() == []
+    job.run_cpu()
+    assert job.mismatches() == []
