@@ -55,3 +55,44 @@ def test_random_layouts_are_exact(seed):
         job.run_cpu()
         assert job.mismatches() == [], label
         done += 1
+
+
+def test_random_block_fp8_layouts_through_the_descriptor_tables():
+    """Block-aligned small architectures served as fp8: plan, lower, encode, run
+    the tables on the host interpreter, compare with the CPU-quantised oracle.
+    Layouts whose quantisation blocks would straddle training ranks must be
+    refused with NotImplementedError, never mis-executed."""
+    from awex_b200.transfer.table_interpreter import HostMemory, run_table
+
+    rng = random.Random(77)
+    done = refused = 0
+    while done < 14:
+        base = rng.choice(["tiny-llama", "tiny-qwen2", "tiny-qwen3-moe"])
+        heads = rng.choice([2, 4, 8])
+        kv = rng.choice([k for k in (1, 2, 4, 8) if heads % k == 0 and k <= heads])
+        arch = dataclasses.replace(get_arch(base), num_heads=heads, num_kv_heads=kv, head_dim=128, hidden=rng.choice([256, 512]), num_layers=1, vocab=512)
+        arch = dataclasses.replace(arch, num_experts=4, expert_ffn=rng.choice([128, 256, 384])) if arch.is_moe else dataclasses.replace(arch, ffn=rng.choice([256, 512, 768]))
+        ttp, tdp, itp = rng.choice([1, 1, 2]), rng.choice([1, 2]), rng.choice([1, 2, 4])
+        tep = iep = 1
+        if arch.is_moe:
+            tep = rng.choice([e for e in (1, 2, 4) if (ttp * tdp) % e == 0])
+            iep = rng.choice([e for e in (1, 2, 4) if itp % e == 0])
+        if heads % ttp or heads % itp or kv % ttp or (itp > kv and itp % kv):
+            continue
+        train = TrainLayout(tp=ttp, dp=tdp, ep=tep)
+        infer = InferLayout(tp=itp, ep=iep, fp8=True, num_engines=rng.choice([1, 2]), engine_name=rng.choice(["vllm", "sglang"]))
+        label = f"{base} h{heads}/kv{kv} {train.label()} -> {infer.label()} {infer.engine_name}"
+        try:
+            job = SimulatedJob(arch, train, infer, dtype=torch.bfloat16)
+            job.compile_all()
+        except NotImplementedError:
+            refused += 1
+            continue
+        assert job.check_coverage() == [], label
+        encoded = job.encode_all(validate=True)
+        mem = HostMemory([p for m in job.train_models for p in m.parameters()] + [p for ms in job.infer_models for m in ms for p in m.parameters()])
+        for table, n_tiles, enc in encoded.values():
+            run_table(table, n_tiles, mem, enc.row_offsets)
+        assert job.mismatches() == [], label
+        done += 1
+    assert refused < 40
