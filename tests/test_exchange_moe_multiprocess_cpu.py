@@ -46,11 +46,14 @@ def _reader(engine_rank, meta_addr, q):
         os.environ["AWEX_DEVICE_TYPE"] = "cpu"
         layout = InferLayout(tp=1, num_engines=2)
         ri = infer_rank_infos(tp=1, engine_rank=engine_rank)[0]
-        engine = SyntheticInferenceEngine(get_arch("tiny-qwen3-moe"), layout, ri, meta_addr, dtype=torch.float32, device="cpu",
-                                          debug_mode_config={"exchange_timeout_s": 120})
+        # the engine has loaded the weights training starts from, so the first update can be validated against
+        # what the engine holds: recorded, cleared, received, compared
+        engine = SyntheticInferenceEngine(get_arch("tiny-qwen3-moe"), layout, ri, meta_addr, dtype=torch.float32, device="cpu", zero=False,
+                                          weights_validation_steps=1, debug_mode_config={"exchange_timeout_s": 120})
         reader = WeightsReader(engine)
         reader.initialize()
         reader.update_weights(step_id=1)
+        assert reader.last_validation_failed == [], reader.last_validation_failed[:5]
         bad1 = engine.mismatches(step=0)
         reader.update_weights(step_id=2)
         bad2 = engine.mismatches(step=2)
