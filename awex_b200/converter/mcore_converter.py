@@ -493,6 +493,12 @@ class McoreToHFWeightConverter:
                 full = get_full_tensor(local[pname], dim=0)
                 n = local[pname].shape[0]
                 gathered[pname] = [full.narrow(0, r * n, n) for r in range(full.shape[0] // n)]
+            if tp_rank >= len(gathered[pname]):
+                raise RuntimeError(
+                    f"{pname}: the canonical tensor draws rows from training TP rank {tp_rank}, but no training TP group of "
+                    f"that size is known here (Megatron's parallel_state is not initialised and set_train_tp_group() was not "
+                    "called); materialised conversion needs it, the transfer path does not"
+                )
             return gathered[pname][tp_rank]
 
         out: List[Tuple[str, torch.Tensor]] = []

@@ -16,12 +16,14 @@ class MegatronEngine(TrainingEngine):
     """``config`` is a plain dict; recognised keys: ``meta_server_addr``,
     ``comm_backend``, ``enable_colocate_mode``, ``enable_debug_mode``,
     ``enable_forward_share_gpu``, validation and dump options, and
-    ``device_wait_timeout_ms``.  ``rank_info`` / ``process_group`` may be given
-    when Megatron's parallel state is not importable."""
+    ``device_wait_timeout_ms``.  ``rank_info`` / ``process_group`` / ``tp_group``
+    (this rank's training tensor-parallel group, needed only by dumps and
+    other materialised conversions) may be given when Megatron's parallel
+    state is not importable."""
 
     engine_name = "mcore"
 
-    def __init__(self, config: dict, hf_config, model, rank_info=None, process_group=None):
+    def __init__(self, config: dict, hf_config, model, rank_info=None, process_group=None, tp_group=None):
         self.config = config
         self.hf_config = hf_config
         self.model = model
@@ -32,6 +34,7 @@ class MegatronEngine(TrainingEngine):
         self.enable_forward_share_gpu = config.get("enable_forward_share_gpu", False)
         self.rank_info = rank_info
         self.process_group = process_group
+        self.tp_group = tp_group
         if self.meta_server_addr:
             ip, port = self.meta_server_addr.rsplit(":", 1)
             os.environ["AWEX_META_SERVER_ADDR"] = self.meta_server_addr

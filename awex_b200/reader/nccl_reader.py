@@ -102,6 +102,25 @@ class WorkerWeightsReader:
         if self.scheduler is not None and hasattr(self.scheduler, "flush_cache"):
             self.scheduler.flush_cache()
 
+    def dump_parameters(self, step_id, names, directory: str) -> List[str]:
+        """Save the received canonical tensors named in ``names`` (as
+        ``reader_<pid>_from_commu_<step>.<name>.pt``, the reference's file names,
+        `awex/reader/weights_reader.py:533-545`) for offline comparison with the
+        writer's dumps."""
+        import os
+
+        os.makedirs(directory, exist_ok=True)
+        written = []
+        for name in names:
+            tensor = self.parameters.get(name)
+            if tensor is None:
+                continue
+            path = os.path.abspath(os.path.join(directory, f"reader_{os.getpid()}_from_commu_{step_id}.{name}.pt"))
+            torch.save(tensor.detach().cpu().contiguous(), path)
+            written.append(path)
+            logger.info(f"[Reader] saved parameter {name} to {path}")
+        return written
+
     # ---- validation: record, clear, compare ----------------------------------------------------------
     def _validation_tensors(self):
         names = sorted(self.required_names)

@@ -224,8 +224,11 @@ class WeightsReader(WeightExchangeReader):
         return _worker_reader(kwargs).snapshot_and_clear()
 
     @staticmethod
-    def _verify_weights_on_tp_worker(**kwargs):
-        return _worker_reader(kwargs).verify_against_snapshot()
+    def _verify_weights_on_tp_worker(step_id=None, dump_weights_list_for_validation=None, dump_weights_dir_for_validation=None, **kwargs):
+        worker = _worker_reader(kwargs)
+        if dump_weights_list_for_validation:
+            worker.dump_parameters(step_id, dump_weights_list_for_validation, dump_weights_dir_for_validation or os.getcwd())
+        return worker.verify_against_snapshot()
 
     # ---- per step -------------------------------------------------------------------------------------
     def _ensure_initialized(self) -> None:
@@ -311,7 +314,11 @@ class WeightsReader(WeightExchangeReader):
             meta.wait_set_until_size("weights_ready_for_send", self.num_engines, timeout=self.timeout)
 
     def _validate_weights(self, step_id) -> bool:
-        results = self.inference_engine.execute_task_in_model_worker(self._verify_weights_on_tp_worker)
+        results = self.inference_engine.execute_task_in_model_worker(
+            self._verify_weights_on_tp_worker, step_id=step_id,
+            dump_weights_list_for_validation=list(self.dump_weights_list_for_validation or []),
+            dump_weights_dir_for_validation=self.dump_weights_dir_for_validation,
+        )
         failed = sorted({name for worker in results for name, ok in worker.items() if not ok})
         verdict = "PASSED" if not failed else "FAILED"
         logger.info(f"[Validation] step {step_id} {verdict}" + (f": {len(failed)} mismatching parameters, e.g. {failed[:8]}" if failed else ""))

@@ -25,12 +25,12 @@ from awex_b200.synthetic.simulate import InferLayout, LocalInferenceEngine
 
 class SyntheticTrainEngine(MegatronEngine):
     def __init__(self, arch: Arch, rank_info: RankInfo, meta_server_addr: str, dtype=torch.bfloat16, device="cpu",
-                 seed: int = 0, process_group=None, comm_backend: str = "nccl", **config):
+                 seed: int = 0, process_group=None, comm_backend: str = "nccl", tp_group=None, **config):
         self.arch, self.dtype, self.device, self.seed = arch, dtype, device, seed
         model = build_megatron_model(arch, rank_info, dtype, device, seed)
         cfg = dict(meta_server_addr=meta_server_addr, comm_backend=comm_backend)
         cfg.update(config)
-        super().__init__(cfg, arch.hf_config(), model, rank_info=rank_info, process_group=process_group)
+        super().__init__(cfg, arch.hf_config(), model, rank_info=rank_info, process_group=process_group, tp_group=tp_group)
 
     def save_hf_checkpoint(self, path: str):
         """Rank 0 writes the canonical tensors (regenerated from the seeds the

@@ -136,6 +136,11 @@ class WeightsExchangeShardingWriter(WeightExchangeWriter):
         check_train_infer_params_meta(self.parameters_meta, self.infer_params_meta, raise_exception=not self.enable_debug_mode)
         self.pp_stage_layer_id_map = resolver.get_pp_stage_layer_id_map()
         self.weight_converter = self._make_converter(self.rank_info)
+        tp_group = getattr(self.train_engine, "tp_group", None)
+        if tp_group is not None:  # materialised conversion (dumps, file oracle) gathers over it
+            from awex_b200.converter.mcore_converter import set_train_tp_group
+
+            set_train_tp_group(tp_group, self.rank_info.tp_size)
         self.num_infer_engines = meta.get_object("num_infer_engines", timeout=self.timeout)
 
     def _make_converter(self, rank_info):

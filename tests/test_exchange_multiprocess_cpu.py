@@ -25,7 +25,8 @@ def _writer(rank, meta_addr, store_port, ckpt_dir, result_q):
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=rank, world_size=WORLD_TRAIN)
     ri = train_rank_infos(tp=WORLD_TRAIN)[rank]
     engine = SyntheticTrainEngine(get_arch("tiny-llama"), ri, meta_addr, dtype=torch.float32, device="cpu", comm_backend="nccl",
-                                  weights_validation_steps=1)
+                                  tp_group=dist.new_group(list(range(WORLD_TRAIN))), weights_validation_steps=1, dump_weights_list_for_validation=["model.norm.weight"],
+                                  dump_weights_dir_for_validation=os.path.join(ckpt_dir, "dumps"))
     writer = NCCLWeightsWriter(engine)
     writer.initialize()
     writer.write_weights(step_id=1, path=ckpt_dir)  # validated step: also saves the file reference
@@ -45,7 +46,9 @@ def _reader(meta_addr, ckpt_dir, result_q):
     os.environ["AWEX_DEVICE_TYPE"] = "cpu"
     layout = InferLayout(tp=1)
     engine = SyntheticInferenceEngine(get_arch("tiny-llama"), layout, infer_rank_infos(tp=1)[0], meta_addr, dtype=torch.float32,
-                                      device="cpu", weights_validation_steps=1, debug_mode_config={"raise_on_validation_fail": True})
+                                      device="cpu", weights_validation_steps=1, debug_mode_config={"raise_on_validation_fail": True},
+                                      dump_weights_list_for_validation=["model.norm.weight"],
+                                      dump_weights_dir_for_validation=os.path.join(ckpt_dir, "dumps"))
     reader = WeightsReader(engine)
     reader.initialize()
     reader.update_weights(step_id=1, path=ckpt_dir)
@@ -76,6 +79,14 @@ def test_two_writers_one_reader_over_gloo():
         for p in procs:
             p.join(timeout=60)
             assert p.exitcode == 0
+        # both sides dumped the listed parameter during the validated step: same values
+        dumps = sorted(os.listdir(os.path.join(ckpt, "dumps")))
+        received = [f for f in dumps if f.startswith("reader_") and f.endswith("_from_commu_1.model.norm.weight.pt")]
+        sent = [f for f in dumps if f.endswith("_converted.pt")]
+        assert len(received) == 1 and len(sent) == WORLD_TRAIN, dumps
+        got = torch.load(os.path.join(ckpt, "dumps", received[0]))
+        want = torch.load(os.path.join(ckpt, "dumps", sent[0]))["model.norm.weight"]
+        assert torch.equal(got, want)
     server.stop()
     reader = next(r for r in results if r[0] == "reader")
     _, bad1, bad2, failed, flushes, bytes_in = reader
