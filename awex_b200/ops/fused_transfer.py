@@ -41,15 +41,16 @@ def _device_array(values, dtype, device) -> torch.Tensor:
 def _max_chunk_shift(table: np.ndarray, n_tiles: int) -> int:
     """log2 of the largest chunk in tiles.  Measured on B200: tables of plain
     copies run fastest with chunks of 4 tiles (the depth of the load pipeline),
-    tables dominated by quantised blocks with 16.  ``AWEX_CHUNK_MB`` (the
-    reference's knob for its chunked co-located mode,
-    `awex/transfer/nccl_stream_batch.py:438-470`) overrides the choice with a
-    chunk size in MiB of staged source data."""
+    tables dominated by quantised blocks with 16.  ``AWEX_XFER_CHUNK_MB``
+    overrides the choice with a chunk size in MiB of staged source data.  (The
+    reference's ``AWEX_CHUNK_MB`` bounds staging memory of its co-located
+    exchange; this kernel stages nothing in device memory, so that knob only
+    acts on the message transport.)"""
     import os
 
     from awex_b200.transfer.descriptors import OP_FP8_BLOCK, STAGE_BYTES
 
-    override = os.environ.get("AWEX_CHUNK_MB")
+    override = os.environ.get("AWEX_XFER_CHUNK_MB")
     if override:
         try:
             tiles = max(1, int(float(override) * 1024 * 1024) // STAGE_BYTES)

@@ -18,7 +18,7 @@ import tempfile
 import threading
 import time
 from dataclasses import dataclass
-from typing import Callable, Dict, Iterable, Optional, Sequence, Tuple
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -179,12 +179,63 @@ def two_phase_send_recv(rank: int, stage: int, world: int, sends: Sequence[P2PRe
 
 
 # ------------------------------------------------------------------------------------ co-located exchange
+def split_by_budget(sizes: Sequence[int], budget: int, max_entries: int = 0) -> List[Tuple[int, int]]:
+    """Cut a list of message-entry sizes into consecutive ``[begin, end)`` runs of
+    at most ``budget`` bytes each (a single entry larger than the budget gets a
+    run of its own) and, with ``max_entries > 0``, at most that many entries.
+    ``budget <= 0`` sets no byte bound.  Sender and receiver call
+    this on the same sizes, so they agree on the runs without a collective; the
+    reference reaches the same agreement with a MIN and a MAX all-reduce
+    (`awex/transfer/nccl_stream_batch.py:594-672`)."""
+    if not sizes:
+        return []
+    if budget <= 0 and max_entries <= 0:
+        return [(0, len(sizes))]
+    runs, begin, acc = [], 0, 0
+    for i, n in enumerate(sizes):
+        if i > begin and ((budget > 0 and acc + n > budget) or (max_entries > 0 and i - begin >= max_entries)):
+            runs.append((begin, i))
+            begin, acc = i, 0
+        acc += n
+    runs.append((begin, len(sizes)))
+    return runs
+
+
+def chunk_budget_from_env() -> int:
+    """Bytes of staging one message may take, from ``AWEX_CHUNK_MB`` (0 or unset:
+    no bound), the reference's knob for its chunked co-located mode
+    (`awex/transfer/nccl_stream_batch.py:115`)."""
+    import os
+
+    try:
+        return max(0, int(float(os.environ.get("AWEX_CHUNK_MB", "0") or "0") * 1024 * 1024))
+    except ValueError:
+        return 0
+
+
+def chunk_entries_from_env() -> int:
+    """Entries per run from ``AWEX_CHUNK_OPS`` (0 or unset: no bound), the
+    reference's override of its computed step
+    (`awex/transfer/nccl_stream_batch.py:612-619`)."""
+    import os
+
+    try:
+        return max(0, int(os.environ.get("AWEX_CHUNK_OPS", "0").strip() or "0"))
+    except ValueError:
+        return 0
+
+
 class NcclColocateTransport:
     """Exchange over ONE communicator whose ranks each hold a training shard and
     an inference shard on the same device (`nccl_comm.py:53-224` in the
     reference).  Messages are the packed per-destination payloads of the lowered
     copy items; the walk over ring stages bounds the staging memory to one
     outgoing and one incoming message at a time, and stage 0 is a local copy.
+    ``chunk_bytes`` (default: ``AWEX_CHUNK_MB``) bounds it further: each message
+    is cut into runs of entries of at most that many bytes, exchanged one run at
+    a time (`awex/transfer/nccl_stream_batch.py:438-805`); ``chunk_entries``
+    (default: ``AWEX_CHUNK_OPS``) bounds the entries per run.  ``peak_staging_bytes``
+    records the largest amount of staging that was live at once.
 
     ``items`` are this rank's copy items (destination = inference transfer
     rank), ``local`` its training tensors, ``views`` its inference views,
@@ -192,14 +243,56 @@ class NcclColocateTransport:
     deliver here.
     """
 
-    def __init__(self, transfer_rank: int, world_size: int, group=None, device="cpu"):
+    def __init__(self, transfer_rank: int, world_size: int, group=None, device="cpu", chunk_bytes: Optional[int] = None,
+                 chunk_entries: Optional[int] = None):
         self.transfer_rank, self.world_size, self.group = transfer_rank, world_size, group
         self.device = torch.device(device)
+        self.chunk_bytes = chunk_budget_from_env() if chunk_bytes is None else int(chunk_bytes)
+        self.chunk_entries = chunk_entries_from_env() if chunk_entries is None else int(chunk_entries)
+        self.peak_staging_bytes = 0
+
+    def _runs(self, entries: Sequence[tuple]) -> List[Tuple[int, int]]:
+        from awex_b200.transfer.cpu_exec import entry_nbytes
+
+        return split_by_budget([entry_nbytes(e) for e in entries], self.chunk_bytes, self.chunk_entries)
+
+    def _exchange_chunked(self, out: Dict[int, list], inc: Dict[int, Sequence[tuple]], local, views, exchange, label: str) -> int:
+        """Exchange the messages ``out`` (peer -> items) and ``inc`` (peer ->
+        manifest entries) run by run: in step ``k`` every message ships its
+        ``k``-th run, so at most one run per message is staged at a time."""
+        from awex_b200.transfer.cpu_exec import entry_nbytes, pack_message, unpack_message
+
+        out_runs = {p: self._runs([it.manifest_entry() for it in items]) for p, items in out.items()}
+        in_runs = {p: self._runs(entries) for p, entries in inc.items()}
+        steps = max([len(r) for r in out_runs.values()] + [len(r) for r in in_runs.values()] + [0])
+        moved = 0
+        for k in range(steps):
+            sends, recvs, landing, live = [], [], [], 0
+            for peer in sorted(out):
+                if k < len(out_runs[peer]):
+                    b, e = out_runs[peer][k]
+                    msg = pack_message(out[peer][b:e], local).to(self.device)
+                    sends.append(P2PRequest(True, msg, peer, f"{label}.{k}->{peer}"))
+                    moved += msg.numel()
+                    live += msg.numel()
+            for peer in sorted(inc):
+                if k < len(in_runs[peer]):
+                    b, e = in_runs[peer][k]
+                    part = inc[peer][b:e]
+                    buf = torch.empty(sum(entry_nbytes(x) for x in part), dtype=torch.uint8, device=self.device)
+                    recvs.append(P2PRequest(False, buf, peer, f"{label}.{k}<-{peer}"))
+                    landing.append((part, buf))
+                    live += buf.numel()
+            self.peak_staging_bytes = max(self.peak_staging_bytes, live)
+            exchange(sends, recvs, f"{label} run {k}")
+            for part, buf in landing:
+                unpack_message(part, buf, views)
+        return moved
 
     def update_weights_in_colocate_mode(self, train_to_infer: Dict[int, int], infer_to_train: Dict[int, int], items, local,
                                         views, incoming: Dict[int, Sequence[tuple]], use_group: bool = True,
                                         schedule: str = "ring") -> Dict[str, float]:
-        from awex_b200.transfer.cpu_exec import entry_nbytes, execute_items, pack_message, unpack_message
+        from awex_b200.transfer.cpu_exec import execute_items
 
         validate_rank_mappings(train_to_infer, infer_to_train)
         me, world = self.transfer_rank, self.world_size
@@ -218,49 +311,34 @@ class NcclColocateTransport:
                 if me in by_dst:
                     moved += execute_items(by_dst[me], local, {me: views})
                 continue
-            sends, recvs = [], []
-            if to in by_dst:
-                msg = pack_message(by_dst[to], local).to(self.device)
-                sends.append(P2PRequest(True, msg, to, f"stage{stage}->{to}"))
-                moved += msg.numel()
-            entries = incoming.get(frm)
-            buf = None
-            if entries:
-                buf = torch.empty(sum(entry_nbytes(e) for e in entries), dtype=torch.uint8, device=self.device)
-                recvs.append(P2PRequest(False, buf, frm, f"stage{stage}<-{frm}"))
-            if use_group:
-                batch_send_recv(sends + recvs, group=self.group, what=f"colocate stage {stage}")
-            else:
-                two_phase_send_recv(me, stage, world, sends, recvs, group=self.group, what=f"colocate stage {stage}")
-            if buf is not None:
-                unpack_message(entries, buf, views)
+            out = {to: by_dst[to]} if to in by_dst else {}
+            inc = {frm: incoming[frm]} if incoming.get(frm) else {}
+
+            def exchange(sends, recvs, what, stage=stage):
+                if use_group:
+                    batch_send_recv(sends + recvs, group=self.group, what=what)
+                else:
+                    two_phase_send_recv(me, stage, world, sends, recvs, group=self.group, what=what)
+
+            moved += self._exchange_chunked(out, inc, local, views, exchange, f"colocate stage {stage}")
         return {"seconds": time.time() - started, "bytes": float(moved)}
 
     def _recursive(self, by_dst, local, views, incoming, started) -> Dict[str, float]:
         """log2(world) rounds of two phases; in each phase all messages of one
         direction between the two halves are in flight together."""
-        from awex_b200.transfer.cpu_exec import entry_nbytes, execute_items, pack_message, unpack_message
+        from awex_b200.transfer.cpu_exec import execute_items
 
         me = self.transfer_rank
         moved = execute_items(by_dst[me], local, {me: views}) if me in by_dst else 0
         for round_idx, (peers, send_first) in enumerate(recursive_partition_rounds(me, self.world_size)):
-            sends = []
-            for peer in peers:
-                if peer in by_dst:
-                    msg = pack_message(by_dst[peer], local).to(self.device)
-                    sends.append(P2PRequest(True, msg, peer, f"round{round_idx}->{peer}"))
-                    moved += msg.numel()
-            recvs, landing = [], []
-            for peer in peers:
-                entries = incoming.get(peer)
-                if entries:
-                    buf = torch.empty(sum(entry_nbytes(e) for e in entries), dtype=torch.uint8, device=self.device)
-                    recvs.append(P2PRequest(False, buf, peer, f"round{round_idx}<-{peer}"))
-                    landing.append((entries, buf))
-            for phase_reqs in ((sends, recvs) if send_first else (recvs, sends)):
-                batch_send_recv(phase_reqs, group=self.group, what=f"recursive round {round_idx}")
-            for entries, buf in landing:
-                unpack_message(entries, buf, views)
+            out = {p: by_dst[p] for p in peers if p in by_dst}
+            inc = {p: incoming[p] for p in peers if incoming.get(p)}
+
+            def exchange(sends, recvs, what, send_first=send_first):
+                for phase_reqs in ((sends, recvs) if send_first else (recvs, sends)):
+                    batch_send_recv(phase_reqs, group=self.group, what=what)
+
+            moved += self._exchange_chunked(out, inc, local, views, exchange, f"recursive round {round_idx}")
         return {"seconds": time.time() - started, "bytes": float(moved)}
 
 

@@ -252,16 +252,16 @@ def test_span_index_agrees_with_a_linear_scan():
 def test_environment_table(monkeypatch):
     from awex_b200.utils import env
 
-    monkeypatch.setenv("AWEX_CHUNK_OPS", "64")
+    monkeypatch.setenv("AWEX_P2P_HCCL_BUFFER_SIZE", "64")
     monkeypatch.setenv("AWEX_P2P_TRACE", "1")
     monkeypatch.setenv("AWEX_TYPO", "x")
     lines = env.describe_env()
-    assert any(line.startswith("AWEX_CHUNK_OPS=64: no effect") for line in lines)
+    assert any(line.startswith("AWEX_P2P_HCCL_BUFFER_SIZE=64: no effect") for line in lines)
     assert any(line.startswith("AWEX_TYPO=x: not a variable") for line in lines)
     assert env.flag("AWEX_P2P_TRACE") and not env.flag("AWEX_MEM_DEBUG")
     warned = []
     env.warn_about_ignored(SimpleNamespace(warning=warned.append))
-    assert len(warned) == 1 and "AWEX_CHUNK_OPS" in warned[0]
+    assert len(warned) == 1 and "AWEX_P2P_HCCL_BUFFER_SIZE" in warned[0]
     # every variable the package reads is in the table
     import os
     import re
