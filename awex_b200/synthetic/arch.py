@@ -30,6 +30,7 @@ class Arch:
     num_experts: int = 0
     expert_ffn: int = 0
     top_k: int = 0
+    norm_head: bool = False  # lm_head is published with unit-norm columns (`mcore_converter.py:668-675` in the reference)
 
     @property
     def is_moe(self) -> bool:
@@ -48,6 +49,8 @@ class Arch:
             tie_word_embeddings=self.tie_embeddings,
             attention_bias=self.qkv_bias,
         )
+        if self.norm_head:
+            cfg.norm_head = True
         if self.is_moe:
             cfg.num_experts = self.num_experts
             cfg.moe_intermediate_size = self.expert_ffn
@@ -94,6 +97,7 @@ PRESETS: Dict[str, Arch] = {
         Arch("tiny-qwen3-moe", "Qwen3MoeForCausalLM", 2, 256, 8, 4, 32, 0, 1024, qk_norm=True,
              num_experts=8, expert_ffn=128, top_k=2),
         Arch("tiny-qwen2", "Qwen2ForCausalLM", 2, 256, 8, 4, 32, 512, 1024, qkv_bias=True),
+        Arch("tiny-llama-norm-head", "LlamaForCausalLM", 2, 256, 4, 2, 64, 512, 1024, norm_head=True),
     )
 }
 

@@ -26,7 +26,9 @@ from awex_b200.synthetic.arch import Arch
 from awex_b200.synthetic.models import FlatModule, build_megatron_model, build_vllm_model, vllm_model_context
 from awex_b200.synthetic.topology import infer_rank_infos, train_rank_infos
 from awex_b200.transfer.cpu_exec import execute_items
-from awex_b200.transfer.lowering import CopyItem, LocalParam, SendProgramCompiler, check_exactly_once, manifest_by_destination
+from awex_b200.transfer.lowering import (
+    CopyItem, LocalParam, SendProgramCompiler, check_exactly_once, manifest_by_destination, refresh_derived,
+)
 from awex_b200.transfer.transfer_plan import TransferPlanBuilder
 from awex_b200.utils.common import check_train_infer_params_meta
 
@@ -183,7 +185,22 @@ class SimulatedJob:
         compiler = SendProgramCompiler(
             ri, self.train_ranks, self._train_converter, self.local_params(train_rank), self.infer_meta, self.train_meta, self.builder
         )
-        return compiler.compile()
+        items = compiler.compile()
+        if not hasattr(self, "derived"):
+            self.derived, self._derived_buffers = {}, {}
+        self.derived[train_rank] = list(compiler.derived.values())
+        return items
+
+    def local_tensors(self, train_rank: int) -> Dict[Tuple[str, int], torch.Tensor]:
+        """(name, chunk) -> tensor for everything ``train_rank``'s items read: its
+        parameters and, freshly recomputed, its derived tensors."""
+        local = {(n, 0): t for n, t in self.train_models[train_rank].named_parameters()}
+        derived = getattr(self, "derived", {}).get(train_rank, [])
+        if derived:
+            local.update(self._derived_buffers.setdefault(train_rank, {}))
+            refresh_derived(derived, local)
+            self._derived_buffers[train_rank] = {d.key: local[d.key] for d in derived}
+        return local
 
     def compile_all(self) -> Dict[int, List[CopyItem]]:
         self.programs = {r: self.compile_send_program(r) for r in range(self.train.world)}
@@ -214,8 +231,7 @@ class SimulatedJob:
         views = self.destination_views()
         total = 0
         for rank, items in self.programs.items():
-            local = {(n, 0): t for n, t in self.train_models[rank].named_parameters()}
-            total += execute_items(items, local, views)
+            total += execute_items(items, self.local_tensors(rank), views)
         return total
 
     # ---- single-GPU emulation of all ranks ------------------------------------------------------------
@@ -229,7 +245,7 @@ class SimulatedJob:
         dst_spans = [TensorAddr.of(p).byte_span() for models in self.infer_models for m in models for p in m.parameters()]
         out = {}
         for rank, items in self.programs.items():
-            src_addrs = {(n, 0): TensorAddr.of(t) for n, t in self.train_models[rank].named_parameters()}
+            src_addrs = {key: TensorAddr.of(t) for key, t in self.local_tensors(rank).items()}
             table, n_tiles, enc = encode_items(items, src_addrs, dst_addrs)
             if validate:
                 problems = validate_table(table, n_tiles, [a.byte_span() for a in src_addrs.values()], dst_spans)
@@ -257,6 +273,9 @@ class SimulatedJob:
         return self.gpu_programs
 
     def run_gpu(self, epoch: int) -> None:
+        for rank, derived in getattr(self, "derived", {}).items():
+            if derived:
+                self.local_tensors(rank)  # recompute derived tensors in place, ahead of the transfer in stream order
         for prog in self.gpu_programs.values():
             prog.launch(epoch)
         self.waiter.launch(epoch)

@@ -88,6 +88,50 @@ class LocalParam:
     dtype: torch.dtype
 
 
+# Value operations that need a whole canonical tensor at once (a reduction over
+# it) cannot ride along tile by tile.  Their result is kept in a persistent
+# sender-side buffer that is refreshed before every update and sent from there
+# with plain copies.
+WHOLE_TENSOR_OPS = ("l2norm_dim0",)
+DERIVED_PREFIX = "__derived__/"
+
+
+@dataclass
+class DerivedTensor:
+    """A sender-side tensor computed from local parameters before each update:
+    ``value_op(rows.gather(local))`` of one canonical tensor, addressed by items
+    as local source ``key`` in canonical coordinates."""
+
+    key: Tuple[str, int]  # (DERIVED_PREFIX + canonical name, vp_stage)
+    spec: TensorSpec
+    tp_rank: int
+
+    def compute(self, local: Dict[Tuple[str, int], torch.Tensor]) -> torch.Tensor:
+        def fetch(src):
+            pname, tp_rank = src
+            if tp_rank != self.tp_rank:
+                raise RuntimeError(f"{self.key[0]}: rows of training TP rank {tp_rank} are not held here")
+            return local[(pname, self.key[1])]
+
+        return self.spec.value_op.apply(self.spec.rows.gather(fetch))
+
+
+def refresh_derived(derived: Iterable[DerivedTensor], local: Dict[Tuple[str, int], torch.Tensor]) -> int:
+    """Recompute every derived tensor into its buffer in ``local`` (allocated on
+    first use, next to the parameters it comes from; never reallocated, so
+    descriptor tables that hold its address stay valid).  Returns the number of
+    tensors refreshed."""
+    n = 0
+    with torch.no_grad():
+        for d in derived:
+            value = d.compute(local)
+            if d.key not in local:
+                local[d.key] = torch.empty_like(value, memory_format=torch.contiguous_format)
+            local[d.key].copy_(value)
+            n += 1
+    return n
+
+
 def _tp_peers(my: RankInfo, all_ranks: Sequence[RankInfo]) -> List[RankInfo]:
     """Training ranks that hold the other TP shards of what ``my`` holds."""
     if my.tp_size <= 1:
@@ -131,6 +175,8 @@ class SendProgramCompiler:
         self.builder = builder
         self.my_transfer_rank = rank_info.global_rank + builder.infer_world_size
         self._param_by_key = {(p.name, p.vp_stage): p for p in self.local_params}
+        # filled by compile(): tensors the sender must compute before each update
+        self.derived: Dict[Tuple[str, int], DerivedTensor] = {}
 
     # ---- symbolic conversion for one (possibly virtual) sender ----------------------------
     def _specs_for(self, sender: RankInfo) -> Dict[str, Tuple[TensorSpec, LocalParam]]:
@@ -194,6 +240,22 @@ class SendProgramCompiler:
         tail_ext = tuple(op.overlap_shape[1:])
         dst_row0 = op.inf_slices[0].start
         out: List[CopyItem] = []
+        if spec.value_op.kind in WHOLE_TENSOR_OPS:
+            owners = {src[1] for src in spec.rows.sources()}
+            if owners != {my_tp}:
+                if my_tp not in owners:
+                    return []
+                raise NotImplementedError(
+                    f"{spec.name}: {spec.value_op.kind} needs the whole tensor on one rank, but its rows come from "
+                    f"training TP ranks {sorted(owners)}"
+                )
+            key = (DERIVED_PREFIX + spec.name, lp.vp_stage)
+            self.derived.setdefault(key, DerivedTensor(key, spec, my_tp))
+            return [CopyItem(
+                src_param=key[0], vp_stage=key[1], src_start=(row0,) + tail_src, extent=(n_rows,) + tail_ext,
+                dst_rank=op.recv_rank, dst_name=spec.name, dst_start=(dst_row0,) + tail_dst,
+                src_dtype=spec.value_op.out_dtype(spec.src_dtype), dst_dtype=dst_dtype, value_op=IDENTITY,
+            )]
         segments = spec.rows.segments(row0, n_rows)
         if spec.value_op.kind == "fp8_block":
             # a quantisation block needs all of its rows at once: keep the box whole
@@ -240,8 +302,6 @@ class SendProgramCompiler:
                         raise ValueError(f"{spec.name}: piece ends inside a block at {end} (dim {d}, shard extent {shard[d]})")
                 item.scale_name = spec.name + SCALE_SUFFIX
                 item.scale_start = (item.dst_start[0] // FP8_BLOCK, item.dst_start[1] // FP8_BLOCK)
-            elif spec.value_op.kind == "l2norm_dim0":
-                raise NotImplementedError(f"{spec.name}: column-normalised tensors must be materialised before transfer")
             out.append(item)
         return out
 

@@ -18,7 +18,7 @@ from typing import List
 import torch
 
 from awex_b200 import logging
-from awex_b200.transfer.lowering import LocalParam, SendProgramCompiler
+from awex_b200.transfer.lowering import LocalParam, SendProgramCompiler, refresh_derived
 from awex_b200.transfer.transfer_plan import TransferPlanBuilder, compute_transfer_plan_stats
 from awex_b200.utils.trace import phase
 from awex_b200.utils.common import compute_statistics
@@ -49,6 +49,11 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
             self.parameters_meta, self.builder,
         )
         self.items = compiler.compile()
+        # tensors that must be computed from whole parameters before each update (a column-normalised
+        # head): persistent buffers beside the parameters, sent with plain copies
+        self.derived = list(compiler.derived.values())
+        self._local = local
+        refresh_derived(self.derived, local)
         self.transfer_plan = self.builder.build_local_transfer_plan(self.infer_params_meta, self.parameters_meta, self.transfer_rank)
         stats = compute_transfer_plan_stats(self.transfer_plan)
         logger.info(f"Rank[{self.transfer_rank}] plan hash {stats['full_hash'][:16]} stats {stats['total']}; {len(self.items)} copy items")
@@ -70,6 +75,9 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
     def _write_weights(self, step_id, **kwargs) -> None:
         t0 = time.time()
         self.epoch += 1
+        if self.derived:
+            with phase("derive_tensors"):
+                refresh_derived(self.derived, self._local)  # same stream as the transfer: ordered before it
         with phase("send_weights"):
             self.transport.send(self.epoch, synchronize=kwargs.get("synchronize", True))
         compute_statistics(self._history, step_id, time.time() - t0, "Send weights")

@@ -108,3 +108,24 @@ def test_random_odd_shaped_items_encode_to_equivalent_tables():
         dst.fill_(-7.0)
         run_chunked(table, n_tiles, HostMemory([src, base]), grid=3, chunk_shift=1, row_offsets=enc.row_offsets)
         assert torch.equal(dst.float(), want.float()), (case, item)
+
+
+def test_derived_sender_buffers_are_ordinary_sources_of_the_table():
+    """A column-normalised head lives in a sender-side buffer; the table reads it
+    like any parameter and address validation covers it."""
+    import dataclasses
+
+    arch = dataclasses.replace(get_arch("tiny-llama"), norm_head=True, name="tiny-llama-norm-head")
+    job = SimulatedJob(arch, TrainLayout(tp=2), InferLayout(tp=2), dtype=torch.bfloat16)
+    job.compile_all()
+    encoded = job.encode_all(validate=True)
+    buffers = [job.local_tensors(r)[("__derived__/lm_head.weight", 0)] for r in encoded]
+    tensors = [p for m in job.train_models for p in m.parameters()] + buffers
+    tensors += [p for models in job.infer_models for m in models for p in m.parameters()]
+    mem = HostMemory(tensors)
+    for rank, (table, n_tiles, enc) in encoded.items():
+        assert run_table(table, n_tiles, mem, enc.row_offsets) == n_tiles
+    assert {m.rsplit("/", 1)[1] for m in job.mismatches()} == {"lm_head.weight"}
+    for r, model in enumerate(job.infer_models[0]):
+        got = dict(model.named_parameters())["lm_head.weight"]
+        assert torch.equal(got, buffers[r])  # training TP2 -> inference TP2: shard r is sender r's buffer

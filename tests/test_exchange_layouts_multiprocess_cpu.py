@@ -17,6 +17,8 @@ def _layouts(case):
         return "tiny-llama", dict(tp=1, pp=2), InferLayout(tp=2), torch.float32
     if case == "tp1_to_tp2_fp8":
         return "tiny-llama", dict(tp=1), InferLayout(tp=2, fp8=True), torch.bfloat16
+    if case == "tp1_to_tp2_norm_head":
+        return "tiny-llama-norm-head", dict(tp=1), InferLayout(tp=2), torch.float32
     raise ValueError(case)
 
 
@@ -70,7 +72,18 @@ def _reader(case, worker_rank, meta_addr, store_port, q):
         reader = WeightsReader(engine)
         reader.initialize()
         reader.update_weights(step_id=1)
-        q.put(("reader", worker_rank, engine.mismatches(step=0)))
+        bad = engine.mismatches(step=0)
+        if case.endswith("norm_head"):
+            # the head arrives with unit-norm columns (computed by the single training rank over the whole vocabulary)
+            from awex_b200.synthetic.models import CanonicalWeights
+
+            a = get_arch(arch)
+            full = CanonicalWeights(a, dtype, "cpu").get("lm_head.weight", (a.vocab, a.hidden))
+            want = torch.nn.functional.normalize(full, dim=0, p=2, eps=1e-7).chunk(layout.tp, 0)[worker_rank]
+            got = dict(engine.model.named_parameters())["lm_head.weight"]
+            assert bad == ["lm_head.weight"] and torch.equal(got, want), bad
+            bad = []
+        q.put(("reader", worker_rank, bad))
         dist.destroy_process_group()
     except BaseException as exc:
         q.put(("error", f"reader {worker_rank}: {exc!r}", 0))
@@ -78,7 +91,7 @@ def _reader(case, worker_rank, meta_addr, store_port, q):
 
 
 @pytest.mark.timeout(400)
-@pytest.mark.parametrize("case", ["pp2_to_tp2", "tp1_to_tp2_fp8"])
+@pytest.mark.parametrize("case", ["pp2_to_tp2", "tp1_to_tp2_fp8", "tp1_to_tp2_norm_head"])
 def test_layout_over_gloo(case):
     from awex_b200.meta.meta_server import MetaServer
     from awex_b200.utils.common import get_free_port

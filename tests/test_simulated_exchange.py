@@ -225,3 +225,51 @@ def test_fp8_slices_that_end_inside_a_block_are_refused_with_a_reason():
     assert job.check_coverage() == []
     job.run_cpu()
     assert job.mismatches() == []
+
+
+@pytest.mark.parametrize("train_tp,infer_tp", [(1, 2), (2, 1), (2, 4)])
+def test_column_normalised_head_is_derived_on_the_sender(train_tp, infer_tp):
+    """``norm_head``: the head is published with unit-norm columns, each training
+    rank normalising the vocabulary slice it holds (`awex/converter/mcore_converter.py:668-675`
+    in the reference).  The reduction needs the whole local tensor, so the sender keeps the
+    result in a buffer of its own and sends it with plain copies; a second update
+    after the parameters changed must send the new values from the same buffer."""
+    import dataclasses
+
+    from awex_b200.synthetic.models import CanonicalWeights
+
+    arch = dataclasses.replace(get_arch("tiny-llama"), norm_head=True, name="tiny-llama-norm-head")
+    job = SimulatedJob(arch, TrainLayout(tp=train_tp), InferLayout(tp=infer_tp), dtype=torch.float32)
+    programs = job.compile_all()
+    assert not job.check_coverage()
+    for rank, items in programs.items():
+        head = [it for it in items if it.dst_name == "lm_head.weight"]
+        assert head and all(it.src_param == "__derived__/lm_head.weight" and it.value_op.kind == "none" for it in head)
+        assert [d.key[0] for d in job.derived[rank]] == ["__derived__/lm_head.weight"]
+
+    def expected_shards(scale: float):
+        full = CanonicalWeights(arch, torch.float32, "cpu").get("lm_head.weight", (arch.vocab, arch.hidden)) * scale
+        normed = torch.cat([torch.nn.functional.normalize(c, dim=0, p=2, eps=1e-7) for c in full.chunk(train_tp, 0)], 0)
+        return list(normed.chunk(infer_tp, 0))
+
+    def received():
+        return [dict(m.named_parameters())["lm_head.weight"] for m in job.infer_models[0]]
+
+    job.run_cpu()
+    assert {m.rsplit("/", 1)[1] for m in job.mismatches()} == {"lm_head.weight"}  # only the head differs from the raw weights
+    for got, want in zip(received(), expected_shards(1.0)):
+        assert torch.equal(got, want)
+    buffers = {r: job.local_tensors(r)[("__derived__/lm_head.weight", 0)].data_ptr() for r in programs}
+    # an "optimizer step": rows scaled unevenly, so that the normalised columns change
+    ramp = torch.linspace(0.5, 2.0, arch.vocab).unsqueeze(1)
+    for r, model in enumerate(job.train_models):
+        w = dict(model.named_parameters())["output_layer.weight"]
+        n = w.shape[0]
+        with torch.no_grad():
+            w.mul_(ramp[r * n : (r + 1) * n])
+    job.run_cpu()
+    full = CanonicalWeights(arch, torch.float32, "cpu").get("lm_head.weight", (arch.vocab, arch.hidden)) * ramp
+    normed = torch.cat([torch.nn.functional.normalize(c, dim=0, p=2, eps=1e-7) for c in full.chunk(train_tp, 0)], 0)
+    for got, want in zip(received(), normed.chunk(infer_tp, 0)):
+        assert torch.equal(got, want)
+    assert buffers == {r: job.local_tensors(r)[("__derived__/lm_head.weight", 0)].data_ptr() for r in programs}
