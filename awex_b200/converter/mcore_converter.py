@@ -76,6 +76,24 @@ def get_full_tensor(weight: torch.Tensor, dim: int = 0) -> torch.Tensor:
     return torch.cat(parts, dim=dim)
 
 
+def gather_tp_shards(weight: torch.Tensor, expected: int) -> List[torch.Tensor]:
+    """The training TP group's shards of ``weight`` in TP rank order
+    (collective).  ``expected`` is the TP size the caller's rank coordinates
+    name; a missing or differently sized group is an error, not a silent
+    single-shard answer."""
+    group, size = _train_tp_group()
+    if size != expected:
+        raise RuntimeError(
+            f"a gather over {expected} training TP ranks is needed, but the known training TP group has size {size} "
+            "(initialise Megatron's parallel_state, pass tp_group= to the training engine, or call set_train_tp_group())"
+        )
+    if size == 1:
+        return [weight]
+    parts = [torch.empty_like(weight, memory_format=torch.contiguous_format) for _ in range(size)]
+    dist.all_gather(parts, weight.contiguous(), group=group)
+    return parts
+
+
 def head_size_of(tf_config) -> int:
     kv_channels = cfg_get(tf_config, "kv_channels")
     if kv_channels is not None:

@@ -198,9 +198,20 @@ class SimulatedJob:
         derived = getattr(self, "derived", {}).get(train_rank, [])
         if derived:
             local.update(self._derived_buffers.setdefault(train_rank, {}))
-            refresh_derived(derived, local)
+            from awex_b200.transfer.lowering import _tp_peers
+
+            peers = _tp_peers(self.train_ranks[train_rank], self.train_ranks)
+
+            def gather(name, _vp):  # all ranks live in this process: read the TP peers' shards directly
+                return [dict(self.train_models[p.global_rank].named_parameters())[name] for p in peers]
+
+            refresh_derived(derived, local, gather)
             self._derived_buffers[train_rank] = {d.key: local[d.key] for d in derived}
         return local
+
+    def source_tensors(self) -> List[torch.Tensor]:
+        """Every tensor any rank's items read: all training parameters and derived buffers."""
+        return [t for r in range(self.train.world) for t in self.local_tensors(r).values()]
 
     def compile_all(self) -> Dict[int, List[CopyItem]]:
         self.programs = {r: self.compile_send_program(r) for r in range(self.train.world)}

@@ -105,26 +105,43 @@ class DerivedTensor:
     key: Tuple[str, int]  # (DERIVED_PREFIX + canonical name, vp_stage)
     spec: TensorSpec
     tp_rank: int
+    # rows of training TP peers are needed (a collective over the training TP group)
+    gathers: bool = False
 
-    def compute(self, local: Dict[Tuple[str, int], torch.Tensor]) -> torch.Tensor:
+    def compute(self, local: Dict[Tuple[str, int], torch.Tensor], gather_fn: Optional[Callable] = None) -> torch.Tensor:
+        shards: Dict[str, Sequence[torch.Tensor]] = {}
+        if self.gathers:
+            # every TP rank gathers every source tensor, in one order, whether or not it uses all of them
+            if gather_fn is None:
+                raise RuntimeError(f"{self.key[0]} draws rows from training TP peers; a gather function is needed")
+            for pname in sorted({src[0] for src in self.spec.rows.sources()}):
+                shards[pname] = gather_fn(pname, self.key[1])
+
         def fetch(src):
             pname, tp_rank = src
-            if tp_rank != self.tp_rank:
+            if tp_rank == self.tp_rank:
+                return local[(pname, self.key[1])]
+            if pname not in shards or tp_rank >= len(shards[pname]):
                 raise RuntimeError(f"{self.key[0]}: rows of training TP rank {tp_rank} are not held here")
-            return local[(pname, self.key[1])]
+            return shards[pname][tp_rank]
 
-        return self.spec.value_op.apply(self.spec.rows.gather(fetch))
+        value = self.spec.rows.gather(fetch)
+        return self.spec.value_op.apply(value) if self.spec.value_op.kind in WHOLE_TENSOR_OPS else value
 
 
-def refresh_derived(derived: Iterable[DerivedTensor], local: Dict[Tuple[str, int], torch.Tensor]) -> int:
+def refresh_derived(derived: Iterable[DerivedTensor], local: Dict[Tuple[str, int], torch.Tensor],
+                    gather_fn: Optional[Callable] = None) -> int:
     """Recompute every derived tensor into its buffer in ``local`` (allocated on
     first use, next to the parameters it comes from; never reallocated, so
-    descriptor tables that hold its address stay valid).  Returns the number of
-    tensors refreshed."""
+    descriptor tables that hold its address stay valid).  ``gather_fn(name,
+    vp_stage)`` returns the training TP group's shards of a local parameter in TP
+    rank order; it is a collective, which every rank of the group reaches in the
+    same order because derived tensors are refreshed sorted by name.  Returns the
+    number of tensors refreshed."""
     n = 0
     with torch.no_grad():
-        for d in derived:
-            value = d.compute(local)
+        for d in sorted(derived, key=lambda d: d.key):
+            value = d.compute(local, gather_fn)
             if d.key not in local:
                 local[d.key] = torch.empty_like(value, memory_format=torch.contiguous_format)
             local[d.key].copy_(value)
@@ -177,6 +194,34 @@ class SendProgramCompiler:
         self._param_by_key = {(p.name, p.vp_stage): p for p in self.local_params}
         # filled by compile(): tensors the sender must compute before each update
         self.derived: Dict[Tuple[str, int], DerivedTensor] = {}
+        # canonical names whose quantisation blocks mix rows of several training TP ranks: their
+        # owner gathers the rows before each update instead of every rank sending its own
+        self.gathered_names: set = set()
+
+    def _names_needing_gather(self, all_specs: Dict[int, Dict[str, Tuple[TensorSpec, LocalParam]]]) -> set:
+        """Block-quantised tensors with a planned box whose rows are held by more
+        than one training TP rank.  Every rank of the TP group computes this from
+        the same peers' plans, so the whole group agrees."""
+        names = set()
+        for sender in self.peers:
+            virtual_rank = sender.global_rank + self.builder.infer_world_size
+            for n, (spec, _lp) in all_specs[sender.global_rank].items():
+                if n in names or spec.rows is None or spec.value_op.kind != "fp8_block" or spec.scale_of is not None:
+                    continue
+                if len({src[1] for src in spec.rows.sources()}) < 2:
+                    continue
+                if n not in self.train_meta or n not in self.infer_meta or n in self.builder.skip_names:
+                    continue
+                for op in self.builder._build_parameter_communication_plan(
+                    n, self.infer_meta[n], self.train_meta[n], global_transfer_rank=virtual_rank
+                ):
+                    if op.send_rank != virtual_rank:
+                        continue
+                    owners = {src[1] for _, src, _, _ in spec.rows.segments(op.train_slices[0].start, op.overlap_shape[0])}
+                    if len(owners) > 1:
+                        names.add(n)
+                        break
+        return names
 
     # ---- symbolic conversion for one (possibly virtual) sender ----------------------------
     def _specs_for(self, sender: RankInfo) -> Dict[str, Tuple[TensorSpec, LocalParam]]:
@@ -195,8 +240,10 @@ class SendProgramCompiler:
         my_tp = self.rank_info.tp_rank
         items: List[CopyItem] = []
         own_plan = self.builder.build_local_transfer_plan(self.infer_meta_list, self.train_meta_list, self.my_transfer_rank)
+        all_specs = {sender.global_rank: self._specs_for(sender) for sender in self.peers}
+        self.gathered_names = self._names_needing_gather(all_specs) if len(self.peers) > 1 else set()
         for sender in self.peers:
-            specs = self._specs_for(sender)
+            specs = all_specs[sender.global_rank]
             is_me = sender.global_rank == self.rank_info.global_rank
             if is_me:
                 ops = own_plan.all_operations()
@@ -206,6 +253,7 @@ class SendProgramCompiler:
                     n for n, (spec, _) in specs.items()
                     if spec.rows is not None and any(src[1] == my_tp for src in spec.rows.sources() if isinstance(src, tuple) and src[0] != "__scale__")
                     and n in self.train_meta and n in self.infer_meta and n not in self.builder.skip_names
+                    and n not in self.gathered_names  # the peer sends those itself, from gathered rows
                 ]
                 virtual_rank = sender.global_rank + self.builder.infer_world_size
                 ops = []
@@ -226,6 +274,25 @@ class SendProgramCompiler:
         items.sort(key=lambda it: (it.dst_rank, it.dst_name, it.dst_start, it.src_param, it.src_start))
         return items
 
+    @staticmethod
+    def _place_fp8_item(item: CopyItem, spec: TensorSpec, op: CommunicationOperation) -> None:
+        """Check that a block-quantised item covers whole blocks of the destination
+        shard and point it at its place in the scale tensor."""
+        if len(item.extent) != 2:
+            raise ValueError(f"{spec.name}: block fp8 needs a 2-D tensor, got extent {item.extent}")
+        if item.dst_start[0] % FP8_BLOCK or item.dst_start[1] % FP8_BLOCK:
+            raise ValueError(
+                f"{spec.name}: a piece starting at {item.dst_start} of the destination shard does not start on a "
+                f"{FP8_BLOCK}x{FP8_BLOCK} block; its block would mix rows of several senders"
+            )
+        shard = op.recv_shard_meta.shape
+        for d in (0, 1):
+            end = item.dst_start[d] + item.extent[d]
+            if end % FP8_BLOCK and end != shard[d]:
+                raise ValueError(f"{spec.name}: piece ends inside a block at {end} (dim {d}, shard extent {shard[d]})")
+        item.scale_name = spec.name + SCALE_SUFFIX
+        item.scale_start = (item.dst_start[0] // FP8_BLOCK, item.dst_start[1] // FP8_BLOCK)
+
     # ---- one planned box -> copy items ----------------------------------------------------------
     def _lower_op(self, op: CommunicationOperation, spec: TensorSpec, lp: LocalParam, my_tp: int) -> List[CopyItem]:
         if spec.scale_of is not None:
@@ -240,9 +307,10 @@ class SendProgramCompiler:
         tail_ext = tuple(op.overlap_shape[1:])
         dst_row0 = op.inf_slices[0].start
         out: List[CopyItem] = []
-        if spec.value_op.kind in WHOLE_TENSOR_OPS:
+        if spec.value_op.kind in WHOLE_TENSOR_OPS or spec.name in self.gathered_names:
+            gathers = spec.name in self.gathered_names
             owners = {src[1] for src in spec.rows.sources()}
-            if owners != {my_tp}:
+            if owners != {my_tp} and not gathers:
                 if my_tp not in owners:
                     return []
                 raise NotImplementedError(
@@ -250,12 +318,17 @@ class SendProgramCompiler:
                     f"training TP ranks {sorted(owners)}"
                 )
             key = (DERIVED_PREFIX + spec.name, lp.vp_stage)
-            self.derived.setdefault(key, DerivedTensor(key, spec, my_tp))
-            return [CopyItem(
+            self.derived.setdefault(key, DerivedTensor(key, spec, my_tp, gathers))
+            whole = spec.value_op.kind in WHOLE_TENSOR_OPS
+            item = CopyItem(
                 src_param=key[0], vp_stage=key[1], src_start=(row0,) + tail_src, extent=(n_rows,) + tail_ext,
                 dst_rank=op.recv_rank, dst_name=spec.name, dst_start=(dst_row0,) + tail_dst,
-                src_dtype=spec.value_op.out_dtype(spec.src_dtype), dst_dtype=dst_dtype, value_op=IDENTITY,
-            )]
+                src_dtype=spec.value_op.out_dtype(spec.src_dtype) if whole else spec.src_dtype, dst_dtype=dst_dtype,
+                value_op=IDENTITY if whole else spec.value_op,
+            )
+            if item.value_op.kind == "fp8_block":
+                self._place_fp8_item(item, spec, op)
+            return [item]
         segments = spec.rows.segments(row0, n_rows)
         if spec.value_op.kind == "fp8_block":
             # a quantisation block needs all of its rows at once: keep the box whole
@@ -288,20 +361,7 @@ class SendProgramCompiler:
             if gather is not None and len(gather) > 1:
                 item.src_rows = gather
             if spec.value_op.kind == "fp8_block":
-                if len(item.extent) != 2:
-                    raise ValueError(f"{spec.name}: block fp8 needs a 2-D tensor, got extent {item.extent}")
-                if item.dst_start[0] % FP8_BLOCK or item.dst_start[1] % FP8_BLOCK:
-                    raise ValueError(
-                        f"{spec.name}: a piece starting at {item.dst_start} of the destination shard does not start on a "
-                        f"{FP8_BLOCK}x{FP8_BLOCK} block; its block would mix rows of several senders"
-                    )
-                shard = op.recv_shard_meta.shape
-                for d in (0, 1):
-                    end = item.dst_start[d] + item.extent[d]
-                    if end % FP8_BLOCK and end != shard[d]:
-                        raise ValueError(f"{spec.name}: piece ends inside a block at {end} (dim {d}, shard extent {shard[d]})")
-                item.scale_name = spec.name + SCALE_SUFFIX
-                item.scale_start = (item.dst_start[0] // FP8_BLOCK, item.dst_start[1] // FP8_BLOCK)
+                self._place_fp8_item(item, spec, op)
             out.append(item)
         return out
 

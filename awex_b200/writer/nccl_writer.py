@@ -53,7 +53,7 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
         # head): persistent buffers beside the parameters, sent with plain copies
         self.derived = list(compiler.derived.values())
         self._local = local
-        refresh_derived(self.derived, local)
+        refresh_derived(self.derived, local, self._gather_tp_shards)
         self.transfer_plan = self.builder.build_local_transfer_plan(self.infer_params_meta, self.parameters_meta, self.transfer_rank)
         stats = compute_transfer_plan_stats(self.transfer_plan)
         logger.info(f"Rank[{self.transfer_rank}] plan hash {stats['full_hash'][:16]} stats {stats['total']}; {len(self.items)} copy items")
@@ -72,12 +72,17 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
         self.transport.connect()
         logger.info(f"Rank[{self.transfer_rank}] writer ready in {time.time() - t0:.2f}s")
 
+    def _gather_tp_shards(self, name: str, vp_stage: int):
+        from awex_b200.converter.mcore_converter import gather_tp_shards
+
+        return gather_tp_shards(self._local[(name, vp_stage)], self.rank_info.tp_size)
+
     def _write_weights(self, step_id, **kwargs) -> None:
         t0 = time.time()
         self.epoch += 1
         if self.derived:
             with phase("derive_tensors"):
-                refresh_derived(self.derived, self._local)  # same stream as the transfer: ordered before it
+                refresh_derived(self.derived, self._local, self._gather_tp_shards)  # same stream as the transfer: ordered before it
         with phase("send_weights"):
             self.transport.send(self.epoch, synchronize=kwargs.get("synchronize", True))
         compute_statistics(self._history, step_id, time.time() - t0, "Send weights")

@@ -17,6 +17,8 @@ def _layouts(case):
         return "tiny-llama", dict(tp=1, pp=2), InferLayout(tp=2), torch.float32
     if case == "tp1_to_tp2_fp8":
         return "tiny-llama", dict(tp=1), InferLayout(tp=2, fp8=True), torch.bfloat16
+    if case == "tp2_to_tp1_fp8":  # quantisation blocks of the fused QKV mix rows of both training ranks: gathered first
+        return "tiny-llama", dict(tp=2), InferLayout(tp=1, fp8=True), torch.bfloat16
     if case == "tp1_to_tp2_norm_head":
         return "tiny-llama-norm-head", dict(tp=1), InferLayout(tp=2), torch.float32
     raise ValueError(case)
@@ -42,7 +44,9 @@ def _writer(case, rank, meta_addr, store_port, q):
         if world > 1:
             dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=rank, world_size=world)
         ri = train_rank_infos(**train)[rank]
-        engine = SyntheticTrainEngine(get_arch(arch), ri, meta_addr, dtype=dtype, device="cpu", process_group=group, exchange_timeout_s=120)
+        tp_group = dist.new_group(list(range(world))) if train.get("tp", 1) == world and world > 1 else None
+        engine = SyntheticTrainEngine(get_arch(arch), ri, meta_addr, dtype=dtype, device="cpu", process_group=group, tp_group=tp_group,
+                                      exchange_timeout_s=120)
         writer = NCCLWeightsWriter(engine)
         writer.initialize()
         writer.write_weights(step_id=1)
@@ -91,7 +95,7 @@ def _reader(case, worker_rank, meta_addr, store_port, q):
 
 
 @pytest.mark.timeout(400)
-@pytest.mark.parametrize("case", ["pp2_to_tp2", "tp1_to_tp2_fp8", "tp1_to_tp2_norm_head"])
+@pytest.mark.parametrize("case", ["pp2_to_tp2", "tp1_to_tp2_fp8", "tp2_to_tp1_fp8", "tp1_to_tp2_norm_head"])
 def test_layout_over_gloo(case):
     from awex_b200.meta.meta_server import MetaServer
     from awex_b200.utils.common import get_free_port

@@ -60,8 +60,9 @@ def test_random_layouts_are_exact(seed):
 def test_random_block_fp8_layouts_through_the_descriptor_tables():
     """Block-aligned small architectures served as fp8: plan, lower, encode, run
     the tables on the host interpreter, compare with the CPU-quantised oracle.
-    Layouts whose quantisation blocks would straddle training ranks must be
-    refused with NotImplementedError, never mis-executed."""
+    Quantisation blocks that mix rows of several training ranks go through a
+    gathered sender-side buffer; slices that end inside a block are refused with
+    NotImplementedError, never mis-executed."""
     from awex_b200.transfer.table_interpreter import HostMemory, run_table
 
     rng = random.Random(77)
@@ -90,7 +91,7 @@ def test_random_block_fp8_layouts_through_the_descriptor_tables():
             continue
         assert job.check_coverage() == [], label
         encoded = job.encode_all(validate=True)
-        mem = HostMemory([p for m in job.train_models for p in m.parameters()] + [p for ms in job.infer_models for m in ms for p in m.parameters()])
+        mem = HostMemory(job.source_tensors() + [p for ms in job.infer_models for m in ms for p in m.parameters()])
         for table, n_tiles, enc in encoded.values():
             run_table(table, n_tiles, mem, enc.row_offsets)
         assert job.mismatches() == [], label

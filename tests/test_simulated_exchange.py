@@ -100,10 +100,30 @@ def test_fp8_serving_exchange(arch, train, infer):
     assert any(it.src_rows for items in job.programs.values() for it in items) == (arch == "tiny-qwen3-moe")
 
 
-def test_fp8_block_that_spans_training_ranks_is_refused():
-    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=2), InferLayout(tp=1, fp8=True), dtype=torch.bfloat16)
-    with pytest.raises(NotImplementedError, match="several training TP ranks"):
-        job.compile_all()
+@pytest.mark.parametrize("train_tp,infer_tp,gathers", [(2, 1, True), (4, 2, True), (4, 1, True), (2, 2, False), (2, 4, False)])
+def test_fp8_blocks_that_span_training_ranks_are_gathered_by_their_owner(train_tp, infer_tp, gathers):
+    """Fused QKV regrouped for fewer inference ranks than training ranks: a
+    quantisation block then mixes rows of several training ranks.  The rank that
+    owns the chunk gathers its rows over the training TP group into a buffer and
+    quantises from there (the reference gathers every fused QKV, always:
+    `awex/converter/mcore_converter.py:1040-1052`); where every block has one
+    owner, no gather is planned and each rank sends its own rows."""
+    import dataclasses
+
+    arch = dataclasses.replace(get_arch("tiny-qwen2"), head_dim=64, name="tiny-qwen2-hd64")
+    job = SimulatedJob(arch, TrainLayout(tp=train_tp), InferLayout(tp=infer_tp, fp8=True), dtype=torch.bfloat16)
+    programs = job.compile_all()
+    assert job.check_coverage() == []
+    qkv = [f"model.layers.{l}.attention.query_key_value_proj.weight" for l in range(arch.num_layers)]
+    for rank, items in programs.items():
+        derived = sorted(d.key[0] for d in job.derived[rank])
+        assert derived == (sorted("__derived__/" + n for n in qkv) if gathers else [])
+        assert all(d.gathers for d in job.derived[rank])
+        for it in items:
+            if it.dst_name in qkv:
+                assert it.src_param.startswith("__derived__/") == gathers and it.value_op.kind == "fp8_block"
+    job.run_cpu()
+    assert job.mismatches() == []
 
 
 def test_spread_replica_pairing_balances_data_parallel_senders():
