@@ -27,6 +27,20 @@ from awex_b200.utils.trace import phase
 logger = logging.getLogger(__name__)
 
 
+def clear_for_validation(t: torch.Tensor, fill: str = "zero") -> None:
+    """Overwrite ``t`` before a validated update: zeros, or with ``fill="poison"``
+    NaNs in floating-point tensors (8-bit floats get their NaN bit pattern)."""
+    with torch.no_grad():
+        if fill == "poison" and t.is_floating_point():
+            if t.dtype.itemsize == 1:
+                # e4m3fn has no infinities: 0x7f is its NaN; 0x7f is a NaN of e5m2 as well
+                t.copy_(torch.full(tuple(t.shape), 0x7F, dtype=torch.uint8, device=t.device).view(t.dtype))
+            else:
+                t.fill_(float("nan"))
+        else:
+            t.zero_()
+
+
 class WorkerWeightsReader:
     def __init__(self, model, model_context: dict, infer_conf: dict, parameters_meta, training_params_meta,
                  engine_rank: int, num_engines: int, meta_server_addr: str, enable_debug_mode: bool = False,
@@ -54,6 +68,12 @@ class WorkerWeightsReader:
         self.training_world_size = training_params_meta[0].shards[0].world_size
         self.timeout = float(self.debug_mode_config.get("host_wait_timeout_s", 10000))
         self.exchange_timeout_s = float(self.debug_mode_config.get("exchange_timeout_s", 1800))
+        # what validation leaves in the parameters before the update: "zero" (the reference's choice) or
+        # "poison" (NaN bit patterns in floating-point tensors, so that an unwritten shard of a
+        # tensor whose true values are zero is caught too)
+        self.validation_fill = str(self.debug_mode_config.get("validation_fill", "zero"))
+        if self.validation_fill not in ("zero", "poison"):
+            raise ValueError(f"debug_mode_config.validation_fill must be 'zero' or 'poison', got {self.validation_fill!r}")
         self.parameters: Dict[str, torch.Tensor] = {}
         self._history: Dict[str, List[float]] = {}
         self._snapshot = None
@@ -139,7 +159,7 @@ class WorkerWeightsReader:
         else:
             self._snapshot = (names, [t.detach().clone() for t in tensors])
         for t in tensors:
-            t.zero_()
+            clear_for_validation(t, self.validation_fill)
         return len(names)
 
     def verify_against_snapshot(self) -> Dict[str, bool]:

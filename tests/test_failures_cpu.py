@@ -150,3 +150,31 @@ def test_reader_notices_reallocated_parameters():
     name, old = next(iter(model.named_parameters()))
     model._tensors[name] = old.clone()  # what a reload or a re-mapping allocator does
     assert reader.parameters_moved() == [name]
+
+
+def test_poison_fill_catches_an_unwritten_tensor_whose_values_are_zero():
+    """Zero-fill validation cannot see that nobody wrote a tensor that is all
+    zeros (a fresh bias); NaN poison can."""
+    import torch
+
+    from awex_b200.reader.nccl_reader import WorkerWeightsReader
+
+    def worker(fill):
+        w = object.__new__(WorkerWeightsReader)
+        w.parameters = {"w": torch.randn(8, 4), "bias": torch.zeros(8), "q": torch.randn(4, 4).to(torch.float8_e4m3fn), "ids": torch.arange(4)}
+        w.required_names = set(w.parameters)
+        w.device, w.validation_fill, w._snapshot = torch.device("cpu"), fill, None
+        return w
+
+    for fill, bias_passes in (("zero", True), ("poison", False)):
+        w = worker(fill)
+        truth = {n: t.clone() for n, t in w.parameters.items()}
+        assert w.snapshot_and_clear() == 4
+        if fill == "poison":
+            assert torch.isnan(w.parameters["w"]).all() and torch.isnan(w.parameters["q"].float()).all()
+            assert (w.parameters["ids"] == 0).all()  # integers have no NaN: zeroed
+        for n in ("w", "q", "ids"):  # the update writes everything but the bias
+            w.parameters[n].copy_(truth[n])
+        result = w.verify_against_snapshot()
+        assert result["w"] and result["q"] and result["ids"]
+        assert result["bias"] == bias_passes
