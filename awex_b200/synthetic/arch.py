@@ -57,6 +57,38 @@ class Arch:
             cfg.num_experts_per_tok = self.top_k
         return cfg
 
+    def hf_config_dict(self, dtype: str = "bfloat16") -> dict:
+        """A ``config.json`` that Hugging Face loaders and inference engines accept
+        for this architecture (random weights are then made by the engine, e.g.
+        vLLM's ``--load-format dummy``)."""
+        model_types = {"LlamaForCausalLM": "llama", "Qwen2ForCausalLM": "qwen2", "Qwen3ForCausalLM": "qwen3",
+                       "Qwen3MoeForCausalLM": "qwen3_moe"}
+        if self.architecture not in model_types:
+            raise KeyError(f"no config.json template for {self.architecture}")
+        cfg = {
+            "architectures": [self.architecture], "model_type": model_types[self.architecture],
+            "num_hidden_layers": self.num_layers, "hidden_size": self.hidden, "num_attention_heads": self.num_heads,
+            "num_key_value_heads": self.num_kv_heads, "head_dim": self.head_dim,
+            "intermediate_size": self.ffn or self.expert_ffn, "vocab_size": self.vocab, "hidden_act": "silu",
+            "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 4096,
+            "tie_word_embeddings": self.tie_embeddings, "attention_bias": self.qkv_bias, "torch_dtype": dtype,
+            "bos_token_id": 1, "eos_token_id": 2,
+        }
+        if self.is_moe:
+            cfg.update(num_experts=self.num_experts, moe_intermediate_size=self.expert_ffn, num_experts_per_tok=self.top_k,
+                       decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True)
+        return cfg
+
+    def write_model_dir(self, path: str, dtype: str = "bfloat16") -> str:
+        """Create ``path`` with this architecture's ``config.json`` (no weights, no tokenizer)."""
+        import json
+        import os
+
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as f:
+            json.dump(self.hf_config_dict(dtype), f, indent=1)
+        return path
+
     def tf_config(self) -> SimpleNamespace:
         """The subset of Megatron's TransformerConfig the converters read."""
         return SimpleNamespace(

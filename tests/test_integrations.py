@@ -392,3 +392,53 @@ def test_server_wrapper_separates_its_own_flags():
     assert own == {"AWEX_COMM_BACKEND": "nccl", "AWEX_META_SERVER_ADDR": "10.0.0.1:80"}
     with pytest.raises(SystemExit):
         split_own_arguments(["--awex-comm-backend"])
+
+
+def test_vllm_integration_script_speaks_the_plugin_protocol(monkeypatch, tmp_path):
+    """The manual vLLM integration script (needs GPUs and a server to run) builds
+    request bodies that the plugin's models accept, picks one training GPU plus
+    tp*pp serving GPUs, and starts the server wrapper with flags the wrapper
+    understands."""
+    import importlib.util
+    import os
+    from types import SimpleNamespace
+
+    from awex_b200.awex_vllm_server import split_own_arguments
+    from awex_b200.vllm_plugin import AwexInitRequest, AwexUpdateRequest
+
+    path = os.path.join(os.path.dirname(__file__), "weights_exchange_vllm_it.py")
+    spec = importlib.util.spec_from_file_location("weights_exchange_vllm_it", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    args = SimpleNamespace(host="127.0.0.1", port=8123, tp=2, pp=1, comm_backend="nccl", debug=False, validate=True,
+                           dump_weights_list_for_validation=["model.norm.weight"], dump_weights_dir_for_validation=None,
+                           gpu_memory_utilization=0.5, startup_timeout=1.0)
+    run = module.VLLMWeightsExchange(args)
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "3,4,5,6")
+    assert run._devices() == ("3", ["4", "5"])
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "3,4")
+    with pytest.raises(SystemExit):
+        run._devices()
+    posted = []
+    run._post = lambda route, payload, timeout: posted.append((route, payload)) or {"success": True}
+    run.awex_init("127.0.0.1:9999")
+    run.step = 7
+    run.awex_update("/ckpt")
+    run.awex_update(None)
+    (r0, init), (r1, up1), (r2, up2) = posted
+    assert (r0, r1, r2) == ("/areal_awex_init", "/areal_awex_update", "/areal_awex_update")
+    request = AwexInitRequest(**init)
+    assert request.comm_backend == "nccl" and request.weights_validation_steps == 1
+    assert request.dump_weights_list_for_validation == ["model.norm.weight"] and request.dump_weights_dir_for_validation == run.workdir
+    assert AwexUpdateRequest(**up1).kwargs == {"path": "/ckpt"} and AwexUpdateRequest(**up2).step_id == 7
+    # the server command: our own flags are separated from vLLM's
+    started = []
+    monkeypatch.setattr(module.subprocess, "Popen", lambda cmd, env: started.append((cmd, env)) or SimpleNamespace(poll=lambda: 1, returncode=1))
+    with pytest.raises(RuntimeError, match="exited"):
+        run.start_server(str(tmp_path), ["4", "5"], "127.0.0.1:9999")
+    cmd, env = started[0]
+    assert cmd[1:3] == ["-m", "awex_b200.awex_vllm_server"] and env["CUDA_VISIBLE_DEVICES"] == "4,5"
+    rest, own = split_own_arguments(cmd[3:])
+    assert own == {"AWEX_COMM_BACKEND": "nccl", "AWEX_META_SERVER_ADDR": "127.0.0.1:9999"}
+    assert "--tensor-parallel-size" in rest and not any(a.startswith("--awex") for a in rest)
+    os.rmdir(run.workdir)
