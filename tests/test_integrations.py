@@ -431,6 +431,14 @@ def test_vllm_integration_script_speaks_the_plugin_protocol(monkeypatch, tmp_pat
     assert request.comm_backend == "nccl" and request.weights_validation_steps == 1
     assert request.dump_weights_list_for_validation == ["model.norm.weight"] and request.dump_weights_dir_for_validation == run.workdir
     assert AwexUpdateRequest(**up1).kwargs == {"path": "/ckpt"} and AwexUpdateRequest(**up2).step_id == 7
+    # the server's processes discover the plugin of this source tree like an installed one
+    import subprocess
+    import sys
+
+    probe = ("from importlib.metadata import entry_points; "
+             "print([(e.name, e.value) for e in entry_points(group='vllm.general_plugins') if e.name == 'awex_adapter'])")
+    found = subprocess.run([sys.executable, "-c", probe], env={**os.environ, "PYTHONPATH": run.plugin_path()}, capture_output=True, text=True)
+    assert "awex_b200.vllm_plugin:register_awex_plugin" in found.stdout, found.stderr
     # the server command: our own flags are separated from vLLM's
     started = []
     monkeypatch.setattr(module.subprocess, "Popen", lambda cmd, env: started.append((cmd, env)) or SimpleNamespace(poll=lambda: 1, returncode=1))
@@ -438,7 +446,10 @@ def test_vllm_integration_script_speaks_the_plugin_protocol(monkeypatch, tmp_pat
         run.start_server(str(tmp_path), ["4", "5"], "127.0.0.1:9999")
     cmd, env = started[0]
     assert cmd[1:3] == ["-m", "awex_b200.awex_vllm_server"] and env["CUDA_VISIBLE_DEVICES"] == "4,5"
+    assert run.plugin_path() in env["PYTHONPATH"].split(os.pathsep)
     rest, own = split_own_arguments(cmd[3:])
     assert own == {"AWEX_COMM_BACKEND": "nccl", "AWEX_META_SERVER_ADDR": "127.0.0.1:9999"}
     assert "--tensor-parallel-size" in rest and not any(a.startswith("--awex") for a in rest)
-    os.rmdir(run.workdir)
+    import shutil
+
+    shutil.rmtree(run.workdir)

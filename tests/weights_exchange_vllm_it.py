@@ -65,10 +65,23 @@ class VLLMWeightsExchange:
         self.meta_server.start()
         return f"127.0.0.1:{self.meta_server.port}"
 
+    def plugin_path(self) -> str:
+        """A directory that announces this source tree's vLLM plugin to
+        ``importlib.metadata`` (what an installed wheel's entry point does), so
+        that worker processes vLLM starts with ``spawn`` register the worker
+        methods too."""
+        meta = os.path.join(self.workdir, "plugin", "awex_b200_in_tree-0.dist-info")
+        os.makedirs(meta, exist_ok=True)
+        with open(os.path.join(meta, "METADATA"), "w") as f:
+            f.write("Metadata-Version: 2.1\nName: awex-b200-in-tree\nVersion: 0\n")
+        with open(os.path.join(meta, "entry_points.txt"), "w") as f:
+            f.write("[vllm.general_plugins]\nawex_adapter = awex_b200.vllm_plugin:register_awex_plugin\n")
+        return os.path.dirname(meta)
+
     def start_server(self, model_dir: str, devices: List[str], meta_addr: str) -> None:
         env = os.environ.copy()
         env["CUDA_VISIBLE_DEVICES"] = ",".join(devices)
-        env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+        env["PYTHONPATH"] = os.pathsep.join([ROOT, self.plugin_path(), env.get("PYTHONPATH", "")])
         cmd = [
             sys.executable, "-m", "awex_b200.awex_vllm_server", "--model", model_dir, "--host", self.host, "--port", str(self.port),
             "--tensor-parallel-size", str(self.args.tp), "--pipeline-parallel-size", str(self.args.pp),
