@@ -231,10 +231,11 @@ class SimulatedJob:
         """Exactly-once check of all programs against all destination views."""
         views = self.destination_views()
         problems: List[str] = []
+        trained = {m.name for m in self.train_meta}
         for rank, rank_views in views.items():
             manifests = [manifest_by_destination(items).get(rank, []) for items in self.programs.values()]
             shapes = {n: (tuple(v.shape), v.dtype) for n, v in rank_views.items()}
-            required = [n for n in shapes if (n in {m.name for m in self.train_meta} or n.endswith("_scale_inv")) and n not in self.aliases]
+            required = [n for n in shapes if (n in trained or n.endswith("_scale_inv")) and n not in self.aliases]
             problems += [f"rank {rank}: {p}" for p in check_exactly_once(manifests, shapes, required)]
         return problems
 
