@@ -140,20 +140,64 @@ def summarize_requests(reqs: Iterable[P2PRequest]) -> list:
     return [("send" if r.send else "recv", r.label, str(r.tensor.dtype), list(r.tensor.shape), r.tensor.is_contiguous(), r.peer) for r in reqs]
 
 
+class PeerStreams:
+    """A fixed pool of side streams per device, one picked per peer (peer ``i`` in
+    sorted order gets stream ``i mod size``), so that messages to one peer keep
+    their order while different peers progress independently; the reference's
+    ungrouped send path does the same with 64 streams
+    (`awex/transfer/nccl_comm.py:34-50,586-624`).  ``make_stream`` is the stream
+    factory (a CUDA stream on the current device by default)."""
+
+    SIZE = 64
+    _pools: Dict[int, list] = {}
+
+    def __init__(self, peers: Iterable[int], device_index: int = 0, make_stream: Optional[Callable] = None, size: Optional[int] = None):
+        size = size or self.SIZE
+        pool = self._pools.setdefault((device_index, id(make_stream)), [])
+        wanted = min(size, len(set(peers)))
+        make = make_stream or (lambda: torch.cuda.Stream(device=device_index))
+        while len(pool) < wanted:
+            pool.append(make())
+        self.by_peer = {peer: pool[i % size] for i, peer in enumerate(sorted(set(peers)))}
+
+    def used(self) -> list:
+        seen, out = set(), []
+        for s in self.by_peer.values():
+            if id(s) not in seen:
+                seen.add(id(s))
+                out.append(s)
+        return out
+
+
 def batch_send_recv(requests: Sequence[P2PRequest], group=None, blocking: bool = True, use_group: bool = True,
-                    watchdog_s: Optional[float] = 30.0, what: str = "batch_send_recv") -> list:
+                    watchdog_s: Optional[float] = 30.0, what: str = "batch_send_recv", use_stream: bool = False) -> list:
     """Issue all requests, interleaved across peers.
 
     ``use_group=True`` coalesces them in one ``batch_isend_irecv`` (one NCCL
     group call: no ordering constraint between peers).  Otherwise they are posted
-    one by one as non-blocking calls in interleaved order.  Returns the pending
-    ``Work`` handles when ``blocking`` is false, else waits for all of them."""
+    one by one as non-blocking calls in interleaved order, on one side stream
+    per peer when ``use_stream`` is set and the tensors are on a GPU (the side
+    streams first wait for the caller's stream, and the caller's stream waits
+    for them at the end).  Returns the pending ``Work`` handles when
+    ``blocking`` is false, else waits for all of them."""
     reqs = interleave_by_peer(list(requests))
     if not reqs:
         return []
     if use_group:
         ops = [dist.P2POp(dist.isend if r.send else dist.irecv, r.tensor, r.peer, group=group) for r in reqs]
         works = dist.batch_isend_irecv(ops)
+    elif use_stream and reqs[0].tensor.is_cuda:
+        device = reqs[0].tensor.device
+        streams = PeerStreams((r.peer for r in reqs), device.index or 0)
+        caller = torch.cuda.current_stream(device)
+        for s in streams.used():
+            s.wait_stream(caller)
+        works = []
+        for r in reqs:
+            with torch.cuda.stream(streams.by_peer[r.peer]):
+                works.append((dist.isend if r.send else dist.irecv)(r.tensor, r.peer, group=group))
+        for s in streams.used():
+            caller.wait_stream(s)
     else:
         works = [(dist.isend if r.send else dist.irecv)(r.tensor, r.peer, group=group) for r in reqs]
     if not blocking:
@@ -410,6 +454,31 @@ def build_recv_requests(plan, tensors: Dict[str, torch.Tensor], staging: RecvSta
             view = slice_tensor(tensors[op.recv_shard_meta.name], op, False)
             per_peer.setdefault(peer, []).append(P2PRequest(False, staging.prepare(view), peer, op.recv_shard_meta.name))
     return _round_robin(per_peer)
+
+
+@torch.no_grad()
+def execute_tensors_to_copy(tensors_to_copy: Sequence[torch.Tensor], copy_ops: Sequence, recv_parameters: Dict[str, torch.Tensor],
+                            stage: str = "local copies") -> float:
+    """Planned operations whose sender and receiver share this process and
+    device: plain device-local copies of each sent piece into the receiving
+    view's slice (`awex/transfer/nccl_comm.py:225-241` in the reference).  The
+    fused kernel does the same through a local destination pointer; this is the
+    library path beside it.  Returns the seconds spent."""
+    from awex_b200.transfer.transfer_plan import slice_tensor
+
+    if len(tensors_to_copy) != len(copy_ops):
+        raise ValueError(f"{stage}: {len(tensors_to_copy)} tensors for {len(copy_ops)} copy operations")
+    started = time.time()
+    on_gpu = False
+    for piece, op in zip(tensors_to_copy, copy_ops):
+        view = slice_tensor(recv_parameters[op.recv_shard_meta.name], op, False)
+        view.copy_(piece)
+        on_gpu = on_gpu or view.is_cuda
+    if on_gpu:
+        torch.cuda.current_stream().synchronize()
+    took = time.time() - started
+    logger.info(f"Finished executing {len(copy_ops)} copy operations for {stage}, took {took:.4f} seconds")
+    return took
 
 
 def execute_p2p_requests(requests: Sequence[P2PRequest], stage: str, group=None, use_group: bool = True,

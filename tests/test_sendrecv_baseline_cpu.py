@@ -92,3 +92,47 @@ def test_recv_staging_and_send_clone():
     view = torch.arange(16.0).reshape(4, 4)[:, 2]
     sent = clone_p2p_send_tensor(view)
     assert sent.is_contiguous() and sent.data_ptr() != view.data_ptr() and torch.equal(sent, view)
+
+
+def test_planned_operations_inside_one_process_run_as_local_copies():
+    """Sender and receiver in one process (the reference's same-GPU operations of
+    its co-located mode): every planned operation is a copy of the sent slice into
+    the receiving slice."""
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+    from awex_b200.transfer.nccl_comm import execute_tensors_to_copy
+    from awex_b200.transfer.transfer_plan import slice_tensor
+
+    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=1), InferLayout(tp=2), dtype=torch.float32)
+    conv = job._train_converter(job.train_ranks[0])
+    tensors = {}
+    for name, p in job.train_models[0].named_parameters():
+        for cname, value in conv.convert_param(name, p, vp_stage=0):
+            tensors[cname] = value
+    views = job.destination_views()
+    plan = job.builder.build_local_transfer_plan(job.infer_meta, job.train_meta, 2)  # the training rank's plan
+    total = 0
+    for peer, ops in plan.operations.items():
+        pieces = [slice_tensor(tensors[op.send_shard_meta.name], op, True) for op in ops]
+        assert execute_tensors_to_copy(pieces, ops, views[peer], stage=f"to {peer}") >= 0
+        total += len(ops)
+    assert total > 0 and job.mismatches() == []
+    with pytest.raises(ValueError, match="copy operations"):
+        execute_tensors_to_copy([], next(iter(plan.operations.values()))[:1], views[0])
+
+
+def test_peer_streams_keep_one_stream_per_peer_within_a_fixed_pool():
+    from awex_b200.transfer.nccl_comm import PeerStreams
+
+    made = []
+
+    def make():
+        made.append(object())
+        return made[-1]
+
+    a = PeerStreams([7, 3, 5, 3], device_index=0, make_stream=make, size=2)
+    assert len(made) == 2  # pool bounded by its size, grown only as far as needed
+    assert a.by_peer[3] is made[0] and a.by_peer[5] is made[1] and a.by_peer[7] is made[0]  # sorted peers, modulo the pool
+    assert a.used() == [made[0], made[1]]
+    b = PeerStreams([1], device_index=0, make_stream=make, size=2)
+    assert len(made) == 2 and b.by_peer[1] is made[0]  # the pool is shared by later calls
