@@ -135,7 +135,11 @@ class PeerMemoryImporter:
                 code = self.lib.awex_ipc_open(handle, ctypes.byref(out))
                 if code != 0:
                     msg = self.lib.awex_cuda_error_string(code)
-                    raise RuntimeError(f"cudaIpcOpenMemHandle failed (CUDA error {code}: {msg.decode() if msg else '?'})")
+                    hint = ""
+                    if tuple(book.owner)[0] != self._me[0]:
+                        hint = (f"; the memory belongs to a process on host {tuple(book.owner)[0]!r}, this is {self._me[0]!r}: peer stores "
+                                "work inside one machine, set data_plane='messages' (or AWEX_DATA_PLANE=messages) on the inference side")
+                    raise RuntimeError(f"cudaIpcOpenMemHandle failed (CUDA error {code}: {msg.decode() if msg else '?'}){hint}")
                 mapped = self._open[handle] = out.value
             bases.append(mapped)
         out_addrs: Dict[str, TensorAddr] = {}

@@ -189,7 +189,10 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
             infer_world=self.infer_world_size, train_world=self.training_world_size, required=self.required_names,
             device=self.device, wait_timeout_s=self.timeout, strict=not self.enable_debug_mode,
         )
-        if self.device.type == "cuda":
+        from awex_b200.transfer.transports import choose_data_plane
+
+        plane = self.infer_conf.get("data_plane") or choose_data_plane(self.device.type, self.debug_mode_config.get("data_plane"))
+        if plane == "peer_stores":
             from awex_b200.transfer.transports import PeerStoreReceiver
 
             self.transport = PeerStoreReceiver(timeout_ms=self.device_wait_timeout_ms, **common)

@@ -22,7 +22,7 @@ import pickle
 import threading
 import time
 from abc import ABC, abstractmethod
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -136,6 +136,8 @@ class WeightsReader(WeightExchangeReader):
             "expected_pp_ranks": self.expected_pp_ranks,
             "device_backend": device_util.get_device_type(),
             "fp8_block_quant": bool(getattr(config, "fp8_block_quant", False)),
+            # how tensors travel (peer stores inside one machine, messages across machines); the training side follows
+            "data_plane": self._data_plane(),
             # second names of memory that another name already covers: nobody sends them
             "aliased_parameters": dict(getattr(self.meta_resolver, "aliases", {}) or {}),
         }
@@ -162,6 +164,17 @@ class WeightsReader(WeightExchangeReader):
             weights_comm_nccl_group_size=self.weights_comm_nccl_group_size,
             device_wait_timeout_ms=getattr(config, "device_wait_timeout_ms", 2000),
         )
+
+    def _data_plane(self) -> Optional[str]:
+        """The configured data plane (``debug_mode_config["data_plane"]`` or
+        ``AWEX_DATA_PLANE``), or None: each side then picks by the device its
+        tensors live on (peer stores on CUDA, messages on CPU)."""
+        from awex_b200.transfer.transports import DATA_PLANES
+
+        choice = os.environ.get("AWEX_DATA_PLANE") or self.debug_mode_config.get("data_plane")
+        if choice is not None and choice not in DATA_PLANES:
+            raise ValueError(f"data plane must be one of {DATA_PLANES}, got {choice!r}")
+        return choice
 
     def _router_dtype(self) -> str:
         """Dtype the training side casts MoE router weights to: the model

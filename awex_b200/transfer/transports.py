@@ -313,6 +313,26 @@ class PeerStoreSender:
             self.importer.close_all()
 
 
+# ------------------------------------------------------------------------------------ choice of the data plane
+DATA_PLANES = ("peer_stores", "messages")
+
+
+def choose_data_plane(device_type: str, configured: Optional[str] = None) -> str:
+    """``peer_stores``: the fused kernel writes through CUDA-IPC mappings; every
+    sender and receiver must sit in one NVLink / PCIe peer domain (one machine).
+    ``messages``: one packed message per (sender, destination) over a process
+    group (NCCL on GPUs, gloo on CPUs); works across machines, as the reference's
+    NCCL mode does.  ``AWEX_DATA_PLANE`` overrides ``configured``; the default is
+    peer stores on CUDA devices and messages elsewhere.  The inference side
+    publishes its choice in ``infer_conf`` and the training side follows it."""
+    choice = os.environ.get("AWEX_DATA_PLANE") or configured or ("peer_stores" if device_type == "cuda" else "messages")
+    if choice not in DATA_PLANES:
+        raise ValueError(f"data plane must be one of {DATA_PLANES}, got {choice!r}")
+    if choice == "peer_stores" and device_type != "cuda":
+        raise ValueError("the peer_stores data plane needs CUDA devices")
+    return choice
+
+
 # ------------------------------------------------------------------------------------ CPU / portable path
 def _join_exchange_group(meta, transfer_rank: int, world: int, wait_timeout_s: float, device, exchange_timeout_s: float = 1800.0):
     from awex_b200.parallel.process_group import init_weights_update_group

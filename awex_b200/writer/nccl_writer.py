@@ -12,6 +12,7 @@ send program is compiled once, on the first update.
 
 from __future__ import annotations
 
+import os
 import time
 from typing import List
 
@@ -61,7 +62,16 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
         device = next(iter(local.values())).device if local else torch.device("cpu")
         common = dict(meta=self.meta_server_client, items=self.items, local=local, train_rank=self.rank_info.global_rank,
                       infer_world=self.infer_world_size, device=device, wait_timeout_s=self.timeout)
-        if device.type == "cuda":
+        from awex_b200.transfer.transports import choose_data_plane
+
+        # the inference side's published choice wins; a contradicting setting here is an error, not a silent mismatch
+        mine = os.environ.get("AWEX_DATA_PLANE") or self.config.get("data_plane")
+        plane = self.infer_conf.get("data_plane") or choose_data_plane(device.type, self.config.get("data_plane"))
+        if mine and mine != plane:
+            raise ValueError(f"training side asks for data plane {mine!r} but the inference side published {plane!r}")
+        if plane == "peer_stores" and device.type != "cuda":
+            raise ValueError("the inference side chose peer stores but this training rank's parameters are not on a CUDA device")
+        if plane == "peer_stores":
             from awex_b200.transfer.transports import PeerStoreSender
 
             self.transport = PeerStoreSender(timeout_ms=self.device_wait_timeout_ms, validate=True, grid=self.grid, **common)

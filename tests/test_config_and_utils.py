@@ -293,3 +293,17 @@ def test_bench_roofline_arithmetic():
     assert layouts == {"separated": "tp4->2xtp2", "colocated": "colocated-tp8->tp8", "moe": "colocated-ep8->2xtp4ep4", "fp8": "colocated-ep8->tp8-fp8"}
     with pytest.raises(SystemExit):
         bd.role_table(3)
+
+
+def test_data_plane_choice(monkeypatch):
+    from awex_b200.transfer.transports import choose_data_plane
+
+    monkeypatch.delenv("AWEX_DATA_PLANE", raising=False)
+    assert choose_data_plane("cuda") == "peer_stores" and choose_data_plane("cpu") == "messages"
+    assert choose_data_plane("cuda", "messages") == "messages"  # several machines: messages over NCCL
+    with pytest.raises(ValueError, match="CUDA"):
+        choose_data_plane("cpu", "peer_stores")
+    with pytest.raises(ValueError, match="one of"):
+        choose_data_plane("cuda", "rdma")
+    monkeypatch.setenv("AWEX_DATA_PLANE", "messages")
+    assert choose_data_plane("cuda", "peer_stores") == "messages"  # the environment wins

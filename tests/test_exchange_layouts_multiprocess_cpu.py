@@ -72,7 +72,7 @@ def _reader(case, worker_rank, meta_addr, store_port, q):
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=worker_rank, world_size=layout.tp)
         ri = infer_rank_infos(tp=layout.tp)[worker_rank]
         engine = SyntheticInferenceEngine(get_arch(arch), layout, ri, meta_addr, dtype=dtype, device="cpu", instance_group=dist.group.WORLD,
-                                          debug_mode_config={"exchange_timeout_s": 120})
+                                          debug_mode_config={"exchange_timeout_s": 120, "data_plane": "messages"})  # published; the writers follow it
         reader = WeightsReader(engine)
         reader.initialize()
         reader.update_weights(step_id=1)
@@ -169,7 +169,7 @@ def _vpp_reader(meta_addr, q):
         os.environ["AWEX_DEVICE_TYPE"] = "cpu"
         arch = dataclasses.replace(get_arch("tiny-llama"), num_layers=4)
         engine = SyntheticInferenceEngine(arch, InferLayout(tp=1), infer_rank_infos()[0], meta_addr, dtype=torch.float32, device="cpu",
-                                          debug_mode_config={"exchange_timeout_s": 120})
+                                          debug_mode_config={"exchange_timeout_s": 120, "data_plane": "messages"})  # published; the writers follow it
         reader = WeightsReader(engine)
         reader.initialize()
         reader.update_weights(step_id=1)
