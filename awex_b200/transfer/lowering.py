@@ -366,6 +366,73 @@ class SendProgramCompiler:
         return out
 
 
+# ---- re-ordering one sender's work across its destinations ------------------------------------------------
+def split_item_rows(item: CopyItem, max_rows: int) -> List[CopyItem]:
+    """Cut ``item`` along dimension 0 into pieces of at most ``max_rows`` rows that
+    together do exactly what ``item`` does.  Block-quantised items are cut on
+    quantisation-block boundaries (``max_rows`` is rounded down to a multiple of
+    the block, at least one block), and their place in the scale tensor moves
+    along; gathered row lists are cut with the rows they cover."""
+    if not item.extent or max_rows <= 0:
+        return [item]
+    if item.value_op.kind == "fp8_block":
+        max_rows = max(FP8_BLOCK, max_rows - max_rows % FP8_BLOCK)
+    rows = item.extent[0]
+    if rows <= max_rows:
+        return [item]
+    pieces: List[CopyItem] = []
+    for r0 in range(0, rows, max_rows):
+        r1 = min(rows, r0 + max_rows)
+        piece = dataclasses.replace(item, extent=(r1 - r0,) + tuple(item.extent[1:]), dst_start=(item.dst_start[0] + r0,) + tuple(item.dst_start[1:]))
+        if item.src_rows is None:
+            piece.src_start = (item.src_start[0] + r0,) + tuple(item.src_start[1:])
+        else:
+            runs = []
+            for rel, srow, n in item.src_rows:
+                lo, hi = max(rel, r0), min(rel + n, r1)
+                if lo < hi:
+                    runs.append((lo - r0, srow + (lo - rel), hi - lo))
+            piece.src_rows = tuple(runs)
+        if item.scale_name is not None:
+            piece.scale_start = (item.scale_start[0] + r0 // FP8_BLOCK, item.scale_start[1])
+        pieces.append(piece)
+    return pieces
+
+
+def _item_src_bytes(item: CopyItem) -> int:
+    return item.numel * item.src_dtype.itemsize
+
+
+def stripe_by_destination(items: Sequence[CopyItem], stripe_bytes: int) -> List[CopyItem]:
+    """The same work in another order: every item is cut into pieces of about
+    ``stripe_bytes`` of source data, and the pieces of the different
+    destinations are merged so that at every point of the list each destination
+    has received the same fraction of its bytes.  A kernel that walks the list
+    with all its CTAs inside one narrow window then writes to all destinations
+    at once, in proportion to what each is owed, instead of one after the other.
+    The order inside a destination is kept."""
+    per_dst: Dict[int, List[CopyItem]] = {}
+    for it in items:
+        row_bytes = max(1, _item_src_bytes(it) // max(it.extent[0], 1)) if it.extent else 1
+        per_dst.setdefault(it.dst_rank, []).extend(split_item_rows(it, max(1, stripe_bytes // row_bytes)))
+    if len(per_dst) < 2:
+        return [p for d in sorted(per_dst) for p in per_dst[d]]
+    totals = {d: max(1, sum(_item_src_bytes(p) for p in ps)) for d, ps in per_dst.items()}
+    done = {d: 0 for d in per_dst}
+    cursor = {d: 0 for d in per_dst}
+    out: List[CopyItem] = []
+    remaining = sum(len(ps) for ps in per_dst.values())
+    while remaining:
+        # the destination that is furthest behind (ties: lowest rank) goes next
+        d = min((d for d in per_dst if cursor[d] < len(per_dst[d])), key=lambda d: (done[d] / totals[d], d))
+        piece = per_dst[d][cursor[d]]
+        out.append(piece)
+        cursor[d] += 1
+        done[d] += _item_src_bytes(piece)
+        remaining -= 1
+    return out
+
+
 def manifest_by_destination(items: Iterable[CopyItem]) -> Dict[int, List[tuple]]:
     """What each destination rank will receive from this sender, as plain
     tuples that can be published through the MetaServer."""

@@ -272,7 +272,17 @@ class PeerStoreSender:
         ``AWEX_XFER_DEST_ROTATE=1`` every sender starts its walk at a different
         destination (rotation by its own rank), so that senders which work on one
         destination at a time (round-robin chunks) take turns at each receiver
-        instead of meeting there.  Experimental: off by default."""
+        instead of meeting there.  With ``AWEX_XFER_DEST_STRIPE_MB=<MiB>`` the items
+        are cut into stripes of that size and the destinations' stripes are merged
+        in proportion to their bytes (:func:`stripe_by_destination`), and tiles are
+        dealt to CTAs in round-robin chunks: every window of the table, hence
+        every moment of the kernel, then feeds all receivers at once.  Both are
+        experimental and off by default."""
+        stripe = self._stripe_bytes()
+        if stripe and len(self.destinations) >= 2:
+            from awex_b200.transfer.lowering import stripe_by_destination
+
+            return stripe_by_destination(self.items, stripe)
         if os.environ.get("AWEX_XFER_DEST_ROTATE", "0") != "1" or len(self.destinations) < 2:
             return self.items
         shift = self.train_rank % len(self.destinations)
@@ -280,13 +290,18 @@ class PeerStoreSender:
         return sorted(self.items, key=lambda it: order[it.dst_rank])  # stable: keeps the order inside a destination
 
     @staticmethod
-    def _interleave(remote) -> bool:
-        import os
+    def _stripe_bytes() -> int:
+        try:
+            return max(0, int(float(os.environ.get("AWEX_XFER_DEST_STRIPE_MB", "0") or "0") * 1024 * 1024))
+        except ValueError:
+            return 0
 
+    @classmethod
+    def _interleave(cls, remote) -> bool:
         forced = os.environ.get("AWEX_XFER_INTERLEAVE")
         if forced in ("0", "1"):
             return forced == "1"
-        return len(remote) == 0
+        return len(remote) == 0 or cls._stripe_bytes() > 0
 
     def send(self, epoch: int, synchronize: bool = True) -> None:
         for d in self.host_destinations:

@@ -129,3 +129,50 @@ def test_derived_sender_buffers_are_ordinary_sources_of_the_table():
     for r, model in enumerate(job.infer_models[0]):
         got = dict(model.named_parameters())["lm_head.weight"]
         assert torch.equal(got, buffers[r])  # training TP2 -> inference TP2: shard r is sender r's buffer
+
+
+@pytest.mark.parametrize("arch,train,infer,dtype", [
+    ("tiny-qwen2", TrainLayout(tp=2), InferLayout(tp=2, num_engines=2), torch.bfloat16),
+    ("tiny-qwen3-moe", TrainLayout(tp=1, dp=2, ep=2), InferLayout(tp=1, fp8=True, num_engines=2), torch.bfloat16),
+    ("tiny-llama", TrainLayout(tp=1), InferLayout(tp=4, fp8=True), torch.bfloat16),
+], ids=lambda v: v.label() if hasattr(v, "label") else str(v))
+def test_striped_order_does_the_same_work(arch, train, infer, dtype):
+    """Cutting items into stripes and merging the destinations' stripes changes
+    the order only: same bytes to the same places, exactly once, through the CPU
+    executor and through the encoded tables; and every window of the striped list
+    serves all destinations."""
+    from awex_b200.transfer.cpu_exec import execute_items
+    from awex_b200.transfer.lowering import check_exactly_once, manifest_by_destination, stripe_by_destination
+
+    job = SimulatedJob(get_arch(arch), train, infer, dtype=dtype)
+    programs = job.compile_all()
+    views = job.destination_views()
+    stripe = 16 * 1024
+    striped = {r: stripe_by_destination(items, stripe) for r, items in programs.items()}
+    for r, items in striped.items():
+        assert sum(it.numel for it in items) == sum(it.numel for it in programs[r])
+        dests = sorted({it.dst_rank for it in items})
+        if len(dests) > 1 and len(items) > 8 * len(dests):
+            quarter = len(items) // 4
+            for k in range(3):  # any quarter of the list touches every destination
+                assert sorted({it.dst_rank for it in items[k * quarter:(k + 1) * quarter]}) == dests
+    # coverage of every receiver by the striped manifests
+    for rank, rank_views in views.items():
+        manifests = [manifest_by_destination(items).get(rank, []) for items in striped.values()]
+        shapes = {n: (tuple(v.shape), v.dtype) for n, v in rank_views.items()}
+        required = [n for n in shapes if n not in job.aliases]
+        assert check_exactly_once(manifests, shapes, required) == []
+    for r, items in striped.items():
+        execute_items(items, job.local_tensors(r), views)
+    assert job.mismatches() == []
+    # and through descriptor tables
+    for models in job.infer_models:
+        for m in models:
+            for p in m.parameters():
+                p.view(torch.uint8).zero_() if p.dtype == torch.float8_e4m3fn else p.zero_()
+    job.programs = striped
+    encoded = job.encode_all(validate=True)
+    mem = HostMemory(job.source_tensors() + [p for ms in job.infer_models for m in ms for p in m.parameters()])
+    for table, n_tiles, enc in encoded.values():
+        assert run_chunked(table, n_tiles, mem, grid=7, chunk_shift=2, row_offsets=enc.row_offsets)
+    assert job.mismatches() == []
