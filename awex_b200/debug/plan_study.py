@@ -48,7 +48,8 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     i_layout = InferLayout(tp=infer.get("tp", 1), ep=infer.get("ep", 1), num_engines=infer.get("engines", 1), fp8=fp8)
     started = time.time()
     job = SimulatedJob(arch, t_layout, i_layout, dtype=torch.bfloat16, device="meta")
-    job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines, replica_pairing=pairing)
+    job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines, replica_pairing=pairing,
+                                      skip_names=job.builder.skip_names)
     meta_s = time.time() - started
     ranks: List[Dict[str, object]] = []
     ingress = [0] * job.infer_world_size

@@ -57,7 +57,7 @@ def find_aliases(views) -> Dict[str, str]:
     first: Dict[tuple, str] = {}
     out: Dict[str, str] = {}
     for name, t in views:
-        if t.numel() == 0:
+        if t.numel() == 0 or t.device.type == "meta":  # shape-only tensors have no memory to share
             continue
         key = (t.data_ptr(), tuple(t.shape), tuple(t.stride()), str(t.dtype))
         if key in first:
