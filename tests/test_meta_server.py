@@ -148,3 +148,29 @@ def test_host_handshake_poll_times_out_quickly(served):
     assert time.time() - started < 2
     c.put_object(host_ready_key(0, 1), 1)
     poll_key(c, host_ready_key(0, 1), timeout_s=0.2)
+
+
+@pytest.mark.timeout(180)
+def test_server_in_a_subprocess_starts_answers_and_stops():
+    """`start_meta_server` spawns the server in a daemon subprocess (with an
+    empty host it picks this machine's address), returns where it listens, and
+    `stop_meta_server` reaps it."""
+    from awex_b200.meta.meta_server import MetaServerClient, start_meta_server, stop_meta_server
+
+    address, port = start_meta_server("127.0.0.1", 0)
+    try:
+        assert address == "127.0.0.1" and port > 0
+        client = MetaServerClient(address, port)
+        assert client.health_check()
+        client.put_object("k", {"a": 1})
+        client.put_binary("b", b"\x00\x01")
+        client.add_object_to_set("s", 3)
+        assert client.get_object("k", timeout=5) == {"a": 1}
+        # one delete route for every kind of value
+        for key in ("k", "b", "s"):
+            assert client.has_key(key)
+            client.delete(key)
+            assert not client.has_key(key)
+    finally:
+        assert stop_meta_server() is True
+    assert stop_meta_server() is False  # nothing left to stop
