@@ -231,3 +231,58 @@ def test_uneven_pipeline_splits_and_explicit_layouts():
     assert [ids(0, 0), ids(1, 0), ids(0, 1), ids(1, 1)] == [[0], [1, 2], [3], [4]]
     with pytest.raises(ValueError, match="do not match num_hidden_layers"):
         resolve_pp_stage_global_layer_ids(SimpleNamespace(pp_rank=0, pp_size=2), SimpleNamespace(num_hidden_layers=6), {"pipeline_model_parallel_layout": flat}, 0)
+
+
+# ---- shard / replica construction from canned worker reports (the reference's mocked cases) ----------------
+def _worker_rank(tp_rank, tp_size, dp_size, attn_tp_rank, attn_tp_size, attn_dp_rank, world, global_rank):
+    return RankInfo(tp_rank=tp_rank, tp_size=tp_size, pp_rank=0, pp_size=1, dp_size=dp_size, dp_rank=0, ep_rank=0, ep_size=1,
+                    ep_tp_rank=0, ep_tp_size=1, attn_tp_rank=attn_tp_rank, attn_tp_size=attn_tp_size, attn_dp_rank=attn_dp_rank,
+                    world_size=world, global_rank=global_rank, local_rank=global_rank, engine_rank=0, is_infer=True)
+
+
+class _ReportingEngine:
+    engine_name = "sglang"
+
+    def __init__(self, tp, dp, dp_attention, names, ranks):
+        self.config = InferenceConfig(tp_size=tp, pp_size=1, dp_size=dp, ep_size=1, enable_dp_attention=dp_attention, moe_dense_tp_size=1)
+        self.hf_config = SimpleNamespace(num_hidden_layers=4, architectures=["Dummy"], tie_word_embeddings=False)
+        self.reports = [{"rank_info": _worker_rank(*r), "model_arch_name": "Dummy",
+                         "params_meta": [raw(n, s, "torch.float32") for n, s in names]} for r in ranks]
+
+    def execute_task_in_model_worker(self, fn, **kwargs):
+        return self.reports
+
+
+@pytest.mark.parametrize("tp,dp,dp_attention,names,ranks,kind,shards,replicas,offsets", [
+    (1, 1, False, [("embed_tokens.weight", (8, 8)), ("mlp.weight", (8, 8)), ("attention.weight", (8, 8))],
+     [(0, 1, 1, 0, 1, 0, 1, 0)], "NO_SHARDING", 1, 1, [(0, 0)]),
+    (2, 1, False, [("mlp.weight", (4, 8)), ("attention.weight", (4, 8))],
+     [(0, 2, 1, 0, 1, 0, 2, 0), (1, 2, 1, 0, 1, 0, 2, 1)], "TP_SHARDING", 2, 1, [(0, 0), (4, 0)]),
+    # DP attention: sharded over the attention-TP ranks, one replica per attention-DP rank
+    (2, 2, True, [("attention.weight", (2, 8))],
+     [(0, 2, 2, 0, 2, 0, 4, 0), (1, 2, 2, 1, 2, 0, 4, 1), (0, 2, 2, 0, 2, 1, 4, 2), (1, 2, 2, 1, 2, 1, 4, 3)],
+     "DP_TP_SHARDING", 4, 2, [(0, 0), (2, 0), (0, 0), (2, 0)]),
+])
+def test_shards_replicas_and_offsets_from_worker_reports(tp, dp, dp_attention, names, ranks, kind, shards, replicas, offsets):
+    from awex_b200.meta.infer_meta_resolver import InferParamMetaResolver
+
+    resolver = InferParamMetaResolver(_ReportingEngine(tp, dp, dp_attention, names, ranks))
+    params = resolver.get_parameters_meta()
+    assert [p.name for p in params] == [n for n, _ in names]
+    for p in params:
+        assert {s.sharding_type.name for s in p.shards} == {kind}
+        assert len(p.shards) == shards and len(p.replicas) == replicas and p.dtype == torch.float32
+        assert [tuple(s.global_offset) for s in p.shards] == offsets
+        for rep in p.replicas:
+            assert sum(s.numel for s in rep.shards) == p.global_numel  # every replica is a whole copy
+            assert sorted(s.tp_rank for s in rep.shards) == sorted({r[0] for r in ranks})
+        shard = p.shards[0]
+        assert (shard.cp_rank, shard.cp_size, shard.cp_mode) == (0, 1, "none")  # context-parallel fields stay at their defaults
+
+
+def test_ranks_that_disagree_on_the_number_of_replicas_are_refused():
+    from awex_b200.meta.infer_meta_resolver import InferParamMetaResolver
+
+    ranks = [(0, 2, 1, 0, 1, 0, 2, 0), (0, 2, 1, 0, 1, 0, 2, 1), (1, 2, 1, 0, 1, 0, 2, 2)]  # two holders of TP shard 0, one of shard 1
+    with pytest.raises(AssertionError, match="Inconsistent number of replicas"):
+        InferParamMetaResolver(_ReportingEngine(2, 1, False, [("mlp.weight", (4, 8))], ranks))
