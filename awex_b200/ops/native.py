@@ -100,6 +100,13 @@ def _declare(lib: ctypes.CDLL) -> None:
         "awex_encode_tensor_map_2d": ([vp, i32, u64, u64, u64, u64, u32, u32], i32),
         "awex_launch_fp8_block_quant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, i32, vp, vp], i32),
         "awex_launch_fp8_block_dequant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, vp], i32),
+        "awex_vmm_available": ([], i32),
+        "awex_vmm_export_fd": ([u64, ctypes.POINTER(i32)], i32),
+        "awex_vmm_reserve": ([u64, u64, ctypes.POINTER(u64)], i32),
+        "awex_vmm_map_fd": ([u64, u64, u64, i32, i32], i32),
+        "awex_vmm_unmap": ([u64, u64, u64], i32),
+        "awex_vmm_release_range": ([u64, u64], i32),
+        "awex_driver_error_string": ([i32], ctypes.c_char_p),
     }
     for name, (argtypes, restype) in optional.items():
         if hasattr(lib, name):

@@ -48,6 +48,9 @@ class AddressBook:
     segments: List[Tuple[bytes, int, int]] = field(default_factory=list)
     # name -> (segment index, byte offset of element 0, shape, strides, dtype name)
     tensors: Dict[str, Tuple[int, int, Tuple[int, ...], Tuple[int, ...], str]] = field(default_factory=dict)
+    # segment index -> (chunk sizes, descriptor server address, token) for segments of virtual-memory-managed
+    # allocations, which have no IPC handle (see parallel/vmm_memory.py)
+    vmm: Dict[int, Tuple[List[int], str, int]] = field(default_factory=dict)
 
     def dtype_of(self, name: str) -> torch.dtype:
         return getattr(torch, self.tensors[name][4])
@@ -68,6 +71,25 @@ class PeerMemoryExporter:
         self.device_index = torch.cuda.current_device() if device_index is None else device_index
         self.epoch = 0
         self._last_bases: Dict[str, int] = {}
+        self._vmm = None  # created on the first allocation that CUDA IPC refuses
+        self._vmm_pending: Dict[int, Tuple[List[int], str, int]] = {}
+
+    def _export_vmm(self, book: AddressBook, name: str, lo: int, hi: int, ipc_code: int) -> Tuple[int, int]:
+        """Export the allocations under ``[lo, hi)`` as file descriptors.  Returns
+        (base, size) of the range they cover, which becomes a segment of its own."""
+        from awex_b200.parallel.vmm_memory import VmmExporter
+
+        if self._vmm is None:
+            self._vmm = VmmExporter(self.lib)
+        try:
+            seg = self._vmm.export_range(lo, hi)
+        except RuntimeError as exc:
+            raise RuntimeError(
+                f"the allocation of {name} can be exported neither as a CUDA IPC handle (cudaIpcGetMemHandle: CUDA error {ipc_code}) "
+                f"nor as file descriptors of virtual-memory allocations ({exc})"
+            ) from exc
+        self._vmm_pending[seg.base] = (list(seg.chunk_sizes), seg.server, seg.token)
+        return seg.base, seg.size
 
     def _segment_of(self, ptr: int) -> Tuple[int, int]:
         base, size = ctypes.c_uint64(0), ctypes.c_uint64(0)
@@ -90,20 +112,29 @@ class PeerMemoryExporter:
                 continue
             lo, _hi = TensorAddr.of(t).byte_span()
             base, size = self._segment_of(lo)
-            if base not in seg_index:
+            idx = seg_index.get(base)
+            vmm_only = False
+            if idx is not None and idx in book.vmm and _hi > base + book.segments[idx][2]:
+                # an earlier tensor's export of this range of allocations ends before this tensor does
+                idx, vmm_only = None, True
+            if idx is None:
                 handle = b""
                 if with_handles:
-                    buf = ctypes.create_string_buffer(hbytes)
-                    code = self.lib.awex_ipc_export(base, buf)
+                    code = -1
+                    if not vmm_only:
+                        buf = ctypes.create_string_buffer(hbytes)
+                        code = self.lib.awex_ipc_export(base, buf)
                     if code != 0:
-                        raise RuntimeError(
-                            f"cudaIpcGetMemHandle failed for the allocation of {name} (CUDA error {code}); allocations made "
-                            "with expandable segments / virtual memory cannot be exported this way"
-                        )
-                    handle = buf.raw
-                seg_index[base] = len(book.segments)
+                        # not a cudaMalloc allocation: try the virtual-memory route over the whole tensor
+                        base, size = self._export_vmm(book, name, lo, _hi, code)
+                    else:
+                        handle = buf.raw
+                idx = len(book.segments)
                 book.segments.append((handle, base, size))
-            book.tensors[name] = (seg_index[base], t.data_ptr() - base, tuple(t.shape), tuple(t.stride()), str(t.dtype).replace("torch.", ""))
+                seg_index[base] = idx  # later tensors of the same allocation reuse the newest export
+                if base in self._vmm_pending:
+                    book.vmm[idx] = self._vmm_pending.pop(base)
+            book.tensors[name] = (idx, t.data_ptr() - base, tuple(t.shape), tuple(t.stride()), str(t.dtype).replace("torch.", ""))
             self._last_bases[name] = t.data_ptr()
         return book
 
@@ -123,9 +154,12 @@ class PeerMemoryImporter:
 
     def resolve(self, book: AddressBook) -> Dict[str, TensorAddr]:
         bases: List[int] = []
-        for handle, owner_base, _size in book.segments:
+        for index, (handle, owner_base, _size) in enumerate(book.segments):
             if tuple(book.owner) == self._me:
                 bases.append(owner_base)
+                continue
+            if index in getattr(book, "vmm", {}):
+                bases.append(self._map_vmm(owner_base, *book.vmm[index]))
                 continue
             if not handle:
                 raise RuntimeError("address book of another process carries no IPC handles")
@@ -147,9 +181,20 @@ class PeerMemoryImporter:
             out_addrs[name] = TensorAddr(bases[seg] + offset, tuple(shape), tuple(strides), getattr(torch, dtype))
         return out_addrs
 
+    def _map_vmm(self, owner_base: int, chunk_sizes, server: str, token: int) -> int:
+        import torch as _torch
+
+        from awex_b200.parallel.vmm_memory import VmmImporter, VmmSegment
+
+        if getattr(self, "_vmm", None) is None:
+            self._vmm = VmmImporter(_torch.cuda.current_device(), self.lib)
+        return self._vmm.map(VmmSegment(owner_base, list(chunk_sizes), server, token))
+
     def close_all(self) -> None:
         """Unmap everything (must happen before the owner frees or re-maps the
         memory)."""
+        if getattr(self, "_vmm", None) is not None:
+            self._vmm.close_all()
         for handle, mapped in list(self._open.items()):
             code = self.lib.awex_ipc_close(mapped)
             if code != 0:
