@@ -12,6 +12,13 @@ a CUDA-IPC mapping.  The native half is ``ops/csrc/vmm_memory.cu``.
 
 The reference documents such memory as unsupported (`docs/README.md:91` there).
 
+An importer's mapping holds a reference to the physical allocations.  An
+allocator that releases them (an engine going to sleep) does not get the memory
+back until importers unmap (:meth:`VmmImporter.close_all`), and one that
+creates new allocations at the old addresses on wake-up must be exported again:
+the addresses are the same but the memory behind them is not, which a pointer
+comparison cannot see.
+
 Limits: one descriptor per physical allocation and per export (process file
 descriptor limits apply: a 60 GB shard in 20 MiB allocations needs about 3000);
 the allocations must have been created with POSIX file descriptors as a
