@@ -15,7 +15,9 @@ the table each CTA walks:
 * ``chunks``: chunks of the table are dealt round-robin, so all CTAs work inside
   one narrow window of the table;
 * ``striped``: the table is first re-ordered by :func:`stripe_by_destination`
-  (every window feeds all destinations), then dealt in chunks.
+  (every window feeds all destinations), then dealt in chunks;
+* ``rotated``: chunks, but sender r starts its walk at its (r mod n)-th
+  destination, so that senders with equal tables take turns at each receiver.
 
 The model has no launch or flag latency and no per-tile overheads: it explains
 ratios (two senders meeting at one receiver run at half rate), not microseconds.
@@ -27,6 +29,10 @@ are the bound (links run at 0.82 to 0.86 of their copy rate under many writers).
 Striped orders can resonate: a stripe of 8 chunks with 148 CTAs makes CTAs
 alternate between two receivers in step and costs 20%; stripes of 2 chunks (CTAs
 pinned to one receiver each) or of 32 and more (no common period) do not.
+Rotation by rank only helps while all senders have the same destination set: in
+the Llama layout two senders also hold a few replicated norm weights for a third
+receiver, their rotation lands on the neighbour's first receiver, and that pair
+runs at half rate (20.9 ms) while the other pair is done in 10.4 ms.
 """
 
 from __future__ import annotations
@@ -147,6 +153,15 @@ def simulate(tables: Dict[int, np.ndarray], order: str, n_gpus: int, grid: int =
     return {"order": order, "ms": max(per_sender.values()), "ms_per_sender": per_sender, "peak_ingress_GBps": (peak_ingress / 1e9).round(1).tolist()}
 
 
+def _rotated(items: Sequence, rank: int) -> List:
+    dests = sorted({it.dst_rank for it in items})
+    if len(dests) < 2:
+        return list(items)
+    shift = rank % len(dests)
+    order = {d: (i - shift) % len(dests) for i, d in enumerate(dests)}
+    return sorted(items, key=lambda it: order[it.dst_rank])
+
+
 def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: str = "colocated", layers: int = 0, fp8: bool = False,
           pairing: str = "spread", orders: Sequence[str] = ("contiguous", "chunks", "striped"), stripe_mb: float = 1.0,
           chunk_tiles: int = 4, grid: int = 148, nvlink_gbps: float = 770.0, hbm_gbps: float = 6540.0) -> List[Dict[str, object]]:
@@ -176,7 +191,8 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     programs = {r: job.compile_send_program(r) for r in range(t_layout.world)}
     out = []
     for order in orders:
-        items = {r: (stripe_by_destination(p, int(stripe_mb * 2**20)) if order == "striped" else p) for r, p in programs.items()}
+        items = {r: (stripe_by_destination(p, int(stripe_mb * 2**20)) if order == "striped" else _rotated(p, r) if order == "rotated" else p)
+                 for r, p in programs.items()}
         tables = {r: segments_of(p, r, gpu_of_dst) for r, p in items.items() if len(p)}
         result = simulate(tables, "contiguous" if order == "contiguous" else "chunks", n_gpus, grid=grid, chunk_bytes=chunk_tiles * 32768,
                           nvlink=nvlink_gbps * 1e9, hbm=hbm_gbps * 1e9)

@@ -29,7 +29,7 @@ KNOBS: Dict[str, Tuple[str, str]] = {
     "AWEX_XFER_VARIANT": ("", "0 | 1: force the launch shape of the fused transfer kernel (one 512-thread or two 256-thread CTAs per SM)"),
     "AWEX_XFER_INTERLEAVE": ("", "0 | 1: force contiguous tile ranges or round-robin chunks"),
     "AWEX_XFER_DEST_STRIPE_MB": ("0", "cut items into stripes of this many MiB and merge the destinations' stripes in proportion to their bytes, with round-robin chunks (experimental)"),
-    "AWEX_XFER_DEST_ROTATE": ("0", "1: each sender starts its table at a different destination (experimental, with AWEX_XFER_INTERLEAVE=1)"),
+    "AWEX_XFER_DEST_ROTATE": ("0", "1: each sender starts its table at a different destination (experimental, with AWEX_XFER_INTERLEAVE=1; only helps when all senders have the same destination set)"),
     "AWEX_USE_BATCH_SEND_RECV": ("1", "message transport only: 0 sends one message at a time and waits for each"),
     "AWEX_SYNTH_FP8_ORACLE": ("cpu", "synthetic models: 'kernel' builds fp8 oracles with the quantisation kernel instead of the CPU"),
     # accepted, no effect here
