@@ -383,17 +383,23 @@ class GlooSender:
         env.warn_about_ignored(logger)
 
     def send(self, epoch: int, synchronize: bool = True) -> None:
+        from awex_b200.transfer.nccl_comm import chunk_budget_from_env, chunk_entries_from_env, split_by_budget
+
         one_by_one = os.environ.get("AWEX_USE_BATCH_SEND_RECV", "1") == "0"
+        budget, max_entries = chunk_budget_from_env(), chunk_entries_from_env()
+        bounded = budget > 0 or max_entries > 0  # staging bounded to one run at a time (the receiver cuts the same runs)
         works = []
         for d in self.destinations:
-            msg = pack_message(self.by_dst[d], self.local).to(self.device)
-            if env.flag("AWEX_P2P_TRACE"):
-                logger.info(f"[p2p] train rank {self.train_rank} epoch {epoch}: {msg.numel()} bytes in {len(self.by_dst[d])} items to rank {d}")
-            work = self.group.send(msg, d, tag=epoch & 0x7FFF)
-            if one_by_one:
-                work.wait()
-            else:
-                works.append((work, msg))
+            runs = split_by_budget([entry_nbytes(e) for e in self.manifest[d]], budget, max_entries)
+            for b, e in runs:
+                msg = pack_message(self.by_dst[d][b:e], self.local).to(self.device)
+                if env.flag("AWEX_P2P_TRACE"):
+                    logger.info(f"[p2p] train rank {self.train_rank} epoch {epoch}: {msg.numel()} bytes in {e - b} items to rank {d}")
+                work = self.group.send(msg, d, tag=epoch & 0x7FFF)
+                if one_by_one or bounded:
+                    work.wait()
+                else:
+                    works.append((work, msg))
         for w, _keepalive in works:
             w.wait()
 
@@ -431,10 +437,17 @@ class GlooReceiver:
         pass
 
     def finish(self, epoch: int, synchronize: bool = True) -> None:
+        from awex_b200.transfer.nccl_comm import chunk_budget_from_env, chunk_entries_from_env, split_by_budget
+
+        budget, max_entries = chunk_budget_from_env(), chunk_entries_from_env()
+        self.peak_staging_bytes = 0
         for r, entries in zip(self.senders, self.entries):
-            buf = torch.empty(sum(entry_nbytes(e) for e in entries), dtype=torch.uint8, device=self.device)
-            self.group.recv(buf, self.infer_world + r, tag=epoch & 0x7FFF).wait()
-            unpack_message(entries, buf, self.views)
+            sizes = [entry_nbytes(e) for e in entries]
+            for b, e in split_by_budget(sizes, budget, max_entries):  # the sender cuts the same runs from the same sizes
+                buf = torch.empty(sum(sizes[b:e]), dtype=torch.uint8, device=self.device)
+                self.peak_staging_bytes = max(self.peak_staging_bytes, buf.numel())
+                self.group.recv(buf, self.infer_world + r, tag=epoch & 0x7FFF).wait()
+                unpack_message(entries[b:e], buf, self.views)
 
     def gpu_launches_per_update(self) -> int:
         return 0

@@ -23,7 +23,7 @@ KNOBS: Dict[str, Tuple[str, str]] = {
     "AWEX_MEM_DEBUG": ("0", "1: log device memory around the phases of an update"),
     "AWEX_DEBUG_INFER_META": ("0", "1: log every inference parameter while metadata is collected"),
     "AWEX_P2P_TRACE": ("0", "1: log, per update, what each sender writes to each destination (bytes, descriptors, tiles)"),
-    "AWEX_CHUNK_MB": ("0", "message transport, co-located exchange: staging bound in MiB per message run (0: whole messages); the fused kernel stages nothing"),
+    "AWEX_CHUNK_MB": ("0", "message data plane and co-located message exchange: staging bound in MiB per message run (0: whole messages), same value on both sides; the fused kernel stages nothing"),
     "AWEX_DATA_PLANE": ("", "peer_stores (fused kernel through CUDA IPC, one machine) or messages (NCCL / gloo messages, any topology); default by device"),
     "AWEX_XFER_CHUNK_MB": ("", "size in MiB of the chunks of tiles dealt to CTAs by the fused transfer kernel (default by op mix)"),
     "AWEX_XFER_VARIANT": ("", "0 | 1: force the launch shape of the fused transfer kernel (one 512-thread or two 256-thread CTAs per SM)"),
@@ -33,7 +33,7 @@ KNOBS: Dict[str, Tuple[str, str]] = {
     "AWEX_USE_BATCH_SEND_RECV": ("1", "message transport only: 0 sends one message at a time and waits for each"),
     "AWEX_SYNTH_FP8_ORACLE": ("cpu", "synthetic models: 'kernel' builds fp8 oracles with the quantisation kernel instead of the CPU"),
     # accepted, no effect here
-    "AWEX_CHUNK_OPS": ("0", "message transport, co-located exchange: entries per message run (0: no bound)"),
+    "AWEX_CHUNK_OPS": ("0", "message data plane and co-located message exchange: entries per message run (0: no bound), same value on both sides"),
     "AWEX_DESTROY_PG_AFTER_UPDATE": ("0", "no effect on the fused path (it holds no communicator); the message transport keeps its group"),
     "AWEX_P2P_HCCL_BUFFER_SIZE": ("", "no effect: Ascend HCCL is not supported"),
     "AWEX_USE_MINDSPEED": ("0", "no effect: the Ascend MindSpeed patch is not applied on CUDA"),

@@ -13,6 +13,8 @@ import torch.multiprocessing as mp
 def _layouts(case):
     from awex_b200.synthetic.simulate import InferLayout
 
+    if case == "pp2_to_tp2_chunked":  # the same layout with staging bounded to 0.25 MiB runs on both sides
+        return "tiny-llama", dict(tp=1, pp=2), InferLayout(tp=2), torch.float32
     if case == "pp2_to_tp2":
         return "tiny-llama", dict(tp=1, pp=2), InferLayout(tp=2), torch.float32
     if case == "tp1_to_tp2_fp8":
@@ -38,6 +40,8 @@ def _writer(case, rank, meta_addr, store_port, q):
 
     try:
         os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        if case.endswith("_chunked"):
+            os.environ["AWEX_CHUNK_MB"] = "0.25"
         arch, train, _infer, dtype = _layouts(case)
         world = _train_world(train)
         group = None
@@ -68,6 +72,8 @@ def _reader(case, worker_rank, meta_addr, store_port, q):
 
     try:
         os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        if case.endswith("_chunked"):
+            os.environ["AWEX_CHUNK_MB"] = "0.25"
         arch, _train, layout, dtype = _layouts(case)
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=worker_rank, world_size=layout.tp)
         ri = infer_rank_infos(tp=layout.tp)[worker_rank]
@@ -77,6 +83,10 @@ def _reader(case, worker_rank, meta_addr, store_port, q):
         reader.initialize()
         reader.update_weights(step_id=1)
         bad = engine.mismatches(step=0)
+        if case.endswith("_chunked"):
+            peak = engine.schedulers[0].awes_weights_reader.transport.peak_staging_bytes
+            # runs of at most a quarter MiB, or one larger tensor travelling alone (the embedding slice: 0.5 MiB)
+            assert 0 < peak <= 1024 * 256 * 4 // 2 + 1024, peak
         if case.endswith("norm_head"):
             # the head arrives with unit-norm columns (computed by the single training rank over the whole vocabulary)
             from awex_b200.synthetic.models import CanonicalWeights
@@ -95,7 +105,7 @@ def _reader(case, worker_rank, meta_addr, store_port, q):
 
 
 @pytest.mark.timeout(400)
-@pytest.mark.parametrize("case", ["pp2_to_tp2", "tp1_to_tp2_fp8", "tp2_to_tp1_fp8", "tp1_to_tp2_norm_head"])
+@pytest.mark.parametrize("case", ["pp2_to_tp2", "pp2_to_tp2_chunked", "tp1_to_tp2_fp8", "tp2_to_tp1_fp8", "tp1_to_tp2_norm_head"])
 def test_layout_over_gloo(case):
     from awex_b200.meta.meta_server import MetaServer
     from awex_b200.utils.common import get_free_port
