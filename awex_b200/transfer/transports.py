@@ -10,8 +10,10 @@
   the path; ordering is carried by per-(sender, receiver) epoch flags in
   device memory with bounded waits.
 * :class:`GlooSender` / :class:`GlooReceiver` — the same items moved as packed
-  byte messages over a Gloo exchange group; used on CPU-only hosts and as the
-  portable fallback.
+  byte messages over an exchange group that spans both worlds (gloo on CPUs,
+  NCCL on GPUs); used on CPU-only hosts and where peer mapping is impossible
+  (several machines).  ``AWEX_CHUNK_MB`` / ``AWEX_CHUNK_OPS`` bound the staging
+  of one message run.  :func:`choose_data_plane` picks between the two planes.
 
 What both replace in the reference: per-operation ``isend``/``irecv`` lists
 inside one NCCL group, staging copies for strided views and a barrier per step
