@@ -66,14 +66,14 @@ def test_random_block_fp8_layouts_through_the_descriptor_tables():
     from awex_b200.transfer.table_interpreter import HostMemory, run_table
 
     rng = random.Random(77)
-    done = refused = 0
-    while done < 14:
+    done = refused = gathered = 0
+    while done < 18:
         base = rng.choice(["tiny-llama", "tiny-qwen2", "tiny-qwen3-moe"])
         heads = rng.choice([2, 4, 8])
         kv = rng.choice([k for k in (1, 2, 4, 8) if heads % k == 0 and k <= heads])
         arch = dataclasses.replace(get_arch(base), num_heads=heads, num_kv_heads=kv, head_dim=128, hidden=rng.choice([256, 512]), num_layers=1, vocab=512)
         arch = dataclasses.replace(arch, num_experts=4, expert_ffn=rng.choice([128, 256, 384])) if arch.is_moe else dataclasses.replace(arch, ffn=rng.choice([256, 512, 768]))
-        ttp, tdp, itp = rng.choice([1, 1, 2]), rng.choice([1, 2]), rng.choice([1, 2, 4])
+        ttp, tdp, itp = rng.choice([1, 2, 2, 4]), rng.choice([1, 2]), rng.choice([1, 2, 4])
         tep = iep = 1
         if arch.is_moe:
             tep = rng.choice([e for e in (1, 2, 4) if (ttp * tdp) % e == 0])
@@ -90,6 +90,7 @@ def test_random_block_fp8_layouts_through_the_descriptor_tables():
             refused += 1
             continue
         assert job.check_coverage() == [], label
+        gathered += any(d.gathers for ds in job.derived.values() for d in ds)
         encoded = job.encode_all(validate=True)
         mem = HostMemory(job.source_tensors() + [p for ms in job.infer_models for m in ms for p in m.parameters()])
         for table, n_tiles, enc in encoded.values():
@@ -97,3 +98,4 @@ def test_random_block_fp8_layouts_through_the_descriptor_tables():
         assert job.mismatches() == [], label
         done += 1
     assert refused < 40
+    assert gathered >= 2  # some layouts needed rows of training TP peers for their quantisation blocks
