@@ -1,0 +1,172 @@
+"""The host protocol of the peer-store data plane, run on the CPU: real
+`PeerStoreSender` / `PeerStoreReceiver`, real MetaServer, real lowering,
+descriptor encoding and validation; the device pieces are stand-ins (address
+books over host pointers, a "kernel" that runs the descriptor table through the
+host interpreter, flag kernels that do nothing).  What is checked: who publishes
+what, in which order the sides shake hands, that the table the sender built
+moves the right bytes, and what happens when a receiver's parameters move."""
+
+import contextlib
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from awex_b200.parallel import peer_memory
+from awex_b200.parallel.peer_memory import AddressBook
+from awex_b200.transfer.descriptors import TensorAddr
+from awex_b200.transfer.table_interpreter import HostMemory, run_table
+
+ACTING = ["nobody"]  # which "process" the code under test currently belongs to
+GPU_OF = {}  # process -> GPU identity
+MEMORY = []  # every tensor a fake kernel may touch
+
+
+@contextlib.contextmanager
+def acting_as(who):
+    previous, ACTING[0] = ACTING[0], who
+    try:
+        yield
+    finally:
+        ACTING[0] = previous
+
+
+class FakeExporter:
+    def __init__(self, device_index=None):
+        self.device_index, self.epoch, self._last = 0, 0, {}
+
+    def export(self, named, with_handles=True):
+        self.epoch += 1
+        book = AddressBook(("box", ACTING[0]), 0, GPU_OF[ACTING[0]], self.epoch)
+        for name, t in named:
+            lo, hi = TensorAddr.of(t).byte_span()
+            book.segments.append((b"", lo, hi - lo))
+            book.tensors[name] = (len(book.segments) - 1, t.data_ptr() - lo, tuple(t.shape), tuple(t.stride()), str(t.dtype).replace("torch.", ""))
+            self._last[name] = t.data_ptr()
+        return book
+
+    def changed(self, named):
+        return any(self._last.get(n) != t.data_ptr() for n, t in named if t.numel())
+
+
+class FakeImporter:
+    opened = closed = 0
+
+    def __init__(self):
+        FakeImporter.opened += 1
+
+    def resolve(self, book):
+        return {n: TensorAddr(book.segments[seg][1] + off, tuple(shape), tuple(strides), getattr(torch, dtype))
+                for n, (seg, off, shape, strides, dtype) in book.tensors.items()}
+
+    def close_all(self):
+        FakeImporter.closed += 1
+
+
+class FakeProgram:
+    built = 0
+
+    def __init__(self, table, n_tiles, device, ready_pad=None, ready_slots=(), done_flag_addrs=(), timeout_ms=0, grid=0, encoder=None, interleave=True):
+        FakeProgram.built += 1
+        self.table, self.n_tiles, self.encoder = table, n_tiles, encoder
+        self.ready_slots, self.interleave, self.launches = list(ready_slots), interleave, []
+
+    def launch(self, epoch):
+        self.launches.append(epoch)
+        assert run_table(self.table, self.n_tiles, HostMemory(MEMORY), self.encoder.row_offsets) == self.n_tiles
+
+    def check(self):
+        pass
+
+
+class FakeFlags:
+    def __init__(self, first, *rest, **kw):
+        self.n = len(first if isinstance(first, (list, tuple)) else rest[0])
+        self.status = SimpleNamespace(raise_if_failed=lambda: None)
+        self.launches = []
+
+    def launch(self, epoch, stream_ptr=None):
+        self.launches.append(epoch)
+
+
+@pytest.fixture
+def fakes(monkeypatch):
+    from awex_b200.ops import fused_transfer
+
+    monkeypatch.setattr(peer_memory, "PeerMemoryExporter", FakeExporter)
+    monkeypatch.setattr(peer_memory, "PeerMemoryImporter", FakeImporter)
+    monkeypatch.setattr(peer_memory, "process_identity", lambda: ("box", ACTING[0]))
+    monkeypatch.setattr(peer_memory, "_device_uuid", lambda index: GPU_OF[ACTING[0]])
+    monkeypatch.setattr(fused_transfer, "TransferProgram", FakeProgram)
+    monkeypatch.setattr(fused_transfer, "FlagPoster", FakeFlags)
+    monkeypatch.setattr(fused_transfer, "FlagWaiter", FakeFlags)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: SimpleNamespace(synchronize=lambda: None))
+    FakeImporter.opened = FakeImporter.closed = FakeProgram.built = 0
+    MEMORY.clear()
+    GPU_OF.clear()
+    yield
+
+
+def build_pair(gpus):
+    """One training rank (TP1) and one inference rank (TP1) of the tiny model as
+    two "processes"; ``gpus`` = (GPU of the trainer, GPU of the server)."""
+    from awex_b200.meta.meta_server import MetaServer, MetaServerClient
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+
+    GPU_OF.update(train0=gpus[0], infer0=gpus[1])
+    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=1), InferLayout(tp=1), dtype=torch.float32)
+    items = job.compile_all()[0]
+    local = job.local_tensors(0)
+    views = job.destination_views()[0]
+    MEMORY.extend(list(local.values()) + [p for m in job.infer_models[0] for p in m.parameters()])
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    meta = MetaServerClient("127.0.0.1", server.port)
+    return job, items, local, views, server, meta
+
+
+def make_sides(job, items, local, views, meta, **receiver_kw):
+    from awex_b200.transfer.transports import PeerStoreReceiver, PeerStoreSender
+
+    required = sorted(n for n in views)
+    with acting_as("infer0"):
+        receiver = PeerStoreReceiver(meta, views, 0, 1, 1, required, "cpu", wait_timeout_s=20, **receiver_kw)
+    with acting_as("train0"):
+        sender = PeerStoreSender(meta, items, local, 0, 1, "cpu", wait_timeout_s=20)
+    with acting_as("infer0"):
+        receiver.connect()
+    with acting_as("train0"):
+        sender.connect()
+    return sender, receiver
+
+
+def update(sender, receiver, epoch):
+    with acting_as("infer0"):
+        receiver.begin(epoch)
+    with acting_as("train0"):
+        sender.send(epoch)
+    with acting_as("infer0"):
+        receiver.finish(epoch)
+
+
+@pytest.mark.parametrize("gpus,host_pair", [(("GPU-a", "GPU-a"), True), (("GPU-a", "GPU-b"), False)])
+def test_two_processes_exchange_through_books_manifests_and_handshakes(fakes, gpus, host_pair):
+    job, items, local, views, server, meta = build_pair(gpus)
+    try:
+        sender, receiver = make_sides(job, items, local, views, meta)
+        assert sender.host_destinations == ([0] if host_pair else []) and receiver.host_senders == ([0] if host_pair else [])
+        assert sender.program.ready_slots == ([] if host_pair else [0])  # a peer GPU announces readiness through a device flag
+        assert sender.program.interleave == host_pair  # round-robin chunks only while nothing crosses NVLink
+        assert receiver.bytes_in == sender.bytes_out and sender.bytes_remote == (0 if host_pair else sender.bytes_out)
+        update(sender, receiver, 1)
+        assert job.mismatches() == [] and sender.program.launches == [1]
+        if host_pair:  # same GPU, two processes: the sides met on the host
+            from awex_b200.transfer.transports import host_done_key, host_ready_key
+
+            assert meta.has_key(host_ready_key(0, 1)) and meta.has_key(host_done_key(1, 1))
+            update(sender, receiver, 2)
+            assert not meta.has_key(host_ready_key(0, 1)) and meta.has_key(host_ready_key(0, 2))  # old epochs are cleaned up
+        assert FakeProgram.built == 1 and FakeImporter.opened == 2  # planned and mapped once, whatever the number of updates
+    finally:
+        server.stop()
