@@ -51,6 +51,9 @@ class AddressBook:
     # segment index -> (chunk sizes, descriptor server address, token) for segments of virtual-memory-managed
     # allocations, which have no IPC handle (see parallel/vmm_memory.py)
     vmm: Dict[int, Tuple[List[int], str, int]] = field(default_factory=dict)
+    # the owner may move or re-map these tensors between updates: senders then wait on the host, before
+    # every update, for the epoch of the book that is valid for it
+    may_move: bool = False
 
     def dtype_of(self, name: str) -> torch.dtype:
         return getattr(torch, self.tensors[name][4])

@@ -94,6 +94,24 @@ class WorkerWeightsReader:
         self.device = next(iter(self.parameters.values())).device if self.parameters else torch.device("cpu")
         self._published_ptrs = self._model_ptrs()
 
+    def _rebind_views(self) -> None:
+        """Canonical views of the model as it is now, under the names published before."""
+        converter = get_infer_weights_converter(
+            self.engine_name, type(self.model).__name__, hf_config=self.model.config, infer_engine_config=self.infer_engine_config,
+            rank_info=self.rank_info,
+        )
+        fresh = dict(canonical_named_views(self.model, converter, self.model_context, convert_params=True))
+        if set(fresh) != set(self.parameters):
+            raise RuntimeError("the model exposes other parameters than it did when the plan was made")
+        for name, t in fresh.items():
+            old = self.parameters[name]
+            if tuple(t.shape) != tuple(old.shape) or t.dtype != old.dtype:
+                raise RuntimeError(f"{name} changed shape or dtype ({tuple(old.shape)} {old.dtype} -> {tuple(t.shape)} {t.dtype})")
+        self.parameters = fresh
+        self._published_ptrs = self._model_ptrs()
+        self._sum_plan = None  # device checksum plans hold the old addresses
+        self.transport.rebind(self.parameters)
+
     def _model_ptrs(self) -> Dict[str, int]:
         """Address of every parameter of the model as it is now.  The canonical
         views keep the storages alive that they were cut from, so only the model
@@ -195,7 +213,8 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
         if plane == "peer_stores":
             from awex_b200.transfer.transports import PeerStoreReceiver
 
-            self.transport = PeerStoreReceiver(timeout_ms=self.device_wait_timeout_ms, **common)
+            self.transport = PeerStoreReceiver(timeout_ms=self.device_wait_timeout_ms,
+                                               may_move=bool(self.debug_mode_config.get("parameters_may_move", False)), **common)
         else:
             from awex_b200.transfer.transports import GlooReceiver
 
@@ -206,10 +225,16 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
     def begin_update(self, step_id) -> None:
         self.epoch += 1
         moved = self.parameters_moved()
-        if moved:
+        if moved and getattr(self.transport, "may_move", False):
+            # the engine re-allocated or re-mapped its weights (sleep / wake-up): cut the canonical views again;
+            # the transport publishes their addresses and the senders rebuild their tables before they write
+            logger.info(f"Rank[{self.transfer_rank}] {len(moved)} parameters moved; publishing their new addresses")
+            self._rebind_views()
+        elif moved:
             raise RuntimeError(
                 f"{len(moved)} inference parameters (e.g. {moved[:3]}) moved since they were published; senders hold "
-                "stale addresses (re-create the writer and reader after the engine re-maps its weights)"
+                "stale addresses (re-create the writer and reader after the engine re-maps its weights, or set "
+                "debug_mode_config['parameters_may_move'] on the inference side)"
             )
         with phase("announce_ready"):
             self.transport.begin(self.epoch)

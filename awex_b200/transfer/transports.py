@@ -119,10 +119,13 @@ def _check_coverage(entries, views: Dict[str, torch.Tensor], required: Sequence[
 class PeerStoreReceiver:
     def __init__(self, meta, views: Dict[str, torch.Tensor], transfer_rank: int, infer_world: int, train_world: int,
                  required: Sequence[str], device, timeout_ms: int = 2000, wait_timeout_s: float = 10000, strict: bool = True,
-                 host_wait_timeout_s: Optional[float] = None):
+                 host_wait_timeout_s: Optional[float] = None, may_move: bool = False):
         from awex_b200.ops.fused_transfer import FlagPad
         from awex_b200.parallel.peer_memory import PeerMemoryExporter
 
+        # the engine may re-allocate or re-map its weights between updates (sleep / wake-up): the address book is
+        # re-published when they moved and every update starts with a host handshake that names the valid book
+        self.may_move = bool(may_move)
         self.meta, self.views, self.rank = meta, views, transfer_rank
         self.infer_world, self.train_world = infer_world, train_world
         self.required, self.device, self.strict = list(required), torch.device(device), strict
@@ -140,13 +143,25 @@ class PeerStoreReceiver:
         return list(self.views.items()) + [(DONE_PAD, self.done_pad.t)]
 
     def publish(self) -> None:
-        self.meta.put_object(addr_key(self.rank), self.exporter.export(self._named()))
+        book = self.exporter.export(self._named())
+        if self.may_move:
+            book.may_move = True
+        self.meta.put_object(addr_key(self.rank), book)
 
-    def republish_if_moved(self) -> bool:
-        if self.exporter.changed(self._named()):
+    def republish_if_moved(self, force: bool = False) -> bool:
+        """Publish a new book when a tensor's address changed (or on ``force``: the
+        addresses are the same but the memory behind them is new)."""
+        if force or self.exporter.changed(self._named()):
             self.publish()
             return True
         return False
+
+    def rebind(self, views: Dict[str, torch.Tensor]) -> None:
+        """The same names now live in other tensors (the next ``begin`` publishes them)."""
+        missing = [n for n in self.required if n not in views]
+        if missing:
+            raise KeyError(f"rebound views lack {missing[:5]}")
+        self.views = views
 
     def connect(self) -> None:
         """Learn who writes here, check their manifests, map their ready pads."""
@@ -173,11 +188,14 @@ class PeerStoreReceiver:
 
     def begin(self, epoch: int) -> None:
         """Tell every sender that parameters may be overwritten now."""
+        if self.may_move:
+            self.republish_if_moved()
         self.poster.launch(epoch)
-        if self.host_senders:
+        if self.host_senders or self.may_move:
             # work queued on this GPU before the update must not read half-written weights
             torch.cuda.current_stream(self.device).synchronize()
-            self.meta.put_object(host_ready_key(self.rank, epoch), 1)
+            # the value is the epoch of the address book that is valid for this update
+            self.meta.put_object(host_ready_key(self.rank, epoch), self.exporter.epoch)
             if self._last_host_epoch is not None and self._last_host_epoch != epoch:
                 self.meta.delete_if_exists(host_ready_key(self.rank, self._last_host_epoch))
             self._last_host_epoch = epoch
@@ -212,6 +230,10 @@ class PeerStoreSender:
         self.timeout_ms, self.wait_timeout_s, self.validate, self.grid = timeout_ms, wait_timeout_s, validate, grid
         self.host_wait_timeout_s = wait_timeout_s if host_wait_timeout_s is None else host_wait_timeout_s
         self.host_destinations: List[int] = []
+        # destinations whose owner may move its tensors, and the epoch of the book the current table was built from
+        self.moving_destinations: List[int] = []
+        self._book_epochs: Dict[int, int] = {}
+        self.rebuilds = 0
         self._last_host_epoch: Optional[int] = None
         self.ready_pad = FlagPad(infer_world, self.device)
         self.exporter = PeerMemoryExporter(self.device.index)
@@ -238,6 +260,9 @@ class PeerStoreSender:
             addrs = self.importer.resolve(book)
             dst_addrs[d] = addrs
             done_flags.append(addrs[DONE_PAD].ptr + 8 * self.train_rank)
+            self._book_epochs[d] = book.epoch
+            if getattr(book, "may_move", False) and tuple(book.owner) != me:
+                self.moving_destinations.append(d)
             if shares_gpu(book, my_uuid, me):
                 self.host_destinations.append(d)  # same GPU, other process: host handshake
             elif tuple(book.owner) != me:
@@ -305,7 +330,26 @@ class PeerStoreSender:
             return forced == "1"
         return len(remote) == 0 or cls._stripe_bytes() > 0
 
+    def _follow_moves(self, epoch: int) -> None:
+        """Wait until every destination that may move has named the address book
+        that is valid for this update; when one of them is newer than the book the
+        table was built from, unmap everything, fetch the books again and rebuild
+        the table."""
+        stale = False
+        for d in self.moving_destinations:
+            key = host_ready_key(d, epoch)
+            poll_key(self.meta, key, self.host_wait_timeout_s)
+            stale = stale or int(self.meta.get_object(key, timeout=self.host_wait_timeout_s)) != self._book_epochs.get(d)
+        if stale:
+            self.importer.close_all()
+            self.host_destinations, self.moving_destinations, self._book_epochs = [], [], {}
+            self.connect()
+            self.rebuilds += 1
+            logger.info(f"training rank {self.train_rank}: destinations moved, table rebuilt ({self.rebuilds} so far)")
+
     def send(self, epoch: int, synchronize: bool = True) -> None:
+        if self.moving_destinations:
+            self._follow_moves(epoch)
         for d in self.host_destinations:
             poll_key(self.meta, host_ready_key(d, epoch), self.host_wait_timeout_s)
         if env.flag("AWEX_P2P_TRACE"):
@@ -421,11 +465,17 @@ class GlooReceiver:
         self.required, self.device, self.strict, self.wait_timeout_s = list(required), torch.device(device), strict, wait_timeout_s
         self.group = None
 
+    # messages land in whatever the views are when they arrive: moved parameters only need fresh views
+    may_move = True
+
     def publish(self) -> None:
         pass
 
-    def republish_if_moved(self) -> bool:
+    def republish_if_moved(self, force: bool = False) -> bool:
         return False
+
+    def rebind(self, views: Dict[str, torch.Tensor]) -> None:
+        self.views = views
 
     def connect(self) -> None:
         self.group = _join_exchange_group(self.meta, self.rank, self.infer_world + self.train_world, self.wait_timeout_s, self.device,

@@ -152,6 +152,43 @@ def test_reader_notices_reallocated_parameters():
     assert reader.parameters_moved() == [name]
 
 
+def test_worker_reader_refuses_or_follows_moved_parameters():
+    """Without ``parameters_may_move`` an update through stale addresses is refused
+    with the way out named; with it the worker cuts its views again from the live
+    model and hands them to the transport before it announces the update."""
+    from types import SimpleNamespace
+
+    from awex_b200.config import InferenceConfig
+    from awex_b200.reader.nccl_reader import NCCLWorkerWeightsReader, WorkerWeightsReader
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.models import build_vllm_model, vllm_model_context
+    from awex_b200.synthetic.topology import infer_rank_infos
+
+    arch, ri = get_arch("tiny-llama"), infer_rank_infos(tp=1)[0]
+    model = build_vllm_model(arch, ri, torch.float32, "cpu")
+    cfg = InferenceConfig(tp_size=1, pp_size=1, dp_size=1, ep_size=1)
+    fake_meta = [type("M", (), {"name": n, "shards": [type("S", (), {"world_size": 1})()]})() for n in ("model.norm.weight",)]
+    reader = NCCLWorkerWeightsReader(model, vllm_model_context(ri, infer_engine_config=cfg),
+                                     {"engine_name": "vllm", "infer_engine_config": cfg, "infer_world_size": 1}, [], fake_meta,
+                                     engine_rank=0, num_engines=1, meta_server_addr="127.0.0.1:1")
+    WorkerWeightsReader.initialize(reader)  # views only; no transport is connected in this test
+    calls = []
+    reader.transport = SimpleNamespace(may_move=False, begin=lambda epoch: calls.append(("begin", epoch)),
+                                       rebind=lambda views: calls.append(("rebind", dict(views))))
+    reader.begin_update(1)
+    assert calls == [("begin", 1)]
+    moved_name = "norm.weight" if "norm.weight" in model._tensors else next(n for n in model._tensors if n.endswith("norm.weight"))
+    model._tensors[moved_name] = model._tensors[moved_name].clone()
+    with pytest.raises(RuntimeError, match="parameters_may_move"):
+        reader.begin_update(2)
+    reader.transport.may_move = True
+    reader.begin_update(3)
+    (kind, views), last = calls[-2], calls[-1]
+    assert kind == "rebind" and last == ("begin", 3)
+    assert any(v.data_ptr() == model._tensors[moved_name].data_ptr() for v in views.values())  # the views follow the live model
+    assert reader.parameters_moved() == [] and reader.parameters is not None
+
+
 def test_poison_fill_catches_an_unwritten_tensor_whose_values_are_zero():
     """Zero-fill validation cannot see that nobody wrote a tensor that is all
     zeros (a fresh bias); NaN poison can."""

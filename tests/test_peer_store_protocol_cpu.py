@@ -170,3 +170,44 @@ def test_two_processes_exchange_through_books_manifests_and_handshakes(fakes, gp
         assert FakeProgram.built == 1 and FakeImporter.opened == 2  # planned and mapped once, whatever the number of updates
     finally:
         server.stop()
+
+
+@pytest.mark.parametrize("gpus", [("GPU-a", "GPU-a"), ("GPU-a", "GPU-b")])
+def test_a_receiver_whose_parameters_move_is_followed_by_its_senders(fakes, gpus):
+    """An engine that re-allocates its weights between updates (sleep / wake-up):
+    the receiver publishes a new address book before it announces the update, the
+    announcement names the book's epoch, and a sender that built its table from
+    an older book unmaps, fetches and rebuilds before it writes."""
+    from awex_b200.transfer.transports import addr_key, host_ready_key
+
+    job, items, local, views, server, meta = build_pair(gpus)
+    try:
+        sender, receiver = make_sides(job, items, local, views, meta, may_move=True)
+        assert sender.moving_destinations == [0] and meta.get_object(addr_key(0), timeout=5).may_move
+        update(sender, receiver, 1)
+        assert job.mismatches() == [] and sender.rebuilds == 0
+        assert meta.get_object(host_ready_key(0, 1), timeout=5) == 1  # the announcement carries the epoch of the valid book
+        update(sender, receiver, 2)
+        assert sender.rebuilds == 0 and FakeProgram.built == 1  # nothing moved: one extra host round trip, nothing else
+
+        # the engine re-allocates every parameter; the old tensors keep their (now stale) contents
+        model = job.infer_models[0][0]
+        old = dict(model._tensors)
+        for name in list(model._tensors):
+            model._tensors[name] = torch.zeros_like(old[name])
+        MEMORY.extend(model._tensors.values())
+        for t in old.values():
+            t.fill_(7.0)
+        with acting_as("infer0"):
+            receiver.rebind(job.destination_views()[0])
+        update(sender, receiver, 3)
+        assert sender.rebuilds == 1 and FakeProgram.built == 2 and FakeImporter.closed == 1
+        assert meta.get_object(addr_key(0), timeout=5).epoch == 2 and meta.get_object(host_ready_key(0, 3), timeout=5) == 2
+        assert job.mismatches() == []                                 # the new tensors hold the weights
+        assert all(bool((t == 7.0).all()) for t in old.values())      # and nobody wrote through the stale addresses
+        update(sender, receiver, 4)
+        assert sender.rebuilds == 1 and sender.program.launches == [3, 4]
+        with pytest.raises(KeyError):
+            receiver.rebind({})
+    finally:
+        server.stop()
