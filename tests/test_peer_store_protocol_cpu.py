@@ -211,3 +211,59 @@ def test_a_receiver_whose_parameters_move_is_followed_by_its_senders(fakes, gpus
             receiver.rebind({})
     finally:
         server.stop()
+
+
+@pytest.mark.parametrize("stripe_mb", ["0", "0.0625"])
+def test_two_senders_four_receivers_on_six_gpus(fakes, monkeypatch, stripe_mb):
+    """Training TP2 -> two engines of inference TP2, every process on a GPU of its
+    own: every receiver checks that the senders' manifests tile its views exactly
+    once, every sender writes to receivers of both engines; with striping switched on the senders'
+    tables are re-ordered and dealt in chunks, and move the same bytes."""
+    from awex_b200.meta.meta_server import MetaServer, MetaServerClient
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+    from awex_b200.transfer.transports import PeerStoreReceiver, PeerStoreSender
+
+    monkeypatch.setenv("AWEX_XFER_DEST_STRIPE_MB", stripe_mb)
+    job = SimulatedJob(get_arch("tiny-qwen2"), TrainLayout(tp=2), InferLayout(tp=2, num_engines=2), dtype=torch.bfloat16)
+    programs = job.compile_all()
+    views = job.destination_views()
+    GPU_OF.update({f"train{r}": f"GPU-t{r}" for r in programs}, **{f"infer{i}": f"GPU-i{i}" for i in views})
+    for r in programs:
+        MEMORY.extend(job.local_tensors(r).values())
+    MEMORY.extend(p for ms in job.infer_models for m in ms for p in m.parameters())
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    meta = MetaServerClient("127.0.0.1", server.port)
+    try:
+        receivers, senders = {}, {}
+        for i, vs in views.items():
+            with acting_as(f"infer{i}"):
+                receivers[i] = PeerStoreReceiver(meta, vs, i, len(views), len(programs), sorted(n for n in vs if n not in job.aliases), "cpu", wait_timeout_s=20)
+        for r, items in programs.items():
+            with acting_as(f"train{r}"):
+                senders[r] = PeerStoreSender(meta, items, job.local_tensors(r), r, len(views), "cpu", wait_timeout_s=20)
+        for i, rx in receivers.items():
+            with acting_as(f"infer{i}"):
+                rx.connect()
+            assert rx.senders and rx.host_senders == []
+        for r, tx in senders.items():
+            with acting_as(f"train{r}"):
+                tx.connect()
+            assert len(tx.destinations) >= 2 and tx.program.ready_slots == tx.destinations  # one per engine at least, all on peer GPUs
+            assert tx.program.interleave == (stripe_mb != "0")
+        for i, rx in receivers.items():
+            with acting_as(f"infer{i}"):
+                rx.begin(1)
+        for r, tx in senders.items():
+            with acting_as(f"train{r}"):
+                tx.send(1)
+        for i, rx in receivers.items():
+            with acting_as(f"infer{i}"):
+                rx.finish(1)
+        assert job.mismatches() == []
+        assert sum(tx.bytes_out for tx in senders.values()) == sum(rx.bytes_in for rx in receivers.values())
+        if stripe_mb != "0":
+            assert all(tx.program.table.shape[0] > len(programs[r]) for r, tx in senders.items())  # items were cut into stripes
+    finally:
+        server.stop()
