@@ -112,6 +112,11 @@ class WorkerWeightsReader:
         self._sum_plan = None  # device checksum plans hold the old addresses
         self.transport.rebind(self.parameters)
 
+    def invalidate_addresses(self) -> None:
+        """The memory behind the parameters may have been replaced without the
+        addresses changing: publish them again before the next update."""
+        self._addresses_invalid = True
+
     def _model_ptrs(self) -> Dict[str, int]:
         """Address of every parameter of the model as it is now.  The canonical
         views keep the storages alive that they were cut from, so only the model
@@ -236,6 +241,12 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
                 "stale addresses (re-create the writer and reader after the engine re-maps its weights, or set "
                 "debug_mode_config['parameters_may_move'] on the inference side)"
             )
+        if getattr(self, "_addresses_invalid", False):
+            if not getattr(self.transport, "may_move", False):
+                raise RuntimeError("invalidate_addresses() needs debug_mode_config['parameters_may_move'] on the inference side")
+            self._rebind_views()
+            self.transport.republish_if_moved(force=True)
+            self._addresses_invalid = False
         with phase("announce_ready"):
             self.transport.begin(self.epoch)
 

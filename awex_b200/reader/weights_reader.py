@@ -228,6 +228,20 @@ class WeightsReader(WeightExchangeReader):
         return True
 
     @staticmethod
+    def _invalidate_addresses_in_tp_worker(**kwargs):
+        _worker_reader(kwargs).invalidate_addresses()
+        return True
+
+    def invalidate_addresses(self) -> None:
+        """Tell every worker that the memory behind its parameters may be new even
+        where the addresses are the same (an allocator that re-creates physical
+        memory at fixed virtual addresses after a sleep / wake-up cycle): the next
+        update publishes fresh address books and the senders map them again.  Needs
+        ``debug_mode_config["parameters_may_move"]``."""
+        if self.initialized:
+            self.inference_engine.execute_task_in_model_worker(self._invalidate_addresses_in_tp_worker)
+
+    @staticmethod
     def _update_parameters_in_tp_worker(step_id, **kwargs):
         _worker_reader(kwargs).update_weights(step_id)
         return True

@@ -40,6 +40,7 @@ AWEX_WORKER_METHODS: Dict[str, tuple] = {
     "_update_parameters_in_tp_worker": ("awex_b200.reader.weights_reader", "WeightsReader._update_parameters_in_tp_worker"),
     "_begin_update_in_tp_worker": ("awex_b200.reader.weights_reader", "WeightsReader._begin_update_in_tp_worker"),
     "_finish_update_in_tp_worker": ("awex_b200.reader.weights_reader", "WeightsReader._finish_update_in_tp_worker"),
+    "_invalidate_addresses_in_tp_worker": ("awex_b200.reader.weights_reader", "WeightsReader._invalidate_addresses_in_tp_worker"),
     "_pre_validate_weights_on_tp_worker": ("awex_b200.reader.weights_reader", "WeightsReader._pre_validate_weights_on_tp_worker"),
     "_verify_weights_on_tp_worker": ("awex_b200.reader.weights_reader", "WeightsReader._verify_weights_on_tp_worker"),
 }
@@ -58,6 +59,7 @@ AWEX_WORKER_SIGNATURES: Dict[str, Dict[str, List[str]]] = {
     "_update_parameters_in_tp_worker": {"required": ["step_id"], "optional": []},
     "_begin_update_in_tp_worker": {"required": ["step_id"], "optional": []},
     "_finish_update_in_tp_worker": {"required": ["step_id"], "optional": ["synchronize"]},
+    "_invalidate_addresses_in_tp_worker": {"required": [], "optional": []},
     "_pre_validate_weights_on_tp_worker": {"required": [], "optional": ["step_id"]},
     "_verify_weights_on_tp_worker": {
         "required": [], "optional": ["step_id", "dump_weights_list_for_validation", "dump_weights_dir_for_validation"],

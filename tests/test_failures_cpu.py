@@ -187,6 +187,17 @@ def test_worker_reader_refuses_or_follows_moved_parameters():
     assert kind == "rebind" and last == ("begin", 3)
     assert any(v.data_ptr() == model._tensors[moved_name].data_ptr() for v in views.values())  # the views follow the live model
     assert reader.parameters_moved() == [] and reader.parameters is not None
+    # same addresses, new memory behind them: the owner says so and the next update publishes again
+    reader.transport.republish_if_moved = lambda force=False: calls.append(("republish", force))
+    reader.invalidate_addresses()
+    reader.begin_update(4)
+    assert [c[0] for c in calls[-3:]] == ["rebind", "republish", "begin"] and calls[-2] == ("republish", True)
+    reader.begin_update(5)
+    assert calls[-1] == ("begin", 5) and calls[-2][0] == "begin"  # only once
+    reader.transport.may_move = False
+    reader.invalidate_addresses()
+    with pytest.raises(RuntimeError, match="parameters_may_move"):
+        reader.begin_update(6)
 
 
 def test_poison_fill_catches_an_unwritten_tensor_whose_values_are_zero():
