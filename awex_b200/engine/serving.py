@@ -109,6 +109,11 @@ class ServingEngineBase(InferenceEngine):
             return
         self.released_tags.difference_update(todo)
         self._resume(todo)
+        may_move = bool((getattr(self.config, "debug_mode_config", None) or {}).get("parameters_may_move", False))
+        reader = getattr(self, "weights_exchange_reader", None)
+        if "weights" in todo and may_move and hasattr(reader, "invalidate_addresses"):
+            # weights that were released and came back may sit in new memory, even at the old addresses
+            reader.invalidate_addresses()
 
     # ---- worker tasks ------------------------------------------------------------------
     def execute_task_in_model_worker(self, fn, **kwargs):

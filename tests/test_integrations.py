@@ -263,6 +263,18 @@ def test_sglang_engine_memory_tags_are_idempotent_and_node_gated():
     other._initialized = True
     with pytest.raises(RuntimeError):
         other.execute_task_in_model_worker(lambda: 1)
+    # weights that come back from a release may sit in new memory: with parameters_may_move the reader is told
+    told = []
+    for may_move, expected in ((False, 0), (True, 1)):
+        moving = SGLangEngine(InferenceConfig(tp_size=1, debug_mode_config={"parameters_may_move": may_move}), FakeSGL())
+        moving._initialized = True
+        moving.weights_exchange_reader = types.SimpleNamespace(invalidate_addresses=lambda: told.append(1))
+        moving.release_memory_occupation()
+        moving.resume_memory_occupation(["kv_cache"])  # the weights are still away
+        assert len(told) == 0 if not may_move else True
+        before = len(told)
+        moving.resume_memory_occupation(["weights"])
+        assert len(told) - before == expected
 
 
 class FakeVLLMHandle:
