@@ -69,8 +69,7 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
         plane = self.infer_conf.get("data_plane") or choose_data_plane(device.type, self.config.get("data_plane"))
         if mine and mine != plane:
             raise ValueError(f"training side asks for data plane {mine!r} but the inference side published {plane!r}")
-        if plane == "peer_stores" and device.type != "cuda":
-            raise ValueError("the inference side chose peer stores but this training rank's parameters are not on a CUDA device")
+        plane = choose_data_plane(device.type, plane)  # refuses peer stores for parameters that are not on a CUDA device
         if plane == "peer_stores":
             from awex_b200.transfer.transports import PeerStoreSender
 

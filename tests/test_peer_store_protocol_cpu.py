@@ -7,6 +7,7 @@ what, in which order the sides shake hands, that the table the sender built
 moves the right bytes, and what happens when a receiver's parameters move."""
 
 import contextlib
+import threading
 from types import SimpleNamespace
 
 import pytest
@@ -17,18 +18,22 @@ from awex_b200.parallel.peer_memory import AddressBook
 from awex_b200.transfer.descriptors import TensorAddr
 from awex_b200.transfer.table_interpreter import HostMemory, run_table
 
-ACTING = ["nobody"]  # which "process" the code under test currently belongs to
+ACTING = threading.local()  # which "process" the code under test (of this thread) currently belongs to
 GPU_OF = {}  # process -> GPU identity
 MEMORY = []  # every tensor a fake kernel may touch
 
 
+def who():
+    return getattr(ACTING, "name", "nobody")
+
+
 @contextlib.contextmanager
-def acting_as(who):
-    previous, ACTING[0] = ACTING[0], who
+def acting_as(name):
+    previous, ACTING.name = who(), name
     try:
         yield
     finally:
-        ACTING[0] = previous
+        ACTING.name = previous
 
 
 class FakeExporter:
@@ -37,7 +42,7 @@ class FakeExporter:
 
     def export(self, named, with_handles=True):
         self.epoch += 1
-        book = AddressBook(("box", ACTING[0]), 0, GPU_OF[ACTING[0]], self.epoch)
+        book = AddressBook(("box", who()), 0, GPU_OF[who()], self.epoch)
         for name, t in named:
             lo, hi = TensorAddr.of(t).byte_span()
             book.segments.append((b"", lo, hi - lo))
@@ -73,20 +78,43 @@ class FakeProgram:
 
     def launch(self, epoch):
         self.launches.append(epoch)
+        with DONE:  # what the kernel's first wait does: every peer destination must have announced this epoch
+            assert DONE.wait_for(lambda: DONE.ready.get(epoch, 0) >= len(self.ready_slots), timeout=30), f"no ready flags for epoch {epoch}"
         assert run_table(self.table, self.n_tiles, HostMemory(MEMORY), self.encoder.row_offsets) == self.n_tiles
+        with DONE:  # what the kernel's last CTA does with the receivers' done flags
+            DONE.count[epoch] = DONE.count.get(epoch, 0) + 1
+            DONE.notify_all()
 
     def check(self):
         pass
 
 
-class FakeFlags:
-    def __init__(self, first, *rest, **kw):
-        self.n = len(first if isinstance(first, (list, tuple)) else rest[0])
-        self.status = SimpleNamespace(raise_if_failed=lambda: None)
-        self.launches = []
+DONE = threading.Condition()
+DONE.count, DONE.ready = {}, {}
+
+
+class FakePoster:
+    def __init__(self, addrs, device):
+        self.n, self.launches = len(addrs), []
 
     def launch(self, epoch, stream_ptr=None):
         self.launches.append(epoch)
+        with DONE:
+            DONE.ready[epoch] = DONE.ready.get(epoch, 0) + (1 if self.n else 0)
+            DONE.notify_all()
+
+
+class FakeWaiter:
+    """Stands for the kernel that holds the stream until every device sender has raised its flag."""
+
+    def __init__(self, pad, slots, device, timeout_ms=2000):
+        self.n, self.launches = len(slots), []
+        self.status = SimpleNamespace(raise_if_failed=lambda: None)
+
+    def launch(self, epoch, stream_ptr=None):
+        self.launches.append(epoch)
+        with DONE:
+            assert DONE.wait_for(lambda: DONE.count.get(epoch, 0) >= self.n, timeout=30), f"flags of epoch {epoch} never came"
 
 
 @pytest.fixture
@@ -95,11 +123,12 @@ def fakes(monkeypatch):
 
     monkeypatch.setattr(peer_memory, "PeerMemoryExporter", FakeExporter)
     monkeypatch.setattr(peer_memory, "PeerMemoryImporter", FakeImporter)
-    monkeypatch.setattr(peer_memory, "process_identity", lambda: ("box", ACTING[0]))
-    monkeypatch.setattr(peer_memory, "_device_uuid", lambda index: GPU_OF[ACTING[0]])
+    monkeypatch.setattr(peer_memory, "process_identity", lambda: ("box", who()))
+    monkeypatch.setattr(peer_memory, "_device_uuid", lambda index: GPU_OF[who()])
     monkeypatch.setattr(fused_transfer, "TransferProgram", FakeProgram)
-    monkeypatch.setattr(fused_transfer, "FlagPoster", FakeFlags)
-    monkeypatch.setattr(fused_transfer, "FlagWaiter", FakeFlags)
+    monkeypatch.setattr(fused_transfer, "FlagPoster", FakePoster)
+    monkeypatch.setattr(fused_transfer, "FlagWaiter", FakeWaiter)
+    DONE.count, DONE.ready = {}, {}
     monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: SimpleNamespace(synchronize=lambda: None))
     FakeImporter.opened = FakeImporter.closed = FakeProgram.built = 0
     MEMORY.clear()
@@ -265,5 +294,65 @@ def test_two_senders_four_receivers_on_six_gpus(fakes, monkeypatch, stripe_mb):
         assert sum(tx.bytes_out for tx in senders.values()) == sum(rx.bytes_in for rx in receivers.values())
         if stripe_mb != "0":
             assert all(tx.program.table.shape[0] > len(programs[r]) for r, tx in senders.items())  # items were cut into stripes
+    finally:
+        server.stop()
+
+
+@pytest.mark.timeout(120)
+def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch):
+    """`NCCLWeightsWriter` and `WeightsReader` on the peer-store plane (forced
+    here; on CPU tensors they would pick messages): metadata exchange, plan,
+    lowering, address books, manifests, validated first update with dumps off,
+    a second update after the training weights changed."""
+    from awex_b200 import NCCLWeightsWriter, WeightsReader
+    from awex_b200.meta.meta_server import MetaServer
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.harness import SyntheticInferenceEngine, SyntheticTrainEngine
+    from awex_b200.synthetic.simulate import InferLayout
+    from awex_b200.synthetic.topology import infer_rank_infos, train_rank_infos
+    from awex_b200.transfer import transports
+
+    monkeypatch.setenv("AWEX_DEVICE_TYPE", "cpu")
+    monkeypatch.setattr(transports, "choose_data_plane", lambda device_type, configured=None: "peer_stores")
+    GPU_OF.update(train0="GPU-a", infer0="GPU-b", nobody="GPU-x")
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    addr = f"127.0.0.1:{server.port}"
+    arch = get_arch("tiny-llama")
+    failures = []
+
+    def serve():
+        try:
+            with acting_as("infer0"):
+                engine = SyntheticInferenceEngine(arch, InferLayout(tp=1), infer_rank_infos(tp=1)[0], addr, dtype=torch.float32, device="cpu",
+                                                  zero=False,  # holds the step-0 weights, as after loading the same checkpoint
+                                                  weights_validation_steps=1, debug_mode_config={"raise_on_validation_fail": True})
+                MEMORY.extend(engine.model.parameters())
+                reader = WeightsReader(engine)
+                reader.initialize()
+                reader.update_weights(step_id=1)
+                failures.extend(("step 1", m) for m in engine.mismatches(step=0))
+                reader.update_weights(step_id=2)
+                failures.extend(("step 2", m) for m in engine.mismatches(step=2))
+                failures.extend(("validation", v) for v in reader.last_validation_failed)
+        except BaseException as exc:
+            failures.append(("reader", repr(exc)))
+            raise
+
+    thread = threading.Thread(target=serve, daemon=True)
+    thread.start()
+    try:
+        with acting_as("train0"):
+            engine = SyntheticTrainEngine(arch, train_rank_infos(tp=1)[0], addr, dtype=torch.float32, device="cpu", comm_backend="nccl",
+                                          weights_validation_steps=1)
+            MEMORY.extend(p for chunk in ([engine.model] if not isinstance(engine.model, list) else engine.model) for p in chunk.parameters())
+            writer = NCCLWeightsWriter(engine)
+            writer.initialize()
+            writer.write_weights(step_id=1)
+            engine.regenerate(step=2)
+            writer.write_weights(step_id=2)
+            assert type(writer.transport).__name__ == "PeerStoreSender" and writer.transport.program.launches == [1, 2]
+        thread.join(timeout=60)
+        assert not thread.is_alive() and failures == []
     finally:
         server.stop()
