@@ -100,6 +100,7 @@ class WeightsReader(WeightExchangeReader):
         self.infer_world_size = self.num_engines * self.tp_size * self.pp_size * self.dp_size
         self.validated_steps = 0
         self.start_step = -1
+        self.last_validation_failed: List[str] = []  # names that differed in the most recent validated update
         self.weights_validation_steps = config.weights_validation_steps
         self.validate_weights_every_n_steps = config.validate_weights_every_n_steps
         self.dump_weights_list_for_validation = config.dump_weights_list_for_validation

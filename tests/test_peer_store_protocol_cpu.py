@@ -298,8 +298,14 @@ def test_two_senders_four_receivers_on_six_gpus(fakes, monkeypatch, stripe_mb):
         server.stop()
 
 
+def _drop_expected_head_difference(arch, engine, bad):
+    """With ``norm_head`` the served head has unit-norm columns: the raw oracle differs there and only there."""
+    return [b for b in bad if b != "lm_head.weight"] if arch.norm_head else bad
+
+
 @pytest.mark.timeout(120)
-def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch):
+@pytest.mark.parametrize("arch_name,validate", [("tiny-llama", 1), ("tiny-llama-norm-head", 0)])
+def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, validate):
     """`NCCLWeightsWriter` and `WeightsReader` on the peer-store plane (forced
     here; on CPU tensors they would pick messages): metadata exchange, plan,
     lowering, address books, manifests, validated first update with dumps off,
@@ -318,7 +324,7 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch):
     server = MetaServer("127.0.0.1", 0)
     server.start()
     addr = f"127.0.0.1:{server.port}"
-    arch = get_arch("tiny-llama")
+    arch = get_arch(arch_name)
     failures = []
 
     def serve():
@@ -326,14 +332,18 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch):
             with acting_as("infer0"):
                 engine = SyntheticInferenceEngine(arch, InferLayout(tp=1), infer_rank_infos(tp=1)[0], addr, dtype=torch.float32, device="cpu",
                                                   zero=False,  # holds the step-0 weights, as after loading the same checkpoint
-                                                  weights_validation_steps=1, debug_mode_config={"raise_on_validation_fail": True})
+                                                  weights_validation_steps=validate, debug_mode_config={"raise_on_validation_fail": True})
                 MEMORY.extend(engine.model.parameters())
                 reader = WeightsReader(engine)
                 reader.initialize()
                 reader.update_weights(step_id=1)
-                failures.extend(("step 1", m) for m in engine.mismatches(step=0))
+                failures.extend(("step 1", m) for m in _drop_expected_head_difference(arch, engine, engine.mismatches(step=0)))
+                if arch.norm_head:
+                    head = dict(engine.model.named_parameters())["lm_head.weight"]
+                    norms = head.float().norm(dim=0)
+                    assert torch.allclose(norms, torch.ones_like(norms), atol=1e-5), "the head did not arrive with unit-norm columns"
                 reader.update_weights(step_id=2)
-                failures.extend(("step 2", m) for m in engine.mismatches(step=2))
+                failures.extend(("step 2", m) for m in _drop_expected_head_difference(arch, engine, engine.mismatches(step=2)))
                 failures.extend(("validation", v) for v in reader.last_validation_failed)
         except BaseException as exc:
             failures.append(("reader", repr(exc)))
@@ -344,10 +354,13 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch):
     try:
         with acting_as("train0"):
             engine = SyntheticTrainEngine(arch, train_rank_infos(tp=1)[0], addr, dtype=torch.float32, device="cpu", comm_backend="nccl",
-                                          weights_validation_steps=1)
+                                          weights_validation_steps=validate)
             MEMORY.extend(p for chunk in ([engine.model] if not isinstance(engine.model, list) else engine.model) for p in chunk.parameters())
             writer = NCCLWeightsWriter(engine)
             writer.initialize()
+            writer.prepare()  # metadata exchange and planning now: sender-side derived buffers exist afterwards
+            MEMORY.extend(t for key, t in writer._local.items() if key[0].startswith("__derived__/"))
+            assert bool(writer.derived) == arch.norm_head
             writer.write_weights(step_id=1)
             engine.regenerate(step=2)
             writer.write_weights(step_id=2)
