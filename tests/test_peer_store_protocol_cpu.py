@@ -304,8 +304,8 @@ def _drop_expected_head_difference(arch, engine, bad):
 
 
 @pytest.mark.timeout(120)
-@pytest.mark.parametrize("arch_name,validate", [("tiny-llama", 1), ("tiny-llama-norm-head", 0)])
-def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, validate):
+@pytest.mark.parametrize("arch_name,validate,moving", [("tiny-llama", 1, False), ("tiny-llama-norm-head", 0, False), ("tiny-llama", 0, True)])
+def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, validate, moving):
     """`NCCLWeightsWriter` and `WeightsReader` on the peer-store plane (forced
     here; on CPU tensors they would pick messages): metadata exchange, plan,
     lowering, address books, manifests, validated first update with dumps off,
@@ -320,7 +320,8 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
 
     monkeypatch.setenv("AWEX_DEVICE_TYPE", "cpu")
     monkeypatch.setattr(transports, "choose_data_plane", lambda device_type, configured=None: "peer_stores")
-    GPU_OF.update(train0="GPU-a", infer0="GPU-b", nobody="GPU-x")
+    # the moving case also shares one GPU between the two processes (host handshake in both directions)
+    GPU_OF.update(train0="GPU-a", infer0="GPU-a" if moving else "GPU-b", nobody="GPU-x")
     server = MetaServer("127.0.0.1", 0)
     server.start()
     addr = f"127.0.0.1:{server.port}"
@@ -332,7 +333,8 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
             with acting_as("infer0"):
                 engine = SyntheticInferenceEngine(arch, InferLayout(tp=1), infer_rank_infos(tp=1)[0], addr, dtype=torch.float32, device="cpu",
                                                   zero=False,  # holds the step-0 weights, as after loading the same checkpoint
-                                                  weights_validation_steps=validate, debug_mode_config={"raise_on_validation_fail": True})
+                                                  weights_validation_steps=validate,
+                                                  debug_mode_config={"raise_on_validation_fail": True, "parameters_may_move": moving})
                 MEMORY.extend(engine.model.parameters())
                 reader = WeightsReader(engine)
                 reader.initialize()
@@ -342,6 +344,10 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
                     head = dict(engine.model.named_parameters())["lm_head.weight"]
                     norms = head.float().norm(dim=0)
                     assert torch.allclose(norms, torch.ones_like(norms), atol=1e-5), "the head did not arrive with unit-norm columns"
+                if moving:  # the engine re-allocates all its weights between the updates
+                    for name, t in list(engine.model._tensors.items()):
+                        engine.model._tensors[name] = torch.zeros_like(t)
+                    MEMORY.extend(engine.model._tensors.values())
                 reader.update_weights(step_id=2)
                 failures.extend(("step 2", m) for m in _drop_expected_head_difference(arch, engine, engine.mismatches(step=2)))
                 failures.extend(("validation", v) for v in reader.last_validation_failed)
@@ -364,7 +370,11 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
             writer.write_weights(step_id=1)
             engine.regenerate(step=2)
             writer.write_weights(step_id=2)
-            assert type(writer.transport).__name__ == "PeerStoreSender" and writer.transport.program.launches == [1, 2]
+            assert type(writer.transport).__name__ == "PeerStoreSender"
+            if moving:
+                assert writer.transport.rebuilds == 1 and writer.transport.program.launches == [2]  # a new table for the new addresses
+            else:
+                assert writer.transport.rebuilds == 0 and writer.transport.program.launches == [1, 2]
         thread.join(timeout=60)
         assert not thread.is_alive() and failures == []
     finally:
