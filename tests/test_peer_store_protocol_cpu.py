@@ -75,6 +75,7 @@ class FakeProgram:
         FakeProgram.built += 1
         self.table, self.n_tiles, self.encoder = table, n_tiles, encoder
         self.ready_slots, self.interleave, self.launches = list(ready_slots), interleave, []
+        self.status = SimpleNamespace(raise_if_failed=lambda: None)
 
     def launch(self, epoch):
         self.launches.append(epoch)
@@ -379,3 +380,20 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
         assert not thread.is_alive() and failures == []
     finally:
         server.stop()
+
+
+def test_single_process_emulation_of_all_ranks(fakes):
+    """What the smoke test and the one-GPU benchmark do: every rank's program in
+    one process on one device, launched in stream order, followed by one waiter."""
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+
+    job = SimulatedJob(get_arch("tiny-qwen2"), TrainLayout(tp=2), InferLayout(tp=2, num_engines=2), dtype=torch.bfloat16, device="cpu")
+    job.compile_all()
+    assert job.check_coverage() == []
+    MEMORY.extend(job.source_tensors() + [p for ms in job.infer_models for m in ms for p in m.parameters()])
+    programs = job.build_gpu_programs()
+    assert len(programs) == 2 and all(p.ready_slots == [] for p in programs.values())  # nobody waits for anybody: stream order
+    job.run_gpu(epoch=1)
+    job.gpu_status()
+    assert job.mismatches() == []
