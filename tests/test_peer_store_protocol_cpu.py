@@ -397,3 +397,23 @@ def test_single_process_emulation_of_all_ranks(fakes):
     job.run_gpu(epoch=1)
     job.gpu_status()
     assert job.mismatches() == []
+
+
+def test_a_receiver_refuses_senders_that_do_not_cover_its_views(fakes):
+    """The manifests are checked before anything is mapped or written: a sender
+    that lost one item leaves a hole, one that sends an item twice overlaps."""
+    from awex_b200.transfer.transports import PeerStoreReceiver, PeerStoreSender
+
+    job, items, local, views, server, meta = build_pair(("GPU-a", "GPU-b"))
+    try:
+        for broken, word in ((items[:-1], "exactly once.*receives nothing"), (items + items[:1], "exactly once")):
+            for key in list(meta.list_keys()):
+                meta.delete_if_exists(key)
+            with acting_as("infer0"):
+                receiver = PeerStoreReceiver(meta, views, 0, 1, 1, sorted(views), "cpu", wait_timeout_s=20)
+            with acting_as("train0"):
+                PeerStoreSender(meta, broken, local, 0, 1, "cpu", wait_timeout_s=20)
+            with acting_as("infer0"), pytest.raises(Exception, match=word):
+                receiver.connect()
+    finally:
+        server.stop()
