@@ -48,7 +48,7 @@ import numpy as np
 CTA_RATE = {"copy": 6.42e12 / 2 / 148, "fp8_block": 2.68e12 * (2 / 3) / 148, "cast": 1.59e12 / 3 / 148}
 
 
-def segments_of(items: Sequence, sender_gpu: int, gpu_of_dst: Dict[int, int]) -> np.ndarray:
+def segments_of(items: Sequence, gpu_of_dst: Dict[int, int]) -> np.ndarray:
     """One row per item: (destination GPU, source bytes, wire bytes per source byte, per-CTA rate)."""
     rows = np.zeros((len(items), 4))
     for i, it in enumerate(items):
@@ -193,7 +193,7 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     for order in orders:
         items = {r: (stripe_by_destination(p, int(stripe_mb * 2**20)) if order == "striped" else _rotated(p, r) if order == "rotated" else p)
                  for r, p in programs.items()}
-        tables = {r: segments_of(p, r, gpu_of_dst) for r, p in items.items() if len(p)}
+        tables = {r: segments_of(p, gpu_of_dst) for r, p in items.items() if len(p)}
         result = simulate(tables, "contiguous" if order == "contiguous" else "chunks", n_gpus, grid=grid, chunk_bytes=chunk_tiles * 32768,
                           nvlink=nvlink_gbps * 1e9, hbm=hbm_gbps * 1e9)
         result["order"] = order

@@ -149,7 +149,7 @@ class PeerStreams:
     factory (a CUDA stream on the current device by default)."""
 
     SIZE = 64
-    _pools: Dict[int, list] = {}
+    _pools: Dict[Tuple[int, int], list] = {}  # (device, stream factory) -> streams
 
     def __init__(self, peers: Iterable[int], device_index: int = 0, make_stream: Optional[Callable] = None, size: Optional[int] = None):
         size = size or self.SIZE
