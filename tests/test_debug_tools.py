@@ -164,3 +164,12 @@ def test_contention_model_two_senders_meeting_at_one_receiver():
     assert max(convoy["peak_ingress_GBps"]) <= 770.0 + 1e-6
     local = simulate({0: np.array([[0, 100 * mb, 1.0, CTA_RATE["copy"]]])}, "contiguous", 1, dt=1e-6)
     assert abs(local["ms"] - 100 * mb / (6.42e12 / 2) * 1e3) < 0.1 * local["ms"]  # 148 CTAs at the copy rate
+
+
+def test_contention_model_cli_on_a_tiny_layout(capsys):
+    from awex_b200.debug import contention_model
+
+    assert contention_model.main(["--model", "tiny-llama", "--train", "tp2", "--infer", "tp1,engines2", "--placement", "separated",
+                                  "--orders", "contiguous,chunks,striped,rotated", "--stripe-mb", "0.0625"]) == 0
+    lines = [l for l in capsys.readouterr().out.splitlines() if " ms " in l]
+    assert [l.split(":")[0].strip() for l in lines] == ["contiguous", "chunks", "striped", "rotated"]
