@@ -24,6 +24,7 @@ KNOBS: Dict[str, Tuple[str, str]] = {
     "AWEX_DEBUG_INFER_META": ("0", "1: log every inference parameter while metadata is collected"),
     "AWEX_P2P_TRACE": ("0", "1: log, per update, what each sender writes to each destination (bytes, descriptors, tiles)"),
     "AWEX_CHUNK_MB": ("0", "message data plane and co-located message exchange: staging bound in MiB per message run (0: whole messages), same value on both sides; the fused kernel stages nothing"),
+    "AWEX_META_SERVER_TOKEN": ("", "shared secret: a MetaServer started with it refuses requests that do not carry it, clients send it (set it on every process)"),
     "AWEX_DATA_PLANE": ("", "peer_stores (fused kernel through CUDA IPC, one machine) or messages (NCCL / gloo messages, any topology); default by device"),
     "AWEX_XFER_CHUNK_MB": ("", "size in MiB of the chunks of tiles dealt to CTAs by the fused transfer kernel (default by op mix)"),
     "AWEX_XFER_VARIANT": ("", "0 | 1: force the launch shape of the fused transfer kernel (one 512-thread or two 256-thread CTAs per SM)"),

@@ -174,3 +174,32 @@ def test_server_in_a_subprocess_starts_answers_and_stops():
     finally:
         assert stop_meta_server() is True
     assert stop_meta_server() is False  # nothing left to stop
+
+
+def test_optional_shared_secret(monkeypatch):
+    """With AWEX_META_SERVER_TOKEN set, requests without the secret are refused
+    (the health probe stays open); clients created with it in their environment
+    work as before."""
+    import requests
+
+    from awex_b200.meta.meta_server import MetaServer, MetaServerClient
+
+    monkeypatch.setenv("AWEX_META_SERVER_TOKEN", "s3cret")
+    server = MetaServer("127.0.0.1", 0)
+    server.start()
+    try:
+        base = f"http://127.0.0.1:{server.port}/v1"
+        assert requests.get(f"{base}/health").status_code == 200
+        assert requests.put(f"{base}/put_binary/k", data=b"x").status_code == 401
+        assert requests.get(f"{base}/keys").status_code == 401
+        assert requests.get(f"{base}/keys", headers={"X-Awex-Token": "wrong"}).status_code == 401
+        client = MetaServerClient("127.0.0.1", server.port)
+        client.put_object("k", [1, 2])
+        assert client.get_object("k", timeout=5) == [1, 2] and client.list_keys() == ["k"]
+        monkeypatch.delenv("AWEX_META_SERVER_TOKEN")
+        stranger = MetaServerClient("127.0.0.1", server.port, max_retries=1)
+        monkeypatch.setenv("AWEX_META_SERVER_TOKEN", "s3cret")  # the server still has it; the stranger's session was made without
+        with pytest.raises(requests.HTTPError, match="401"):
+            stranger.has_key("k")
+    finally:
+        server.stop()
