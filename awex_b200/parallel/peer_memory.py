@@ -159,6 +159,7 @@ class PeerMemoryImporter:
         bases: List[int] = []
         for index, (handle, owner_base, _size) in enumerate(book.segments):
             if tuple(book.owner) == self._me:
+                self._own_process_access(book.device_index)
                 bases.append(owner_base)
                 continue
             if index in getattr(book, "vmm", {}):
@@ -183,6 +184,22 @@ class PeerMemoryImporter:
         for name, (seg, offset, shape, strides, dtype) in book.tensors.items():
             out_addrs[name] = TensorAddr(bases[seg] + offset, tuple(shape), tuple(strides), getattr(torch, dtype))
         return out_addrs
+
+    def _own_process_access(self, device_index: int) -> None:
+        """Memory that this very process holds on another GPU is reached through its
+        plain addresses, which needs peer access between the two devices; without
+        it a kernel that writes there faults.  Refuse instead."""
+        current = torch.cuda.current_device()
+        enabled = self.__dict__.setdefault("_peers", set())
+        if device_index == current or device_index in enabled:
+            return
+        code = self.lib.awex_enable_peer_access(current, device_index)
+        if code != 0:
+            raise RuntimeError(
+                f"device {current} cannot be given access to memory of device {device_index} of this process "
+                f"({'no peer path between them' if code == -2 else f'CUDA error {code}'})"
+            )
+        enabled.add(device_index)
 
     def _map_vmm(self, owner_base: int, chunk_sizes, server: str, token: int) -> int:
         import torch as _torch

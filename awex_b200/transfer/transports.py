@@ -265,7 +265,8 @@ class PeerStoreSender:
                 self.moving_destinations.append(d)
             if shares_gpu(book, my_uuid, me):
                 self.host_destinations.append(d)  # same GPU, other process: host handshake
-            elif tuple(book.owner) != me:
+            elif tuple(book.owner) != me or book.device_uuid != my_uuid:
+                # another process, or this process on another GPU (no stream orders the two devices): device flags
                 remote.append(d)
         src_addrs = {key: TensorAddr.of(t) for key, t in self.local.items()}
         table, n_tiles, enc = encode_items(self._ordered_items(), src_addrs, dst_addrs)

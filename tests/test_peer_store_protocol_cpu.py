@@ -27,13 +27,17 @@ def who():
     return getattr(ACTING, "name", "nobody")
 
 
+def gpu():
+    return getattr(ACTING, "gpu", None) or GPU_OF[who()]
+
+
 @contextlib.contextmanager
-def acting_as(name):
-    previous, ACTING.name = who(), name
+def acting_as(name, on_gpu=None):
+    previous, ACTING.name, ACTING.gpu = (who(), getattr(ACTING, "gpu", None)), name, on_gpu
     try:
         yield
     finally:
-        ACTING.name = previous
+        ACTING.name, ACTING.gpu = previous
 
 
 class FakeExporter:
@@ -42,7 +46,7 @@ class FakeExporter:
 
     def export(self, named, with_handles=True):
         self.epoch += 1
-        book = AddressBook(("box", who()), 0, GPU_OF[who()], self.epoch)
+        book = AddressBook(("box", who()), 0, gpu(), self.epoch)
         for name, t in named:
             lo, hi = TensorAddr.of(t).byte_span()
             book.segments.append((b"", lo, hi - lo))
@@ -125,7 +129,7 @@ def fakes(monkeypatch):
     monkeypatch.setattr(peer_memory, "PeerMemoryExporter", FakeExporter)
     monkeypatch.setattr(peer_memory, "PeerMemoryImporter", FakeImporter)
     monkeypatch.setattr(peer_memory, "process_identity", lambda: ("box", who()))
-    monkeypatch.setattr(peer_memory, "_device_uuid", lambda index: GPU_OF[who()])
+    monkeypatch.setattr(peer_memory, "_device_uuid", lambda index: gpu())
     monkeypatch.setattr(fused_transfer, "TransferProgram", FakeProgram)
     monkeypatch.setattr(fused_transfer, "FlagPoster", FakePoster)
     monkeypatch.setattr(fused_transfer, "FlagWaiter", FakeWaiter)
@@ -417,3 +421,34 @@ def test_a_receiver_refuses_senders_that_do_not_cover_its_views(fakes):
                 receiver.connect()
     finally:
         server.stop()
+
+
+def test_one_process_with_its_two_roles_on_two_gpus_uses_device_flags(fakes):
+    """No stream orders two devices: a destination of the sender's own process on
+    another GPU announces readiness through a device flag like any peer; on the
+    same GPU the stream order is enough."""
+    from awex_b200.transfer.transports import PeerStoreReceiver, PeerStoreSender
+
+    for trainer_gpu, server_gpu, slots in (("GPU-a", "GPU-b", [0]), ("GPU-a", "GPU-a", [])):
+        job, items, local, views, server, meta = build_pair((trainer_gpu, server_gpu))
+        try:
+            with acting_as("both", on_gpu=server_gpu):
+                receiver = PeerStoreReceiver(meta, views, 0, 1, 1, sorted(views), "cpu", wait_timeout_s=20)
+            with acting_as("both", on_gpu=trainer_gpu):
+                sender = PeerStoreSender(meta, items, local, 0, 1, "cpu", wait_timeout_s=20)
+            with acting_as("both", on_gpu=server_gpu):
+                receiver.connect()
+            with acting_as("both", on_gpu=trainer_gpu):
+                sender.connect()
+            assert sender.host_destinations == [] and receiver.host_senders == []  # one process: no host handshake
+            assert sender.program.ready_slots == slots
+            with acting_as("both", on_gpu=server_gpu):
+                receiver.begin(1)
+            with acting_as("both", on_gpu=trainer_gpu):
+                sender.send(1)
+            with acting_as("both", on_gpu=server_gpu):
+                receiver.finish(1)
+            assert job.mismatches() == []
+        finally:
+            server.stop()
+            MEMORY.clear()

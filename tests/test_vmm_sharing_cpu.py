@@ -228,3 +228,29 @@ def test_address_book_mixes_ipc_segments_and_descriptor_segments(monkeypatch):
         assert all(c[-1] == 5 for c in lib.calls if c[0] == "map")
     finally:
         exporter._vmm.close()
+
+
+def test_books_of_this_process_on_another_gpu_need_peer_access(monkeypatch):
+    """One process that holds the training shard on one GPU and the engine on
+    another: the sender uses plain addresses, so the importer enables peer access
+    first and refuses when the devices have no peer path (a kernel would fault)."""
+    from awex_b200.parallel import peer_memory
+
+    calls = []
+    lib = type("Lib", (), {"awex_enable_peer_access": lambda self, a, b: calls.append((a, b)) or (0 if b == 1 else -2)})()
+    importer = peer_memory.PeerMemoryImporter.__new__(peer_memory.PeerMemoryImporter)
+    importer.lib, importer._open, importer._me = lib, {}, ("here", 7)
+    monkeypatch.setattr("torch.cuda.current_device", lambda: 0)
+
+    def book(device):
+        b = peer_memory.AddressBook(("here", 7), device, f"GPU-{device}", 1)
+        b.segments.append((b"", 0x1000, 0x100))
+        b.tensors["w"] = (0, 0x10, (4,), (1,), "float32")
+        return b
+
+    assert importer.resolve(book(0))["w"].ptr == 0x1010 and calls == []  # same device: nothing to enable
+    assert importer.resolve(book(1))["w"].ptr == 0x1010 and calls == [(0, 1)]
+    importer.resolve(book(1))
+    assert calls == [(0, 1)]  # once per pair
+    with pytest.raises(RuntimeError, match="no peer path"):
+        importer.resolve(book(2))
