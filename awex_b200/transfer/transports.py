@@ -342,11 +342,21 @@ class PeerStoreSender:
             poll_key(self.meta, key, self.host_wait_timeout_s)
             stale = stale or int(self.meta.get_object(key, timeout=self.host_wait_timeout_s)) != self._book_epochs.get(d)
         if stale:
-            self.importer.close_all()
-            self.host_destinations, self.moving_destinations, self._book_epochs = [], [], {}
-            self.connect()
-            self.rebuilds += 1
-            logger.info(f"training rank {self.train_rank}: destinations moved, table rebuilt ({self.rebuilds} so far)")
+            self._rebuild("destinations moved")
+
+    def _rebuild(self, why: str) -> None:
+        """Unmap everything, fetch the address books again and encode a new table
+        from the current source and destination addresses."""
+        self.importer.close_all()
+        self.host_destinations, self.moving_destinations, self._book_epochs = [], [], {}
+        self.connect()
+        self.rebuilds += 1
+        logger.info(f"training rank {self.train_rank}: {why}, table rebuilt ({self.rebuilds} so far)")
+
+    def rebind_sources(self) -> None:
+        """The tensors in ``local`` (the dict this sender was given) were replaced:
+        the table holds their old addresses and must be encoded again."""
+        self._rebuild("training tensors moved")
 
     def send(self, epoch: int, synchronize: bool = True) -> None:
         if self.moving_destinations:
@@ -452,6 +462,9 @@ class GlooSender:
 
     def gpu_launches_per_update(self) -> int:
         return 0
+
+    def rebind_sources(self) -> None:
+        """Messages are packed from whatever ``local`` holds when they are sent: nothing to rebuild."""
 
     def close(self) -> None:
         pass

@@ -19,7 +19,7 @@ from typing import List
 import torch
 
 from awex_b200 import logging
-from awex_b200.transfer.lowering import LocalParam, SendProgramCompiler, refresh_derived
+from awex_b200.transfer.lowering import DERIVED_PREFIX, LocalParam, SendProgramCompiler, refresh_derived
 from awex_b200.transfer.transfer_plan import TransferPlanBuilder, compute_transfer_plan_stats
 from awex_b200.utils.trace import phase
 from awex_b200.utils.common import compute_statistics
@@ -54,6 +54,10 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
         # head): persistent buffers beside the parameters, sent with plain copies
         self.derived = list(compiler.derived.values())
         self._local = local
+        # the parameter objects behind ``local``: a training framework that re-allocates a parameter leaves the
+        # detached tensors here pointing at the old storage, which would be sent again and again
+        self._watched = [((name, vp), p) for vp, chunk in enumerate(self.model) for name, p in chunk.named_parameters()]
+        self._encoded_ptrs = {key: p.data_ptr() for key, p in self._watched}  # the addresses the send table was built from
         refresh_derived(self.derived, local, self._gather_tp_shards)
         self.transfer_plan = self.builder.build_local_transfer_plan(self.infer_params_meta, self.parameters_meta, self.transfer_rank)
         stats = compute_transfer_plan_stats(self.transfer_plan)
@@ -86,9 +90,27 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
 
         return gather_tp_shards(self._local[(name, vp_stage)], self.rank_info.tp_size)
 
+    def _follow_moved_sources(self) -> None:
+        moved = [key for key, p in self._watched if key in self._local and p.data_ptr() != self._encoded_ptrs[key]]
+        if not moved:
+            return
+        logger.info(f"Rank[{self.transfer_rank}] {len(moved)} training tensors were re-allocated (e.g. {moved[0][0]}); rebuilding the send table")
+        kept = {k: t for k, t in self._local.items() if k[0].startswith(DERIVED_PREFIX)}
+        fresh = self.local_tensors()
+        for key, t in fresh.items():
+            old = self._local.get(key)
+            if old is not None and (tuple(old.shape) != tuple(t.shape) or old.dtype != t.dtype):
+                raise RuntimeError(f"{key[0]} changed shape or dtype ({tuple(old.shape)} {old.dtype} -> {tuple(t.shape)} {t.dtype})")
+        self._local.clear()  # the transport holds this very dict
+        self._local.update(fresh)
+        self._local.update(kept)
+        self._encoded_ptrs = {key: p.data_ptr() for key, p in self._watched}
+        self.transport.rebind_sources()
+
     def _write_weights(self, step_id, **kwargs) -> None:
         t0 = time.time()
         self.epoch += 1
+        self._follow_moved_sources()
         if self.derived:
             with phase("derive_tensors"):
                 refresh_derived(self.derived, self._local, self._gather_tp_shards)  # same stream as the transfer: ordered before it

@@ -309,7 +309,8 @@ def _drop_expected_head_difference(arch, engine, bad):
 
 
 @pytest.mark.timeout(120)
-@pytest.mark.parametrize("arch_name,validate,moving", [("tiny-llama", 1, False), ("tiny-llama-norm-head", 0, False), ("tiny-llama", 0, True)])
+@pytest.mark.parametrize("arch_name,validate,moving", [("tiny-llama", 1, False), ("tiny-llama-norm-head", 0, False), ("tiny-llama", 0, True),
+                                                     ("tiny-llama-norm-head", 0, "sources")])
 def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, validate, moving):
     """`NCCLWeightsWriter` and `WeightsReader` on the peer-store plane (forced
     here; on CPU tensors they would pick messages): metadata exchange, plan,
@@ -326,7 +327,7 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
     monkeypatch.setenv("AWEX_DEVICE_TYPE", "cpu")
     monkeypatch.setattr(transports, "choose_data_plane", lambda device_type, configured=None: "peer_stores")
     # the moving case also shares one GPU between the two processes (host handshake in both directions)
-    GPU_OF.update(train0="GPU-a", infer0="GPU-a" if moving else "GPU-b", nobody="GPU-x")
+    GPU_OF.update(train0="GPU-a", infer0="GPU-a" if moving is True else "GPU-b", nobody="GPU-x")
     server = MetaServer("127.0.0.1", 0)
     server.start()
     addr = f"127.0.0.1:{server.port}"
@@ -339,7 +340,7 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
                 engine = SyntheticInferenceEngine(arch, InferLayout(tp=1), infer_rank_infos(tp=1)[0], addr, dtype=torch.float32, device="cpu",
                                                   zero=False,  # holds the step-0 weights, as after loading the same checkpoint
                                                   weights_validation_steps=validate,
-                                                  debug_mode_config={"raise_on_validation_fail": True, "parameters_may_move": moving})
+                                                  debug_mode_config={"raise_on_validation_fail": True, "parameters_may_move": moving is True})
                 MEMORY.extend(engine.model.parameters())
                 reader = WeightsReader(engine)
                 reader.initialize()
@@ -349,7 +350,7 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
                     head = dict(engine.model.named_parameters())["lm_head.weight"]
                     norms = head.float().norm(dim=0)
                     assert torch.allclose(norms, torch.ones_like(norms), atol=1e-5), "the head did not arrive with unit-norm columns"
-                if moving:  # the engine re-allocates all its weights between the updates
+                if moving is True:  # the engine re-allocates all its weights between the updates
                     for name, t in list(engine.model._tensors.items()):
                         engine.model._tensors[name] = torch.zeros_like(t)
                     MEMORY.extend(engine.model._tensors.values())
@@ -374,10 +375,16 @@ def test_public_api_drives_the_peer_store_plane(fakes, monkeypatch, arch_name, v
             assert bool(writer.derived) == arch.norm_head
             writer.write_weights(step_id=1)
             engine.regenerate(step=2)
+            if moving == "sources":  # the training framework re-allocates its parameters (same objects, new storage)
+                for _name, p in engine.model.named_parameters():
+                    p.data = p.data.clone()
+                MEMORY.extend(p for _n, p in engine.model.named_parameters())
             writer.write_weights(step_id=2)
             assert type(writer.transport).__name__ == "PeerStoreSender"
             if moving:
                 assert writer.transport.rebuilds == 1 and writer.transport.program.launches == [2]  # a new table for the new addresses
+                if moving == "sources":
+                    assert all(writer._local[key].data_ptr() == p.data_ptr() == writer._encoded_ptrs[key] for key, p in writer._watched)
             else:
                 assert writer.transport.rebuilds == 0 and writer.transport.program.launches == [1, 2]
         thread.join(timeout=60)
