@@ -141,7 +141,7 @@ def fakes(monkeypatch):
     yield
 
 
-def build_pair(gpus):
+def build_pair(gpus, fp8=False):
     """One training rank (TP1) and one inference rank (TP1) of the tiny model as
     two "processes"; ``gpus`` = (GPU of the trainer, GPU of the server)."""
     from awex_b200.meta.meta_server import MetaServer, MetaServerClient
@@ -149,7 +149,7 @@ def build_pair(gpus):
     from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
 
     GPU_OF.update(train0=gpus[0], infer0=gpus[1])
-    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=1), InferLayout(tp=1), dtype=torch.float32)
+    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=1), InferLayout(tp=1, fp8=fp8), dtype=torch.bfloat16 if fp8 else torch.float32)
     items = job.compile_all()[0]
     local = job.local_tensors(0)
     views = job.destination_views()[0]
@@ -459,3 +459,17 @@ def test_one_process_with_its_two_roles_on_two_gpus_uses_device_flags(fakes):
         finally:
             server.stop()
             MEMORY.clear()
+
+
+def test_block_fp8_serving_through_the_peer_store_plane(fakes):
+    """bf16 training shards, block-scaled fp8 inference shards: the sender's table
+    quantises on the way (weights and scales land in the receiver's tensors)."""
+    job, items, local, views, server, meta = build_pair(("GPU-a", "GPU-b"), fp8=True)
+    try:
+        assert any(it.value_op.kind == "fp8_block" for it in items) and any(n.endswith("_scale_inv") for n in views)
+        sender, receiver = make_sides(job, items, local, views, meta)
+        update(sender, receiver, 1)
+        assert job.mismatches() == []
+        assert sender.bytes_out < sender.bytes_in  # one byte per element plus scales leave, two bytes per element are read
+    finally:
+        server.stop()
