@@ -344,7 +344,14 @@ class SendProgramCompiler:
             names = {src[0] for _, src, _, _ in segments}
             if len(names) != 1:
                 raise NotImplementedError(f"{spec.name}: a block-quantised box draws rows from several tensors {sorted(names)}")
-            segments = [(0, segments[0][1], segments[0][2], n_rows, tuple((rel, srow, n) for rel, _, srow, n in segments))]
+            whole_blocks = all(rel % FP8_BLOCK == 0 for rel, _, _, _ in segments) and all(n % FP8_BLOCK == 0 for _, _, _, n in segments[:-1])
+            if len(segments) > 1 and whole_blocks:
+                # every contiguous source run covers whole quantisation blocks of the destination (de-interleaved
+                # Q / K / V with head sizes that are multiples of the block): one plain slab per run, which the
+                # kernel fetches with one tiled load per tile instead of one copy per gathered row
+                segments = [(rel, src, src_row, n, None) for rel, src, src_row, n in segments]
+            else:
+                segments = [(0, segments[0][1], segments[0][2], n_rows, tuple((rel, srow, n) for rel, _, srow, n in segments))]
         else:
             segments = [(rel, src, src_row, n, None) for rel, src, src_row, n in segments]
         for rel, src, src_row, n, gather in segments:

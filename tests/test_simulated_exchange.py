@@ -293,3 +293,33 @@ def test_column_normalised_head_is_derived_on_the_sender(train_tp, infer_tp):
     for got, want in zip(received(), normed.chunk(infer_tp, 0)):
         assert torch.equal(got, want)
     assert buffers == {r: job.local_tensors(r)[("__derived__/lm_head.weight", 0)].data_ptr() for r in programs}
+
+
+def test_block_aligned_head_runs_become_plain_fp8_slabs():
+    """De-interleaving Q / K / V for fp8 serving gathers rows of the fused Megatron
+    tensor; when every head run is a whole number of quantisation blocks (head size
+    128) each run is lowered to a plain slab (fetched with tiled loads by the
+    kernel) instead of a row-gather list, and the result is the same."""
+    import dataclasses
+
+    from awex_b200.transfer.table_interpreter import HostMemory, run_table
+
+    base = get_arch("tiny-qwen3-moe")
+    for head_dim, gathered in ((128, False), (32, True)):
+        arch = dataclasses.replace(base, head_dim=head_dim, name=f"tiny-qwen3-moe-hd{head_dim}")
+        job = SimulatedJob(arch, TrainLayout(tp=1, dp=2, ep=2), InferLayout(tp=1, fp8=True), dtype=torch.bfloat16)
+        programs = job.compile_all()
+        assert job.check_coverage() == []
+        qkv = [it for items in programs.values() for it in items if ".self_attn." in it.dst_name and it.dst_name.endswith("_proj.weight")
+               and "o_proj" not in it.dst_name]
+        assert qkv and all(it.value_op.kind == "fp8_block" for it in qkv)
+        assert any(it.src_rows for it in qkv) == gathered
+        if not gathered:  # one item per head run, each a whole number of blocks
+            assert all(it.extent[0] % 128 == 0 and it.dst_start[0] % 128 == 0 for it in qkv)
+        encoded = job.encode_all(validate=True)
+        mem = HostMemory(job.source_tensors() + [p for ms in job.infer_models for m in ms for p in m.parameters()])
+        for table, n_tiles, enc in encoded.values():
+            assert run_table(table, n_tiles, mem, enc.row_offsets) == n_tiles
+            if not gathered:
+                assert len(enc.row_offsets) == 0 and len(enc.tensor_map_descs) > 0  # no gathered rows left; tiled loads everywhere
+        assert job.mismatches() == []
