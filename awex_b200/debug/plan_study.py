@@ -55,9 +55,10 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     ingress = [0] * job.infer_world_size
     local_in = [0] * job.infer_world_size
     compile_s = 0.0
+    job.programs = {}
     for r in range(t_layout.world):
         t0 = time.time()
-        items = job.compile_send_program(r)
+        items = job.programs[r] = job.compile_send_program(r)
         compile_s += time.time() - t0
         remote = local = read = quantised = 0
         for it in items:
@@ -73,7 +74,7 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
                 quantised += it.numel * it.src_dtype.itemsize + it.dst_bytes
         ranks.append({"rank": r, "items": len(items), "destinations": len({it.dst_rank for it in items}), "read": read,
                       "remote_egress": remote, "local_written": local, "quantised_in_plus_out": quantised})
-    problems = job.check_coverage() if hasattr(job, "programs") or job.compile_all() is not None else []
+    problems = job.check_coverage()
     per_gpu_ms = {
         "nvlink_egress": max(x["remote_egress"] for x in ranks) / (nvlink_gbps * 1e9) * 1e3,
         "nvlink_ingress": max(ingress) / (nvlink_gbps * 1e9) * 1e3,
