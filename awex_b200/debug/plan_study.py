@@ -7,7 +7,11 @@ report items, bytes per link and the time the update cannot beat.
 
 ``--placement separated`` puts training ranks and inference workers on disjoint
 GPUs (every byte crosses NVLink); ``colocated`` puts training rank r and
-inference transfer rank r on GPU r (bytes between them stay in local memory).
+inference transfer rank r on GPU r (bytes between them stay in local memory);
+``colocated-best`` chooses which inference worker shares a GPU with which
+training rank so that as many bytes as possible stay local (an assignment
+problem over the bytes each training rank sends to each inference worker) and
+prints the pairing.
 Peak rates default to what was measured on an 8xB200 box and can be overridden.
 """
 
@@ -52,17 +56,30 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
                                       skip_names=job.builder.skip_names)
     meta_s = time.time() - started
     ranks: List[Dict[str, object]] = []
+    job.programs = {r: None for r in range(t_layout.world)}
+    gpu_of_infer = {i: i for i in range(job.infer_world_size)}  # inference transfer rank -> GPU (= training rank it sits with)
+    if placement == "colocated-best":
+        import numpy as np
+        from scipy.optimize import linear_sum_assignment
+
+        n = max(t_layout.world, job.infer_world_size)
+        sent = np.zeros((n, n))
+        for r in range(t_layout.world):
+            job.programs[r] = job.compile_send_program(r)
+            for it in job.programs[r]:
+                sent[r, it.dst_rank] += it.dst_bytes
+        rows, cols = linear_sum_assignment(-sent)  # maximise the bytes that stay on their GPU
+        gpu_of_infer = {int(i): int(r) for r, i in zip(rows, cols)}
     ingress = [0] * job.infer_world_size
     local_in = [0] * job.infer_world_size
     compile_s = 0.0
-    job.programs = {}
     for r in range(t_layout.world):
         t0 = time.time()
-        items = job.programs[r] = job.compile_send_program(r)
+        items = job.programs[r] = job.programs[r] or job.compile_send_program(r)
         compile_s += time.time() - t0
         remote = local = read = quantised = 0
         for it in items:
-            same_gpu = placement == "colocated" and it.dst_rank == r
+            same_gpu = placement.startswith("colocated") and gpu_of_infer.get(it.dst_rank) == r
             if same_gpu:
                 local += it.dst_bytes
                 local_in[it.dst_rank] += it.dst_bytes
@@ -84,6 +101,7 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     bound = max(per_gpu_ms, key=per_gpu_ms.get)
     return {
         "model": arch.name, "train": t_layout.label(), "infer": i_layout.label(), "placement": placement, "pairing": pairing,
+        "gpu_of_inference_rank": gpu_of_infer,
         "parameters": arch.param_count(), "coverage_problems": problems[:5], "senders": ranks,
         "ingress_per_inference_rank": ingress, "bound_ms": per_gpu_ms, "bound": bound, "lower_bound_ms": per_gpu_ms[bound],
         "host_seconds": {"metadata_all_ranks": round(meta_s, 2), "plan_and_lowering_per_rank": round(compile_s / max(t_layout.world, 1), 2)},
@@ -97,7 +115,7 @@ def main(argv=None) -> int:
     ap.add_argument("--train", default="tp1", help="e.g. tp4 or tp1,dp8,ep8 or tp2,pp2")
     ap.add_argument("--infer", default="tp1", help="e.g. tp2,engines2 or tp4,ep4,engines2")
     ap.add_argument("--fp8", action="store_true", help="inference side serves block-scaled fp8")
-    ap.add_argument("--placement", default="colocated", choices=["colocated", "separated"])
+    ap.add_argument("--placement", default="colocated", choices=["colocated", "colocated-best", "separated"])
     ap.add_argument("--pairing", default="spread", choices=["spread", "round_robin"])
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (quick look)")
     ap.add_argument("--nvlink-gbps", type=float, default=770.0)
@@ -114,6 +132,8 @@ def main(argv=None) -> int:
     print(" rank  items  dests   read GB  egress GB   local GB")
     for x in report["senders"]:
         print(f"{x['rank']:5d} {x['items']:6d} {x['destinations']:6d} {gb(x['read'])} {gb(x['remote_egress'])}  {gb(x['local_written'])}")
+    if report["placement"] == "colocated-best":
+        print("inference transfer rank -> GPU (training rank it shares):", report["gpu_of_inference_rank"])
     print("ingress GB per inference rank:", [round(b / 1e9, 3) for b in report["ingress_per_inference_rank"]])
     print("lower bounds (ms):", {k: round(v, 2) for k, v in report["bound_ms"].items()}, "->", report["bound"])
     print("host seconds:", report["host_seconds"], "coverage problems:", report["coverage_problems"])

@@ -40,6 +40,8 @@ def parse_args():
     ap.add_argument("--config", default="separated", choices=["separated", "colocated", "moe", "fp8"],
                     help="separated: Llama-3-8B, training and inference on disjoint GPUs; colocated: Qwen2.5-32B TP n -> TP n on the same GPUs; "
                          "moe: Qwen3-30B-A3B EP n -> 2 x (TP n/2, EP n/2); fp8: Qwen3-235B-A22B EP n -> TP n block-fp8")
+    ap.add_argument("--placement", default="blocked", choices=["blocked", "interleaved"],
+                    help="moe configuration: which GPUs the two inference instances sit on (see role_table)")
     ap.add_argument("--model", default=None, help="architecture preset; default is the one the configuration names")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model to this many layers (result is then not a valid benchmark)")
     ap.add_argument("--no-validate", action="store_true")
