@@ -173,3 +173,18 @@ def test_contention_model_cli_on_a_tiny_layout(capsys):
                                   "--orders", "contiguous,chunks,striped,rotated", "--stripe-mb", "0.0625"]) == 0
     lines = [l for l in capsys.readouterr().out.splitlines() if " ms " in l]
     assert [l.split(":")[0].strip() for l in lines] == ["contiguous", "chunks", "striped", "rotated"]
+
+
+def test_plan_study_finds_a_placement_that_keeps_more_bytes_local():
+    from awex_b200.debug.plan_study import parse_layout, study
+
+    train, infer = parse_layout("tp1,dp4,ep4"), parse_layout("tp2,ep2,engines2")
+    plain = study("tiny-qwen3-moe", train, infer, placement="colocated")
+    best = study("tiny-qwen3-moe", train, infer, placement="colocated-best")
+    local = lambda report: sum(x["local_written"] for x in report["senders"])  # noqa: E731
+    assert sorted(best["gpu_of_inference_rank"].values()) == [0, 1, 2, 3] and best["coverage_problems"] == []
+    assert local(best) > local(plain)
+    assert best["bound_ms"]["nvlink_egress"] < plain["bound_ms"]["nvlink_egress"]
+    # the same bytes move either way
+    total = lambda report: sum(x["local_written"] + x["remote_egress"] for x in report["senders"])  # noqa: E731
+    assert total(best) == total(plain)
