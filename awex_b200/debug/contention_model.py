@@ -182,13 +182,22 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     job = SimulatedJob(arch, t_layout, i_layout, dtype=torch.bfloat16, device="meta")
     job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines, replica_pairing=pairing,
                                       skip_names=job.builder.skip_names)
-    if placement == "colocated":
+    programs = {r: job.compile_send_program(r) for r in range(t_layout.world)}
+    if placement.startswith("colocated"):
         n_gpus = max(t_layout.world, job.infer_world_size)
         gpu_of_dst = {i: i for i in range(job.infer_world_size)}
+        if placement == "colocated-best":  # every inference worker beside the training rank that sends it most
+            from scipy.optimize import linear_sum_assignment
+
+            sent = np.zeros((n_gpus, n_gpus))
+            for r, items in programs.items():
+                for it in items:
+                    sent[r, it.dst_rank] += it.dst_bytes
+            rows, cols = linear_sum_assignment(-sent)
+            gpu_of_dst = {int(i): int(r) for r, i in zip(rows, cols)}
     else:
         n_gpus = t_layout.world + job.infer_world_size
         gpu_of_dst = {i: t_layout.world + i for i in range(job.infer_world_size)}
-    programs = {r: job.compile_send_program(r) for r in range(t_layout.world)}
     out = []
     for order in orders:
         items = {r: (stripe_by_destination(p, int(stripe_mb * 2**20)) if order == "striped" else _rotated(p, r) if order == "rotated" else p)
@@ -209,7 +218,7 @@ def main(argv=None) -> int:
     ap.add_argument("--train", default="tp1")
     ap.add_argument("--infer", default="tp1")
     ap.add_argument("--fp8", action="store_true")
-    ap.add_argument("--placement", default="colocated", choices=["colocated", "separated"])
+    ap.add_argument("--placement", default="colocated", choices=["colocated", "colocated-best", "separated"])
     ap.add_argument("--pairing", default="spread", choices=["spread", "round_robin"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--stripe-mb", type=float, default=1.0)
