@@ -221,8 +221,13 @@ def run_distributed(args):
     writer = reader = train_engine = infer_engine = None
     if is_train:
         ri = train_rank_infos(train_layout.tp, train_layout.pp, train_layout.dp, train_layout.ep, train_layout.etp)[train_ranks.index(rank)]
+        pairing = {}
+        if getattr(args, "pairing", None):
+            # which training rank shares a GPU with each inference worker: process rank = GPU in this benchmark
+            mate = {e * len(ranks) + j: train_ranks.index(g) for e, ranks in enumerate(engines) for j, g in enumerate(ranks) if g in train_ranks}
+            pairing = dict(replica_pairing=args.pairing, colocation=mate)
         train_engine = SyntheticTrainEngine(arch, ri, meta_addr, dtype=torch.bfloat16, device=device,
-                                            process_group=train_group, transfer_grid=args.grid)
+                                            process_group=train_group, transfer_grid=args.grid, **pairing)
         writer = NCCLWeightsWriter(train_engine)
         writer.initialize()
         note("training shard built")

@@ -52,8 +52,9 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     i_layout = InferLayout(tp=infer.get("tp", 1), ep=infer.get("ep", 1), num_engines=infer.get("engines", 1), fp8=fp8)
     started = time.time()
     job = SimulatedJob(arch, t_layout, i_layout, dtype=torch.bfloat16, device="meta")
-    job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines, replica_pairing=pairing,
-                                      skip_names=job.builder.skip_names)
+    skip = job.builder.skip_names
+    job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines,
+                                      replica_pairing="spread" if pairing == "local" else pairing, skip_names=skip)
     meta_s = time.time() - started
     ranks: List[Dict[str, object]] = []
     job.programs = {r: None for r in range(t_layout.world)}
@@ -70,6 +71,12 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
                 sent[r, it.dst_rank] += it.dst_bytes
         rows, cols = linear_sum_assignment(-sent)  # maximise the bytes that stay on their GPU
         gpu_of_infer = {int(i): int(r) for r, i in zip(rows, cols)}
+    if pairing == "local":
+        # the placement above was found with least-loaded pairing; now let every shard prefer the replica on its own GPU
+        mates = gpu_of_infer if placement.startswith("colocated") else {}
+        job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines, replica_pairing="local",
+                                          skip_names=skip, colocation=mates)
+        job.programs = {r: None for r in range(t_layout.world)}
     ingress = [0] * job.infer_world_size
     local_in = [0] * job.infer_world_size
     compile_s = 0.0
@@ -116,7 +123,7 @@ def main(argv=None) -> int:
     ap.add_argument("--infer", default="tp1", help="e.g. tp2,engines2 or tp4,ep4,engines2")
     ap.add_argument("--fp8", action="store_true", help="inference side serves block-scaled fp8")
     ap.add_argument("--placement", default="colocated", choices=["colocated", "colocated-best", "separated"])
-    ap.add_argument("--pairing", default="spread", choices=["spread", "round_robin"])
+    ap.add_argument("--pairing", default="spread", choices=["spread", "round_robin", "local"])
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (quick look)")
     ap.add_argument("--nvlink-gbps", type=float, default=770.0)
     ap.add_argument("--hbm-gbps", type=float, default=6540.0)

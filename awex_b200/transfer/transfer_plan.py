@@ -146,11 +146,18 @@ class TransferPlanBuilder:
         strict_param_key_match: bool = False,
         replica_pairing: str = "round_robin",
         skip_names: Iterable[str] = (),
+        colocation: Optional[Dict[int, int]] = None,
     ):
         # names that are planned for nobody (aliases of memory another name covers)
         self.skip_names = frozenset(skip_names)
-        if replica_pairing not in ("round_robin", "spread"):
+        if replica_pairing not in ("round_robin", "spread", "local"):
             raise ValueError(f"unknown replica_pairing {replica_pairing!r}")
+        # "local": like "spread", but an inference shard whose GPU also holds a training replica of the tensor takes
+        # it from there.  ``colocation`` maps inference transfer ranks to the training global rank on the same GPU
+        # (default: inference transfer rank t sits with training rank t).
+        self.locality = replica_pairing == "local"
+        self.colocation = None if colocation is None else {int(k): int(v) for k, v in colocation.items()}
+        replica_pairing = "spread" if self.locality else replica_pairing
         self.replica_pairing = replica_pairing
         self._replica_choice: Dict[Tuple[str, int], int] = {}
         if num_infer_engines <= 0:
@@ -307,13 +314,27 @@ class TransferPlanBuilder:
         only_infer = global_transfer_rank if (global_transfer_rank is not None and global_transfer_rank < self.infer_world_size) else None
         only_train = global_transfer_rank if (global_transfer_rank is not None and global_transfer_rank >= self.infer_world_size) else None
         ops: List[CommunicationOperation] = []
+        home = self._replica_of_train_rank(training_meta) if self.locality and len(train_replicas) > 1 else None
         for i, (engine, inf_replica) in enumerate(infer_replicas):
-            trn_replica = train_replicas[self._pick_train_replica(i, training_meta)]
+            chosen = self._pick_train_replica(i, training_meta)
             inf_boxes = self._create_shard_offset_for_replica(inf_replica, engine, True, only_infer)
-            trn_boxes = self._create_shard_offset_for_replica(trn_replica, 0, False, only_train)
-            for region in self._find_overlapping_regions(inf_boxes, trn_boxes):
-                ops.extend(self._build_region_communication_plan(region))
+            groups: Dict[int, List[ShardOffset]] = {chosen: inf_boxes}
+            if home is not None:
+                # every inference shard takes the tensor from the replica on its own GPU where there is one
+                groups = {}
+                for box in inf_boxes:
+                    mate = box.rank if self.colocation is None else self.colocation.get(box.rank)
+                    groups.setdefault(home.get(mate, chosen), []).append(box)
+            for k in sorted(groups):
+                trn_boxes = self._create_shard_offset_for_replica(train_replicas[k], 0, False, only_train)
+                for region in self._find_overlapping_regions(groups[k], trn_boxes):
+                    ops.extend(self._build_region_communication_plan(region))
         return ops
+
+    @staticmethod
+    def _replica_of_train_rank(training_meta: ParameterMeta) -> Dict[int, int]:
+        """training global rank -> index of the replica it holds a shard of."""
+        return {int(s.global_rank): k for k, rep in enumerate(training_meta.replicas) for s in rep.shards}
 
     def _pick_train_replica(self, i: int, training_meta: ParameterMeta) -> int:
         """Index of the training replica that feeds inference replica ``i``.

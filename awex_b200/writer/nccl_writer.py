@@ -42,6 +42,8 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
             self.infer_world_size, self.training_world_size, self.num_infer_engines, enable_debug_mode=self.enable_debug_mode,
             replica_pairing=str(self.config.get("replica_pairing", "spread")),
             skip_names=(self.infer_conf.get("aliased_parameters") or {}),
+            # with replica_pairing="local": inference transfer rank -> training global rank on the same GPU
+            colocation=self.config.get("colocation") or self.infer_conf.get("colocation"),
         )
         local = self.local_tensors()
         params = [LocalParam(name, vp, tuple(t.shape), t.dtype) for (name, vp), t in local.items()]

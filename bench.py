@@ -42,6 +42,8 @@ def parse_args():
                          "moe: Qwen3-30B-A3B EP n -> 2 x (TP n/2, EP n/2); fp8: Qwen3-235B-A22B EP n -> TP n block-fp8")
     ap.add_argument("--placement", default="blocked", choices=["blocked", "interleaved"],
                     help="moe configuration: which GPUs the two inference instances sit on (see role_table)")
+    ap.add_argument("--pairing", default=None, choices=["spread", "round_robin", "local"],
+                    help="replica pairing of the planner (default: the writer's own, least-loaded); 'local' prefers the replica on the same GPU")
     ap.add_argument("--model", default=None, help="architecture preset; default is the one the configuration names")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model to this many layers (result is then not a valid benchmark)")
     ap.add_argument("--no-validate", action="store_true")

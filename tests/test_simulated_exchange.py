@@ -323,3 +323,34 @@ def test_block_aligned_head_runs_become_plain_fp8_slabs():
             if not gathered:
                 assert len(enc.row_offsets) == 0 and len(enc.tensor_map_descs) > 0  # no gathered rows left; tiled loads everywhere
         assert job.mismatches() == []
+
+
+def test_local_replica_pairing_keeps_replicated_tensors_on_their_gpu():
+    """A TP1 / DP4 / EP4 trainer holds attention, norms and embeddings on every
+    rank.  With ``replica_pairing="local"`` and the map of which inference worker
+    shares a GPU with which training rank, every inference shard of those tensors
+    is written by the training rank on its own GPU; experts still come from
+    whoever holds them; the update stays exact and exactly-once."""
+    from awex_b200.transfer.transfer_plan import TransferPlanBuilder
+
+    arch = get_arch("tiny-qwen3-moe")
+    train, infer = TrainLayout(tp=1, dp=4, ep=4), InferLayout(tp=2, ep=2, num_engines=2)
+    colocation = {0: 0, 1: 2, 2: 1, 3: 3}  # worker j of instance 0 on GPU 2j, of instance 1 on GPU 2j+1
+
+    def remote_dense_bytes(pairing, **kw):
+        job = SimulatedJob(arch, train, infer, dtype=torch.float32)
+        job.builder = TransferPlanBuilder(job.infer_world_size, train.world, infer.num_engines, replica_pairing=pairing,
+                                          skip_names=job.builder.skip_names, **kw)
+        programs = job.compile_all()
+        assert job.check_coverage() == []
+        job.run_cpu()
+        assert job.mismatches() == []
+        dense = [(r, it) for r, items in programs.items() for it in items if ".experts." not in it.dst_name]
+        return sum(it.dst_bytes for r, it in dense if colocation[it.dst_rank] != r), sum(it.dst_bytes for _r, it in dense)
+
+    spread_remote, total = remote_dense_bytes("spread")
+    local_remote, same_total = remote_dense_bytes("local", colocation=colocation)
+    assert same_total == total and spread_remote > 0.5 * total  # least-loaded pairing ignores where things sit
+    assert local_remote == 0                                    # every dense shard comes from its own GPU
+    with pytest.raises(ValueError):
+        TransferPlanBuilder(4, 4, 2, replica_pairing="nearest")
