@@ -180,8 +180,9 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     t_layout = TrainLayout(tp=train.get("tp", 1), pp=train.get("pp", 1), dp=train.get("dp", 1), ep=train.get("ep", 1), etp=train.get("etp", 1))
     i_layout = InferLayout(tp=infer.get("tp", 1), ep=infer.get("ep", 1), num_engines=infer.get("engines", 1), fp8=fp8)
     job = SimulatedJob(arch, t_layout, i_layout, dtype=torch.bfloat16, device="meta")
-    job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines, replica_pairing=pairing,
-                                      skip_names=job.builder.skip_names)
+    skip = job.builder.skip_names
+    job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines,
+                                      replica_pairing="spread" if pairing == "local" else pairing, skip_names=skip)
     programs = {r: job.compile_send_program(r) for r in range(t_layout.world)}
     if placement.startswith("colocated"):
         n_gpus = max(t_layout.world, job.infer_world_size)
@@ -198,6 +199,11 @@ def study(model: str, train: Dict[str, int], infer: Dict[str, int], placement: s
     else:
         n_gpus = t_layout.world + job.infer_world_size
         gpu_of_dst = {i: t_layout.world + i for i in range(job.infer_world_size)}
+    if pairing == "local" and placement.startswith("colocated"):
+        # the placement was found with least-loaded pairing; now every shard prefers the replica on its own GPU
+        job.builder = TransferPlanBuilder(job.infer_world_size, t_layout.world, i_layout.num_engines, replica_pairing="local",
+                                          skip_names=skip, colocation=gpu_of_dst)
+        programs = {r: job.compile_send_program(r) for r in range(t_layout.world)}
     out = []
     for order in orders:
         items = {r: (stripe_by_destination(p, int(stripe_mb * 2**20)) if order == "striped" else _rotated(p, r) if order == "rotated" else p)
@@ -219,7 +225,7 @@ def main(argv=None) -> int:
     ap.add_argument("--infer", default="tp1")
     ap.add_argument("--fp8", action="store_true")
     ap.add_argument("--placement", default="colocated", choices=["colocated", "colocated-best", "separated"])
-    ap.add_argument("--pairing", default="spread", choices=["spread", "round_robin"])
+    ap.add_argument("--pairing", default="spread", choices=["spread", "round_robin", "local"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--stripe-mb", type=float, default=1.0)
     ap.add_argument("--chunk-tiles", type=int, default=4)
