@@ -51,3 +51,18 @@ def test_reference_arm_declines_co_located_configurations():
     assert proc.returncode == 0
     line = json.loads(proc.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_role_table_placements():
+    """The MoE configuration's two placements: instances on halves of the box, or
+    every worker beside the two training ranks that hold its experts."""
+    from awex_b200.bench_distributed import role_table
+
+    train, infer, train_ranks, engines, label = role_table(8, "moe")
+    assert engines == [[0, 1, 2, 3], [4, 5, 6, 7]] and train_ranks == list(range(8)) and "interleaved" not in label
+    _t, _i, _r, engines, label = role_table(8, "moe", "interleaved")
+    assert engines == [[0, 2, 4, 6], [1, 3, 5, 7]] and label.endswith("-interleaved")
+    assert role_table(4, "moe", "interleaved")[3] == [[0, 2], [1, 3]]
+    # other configurations ignore the placement
+    assert role_table(8, "separated", "interleaved")[3] == role_table(8, "separated")[3] == [[4, 5], [6, 7]]
+    assert role_table(8, "fp8", "interleaved")[3] == [list(range(8))]
