@@ -10,7 +10,7 @@ import torch
 import torch.multiprocessing as mp
 
 
-def _writer(rank, meta_addr, store_port, q):
+def _writer(rank, meta_addr, store_port, q, pairing):
     import torch.distributed as dist
 
     from awex_b200 import NCCLWeightsWriter
@@ -22,13 +22,17 @@ def _writer(rank, meta_addr, store_port, q):
         os.environ["AWEX_DEVICE_TYPE"] = "cpu"
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{store_port}", rank=rank, world_size=2)
         ri = train_rank_infos(tp=1, dp=2, ep=2)[rank]
-        engine = SyntheticTrainEngine(get_arch("tiny-qwen3-moe"), ri, meta_addr, dtype=torch.float32, device="cpu", exchange_timeout_s=120)
+        engine = SyntheticTrainEngine(get_arch("tiny-qwen3-moe"), ri, meta_addr, dtype=torch.float32, device="cpu", exchange_timeout_s=120,
+                                      **({"replica_pairing": pairing} if pairing else {}))  # "local": engine e shares a GPU with writer e
         writer = NCCLWeightsWriter(engine)
         writer.initialize()
         writer.write_weights(step_id=1)
         engine.regenerate(step=2)
         writer.write_weights(step_id=2)
-        q.put(("writer", rank, writer.transport.bytes_out, sorted(writer.transport.destinations)))
+        from awex_b200.transfer.cpu_exec import entry_nbytes
+
+        per_dst = {d: sum(entry_nbytes(e) for e in es) for d, es in writer.transport.manifest.items()}
+        q.put(("writer", rank, writer.transport.bytes_out, (sorted(writer.transport.destinations), per_dst)))
         dist.destroy_process_group()
     except BaseException as exc:
         q.put(("error", f"writer {rank}: {exc!r}", 0, []))
@@ -65,7 +69,8 @@ def _reader(engine_rank, meta_addr, q):
 
 
 @pytest.mark.timeout(400)
-def test_expert_parallel_writers_to_two_engines_over_gloo():
+@pytest.mark.parametrize("pairing", [None, "local"])
+def test_expert_parallel_writers_to_two_engines_over_gloo(pairing):
     from awex_b200.meta.meta_server import MetaServer
     from awex_b200.utils.common import get_free_port
 
@@ -75,7 +80,7 @@ def test_expert_parallel_writers_to_two_engines_over_gloo():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = get_free_port()
-    procs = [ctx.Process(target=_writer, args=(r, addr, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_writer, args=(r, addr, port, q, pairing)) for r in range(2)]
     procs += [ctx.Process(target=_reader, args=(e, addr, q)) for e in range(2)]
     for p in procs:
         p.start()
@@ -94,6 +99,10 @@ def test_expert_parallel_writers_to_two_engines_over_gloo():
         assert bad1 == [] and bad2 == [], (engine_rank, bad1[:3], bad2[:3])
         assert senders == [0, 1]  # experts come from both expert-parallel ranks
     assert readers[0][2] == readers[1][2] and sum(w[2] for w in writers) == 2 * readers[0][2]
-    assert all(w[3] == [0, 1] for w in writers)  # every writer feeds both engines
-    # dense parameters are replicated on both writers: the least-loaded pairing shares them out
+    assert all(w[3][0] == [0, 1] for w in writers)  # every writer feeds both engines
+    # dense parameters are replicated on both writers: the pairing shares them out evenly
     assert abs(writers[0][2] - writers[1][2]) < 0.1 * writers[0][2]
+    if pairing == "local":
+        # ... and each engine takes them from the writer it shares a GPU with: only experts cross
+        for _, rank, _total, (_dests, per_dst) in writers:
+            assert per_dst[rank] > 1.5 * per_dst[1 - rank], per_dst
