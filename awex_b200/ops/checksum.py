@@ -1,8 +1,9 @@
 """Device checksums of many tensors in one launch (``csrc/checksum.cu``) and
 the same function in numpy as its oracle.
 
-``checksum = sum_i word_i * (GOLDEN * (2 i + 1)) mod 2**64`` over the 8-byte
-words of each row (last word zero-padded), ``i = row * words_per_row + j``.
+``checksum = sum_i mix(word_i) * (GOLDEN * (2 i + 1)) mod 2**64`` with
+``mix(w) = w ^ (w >> 32)`` over the 8-byte words of each row (last word
+zero-padded), ``i = row * words_per_row + j``.
 Contiguous tensors are hashed as one long row.
 """
 
@@ -46,7 +47,8 @@ def checksum_reference(t: torch.Tensor) -> int:
     with np.errstate(over="ignore"):
         idx = np.arange(words.size, dtype=np.uint64)
         keys = GOLDEN * (np.uint64(2) * idx + np.uint64(1))
-        return int((words * keys).sum(dtype=np.uint64))
+        mixed = words ^ (words >> np.uint64(32))
+        return int((mixed * keys).sum(dtype=np.uint64))
 
 
 class ChecksumPlan:

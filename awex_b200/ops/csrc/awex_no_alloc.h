@@ -25,6 +25,17 @@
 //    own device buffers; the call copies the table into the library's scratch.
 //    If the table lives in pinned memory it must stay unchanged until the work
 //    queued on `stream` by this call has run.
+//  * The table is checked on the host before anything is queued: tile numbering
+//    (`tile_begin` starts at 0 and continues the running count, `n_tiles` equals
+//    the total), non-zero tile geometry that matches the slab, the alignment and
+//    stage-size rules of slabs flagged for bulk copies, and that `src`, `dst`, the
+//    scale address of an fp8 slab, `row_table` and `tensor_map` are device
+//    addresses (`row_table` and `tensor_map` may be 0).  An encoder's raw output
+//    holds indices in `row_table` and no tensor maps: gathered rows and tensor
+//    maps must be given device addresses by the caller first.  A table that
+//    fails is refused with cudaErrorInvalidValue and a message naming the
+//    descriptor; nothing is launched.  The checks cannot see extents: that every
+//    slab stays inside the caller's buffers remains the caller's promise.
 //  * `n_desc` above AWEX_NO_ALLOC_MAX_DESCS is refused with cudaErrorInvalidValue
 //    and a message; nothing is launched.  Split the table and call again.
 //  * No flags are waited for or raised: the call is ordered by `stream` alone.

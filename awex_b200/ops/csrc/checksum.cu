@@ -4,13 +4,19 @@
 // A tensor is seen as `rows` rows of `row_bytes` bytes, `stride` bytes apart.
 // Each row is cut into 8-byte words (the last one zero-padded); word j of row r
 // has index i = r * words_per_row + j.  The checksum is
-//     sum_i word_i * K_i   (mod 2^64),   K_i = GOLDEN * (2 i + 1)
-// Every K_i is odd, so a flipped bit always changes the sum, and exchanging two
-// different words at i != j changes it by (w_i - w_j) * 2 (j - i) * GOLDEN, which is
-// non-zero modulo 2^64 for any tensor that fits in memory: swapped rows, shifted
-// shards and missing writes are all visible.  The sum is order-independent, so
-// CTAs combine partial sums with one atomic add each, and it costs one 64-bit
-// multiply-add per word, which keeps the kernel on the memory roofline.
+//     sum_i mix(word_i) * K_i   (mod 2^64),   mix(w) = w ^ (w >> 32),   K_i = GOLDEN * (2 i + 1)
+// mix is a bijection and every K_i is odd, so a change confined to one word
+// always changes the sum.  Exchanging two different words at i != j changes it
+// by (m_i - m_j) * 2 (j - i) * GOLDEN with m = mix(w); that vanishes modulo 2^64
+// only when the powers of two dividing (m_i - m_j) and (j - i) add up to 63 or
+// more.  Folding the high half into the low half keeps a difference in the top
+// bits (the sign of a word's last element) from being such a case: words that
+// differ only in bit 63 differ in bit 31 after mixing.  The check is a structured
+// hash, not a proof: it catches swapped rows, shifted shards and missing writes,
+// and two different tensors collide only by accident.  The sum is
+// order-independent, so CTAs combine partial sums with one atomic add each, and
+// it costs one 64-bit multiply-add per word, which keeps the kernel on the
+// memory roofline.
 //
 // Used for weight validation: the reference copies every parameter to the host
 // and compares there (awex/reader/weights_reader.py:436-587); here only 16
@@ -41,6 +47,13 @@ constexpr uint32_t kChunkWords = 16384;
 constexpr uint64_t kGolden = 0x9E3779B97F4A7C15ull;
 
 __device__ __forceinline__ uint64_t key_of(uint64_t i) { return kGolden * (2 * i + 1); }
+__device__ __forceinline__ uint64_t mix(uint64_t w) { return w ^ (w >> 32); }
+// 16 bytes that are read once: keep them out of L1
+__device__ __forceinline__ ulonglong2 load_stream16(const unsigned char* p) {
+  ulonglong2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p));
+  return v;
+}
 
 // NaNs in a full 8-byte word, two SIMD compares per word.
 __device__ __forceinline__ uint32_t count_nans_full(uint64_t w, uint32_t dtype) {
@@ -111,21 +124,27 @@ __global__ void __launch_bounds__(256) checksum_kernel(const SumDesc* descs, uin
       const uint64_t jv1 = min(j1, full_words) & ~1ull;
       const uint64_t idx0 = r * wpr;
       uint64_t j = j0;
-      if (aligned && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {  // two words per 16-byte load, two loads in flight
+      if (aligned && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+        // two words per 16-byte load, kUnroll independent loads in flight per thread
+        constexpr int kUnroll = 8;
         const uint64_t step = 2ull * blockDim.x;
         const uint64_t key_step = kGolden * 2 * step;
         j = j0 + 2ull * threadIdx.x;
         uint64_t key = key_of(idx0 + j);
-        for (; j + step < jv1; j += 2 * step, key += 2 * key_step) {
-          const ulonglong2 a = __ldg(reinterpret_cast<const ulonglong2*>(row + j * 8));
-          const ulonglong2 b = __ldg(reinterpret_cast<const ulonglong2*>(row + (j + step) * 8));
-          acc += a.x * key + a.y * (key + 2 * kGolden) + b.x * (key + key_step) + b.y * (key + key_step + 2 * kGolden);
-          nan_acc += count_nans_full(a.x, d.dtype) + count_nans_full(a.y, d.dtype) + count_nans_full(b.x, d.dtype) +
-                     count_nans_full(b.y, d.dtype);
+        for (; j + (kUnroll - 1) * step < jv1; j += kUnroll * step) {
+          ulonglong2 v[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) v[u] = load_stream16(row + (j + u * step) * 8);
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            acc += mix(v[u].x) * key + mix(v[u].y) * (key + 2 * kGolden);
+            nan_acc += count_nans_full(v[u].x, d.dtype) + count_nans_full(v[u].y, d.dtype);
+            key += key_step;
+          }
         }
         for (; j < jv1; j += step, key += key_step) {
-          const ulonglong2 a = __ldg(reinterpret_cast<const ulonglong2*>(row + j * 8));
-          acc += a.x * key + a.y * (key + 2 * kGolden);
+          const ulonglong2 a = load_stream16(row + j * 8);
+          acc += mix(a.x) * key + mix(a.y) * (key + 2 * kGolden);
           nan_acc += count_nans_full(a.x, d.dtype) + count_nans_full(a.y, d.dtype);
         }
         j = max(j0, jv1);
@@ -133,7 +152,7 @@ __global__ void __launch_bounds__(256) checksum_kernel(const SumDesc* descs, uin
       for (j += threadIdx.x; j < j1; j += blockDim.x) {
         uint32_t valid;
         uint64_t w = load_word(row, j, d.row_bytes, aligned, &valid);
-        acc += w * key_of(idx0 + j);
+        acc += mix(w) * key_of(idx0 + j);
         nan_acc += count_nans(w, d.dtype, valid);
       }
     } else {  // several whole (short) rows: one warp per row
@@ -144,7 +163,7 @@ __global__ void __launch_bounds__(256) checksum_kernel(const SumDesc* descs, uin
         for (uint64_t j = threadIdx.x & 31; j < wpr; j += 32) {
           uint32_t valid;
           uint64_t w = load_word(row, j, d.row_bytes, aligned, &valid);
-          acc += w * key_of(r * wpr + j);
+          acc += mix(w) * key_of(r * wpr + j);
           nan_acc += count_nans(w, d.dtype, valid);
         }
       }

@@ -22,6 +22,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 #include <type_traits>
 
@@ -43,16 +44,34 @@ __device__ __forceinline__ float to_float<__half>(__half v) { return __half2floa
 template <>
 __device__ __forceinline__ float to_float<float>(float v) { return v; }
 
+// Bounded wait for one phase of an mbarrier (spin budget far beyond any real latency).
+__device__ __forceinline__ bool q_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done = 0;
+  for (uint32_t spin = 0; !done && spin <= (1u << 24); ++spin)
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+  return done != 0;
+}
+
 // status: int32[4]; code 2 = a TMA load did not complete within the spin budget
+//
+// One pass over each staged block: a thread keeps its 16-byte chunks in
+// registers from the maximum search, the CTA agrees on the block maximum with
+// one barrier (the reduction scratch alternates between two halves, so nothing
+// else has to protect it), and the values are quantised from the registers.
+// After that barrier nobody reads the stage, so the load of the block after
+// next goes into it right away: two loads are in flight while a block is
+// quantised.
 template <typename T>
-__global__ void __launch_bounds__(kQThreads, 1)
+__global__ void __launch_bounds__(kQThreads, sizeof(T) == 4 ? 1 : 3)
 fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char* __restrict__ q, float* __restrict__ scales,
                        uint32_t rows, uint32_t cols, int64_t q_stride, int64_t scale_stride, uint32_t blocks_n,
                        uint32_t n_blocks, int ue8m0, int32_t* status) {
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t bars[2];
-  __shared__ uint32_t red[kQThreads / 32];
-  __shared__ int give_up;
+  __shared__ uint32_t red[2][kQThreads / 32];
   constexpr uint32_t kStage = kBlk * kBlk * sizeof(T);
   constexpr int kChunkElems = 16 / sizeof(T);          // elements per 16-byte chunk
   constexpr int kChunksPerRow = kBlk / kChunkElems;    // 16 (2-byte types) or 32 (fp32)
@@ -60,7 +79,6 @@ fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char*
   constexpr int kPasses = kBlk / kRowsPerPass;
   const uint32_t tid = threadIdx.x;
   if (tid == 0) {
-    give_up = 0;
     for (int s = 0; s < 2; ++s)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(q_smem_addr(&bars[s])), "r"(1) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -80,50 +98,48 @@ fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char*
   };
 
   uint32_t it = 0;
-  if (tid == 0 && blockIdx.x < n_blocks) issue(blockIdx.x, 0);
+  uint32_t issued = 0;  // thread 0: loads issued so far (block numbers blockIdx.x + k * gridDim.x)
+  if (tid == 0)
+    for (; issued < 2 && blockIdx.x + static_cast<uint64_t>(issued) * gridDim.x < n_blocks; ++issued)
+      issue(blockIdx.x + issued * gridDim.x, issued);
+  bool gave_up = false;
   for (uint32_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x, ++it) {
     const uint32_t stage = it & 1, parity = (it >> 1) & 1;
-    const uint32_t next = blk + gridDim.x;
-    if (tid == 0) {
-      if (next < n_blocks) issue(next, stage ^ 1);  // the other stage was released by the barrier ending the last iteration
-      const uint32_t bar = q_smem_addr(&bars[stage]);
-      uint32_t done = 0;
-      for (uint32_t spin = 0; !done; ++spin) {
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done)
-                     : "r"(bar), "r"(parity)
-                     : "memory");
-        if (!done && spin > (1u << 24)) {  // far beyond any real latency: report and stop
-          if (status && atomicCAS(status, 0, 2) == 0) status[1] = static_cast<int32_t>(blk);
-          give_up = 1;
-          break;
-        }
-      }
-    }
-    __syncthreads();
-    if (give_up) break;
+    // every thread observes the completed phase itself, which orders the staged bytes before its reads
+    const bool arrived = q_wait(q_smem_addr(&bars[stage]), parity);
+    if (!arrived && status && atomicCAS(status, 0, 2) == 0) status[1] = static_cast<int32_t>(blk);
     const unsigned char* stage_ptr = stage_mem + stage * kStage;
     const uint32_t chunk = tid % kChunksPerRow, row_in_pass = tid / kChunksPerRow;
-    // pass 1: amax as ordered magnitude bits (NaN sorts above infinity)
+    // the block's values, and their maximum as ordered magnitude bits (NaN sorts above infinity)
+    uint4 raw[kPasses];
     uint32_t m = 0;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
       const uint32_t r = p * kRowsPerPass + row_in_pass;
-      const uint4 raw = *reinterpret_cast<const uint4*>(stage_ptr + (r * kChunksPerRow + chunk) * 16);
+      raw[p] = arrived ? *reinterpret_cast<const uint4*>(stage_ptr + (r * kChunksPerRow + chunk) * 16) : make_uint4(0, 0, 0, 0);
       if constexpr (sizeof(T) == 2) {
-        m = amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(m, raw.x), raw.y), raw.z), raw.w);
+        m = amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(m, raw[p].x), raw[p].y), raw[p].z), raw[p].w);
       } else {
-        m = max(max(m, raw.x & 0x7FFFFFFFu), max(raw.y & 0x7FFFFFFFu, max(raw.z & 0x7FFFFFFFu, raw.w & 0x7FFFFFFFu)));
+        m = max(max(m, raw[p].x & 0x7FFFFFFFu), max(raw[p].y & 0x7FFFFFFFu, max(raw[p].z & 0x7FFFFFFFu, raw[p].w & 0x7FFFFFFFu)));
       }
     }
     if constexpr (sizeof(T) == 2) m = max(m & 0xFFFFu, m >> 16);
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((tid & 31) == 0) red[it & 1][tid >> 5] = m;
+    if (__syncthreads_or(arrived ? 0 : 1)) {  // the same verdict for every thread
+      gave_up = true;
+      break;
+    }
+    if (tid == 0) {
+      const uint64_t after_next = blk + 2ull * gridDim.x;
+      if (after_next < n_blocks) {
+        issue(static_cast<uint32_t>(after_next), stage);  // everyone holds this stage's values in registers
+        ++issued;
+      }
+    }
+    uint32_t all = red[it & 1][0];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, off));
-    if ((tid & 31) == 0) red[tid >> 5] = m;
-    __syncthreads();
-    uint32_t all = red[0];
-#pragma unroll
-    for (int w = 1; w < kQThreads / 32; ++w) all = max(all, red[w]);
+    for (int w = 1; w < kQThreads / 32; ++w) all = max(all, red[it & 1][w]);
     float amax;
     if constexpr (std::is_same<T, __nv_bfloat16>::value) amax = __uint_as_float(all << 16);
     else if constexpr (std::is_same<T, __half>::value) amax = __half2float(__ushort_as_half(static_cast<unsigned short>(all)));
@@ -131,17 +147,15 @@ fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char*
     const QuantScale qs = make_quant_scale(amax, ue8m0 != 0);
     const uint32_t brow = blk / blocks_n, bcol = blk % blocks_n;
     if (tid == 0) scales[static_cast<int64_t>(brow) * scale_stride + bcol] = qs.s;
-    // pass 2: re-read the stage, quantise, store
     const uint32_t col0 = bcol * kBlk + chunk * kChunkElems;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
       const uint32_t r = brow * kBlk + p * kRowsPerPass + row_in_pass;
       if (r >= rows || col0 >= cols) continue;
-      const uint4 raw = *reinterpret_cast<const uint4*>(stage_ptr + ((p * kRowsPerPass + row_in_pass) * kChunksPerRow + chunk) * 16);
       unsigned char* o = q + static_cast<int64_t>(r) * q_stride + col0;
       const bool whole = col0 + kChunkElems <= cols;
       if constexpr (sizeof(T) == 2) {
-        const uint2 out = quant_chunk16<std::is_same<T, __nv_bfloat16>::value>(raw, qs);
+        const uint2 out = quant_chunk16<std::is_same<T, __nv_bfloat16>::value>(raw[p], qs);
         if (whole && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
           *reinterpret_cast<uint2*>(o) = out;
         } else {
@@ -150,8 +164,8 @@ fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char*
             if (col0 + j < cols) o[j] = b[j];
         }
       } else {
-        const uint32_t out = quant_pair(__uint_as_float(raw.x), __uint_as_float(raw.y), qs) |
-                             (quant_pair(__uint_as_float(raw.z), __uint_as_float(raw.w), qs) << 16);
+        const uint32_t out = quant_pair(__uint_as_float(raw[p].x), __uint_as_float(raw[p].y), qs) |
+                             (quant_pair(__uint_as_float(raw[p].z), __uint_as_float(raw[p].w), qs) << 16);
         if (whole && (reinterpret_cast<uintptr_t>(o) & 3) == 0) {
           *reinterpret_cast<uint32_t*>(o) = out;
         } else {
@@ -160,7 +174,12 @@ fp8_block_quant_kernel(const __grid_constant__ CUtensorMap x_map, unsigned char*
         }
       }
     }
-    __syncthreads();  // stage and `red` may be reused
+  }
+  if (gave_up && tid == 0) {
+    // loads that were issued but not consumed may still be writing into this
+    // CTA's shared memory: one more bounded wait for each, oldest first
+    for (uint32_t k = it; k < issued; ++k)
+      if (!q_wait(q_smem_addr(&bars[k & 1]), (k >> 1) & 1)) break;
   }
 }
 
@@ -200,6 +219,12 @@ __global__ void __launch_bounds__(256) fp8_block_dequant_kernel(const unsigned c
         if (c0 + j < cols) dst[j] = vals[j];
     }
   }
+}
+
+// scale[i] = the scale the quantisation kernels derive from a block maximum amax[i].
+__global__ void fp8_scale_table_kernel(const float* __restrict__ amax, float* __restrict__ scale, uint32_t n, int ue8m0) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) scale[i] = make_quant_scale(amax[i], ue8m0 != 0).s;
 }
 
 }  // namespace awex
@@ -242,14 +267,17 @@ int launch_quant(const void* x, void* q, void* scales, uint64_t rows, uint64_t c
   const uint32_t n_blocks = blocks_m * blocks_n;
   if (n_blocks == 0) return cudaSuccess;
   const int smem = 2 * awex::kBlk * awex::kBlk * sizeof(T);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(awex::fp8_block_quant_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
   int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  // the shared-memory attribute belongs to a (function, device) pair: one process may drive several GPUs
+  static std::atomic<uint64_t> configured{0};
+  const uint64_t bit = dev < 64 ? (uint64_t{1} << dev) : 0;
+  if (!(configured.load(std::memory_order_acquire) & bit) || bit == 0) {
+    e = cudaFuncSetAttribute(awex::fp8_block_quant_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured.fetch_or(bit, std::memory_order_release);
+  }
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int per_sm = sizeof(T) == 4 ? 1 : 3;  // 64 KiB (2-byte types) or 128 KiB (fp32) of stages per CTA
   uint32_t grid = static_cast<uint32_t>(sms * per_sm);
@@ -311,6 +339,14 @@ int awex_launch_fp8_block_quant(const void* x, void* q, void* scales, uint64_t r
     case 3: return launch_quant<float>(x, q, scales, rows, cols, x_stride, q_stride, scale_stride, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, ue8m0, status, s);
     default: return -3;
   }
+}
+
+// The scale rule alone, for exhaustive checks of its rounding: scale[i] from amax[i].
+int awex_launch_fp8_scale_table(const void* amax, void* scale, uint32_t n, int ue8m0, void* stream) {
+  if (n == 0) return cudaSuccess;
+  awex::fp8_scale_table_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(amax), static_cast<float*>(scale), n, ue8m0);
+  return cudaGetLastError();
 }
 
 int awex_launch_fp8_block_dequant(const void* q, const void* scales, void* out, uint64_t rows, uint64_t cols, int64_t q_stride,

@@ -29,9 +29,14 @@ struct QuantScale {
 __device__ __forceinline__ QuantScale make_quant_scale(float amax, bool ue8m0) {
   float s = (amax < 1e-4f ? 1e-4f : amax) / 448.0f;  // NaN stays NaN
   if (ue8m0) {
-    // round up to a power of two as fp32 log2 -> ceil -> exp2 does
-    float c = s < 1e-10f ? 1e-10f : s;
-    s = exp2f(ceilf(static_cast<float>(log2(static_cast<double>(c)))));
+    // Round up to a power of two: the value of fp32 log2 -> ceil -> exp2, which is
+    // exact for every scale a 16-bit amax can produce.  Done on the bits (a
+    // non-zero mantissa bumps the exponent; an exponent that overflows is
+    // infinity, as exp2(128) is), so no rounding of a logarithm is involved.
+    const float c = s < 1e-10f ? 1e-10f : s;  // NaN stays NaN
+    uint32_t b = __float_as_uint(c);
+    if (c == c && (b & 0x007FFFFFu)) b = (b & 0x7F800000u) + 0x00800000u;
+    s = __uint_as_float(b);
   }
   const float r = __frcp_rn(s);
   QuantScale q;

@@ -25,6 +25,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 
 #include "fp8_math.cuh"
@@ -170,8 +171,13 @@ __device__ __forceinline__ void cursor_advance_to(Cursor& c, const XferParams& p
 }
 
 // ---------------------------------------------------------------- tile bodies
+// Every body that all warps take part in contains exactly one CTA-wide barrier,
+// placed after the thread's last read of the staged tile.  The barrier also
+// carries the abort vote (`__syncthreads_or`): a thread whose bounded wait ran
+// out votes to stop, and every thread leaves the tile loop at the same point.
+
 // Elementwise path straight from global memory (unaligned slabs, rare dtypes).
-__device__ void tile_elementwise_global(const XferDesc& d, const Tile& t) {
+__device__ bool tile_elementwise_global(const XferDesc& d, const Tile& t, uint32_t my_abort) {
   const uint32_t ses = dtype_size(d.src_dtype), des = dtype_size(d.dst_dtype);
   const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src);
   unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
@@ -184,69 +190,164 @@ __device__ void tile_elementwise_global(const XferDesc& d, const Tile& t) {
     if (d.op == OP_COPY) *o = *s;
     else store_from_float(o, d.dst_dtype, load_as_float(s, d.src_dtype) + addend);
   }
+  return __syncthreads_or(static_cast<int>(my_abort)) != 0;
 }
 
-// Elementwise path from a staged tile.
-__device__ void tile_elementwise_staged(const XferDesc& d, const Tile& t, const unsigned char* stage) {
-  const uint32_t ses = dtype_size(d.src_dtype), des = dtype_size(d.dst_dtype);
-  const uint32_t pitch = stage_pitch(d);
-  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
-  const uint32_t n = t.rows * t.cols;
-  const float addend = d.op == OP_ADD ? static_cast<float>(d.aux_f) : 0.f;
-  for (uint32_t e = threadIdx.x; e < n; e += blockDim.x) {
-    uint32_t r = e / t.cols, c = e % t.cols;
-    float v = load_as_float(stage + r * pitch + c * ses, d.src_dtype) + addend;
-    store_from_float(dst + (t.row0 + r) * d.dst_stride + (t.col0 + c) * des, d.dst_dtype, v);
+// 16 staged bytes -> floats.  kSrc is an XferDtype with 2- or 4-byte elements.
+template <uint32_t kSrc>
+__device__ __forceinline__ void chunk_to_floats(const uint4& raw, float* v) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  if constexpr (kSrc == DT_F32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(w[i]);
+  } else if constexpr (kSrc == DT_BF16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
   }
 }
 
-// ---- block fp8 tiles -------------------------------------------------------------------------
-// A tile is one 128x128 (or smaller edge) block.  Work is cut into items of one
-// row x 8 columns; two passes over the source: amax, then quantise and store.
-// Nothing is kept in registers between the passes, so the kernel's register
-// budget stays small and all warps of the CTA take part.
-
-// CTA-wide maximum of ordered magnitude bits (see fp8_math.cuh).
-__device__ __forceinline__ uint32_t cta_max_u32(uint32_t m, uint32_t* red) {
+// kN floats -> destination elements at `o` (aligned to kN * element size, at most 32 bytes).
+template <uint32_t kDst, int kN>
+__device__ __forceinline__ void floats_to_dst(const float* v, unsigned char* o) {
+  if constexpr (kDst == DT_F32) {
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, off));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
-  __syncthreads();
-  uint32_t all = 0;
-  for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) all = max(all, red[w]);
-  __syncthreads();  // `red` may be rewritten by the next tile
-  return all;
+    for (int i = 0; i < kN; i += 4) *reinterpret_cast<float4*>(o + 4 * i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+  } else {
+    uint32_t packed[kN / 2];
+#pragma unroll
+    for (int i = 0; i < kN / 2; ++i) {
+      if constexpr (kDst == DT_BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    if constexpr (kN == 8) *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    else *reinterpret_cast<uint2*>(o) = make_uint2(packed[0], packed[1]);
+  }
 }
+
+// Cast / add of a staged tile, one 16-byte chunk of the source per thread and
+// step: vector load from shared memory, packed converts, 16-byte stores.  Rows
+// and chunks advance incrementally; nothing is divided per element.
+template <uint32_t kSrc, uint32_t kDst>
+__device__ __forceinline__ void cast_chunks(const XferDesc& d, const Tile& t, const unsigned char* stage, float addend) {
+  constexpr uint32_t kSes = kSrc == DT_F32 ? 4u : 2u, kDes = kDst == DT_F32 ? 4u : 2u;
+  constexpr int kN = 16 / kSes;                    // elements per chunk
+  const uint32_t pitch = stage_pitch(d);
+  const uint32_t cpr = (t.cols * kSes) >> 4;       // chunks per row (the bulk path keeps rows a multiple of 16 bytes)
+  const uint32_t total = t.rows * cpr;
+  const uint32_t step_rows = blockDim.x / cpr, step_chunks = blockDim.x % cpr;
+  uint32_t row = threadIdx.x / cpr, chunk = threadIdx.x % cpr;
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0 * kDes;
+  for (uint32_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + row * pitch + chunk * 16u);
+    float v[kN];
+    chunk_to_floats<kSrc>(raw, v);
+#pragma unroll
+    for (int i = 0; i < kN; ++i) v[i] += addend;
+    floats_to_dst<kDst, kN>(v, dst + static_cast<int64_t>(row) * d.dst_stride + chunk * (kN * kDes));
+    row += step_rows;
+    chunk += step_chunks;
+    if (chunk >= cpr) {
+      chunk -= cpr;
+      ++row;
+    }
+  }
+}
+
+template <uint32_t kSrc>
+__device__ __forceinline__ bool cast_chunks_from(const XferDesc& d, const Tile& t, const unsigned char* stage, float addend) {
+  switch (d.dst_dtype) {
+    case DT_F32: cast_chunks<kSrc, DT_F32>(d, t, stage, addend); return true;
+    case DT_BF16: cast_chunks<kSrc, DT_BF16>(d, t, stage, addend); return true;
+    case DT_F16: cast_chunks<kSrc, DT_F16>(d, t, stage, addend); return true;
+    default: return false;
+  }
+}
+
+// Elementwise path from a staged tile.  Returns the CTA's abort vote.
+__device__ bool tile_elementwise_staged(const XferDesc& d, const Tile& t, const unsigned char* stage, uint32_t my_abort) {
+  if (!my_abort) {
+    const float addend = d.op == OP_ADD ? static_cast<float>(d.aux_f) : 0.f;
+    bool done = false;
+    if (d.flags & FLAG_DST_VEC16) {
+      if (d.src_dtype == DT_BF16) done = cast_chunks_from<DT_BF16>(d, t, stage, addend);
+      else if (d.src_dtype == DT_F16) done = cast_chunks_from<DT_F16>(d, t, stage, addend);
+      else if (d.src_dtype == DT_F32) done = cast_chunks_from<DT_F32>(d, t, stage, addend);
+    }
+    if (!done) {  // one-byte types or a destination that is not 16-byte aligned: element by element
+      const uint32_t ses = dtype_size(d.src_dtype), des = dtype_size(d.dst_dtype);
+      const uint32_t pitch = stage_pitch(d);
+      unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
+      const uint32_t n = t.rows * t.cols;
+      for (uint32_t e = threadIdx.x; e < n; e += blockDim.x) {
+        uint32_t r = e / t.cols, c = e % t.cols;
+        float v = load_as_float(stage + r * pitch + c * ses, d.src_dtype) + addend;
+        store_from_float(dst + (t.row0 + r) * d.dst_stride + (t.col0 + c) * des, d.dst_dtype, v);
+      }
+    }
+  }
+  return __syncthreads_or(static_cast<int>(my_abort)) != 0;
+}
+
+// ---- block fp8 tiles -------------------------------------------------------------------------
+// A tile is one 128x128 (or smaller edge) block.
 
 __device__ __forceinline__ void store_scale(const XferDesc& d, const Tile& t, float scale) {
   if (threadIdx.x == 0) reinterpret_cast<float*>(d.aux_ptr)[static_cast<int64_t>(t.band) * d.aux_stride + t.ct] = scale;
 }
 
 // Fast form: 2-byte source staged in shared memory with a 256-byte pitch
-// (tile_cols == 128), destination rows 8-byte aligned.
-template <bool kBf16>
-__device__ void tile_fp8_staged(const XferDesc& d, const Tile& t, const unsigned char* stage, uint32_t* red) {
-  const uint32_t chunks = t.cols >> 3;  // the bulk path guarantees cols % 8 == 0
-  const uint32_t items = t.rows * 16u;
+// (tile_cols == 128), destination rows 8-byte aligned.  One pass over the stage:
+// a thread keeps its 16-byte chunks in registers from the maximum search, the
+// CTA agrees on the block maximum with one barrier (`red` is double-buffered by
+// the caller, so no second barrier protects it), and the values are quantised
+// from the registers.  After the barrier nobody reads the stage any more.
+template <int kT, bool kBf16>
+__device__ __forceinline__ bool tile_fp8_staged(const XferDesc& d, const Tile& t, const unsigned char* stage, uint32_t* red,
+                                                uint32_t my_abort) {
+  constexpr int kPasses = (kFp8Block * kFp8Block * 2 / 16) / kT;  // chunks per thread: 8 (256 threads) or 4 (512)
+  constexpr uint32_t kRowStep = kT / 16;
+  const uint32_t chunk = threadIdx.x & 15u, row0 = threadIdx.x >> 4;
+  const bool col_ok = chunk < (t.cols >> 3) && !my_abort;  // the bulk path guarantees cols % 8 == 0
+  uint4 raw[kPasses];
   uint32_t m = 0;
-  for (uint32_t it = threadIdx.x; it < items; it += blockDim.x) {
-    const uint32_t row = it >> 4, chunk = it & 15u;
-    if (chunk >= chunks) continue;
-    const uint4 raw = *reinterpret_cast<const uint4*>(stage + row * 256u + chunk * 16u);
-    m = amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(m, raw.x), raw.y), raw.z), raw.w);
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const uint32_t row = row0 + p * kRowStep;
+    raw[p] = (col_ok && row < t.rows) ? *reinterpret_cast<const uint4*>(stage + row * 256u + chunk * 16u) : make_uint4(0, 0, 0, 0);
+    m = amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(m, raw[p].x), raw[p].y), raw[p].z), raw[p].w);
   }
-  m = cta_max_u32(max(m & 0xFFFFu, m >> 16), red);
-  const float amax = kBf16 ? __uint_as_float(m << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(m)));
+  m = __reduce_max_sync(0xffffffffu, max(m & 0xFFFFu, m >> 16));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  if (__syncthreads_or(static_cast<int>(my_abort))) return true;
+  uint32_t all = red[0];
+#pragma unroll
+  for (int w = 1; w < kT / 32; ++w) all = max(all, red[w]);
+  const float amax = kBf16 ? __uint_as_float(all << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(all)));
   const QuantScale q = make_quant_scale(amax, (d.flags & FLAG_UE8M0) != 0);
   store_scale(d, t, q.s);
-  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0 + chunk * 8u;
   const bool vec = (d.flags & FLAG_DST_VEC16) != 0;
-  for (uint32_t it = threadIdx.x; it < items; it += blockDim.x) {
-    const uint32_t row = it >> 4, chunk = it & 15u;
-    if (chunk >= chunks) continue;
-    const uint4 raw = *reinterpret_cast<const uint4*>(stage + row * 256u + chunk * 16u);
-    const uint2 out = quant_chunk16<kBf16>(raw, q);
-    unsigned char* o = dst + static_cast<int64_t>(row) * d.dst_stride + chunk * 8u;
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const uint32_t row = row0 + p * kRowStep;
+    if (!col_ok || row >= t.rows) continue;
+    const uint2 out = quant_chunk16<kBf16>(raw[p], q);
+    unsigned char* o = dst + static_cast<int64_t>(row) * d.dst_stride;
     if (vec) {
       *reinterpret_cast<uint2*>(o) = out;
     } else {
@@ -254,11 +355,13 @@ __device__ void tile_fp8_staged(const XferDesc& d, const Tile& t, const unsigned
       for (int j = 0; j < 8; ++j) o[j] = b[j];
     }
   }
+  return false;
 }
 
 // General form: any source dtype and alignment, rows read from global memory
-// (directly or through the row table), columns masked at the edge.
-__device__ void tile_fp8_generic(const XferDesc& d, const Tile& t, uint32_t* red) {
+// (directly or through the row table), columns masked at the edge.  Two passes
+// over global memory (the second one mostly hits L2).
+__device__ bool tile_fp8_generic(const XferDesc& d, const Tile& t, uint32_t* red, uint32_t my_abort) {
   const uint32_t ses = dtype_size(d.src_dtype);
   const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src) + t.col0 * ses;
   const uint32_t chunks = (t.cols + 7u) >> 3;
@@ -269,8 +372,12 @@ __device__ void tile_fp8_generic(const XferDesc& d, const Tile& t, uint32_t* red
     const unsigned char* s = src + src_row_offset(d, t.row0 + row) + c0 * ses;
     for (uint32_t j = 0; j < 8u && c0 + j < t.cols; ++j) m = amax_bits_f32(m, load_as_float(s + j * ses, d.src_dtype));
   }
-  m = cta_max_u32(m, red);
-  const QuantScale q = make_quant_scale(__uint_as_float(m), (d.flags & FLAG_UE8M0) != 0);
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  if (__syncthreads_or(static_cast<int>(my_abort))) return true;
+  uint32_t all = 0;
+  for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) all = max(all, red[w]);
+  const QuantScale q = make_quant_scale(__uint_as_float(all), (d.flags & FLAG_UE8M0) != 0);
   store_scale(d, t, q.s);
   unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
   for (uint32_t it = threadIdx.x; it < items; it += blockDim.x) {
@@ -286,83 +393,100 @@ __device__ void tile_fp8_generic(const XferDesc& d, const Tile& t, uint32_t* red
       if (pair) o[j + 1] = static_cast<unsigned char>(out >> 8);
     }
   }
+  return false;
 }
 
 // ---------------------------------------------------------------- the kernel
 __device__ __forceinline__ bool wants_stage(const XferDesc& d) { return (d.flags & FLAG_BULK) != 0; }
 
-template <int kT, int kS, int kL>
+// Bounded wait for a phase of an mbarrier; false when the deadline passed.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t timeout_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (!mbar_try_wait(bar, parity))
+    if (globaltimer_ns() - t0 > timeout_ns) return false;
+  return true;
+}
+
+// Ring of kS stages.  Warp 0 is the copy engine's driver: it issues every load
+// and, for pure copies, the stores; all warps work on computed tiles.  The stage
+// of a computed tile is free once its barrier has been passed, the stage of a
+// copied tile once its store group has finished reading shared memory; warp 0
+// keeps as many loads in flight as that rule allows (kS - 1 ahead of a computed
+// tile, kS - 2 ahead of a copied one).
+template <int kT, int kS>
 __device__ __forceinline__ void transfer_body(const XferParams& p) {
-  // the stage that tile i + kL loads into was last used by tile i - 2, whose
-  // store group is the one `wait_group.read 1` has retired
-  static_assert(kL == kS - 2, "ring depth and lookahead must keep two store groups apart");
+  static_assert(kS >= 3, "a copied tile's stage is released two tiles later");
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kS];
-  __shared__ uint32_t red[kT / 32];
-  __shared__ volatile int abort_flag;
+  __shared__ uint32_t red[2][kT / 32];
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    abort_flag = 0;
     for (int s = 0; s < kS; ++s) mbar_init(smem_addr(&full_bar[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
   // Wait until every destination has announced this epoch (its engine is paused
-  // and its parameters may be overwritten).
+  // and its parameters may be overwritten).  A CTA that gives up skips its tiles
+  // but still drains and counts itself in below, so that the arrival counter is
+  // back at zero when the launch ends.
+  uint32_t my_abort = 0;
   if (p.n_ready) {
     const uint64_t t0 = globaltimer_ns();
-    for (uint32_t i = threadIdx.x; i < p.n_ready; i += blockDim.x) {
+    for (uint32_t i = threadIdx.x; i < p.n_ready && !my_abort; i += blockDim.x) {
       const uint64_t* flag = p.ready_pad + p.ready_slots[i];
       while (ld_acquire_sys(flag) < p.epoch) {
         if (globaltimer_ns() - t0 > p.timeout_ns) {
           if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_READY_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(p.ready_slots[i]);
-          abort_flag = 1;
+          my_abort = 1;
           break;
         }
         __nanosleep(200);
       }
     }
-    __syncthreads();
-    if (abort_flag) return;  // nothing in flight yet
+    my_abort = __syncthreads_or(static_cast<int>(my_abort)) != 0;
   }
 
-  // Which tiles this CTA owns.  Without a chunk index: one contiguous range.
-  // With one: chunks of 2^chunk_shift tiles dealt round-robin to the CTAs, so
-  // that cheap and expensive tiles (plain copies, quantised blocks, gathered
-  // rows, local and remote destinations) are spread over all of them.
-  const bool chunked = p.chunk_desc != nullptr;
-  const uint32_t cs = p.chunk_shift;
+  // Which tiles this CTA owns: its plan entry, or an even contiguous share.
+  const bool planned = p.cta_plan != nullptr;
+  const uint32_t cs = planned ? p.chunk_shift : 0;
   const uint64_t cmask = (uint64_t{1} << cs) - 1;
-  uint64_t t_begin = 0, n = 0;
-  if (!chunked) {
+  uint64_t t_begin, n = 0;
+  uint32_t g_rank = 0, g_size = 1, chunk_off = 0;
+  if (planned) {
+    const CtaPlan plan = p.cta_plan[blockIdx.x];
+    t_begin = plan.tile_begin;
+    g_rank = plan.rank;
+    g_size = plan.size;
+    chunk_off = plan.chunk_off;
+    const uint64_t range = plan.tile_end - plan.tile_begin;
+    const uint64_t n_chunks = (range + cmask) >> cs;
+    if (g_rank < n_chunks) {
+      const uint64_t mine = (n_chunks - g_rank + g_size - 1) / g_size;
+      n = mine << cs;
+      if (g_rank + (mine - 1) * g_size == n_chunks - 1) n -= (n_chunks << cs) - range;  // the range's last chunk may be short
+    }
+  } else {
     t_begin = p.n_tiles * blockIdx.x / gridDim.x;
     n = p.n_tiles * (blockIdx.x + 1) / gridDim.x - t_begin;
-  } else {
-    const uint64_t n_chunks = (p.n_tiles + cmask) >> cs;
-    if (blockIdx.x < n_chunks) {
-      const uint64_t mine = (n_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x;
-      const uint64_t last_chunk = blockIdx.x + (mine - 1) * gridDim.x;
-      n = mine << cs;
-      if (last_chunk == n_chunks - 1) n -= (n_chunks << cs) - p.n_tiles;  // the table's last chunk may be short
-    }
   }
+  if (my_abort) n = 0;
   // relative tile number of this CTA -> tile number in the table
-  auto tile_at = [&](uint64_t j) -> uint64_t {
-    if (!chunked) return t_begin + j;
-    return ((((j >> cs) * gridDim.x) + blockIdx.x) << cs) + (j & cmask);
-  };
   auto cursor_to = [&](Cursor& c, uint64_t j) -> uint64_t {
-    const uint64_t tile = tile_at(j);
-    if (chunked && (j & cmask) == 0) cursor_jump(c, p, tile >> cs);
+    const uint64_t chunk = (j >> cs) * g_size + g_rank;
+    const uint64_t tile = t_begin + (chunk << cs) + (j & cmask);
+    if (planned && (j & cmask) == 0) cursor_jump(c, p, chunk_off + chunk);
     cursor_advance_to(c, p, tile);
     return tile;
   };
 
+  uint64_t next_load = 0;  // warp 0: tiles [0, next_load) have had their loads issued
+  uint64_t waited = 0;     // warp 0: tiles [0, waited) have been seen complete (or were never staged)
   if (n > 0) {
     Cursor load_cur, use_cur;
-    if (chunked) cursor_jump(load_cur, p, blockIdx.x);
+    if (planned) cursor_jump(load_cur, p, chunk_off + g_rank);
     else cursor_seek(load_cur, p, t_begin);
     use_cur = load_cur;
 
@@ -401,10 +525,9 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
       for (uint32_t r = lane; r < t.rows; r += 32) bulk_load(base + r * pitch, src + src_row_offset(d, t.row0 + r), bytes, bar);
     };
 
-    if (warp == 0)
-      for (uint64_t j = 0; j < kL && j < n; ++j) issue_load(j);
-
-    for (uint64_t i = 0; i < n && !abort_flag; ++i) {
+    bool prev_copy = false;  // warp 0: was the previous tile a pure copy?
+    uint32_t n_computed = 0; // selects the half of `red` (two consecutive computed tiles never share one)
+    for (uint64_t i = 0; i < n; ++i) {
       const uint64_t tile_no = cursor_to(use_cur, i);
       const XferDesc d = p.descs[use_cur.di];
       const Tile t = tile_of(d, tile_no - use_cur.begin);
@@ -412,54 +535,81 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
       const uint32_t parity = static_cast<uint32_t>((i / kS) & 1);
       const uint32_t bar = smem_addr(&full_bar[stage]);
       unsigned char* stage_ptr = smem + static_cast<size_t>(stage) * kStageBytes;
+      const bool staged = wants_stage(d);
+      const bool is_copy = d.op == OP_COPY && staged;
 
-      if (warp == 0) {
-        // The stage that tile i+lookahead will use was last read by the stores of
-        // tile i-2: allow only the most recent store group to be still reading.
+      if (warp == 0 && !my_abort) {
+        // Of the store groups committed so far (one per tile) only the most recent
+        // may still be reading shared memory: every stage before tile i - 1 is
+        // free, and the one of tile i - 1 too unless that tile was a pure copy.
         bulk_wait_read_1();
         __syncwarp();
-        if (i + kL < n) issue_load(i + kL);
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(bar, parity)) {
-          if (globaltimer_ns() - t0 > p.timeout_ns) {
-            if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
-            abort_flag = 1;
-            break;
-          }
-        }
+        const uint64_t limit = i + kS - (prev_copy ? 1 : 0);
+        while (next_load < limit && next_load < n) issue_load(next_load++);
       }
+      prev_copy = is_copy;
 
-      const bool staged = wants_stage(d);
-      if (d.op == OP_COPY && staged) {
-        if (warp == 0 && !abort_flag) {
-          const uint32_t pitch = stage_pitch(d);
-          const uint32_t bytes = t.cols;  // OP_COPY counts bytes
-          unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
-          const uint32_t base = smem_addr(stage_ptr);
-          for (uint32_t r = lane; r < t.rows; r += 32) bulk_store(dst + static_cast<int64_t>(r) * d.dst_stride, base + r * pitch, bytes);
-          bulk_commit();
+      if (is_copy) {
+        if (warp == 0 && !my_abort) {
+          const bool arrived = mbar_wait_bounded(bar, parity, p.timeout_ns);
+          if (__any_sync(0xffffffffu, !arrived)) {
+            if (lane == 0 && atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
+            my_abort = 1;  // warp 0 stops moving data; it keeps meeting the other warps at their barriers
+          } else {
+            waited = i + 1;
+            const uint32_t pitch = stage_pitch(d);
+            const uint32_t bytes = t.cols;  // OP_COPY counts bytes
+            unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
+            const uint32_t base = smem_addr(stage_ptr);
+            for (uint32_t r = lane; r < t.rows; r += 32) bulk_store(dst + static_cast<int64_t>(r) * d.dst_stride, base + r * pitch, bytes);
+            bulk_commit();
+          }
         }
         continue;  // other warps have nothing to do for pure copies
       }
-      if (warp == 0) bulk_commit();  // an empty group keeps "one group per tile"
+      if (warp == 0 && !my_abort) bulk_commit();  // an empty group keeps "one group per tile"
 
-      __syncthreads();  // staged data (observed by warp 0) is ordered before everyone's reads
-      if (abort_flag) break;
-      if (d.op == OP_FP8_BLOCK) {
-        if (staged && d.src_dtype == DT_BF16) tile_fp8_staged<true>(d, t, stage_ptr, red);
-        else if (staged && d.src_dtype == DT_F16) tile_fp8_staged<false>(d, t, stage_ptr, red);
-        else tile_fp8_generic(d, t, red);
-      } else if (staged) {
-        tile_elementwise_staged(d, t, stage_ptr);
-      } else {
-        tile_elementwise_global(d, t);
+      if (staged && !my_abort) {
+        // every thread observes the completed phase itself, which orders the
+        // staged bytes before its reads
+        if (!mbar_wait_bounded(bar, parity, p.timeout_ns)) {
+          if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
+          my_abort = 1;
+        } else if (warp == 0) {
+          waited = i + 1;
+        }
+      } else if (!staged && warp == 0 && !my_abort) {
+        waited = i + 1;
       }
-      __syncthreads();  // all reads of the stage are done before it is refilled
+      uint32_t* red_now = red[n_computed & 1];
+      ++n_computed;
+      bool stop;
+      if (d.op == OP_FP8_BLOCK) {
+        if (staged && d.src_dtype == DT_BF16) stop = tile_fp8_staged<kT, true>(d, t, stage_ptr, red_now, my_abort);
+        else if (staged) stop = tile_fp8_staged<kT, false>(d, t, stage_ptr, red_now, my_abort);
+        else stop = tile_fp8_generic(d, t, red_now, my_abort);
+      } else if (staged) {
+        stop = tile_elementwise_staged(d, t, stage_ptr, my_abort);
+      } else {
+        stop = tile_elementwise_global(d, t, my_abort);
+      }
+      if (stop) {  // the same for every thread of the CTA
+        my_abort = 1;
+        break;
+      }
     }
   }
 
-  // Drain: make this CTA's writes visible system-wide, then count it in.
+  // Drain: nothing of this CTA may still be in flight when it returns, and its
+  // writes must be visible system-wide before it counts itself in.
   if (warp == 0) {
+    if (my_abort && lane == 0) {
+      // loads that were issued but never consumed still write into this CTA's
+      // shared memory: give them one more deadline, in issue order
+      for (uint64_t j = waited; j < next_load; ++j)
+        if (!mbar_wait_bounded(smem_addr(&full_bar[j % kS]), static_cast<uint32_t>((j / kS) & 1), p.timeout_ns)) break;
+    }
+    __syncwarp();
     bulk_wait_all();
     fence_proxy_async();
   }
@@ -482,18 +632,18 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
 // One CTA of 512 threads per SM with a 6-stage ring: the variant for tables of
 // plain copies, where one warp moves the data and depth matters.
 __global__ void __launch_bounds__(kThreads, 1) fused_transfer_kernel(const __grid_constant__ XferParams p) {
-  transfer_body<kThreads, kStages, kLookahead>(p);
+  transfer_body<kThreads, kStages>(p);
 }
 
 // Two CTAs of 256 threads per SM with a 3-stage ring each: the variant for
 // tables dominated by tiles that every warp works on (block quantisation,
-// casts).  A tile's barriers and reductions are exposed latency inside one CTA;
-// a second resident CTA fills those gaps with another tile.
+// casts) and for strided copies of short runs.  What one CTA cannot overlap
+// (a tile's barrier, the maximum search before the first store, the issue of
+// many small row copies) a second resident CTA fills with another tile.
 constexpr int kThreadsX2 = 256;
 constexpr int kStagesX2 = 3;
-constexpr int kLookaheadX2 = 1;
 __global__ void __launch_bounds__(kThreadsX2, 2) fused_transfer_kernel_x2(const __grid_constant__ XferParams p) {
-  transfer_body<kThreadsX2, kStagesX2, kLookaheadX2>(p);
+  transfer_body<kThreadsX2, kStagesX2>(p);
 }
 
 // Receiver side: wait (bounded) until every listed sender has raised `epoch`.
@@ -533,28 +683,33 @@ int awex_xfer_stage_bytes() { return awex::kStageBytes; }
 
 // Returns a cudaError_t.  `variant` 0: one CTA of 512 threads per SM; 1: two
 // CTAs of 256 threads per SM.  `grid` == 0 fills the device for the variant.
+// With `cta_plan` (one CtaPlan per CTA, plus `chunk_desc`) `grid` is the number
+// of plan entries and is used as given.
 int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_tiles, uint64_t epoch, uint64_t timeout_ns,
                                const void* ready_pad, const void* ready_slots, uint32_t n_ready, const void* done_flags,
                                uint32_t n_done, void* cta_counter, void* status, int grid, void* stream,
-                               const void* chunk_desc, uint32_t chunk_shift, uint32_t variant) {
-  static int configured_device[2] = {-1, -1};
+                               const void* chunk_desc, uint32_t chunk_shift, uint32_t variant, const void* cta_plan) {
+  // the shared-memory attribute is set once per (variant, device)
+  static std::atomic<uint64_t> configured[2];
   if (variant > 1) return cudaErrorInvalidValue;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   const int smem = (variant ? awex::kStagesX2 : awex::kStages) * awex::kStageBytes;
-  if (configured_device[variant] != dev) {
+  const uint64_t bit = (dev >= 0 && dev < 64) ? (uint64_t{1} << dev) : 0;
+  if (bit == 0 || !(configured[variant].load(std::memory_order_acquire) & bit)) {
     err = variant ? cudaFuncSetAttribute(awex::fused_transfer_kernel_x2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
                   : cudaFuncSetAttribute(awex::fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
-    configured_device[variant] = dev;
+    configured[variant].fetch_or(bit, std::memory_order_release);
   }
+  if (cta_plan != nullptr && (chunk_desc == nullptr || grid <= 0)) return cudaErrorInvalidValue;
   if (grid <= 0) {
     err = cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
     if (variant) grid *= 2;
   }
-  if (n_tiles > 0 && static_cast<uint64_t>(grid) > n_tiles) grid = static_cast<int>(n_tiles);
+  if (cta_plan == nullptr && n_tiles > 0 && static_cast<uint64_t>(grid) > n_tiles) grid = static_cast<int>(n_tiles);
   if (grid < 1) grid = 1;
   awex::XferParams p;
   p.descs = static_cast<const awex::XferDesc*>(descs);
@@ -569,8 +724,9 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
   p.n_done = n_done;
   p.cta_counter = static_cast<unsigned int*>(cta_counter);
   p.status = static_cast<int32_t*>(status);
+  p.cta_plan = static_cast<const awex::CtaPlan*>(cta_plan);
   p.chunk_desc = static_cast<const uint32_t*>(chunk_desc);
-  p.chunk_shift = chunk_desc ? chunk_shift : 0;
+  p.chunk_shift = cta_plan ? chunk_shift : 0;
   if (variant)
     awex::fused_transfer_kernel_x2<<<grid, awex::kThreadsX2, smem, static_cast<cudaStream_t>(stream)>>>(p);
   else
@@ -621,6 +777,58 @@ static int no_alloc_fail(cudaError_t code, char* err, size_t cap, const char* wh
   return static_cast<int>(code);
 }
 
+// Structure of a caller-built table, checked on the host before anything is
+// queued: every rule here is one whose violation would make the kernel compute a
+// tile outside its slab, overrun a pipeline stage or break a bulk copy's
+// alignment.  Returns nullptr or what is wrong; `bad` gets the descriptor index.
+static const char* no_alloc_check_structure(const XferDesc* t, uint32_t n_desc, uint64_t n_tiles, uint32_t* bad) {
+  uint64_t expect = 0;
+  for (uint32_t i = 0; i < n_desc; ++i) {
+    const XferDesc& d = t[i];
+    *bad = i;
+    if (d.op > OP_FP8_BLOCK || d.src_dtype > DT_FP8_E4M3 || d.dst_dtype > DT_FP8_E4M3) return "unknown op or dtype";
+    if (d.rows == 0 || d.row_elems == 0) return "empty slab";
+    if (d.tile_rows == 0 || d.tile_cols == 0 || d.col_tiles == 0) return "tile_rows, tile_cols and col_tiles must be non-zero";
+    if (d.col_tiles != (d.row_elems + d.tile_cols - 1) / d.tile_cols) return "col_tiles does not match row_elems / tile_cols";
+    if (d.tile_begin != expect) return i == 0 ? "tile_begin of the first descriptor must be 0" : "tile_begin must continue the running tile count";
+    expect += static_cast<uint64_t>(d.col_tiles) * ((d.rows + d.tile_rows - 1) / d.tile_rows);
+    if (d.src == 0 || d.dst == 0) return "null source or destination";
+    const uint32_t ses = d.src_dtype == DT_F32 ? 4u : (d.src_dtype == DT_BF16 || d.src_dtype == DT_F16) ? 2u : 1u;
+    if (d.op == OP_COPY && (d.src_dtype != DT_BYTES || d.dst_dtype != DT_BYTES)) return "copies count bytes (dtype 0 on both sides)";
+    if (d.op != OP_COPY && (d.src_dtype == DT_BYTES || d.dst_dtype == DT_BYTES)) return "a computed slab needs element dtypes";
+    if (d.flags & FLAG_BULK) {
+      const uint64_t pitch = (static_cast<uint64_t>(d.tile_cols) * ses + 15u) & ~uint64_t{15};
+      if ((d.src & 15u) || ((d.row_elems * ses) & 15u) || ((static_cast<uint64_t>(d.tile_cols) * ses) & 15u) ||
+          (d.rows > 1 && d.row_table == 0 && (d.src_stride & 15)))
+        return "bulk source rule (16-byte address, stride and size) violated";
+      if (d.op == OP_COPY && ((d.dst & 15u) || (d.rows > 1 && (d.dst_stride & 15)))) return "bulk destination rule (16-byte address and stride) violated";
+      if (static_cast<uint64_t>(d.tile_rows) * pitch > static_cast<uint64_t>(kStageBytes)) return "a tile exceeds one pipeline stage";
+      if (d.op == OP_FP8_BLOCK && ses != 2u) return "staged block quantisation needs a 2-byte source";
+    } else if (d.tensor_map != 0) {
+      return "a tensor map needs the bulk flag";
+    }
+    if (d.op == OP_FP8_BLOCK) {
+      if (d.tile_rows != kFp8Block || d.tile_cols != kFp8Block) return "fp8 tiles must be 128 x 128";
+      if (d.dst_dtype != DT_FP8_E4M3 || d.aux_ptr == 0 || (d.aux_ptr & 3u)) return "fp8 slab without an e4m3 destination or a float-aligned scale address";
+    }
+  }
+  *bad = n_desc;
+  if (expect != n_tiles) return "n_tiles does not match the table";
+  return nullptr;
+}
+
+// Is `addr` memory a kernel on the current device can touch?  (Asks the driver
+// about the pointer; allocates nothing.)  0 is accepted when `optional`.
+static bool no_alloc_device_pointer(uint64_t addr, bool optional) {
+  if (addr == 0) return optional;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, reinterpret_cast<const void*>(addr)) != cudaSuccess) {
+    cudaGetLastError();  // not a pointer the runtime knows: leave no sticky error behind
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
 }  // namespace awex
 
 extern "C" int awex_fused_transfer_no_alloc(const void* host_descs, uint32_t n_desc, uint64_t n_tiles, uint64_t timeout_ns,
@@ -635,6 +843,16 @@ extern "C" int awex_fused_transfer_no_alloc(const void* host_descs, uint32_t n_d
     return static_cast<int>(cudaErrorInvalidValue);
   }
   if (n_desc > 0 && host_descs == nullptr) return no_alloc_fail(cudaErrorInvalidValue, err, err_cap, "null descriptor table");
+  const XferDesc* table = static_cast<const XferDesc*>(host_descs);
+  if (n_desc > 0 && n_tiles > 0) {
+    // The table is in host memory: prove before anything is queued that the kernel
+    // will stay inside what it describes.
+    uint32_t bad = 0;
+    if (const char* what = no_alloc_check_structure(table, n_desc, n_tiles, &bad)) {
+      if (err != nullptr && err_cap > 0) std::snprintf(err, err_cap, "awex_fused_transfer_no_alloc: descriptor %u: %s", bad, what);
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
+  }
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return no_alloc_fail(e, err, err_cap, "cudaGetDevice");
@@ -653,6 +871,24 @@ extern "C" int awex_fused_transfer_no_alloc(const void* host_descs, uint32_t n_d
       g_no_alloc_ptr[dev] = static_cast<unsigned char*>(ptr);
     }
     scratch = g_no_alloc_ptr[dev];
+  }
+  if (n_desc > 0 && n_tiles > 0) {
+    // Addresses the kernel dereferences must be device memory.  A table straight
+    // from an encoder still holds row-table indices and no tensor-map addresses;
+    // both are only meaningful once they point into device memory.
+    for (uint32_t i = 0; i < n_desc; ++i) {
+      const XferDesc& d = table[i];
+      const char* what = nullptr;
+      if (!no_alloc_device_pointer(d.row_table, true)) what = "row_table is neither 0 nor a device address";
+      else if (!no_alloc_device_pointer(d.tensor_map, true)) what = "tensor_map is neither 0 nor a device address";
+      else if (!no_alloc_device_pointer(d.src, false)) what = "src is not a device address";
+      else if (!no_alloc_device_pointer(d.dst, false)) what = "dst is not a device address";
+      else if (d.op == OP_FP8_BLOCK && !no_alloc_device_pointer(d.aux_ptr, false)) what = "the scale address is not a device address";
+      if (what != nullptr) {
+        if (err != nullptr && err_cap > 0) std::snprintf(err, err_cap, "awex_fused_transfer_no_alloc: descriptor %u: %s", i, what);
+        return static_cast<int>(cudaErrorInvalidValue);
+      }
+    }
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The array keeps the previous call's contents: counter and status start at zero.
@@ -682,7 +918,8 @@ extern "C" int awex_fused_transfer_no_alloc(const void* host_descs, uint32_t n_d
     p.n_done = 0;
     p.cta_counter = reinterpret_cast<unsigned int*>(scratch);
     p.status = status;
-    p.chunk_desc = nullptr;  // contiguous tile ranges
+    p.cta_plan = nullptr;  // contiguous tile ranges
+    p.chunk_desc = nullptr;
     p.chunk_shift = 0;
     fused_transfer_kernel<<<grid, kThreads, smem, s>>>(p);
     e = cudaGetLastError();

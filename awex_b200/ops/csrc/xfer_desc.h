@@ -7,8 +7,9 @@
 // written to `dst`, which is either local or a peer-mapped address of another
 // GPU on the same NVLink domain.  The host cuts every slab into tiles of
 // `tile_rows` x `tile_cols` elements; tiles of all descriptors are numbered
-// consecutively (`tile_begin` is the number of the slab's first tile) and the
-// kernel's CTAs split the tile range evenly.
+// consecutively (`tile_begin` is the number of the slab's first tile).  Which
+// tiles a CTA works on is either an even split of the whole range or, when the
+// host supplies one, its entry of a per-CTA plan (`CtaPlan`).
 //
 // The Python encoder (awex_b200/transfer/descriptors.py) mirrors this layout
 // with a numpy structured dtype; sizeof is checked at load time.
@@ -67,8 +68,27 @@ enum XferStatus : int32_t {
 
 constexpr int kStageBytes = 32 * 1024;
 constexpr int kStages = 6;
-constexpr int kLookahead = 4;
 constexpr int kThreads = 512;
+constexpr int kFp8Block = 128;  // quantisation block edge
+
+// One CTA's share of the table.  The CTAs of a group (`size` of them, this one
+// being number `rank`) own the tile range [tile_begin, tile_end), cut into chunks
+// of 2^chunk_shift tiles counted from tile_begin; CTA `rank` takes chunks rank,
+// rank + size, rank + 2 size, ...  `chunk_off` is where the group's chunks start
+// in XferParams::chunk_desc.  The host makes one group per destination GPU, sized
+// in proportion to the destination's bytes, so that every receiver is fed during
+// the whole kernel while cheap and expensive tiles are still spread over the
+// group's CTAs; one group of all CTAs deals the whole table round-robin, groups
+// of one CTA are contiguous ranges.
+struct alignas(16) CtaPlan {
+  uint64_t tile_begin;
+  uint64_t tile_end;
+  uint32_t rank;
+  uint32_t size;
+  uint32_t chunk_off;
+  uint32_t reserved;
+};
+static_assert(sizeof(CtaPlan) == 32, "plan layout is shared with the Python encoder");
 
 struct XferParams {
   const XferDesc* descs;
@@ -87,8 +107,10 @@ struct XferParams {
   // scratch: CTA arrival counter (self-resetting) and status words
   unsigned int* cta_counter;
   int32_t* status;
-  // optional: descriptor index of the first tile of every chunk of 2^chunk_shift
-  // tiles; when given, chunks are dealt round-robin to the CTAs
+  // optional: one plan per CTA (gridDim.x entries) and, for every chunk of every
+  // group, the index of the descriptor that holds the chunk's first tile.  Without
+  // a plan the CTAs split the whole tile range evenly into contiguous ranges.
+  const CtaPlan* cta_plan;
   const uint32_t* chunk_desc;
   uint32_t chunk_shift;
 };

@@ -85,3 +85,15 @@ def block_dequant(q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = tor
     )
     native.check(code, "fp8_block_dequant launch")
     return out
+
+
+def quant_scales(amax: torch.Tensor, scale_ue8m0: bool = False) -> torch.Tensor:
+    """The scale the kernels derive from each block maximum in ``amax`` (fp32,
+    CUDA): ``max(amax, 1e-4) / 448``, optionally rounded up to a power of two."""
+    from awex_b200.ops import native
+
+    amax = amax.contiguous().float()
+    out = torch.empty_like(amax)
+    code = native.load().awex_launch_fp8_scale_table(amax.data_ptr(), out.data_ptr(), amax.numel(), int(scale_ue8m0), native.current_stream_ptr())
+    native.check(code, "fp8_scale_table launch")
+    return out

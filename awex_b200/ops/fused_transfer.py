@@ -64,8 +64,11 @@ def _max_chunk_shift(table: np.ndarray, n_tiles: int) -> int:
 
 
 def _pick_variant(table: np.ndarray, n_tiles: int) -> int:
-    """0: one 512-thread CTA per SM, deep ring (copy-dominated tables); 1: two
-    256-thread CTAs per SM (tables dominated by tiles all warps compute on).
+    """0: one 512-thread CTA per SM, deep ring (tables of long contiguous
+    copies); 1: two 256-thread CTAs per SM (tables dominated by tiles all warps
+    compute on, or by strided copies of short rows, where a single CTA per SM
+    leaves the copy engine idle between its many small requests: 2 KiB rows ran
+    at 0.63 of the copy peak with one CTA per SM and 0.85 with two).
     ``AWEX_XFER_VARIANT`` overrides."""
     import os
 
@@ -78,8 +81,13 @@ def _pick_variant(table: np.ndarray, n_tiles: int) -> int:
         return 0
     begins = table["tile_begin"].astype(np.int64)
     counts = np.diff(np.append(begins, n_tiles))
-    computed = int(counts[table["op"] != OP_COPY].sum())
-    return 1 if 2 * computed > n_tiles else 0
+    is_copy = table["op"] == OP_COPY
+    short_rows = is_copy & (table["tile_rows"] > 1) & (table["row_elems"] <= SHORT_ROW_BYTES)  # copies count bytes
+    slow = int(counts[~is_copy].sum()) + int(counts[short_rows].sum())
+    return 1 if 2 * slow > n_tiles else 0
+
+
+SHORT_ROW_BYTES = 4096
 
 
 class StatusWord:
@@ -125,9 +133,19 @@ class TransferProgram:
     def __init__(self, table: np.ndarray, n_tiles: int, device, ready_pad: Optional[FlagPad] = None,
                  ready_slots: Sequence[int] = (), done_flag_addrs: Sequence[int] = (), timeout_ms: int = 2000,
                  grid: int = 0, row_offsets: Sequence[int] = (), tensor_map_descs: Sequence[int] = (), encoder=None,
-                 interleave: bool = True, variant: Optional[int] = None):
+                 interleave: bool = True, variant: Optional[int] = None, desc_group: Optional[Sequence[int]] = None,
+                 group_cost: Optional[Dict[int, float]] = None):
+        """``interleave``: deal tiles to CTAs in round-robin chunks instead of one
+        contiguous range per CTA.  ``desc_group`` (one id per descriptor, e.g. the
+        destination rank; taken from ``encoder`` when it is given and this is
+        ``True``) makes one group of CTAs per run of equal ids, sized by the bytes it
+        writes times ``group_cost[id]`` (relative time per byte, default 1)."""
         if encoder is not None:  # side tables produced while encoding
             row_offsets, tensor_map_descs = encoder.row_offsets, encoder.tensor_map_descs
+            if desc_group is True:
+                desc_group = encoder.desc_dst
+        if desc_group is True:
+            desc_group = None
         if table.dtype != DESC_DTYPE:
             raise TypeError("descriptor table has the wrong dtype")
         self.lib = native.load()
@@ -157,16 +175,20 @@ class TransferProgram:
         # chunk index for the round-robin deal of tiles to CTAs: chunks of up to 16
         # tiles, smaller when the table is short so that every CTA still gets work
         self.variant = _pick_variant(table, self.n_tiles) if variant is None else int(variant)
-        self.chunk_desc, self.chunk_shift = None, 0
+        self.chunk_desc, self.chunk_shift, self.cta_plan, self.plan_host = None, 0, None, None
         if interleave and self.n_desc and self.n_tiles:
+            from awex_b200.transfer.descriptors import build_cta_plan
+
             ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count * (2 if self.variant else 1)
+            ctas = max(1, min(ctas, self.n_tiles))
             shift = _max_chunk_shift(table, self.n_tiles)
             while shift > 0 and (self.n_tiles >> shift) < 4 * ctas:
                 shift -= 1
-            starts = np.arange(0, self.n_tiles, 1 << shift, dtype=np.uint64)
-            index = np.searchsorted(table["tile_begin"].astype(np.uint64), starts, side="right") - 1
+            self.plan_host, index = build_cta_plan(table, self.n_tiles, ctas, shift, desc_group, group_cost)
+            self.cta_plan = torch.from_numpy(self.plan_host.view(np.uint8).reshape(-1).copy()).to(self.device)
             self.chunk_desc = _device_array(index, np.uint32, self.device)
             self.chunk_shift = shift
+            grid = ctas
         self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.status = StatusWord(self.device)
         self.timeout_ns = int(timeout_ms) * 1_000_000
@@ -218,6 +240,7 @@ class TransferProgram:
             self.done_flags.data_ptr() if self.n_done else None, self.n_done,
             self.counter.data_ptr(), self.status.ptr, self.grid, stream,
             self.chunk_desc.data_ptr() if self.chunk_desc is not None else None, self.chunk_shift, self.variant,
+            self.cta_plan.data_ptr() if self.cta_plan is not None else None,
         )
         native.check(code, "fused_transfer launch")
         self.launches += 1

@@ -44,7 +44,7 @@ def is_stale() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = sources() + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")]
+    deps = sources() + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
@@ -79,7 +79,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "awex_xfer_desc_size": ([], i32),
         "awex_xfer_smem_bytes": ([], i32),
         "awex_xfer_stage_bytes": ([], i32),
-        "awex_launch_fused_transfer": ([vp, u32, u64, u64, u64, vp, vp, u32, vp, u32, vp, vp, i32, vp, vp, u32, u32], i32),
+        "awex_launch_fused_transfer": ([vp, u32, u64, u64, u64, vp, vp, u32, vp, u32, vp, vp, i32, vp, vp, u32, u32, vp], i32),
         "awex_launch_wait_flags": ([vp, vp, u32, u64, u64, vp, vp], i32),
         "awex_launch_post_flags": ([vp, u32, u64, vp], i32),
         "awex_sum_desc_size": ([], i32),
@@ -100,6 +100,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "awex_encode_tensor_map_2d": ([vp, i32, u64, u64, u64, u64, u32, u32], i32),
         "awex_launch_fp8_block_quant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, i32, vp, vp], i32),
         "awex_launch_fp8_block_dequant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, vp], i32),
+        "awex_launch_fp8_scale_table": ([vp, vp, u32, i32, vp], i32),
         "awex_vmm_available": ([], i32),
         "awex_vmm_export_fd": ([u64, ctypes.POINTER(i32)], i32),
         "awex_vmm_reserve": ([u64, u64, ctypes.POINTER(u64)], i32),
@@ -125,7 +126,7 @@ def load() -> ctypes.CDLL:
         return _lib
     with _lock:
         if _lib is None:
-            if not os.path.exists(LIB_PATH):
+            if is_stale():  # missing, or older than a source or header
                 build()
             lib = ctypes.CDLL(LIB_PATH)
             _declare(lib)

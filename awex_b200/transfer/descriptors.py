@@ -32,6 +32,11 @@ FLAG_BULK, FLAG_DST_VEC16, FLAG_UE8M0 = 1, 2, 4
 STAGE_BYTES = 32 * 1024
 MAX_TX_BYTES = (1 << 20) - 1
 
+PLAN_DTYPE = np.dtype(
+    [("tile_begin", "<u8"), ("tile_end", "<u8"), ("rank", "<u4"), ("size", "<u4"), ("chunk_off", "<u4"), ("reserved", "<u4")]
+)
+assert PLAN_DTYPE.itemsize == 32
+
 DESC_DTYPE = np.dtype(
     [
         ("src", "<u8"), ("dst", "<u8"), ("rows", "<u8"), ("row_elems", "<u8"), ("src_stride", "<i8"),
@@ -131,12 +136,16 @@ class DescriptorEncoder:
         self.row_offsets: List[int] = []
         # descriptors (by index) whose tiles are fetched with one tiled TMA load each
         self.tensor_map_descs: List[int] = []
+        # destination rank of every descriptor (the kernel's CTA groups are cut along these)
+        self.desc_dst: List[int] = []
+        self._dst_rank = 0
         self.n_tiles = 0
         self.bytes_out = 0
         self.bytes_in = 0
 
     def add_item(self, item: CopyItem, src: TensorAddr, dst: TensorAddr, scale: Optional[TensorAddr] = None) -> None:
         kind = item.value_op.kind
+        self._dst_rank = int(item.dst_rank)
         ses, des = src.dtype.itemsize, dst.dtype.itemsize
         if src.dtype != item.src_dtype:
             raise ValueError(f"{item.src_param}: tensor dtype {src.dtype} differs from planned {item.src_dtype}")
@@ -195,6 +204,7 @@ class DescriptorEncoder:
         bands = -(-rows // tile_rows)
         if op == OP_FP8_BLOCK and staged and row_offsets is None:
             self.tensor_map_descs.append(len(self.rows))
+        self.desc_dst.append(self._dst_rank)
         self.rows.append(
             (src, dst, rows, row_elems, src_stride, dst_stride, self.n_tiles, aux_ptr, aux_stride, aux_f, op, flags, sdt, ddt,
              tile_rows, tile_cols, col_tiles, 0, row_table, 0)
@@ -241,6 +251,77 @@ def encode_items(items: Iterable[CopyItem], src_addrs: Dict[Tuple[str, int], Ten
         scale = dst_book.get(it.scale_name) if it.scale_name else None
         enc.add_item(it, src_addrs[(it.src_param, it.vp_stage)], dst_book[it.dst_name], scale)
     return enc.table(), enc.n_tiles, enc
+
+
+def table_dst_bytes(table: np.ndarray) -> np.ndarray:
+    """Bytes every descriptor writes (payload only)."""
+    es = np.array([_DT_SIZE[c] for c in range(5)], dtype=np.int64)
+    return table["rows"].astype(np.int64) * table["row_elems"].astype(np.int64) * es[table["dst_dtype"].astype(np.int64)]
+
+
+def build_cta_plan(table: np.ndarray, n_tiles: int, n_ctas: int, chunk_shift: int, desc_group: Optional[Sequence[int]] = None,
+                   group_cost: Optional[Dict[int, float]] = None) -> Tuple[np.ndarray, np.ndarray]:
+    """The per-CTA plan (``PLAN_DTYPE``) and the chunk index of the fused kernel.
+
+    Descriptors with the same group id that follow one another form a group; a
+    group gets CTAs in proportion to ``bytes written x cost per byte`` (at least
+    one) and its tiles are dealt to them in round-robin chunks of
+    ``2**chunk_shift`` tiles.  Without group ids, or when the table alternates
+    between groups more often than there are CTAs to share out, all CTAs form one
+    group over the whole table.  The chunk index holds, group after group, the
+    descriptor of every chunk's first tile."""
+    begins = table["tile_begin"].astype(np.int64)
+    n_desc = int(table.shape[0])
+    runs: List[Tuple[int, int, float]] = []  # (tile_begin, tile_end, weight)
+    if desc_group is not None and n_desc:
+        ids = np.asarray(desc_group, dtype=np.int64)
+        assert ids.shape[0] == n_desc, "one group id per descriptor"
+        cuts = np.flatnonzero(np.diff(ids)) + 1
+        first = np.concatenate(([0], cuts))
+        last = np.concatenate((cuts, [n_desc]))
+        nbytes = table_dst_bytes(table)
+        csum = np.concatenate(([0], np.cumsum(nbytes)))
+        for a, b in zip(first.tolist(), last.tolist()):
+            tb, te = int(begins[a]), int(begins[b]) if b < n_desc else int(n_tiles)
+            cost = float((group_cost or {}).get(int(ids[a]), 1.0))
+            if te > tb:
+                runs.append((tb, te, float(csum[b] - csum[a]) * cost))
+    if not runs or len(runs) > max(1, n_ctas // 2):
+        runs = [(0, int(n_tiles), 1.0)]
+    # apportion the CTAs: at least one each, the rest by largest remainder
+    total = sum(w for _, _, w in runs) or 1.0
+    spare = n_ctas - len(runs)
+    ideal = [spare * w / total for _, _, w in runs]
+    share = [1 + int(x) for x in ideal]
+    order = sorted(range(len(runs)), key=lambda g: ideal[g] - int(ideal[g]), reverse=True)
+    for g in order[: n_ctas - sum(share)]:
+        share[g] += 1
+    plan = np.zeros(n_ctas, dtype=PLAN_DTYPE)
+    index_parts: List[np.ndarray] = []
+    cta = off = 0
+    for (tb, te, _), size in zip(runs, share):
+        starts = np.arange(tb, te, 1 << chunk_shift, dtype=np.int64)
+        index_parts.append((np.searchsorted(begins, starts, side="right") - 1).astype(np.uint32))
+        for r in range(size):
+            plan[cta] = (tb, te, r, size, off, 0)
+            cta += 1
+        off += len(starts)
+    assert cta == n_ctas
+    return plan, np.concatenate(index_parts) if index_parts else np.zeros(0, dtype=np.uint32)
+
+
+def plan_tile_order(plan: np.ndarray, chunk_shift: int) -> List[int]:
+    """Every tile number the CTAs of a plan visit, CTA after CTA, computed the
+    way the kernel computes it.  A correct plan yields every tile exactly once."""
+    order: List[int] = []
+    size = 1 << chunk_shift
+    for e in plan:
+        tb, te, rank, group = int(e["tile_begin"]), int(e["tile_end"]), int(e["rank"]), int(e["size"])
+        n_chunks = -(-(te - tb) // size)
+        for chunk in range(rank, n_chunks, group):
+            first = tb + chunk * size
+            order.extend(range(first, min(first + size, te)))
+    return order
 
 
 # ---- host-side checks ------------------------------------------------------------------------------

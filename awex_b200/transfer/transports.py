@@ -47,6 +47,9 @@ from awex_b200.transfer.lowering import CopyItem, check_exactly_once, manifest_b
 
 logger = logging.getLogger(__name__)
 
+# relative time per byte of a destination in this GPU's own memory (HBM) against one across NVLink
+LOCAL_BYTE_COST = 0.25
+
 DONE_PAD = "__done_flags__"
 READY_PAD = "__ready_flags__"
 
@@ -276,15 +279,20 @@ class PeerStoreSender:
             if problems:
                 raise ValueError(f"training rank {self.train_rank}: descriptor table rejected: {problems[:6]}")
         # destinations in this very process are ordered by the stream; the others
-        # must announce readiness through a flag before they are overwritten
-        # Round-robin chunks keep all CTAs of a sender inside one narrow window of
-        # the table, hence on one destination at a time; senders that walk equal
-        # tables then hit the same receiver together and halve each other's rate
-        # (measured: 8B model, 4 senders -> 2 x 2 receivers, 12.2 ms with contiguous
-        # ranges, 21.7 ms with chunks).  Chunks are used when nothing crosses NVLink.
+        # must announce readiness through a flag before they are overwritten.
+        # Tiles are dealt to CTAs in round-robin chunks inside one group of CTAs
+        # per destination, sized by the destination's bytes (bytes that stay in
+        # this GPU's memory cost about a quarter of bytes that cross NVLink): every
+        # receiver is fed during the whole kernel, and cheap and expensive tiles
+        # are spread over a group's CTAs.  (One group over the whole table puts all
+        # CTAs of a sender on one destination at a time; senders that walk equal
+        # tables then meet at the same receiver and halve each other's rate:
+        # 8B model, 4 senders -> 2 x 2 receivers, 21.7 ms against 12.2 ms.)
+        local = [d for d in self.destinations if d not in remote]
         self.program = TransferProgram(
             table, n_tiles, self.device, ready_pad=self.ready_pad, ready_slots=remote, done_flag_addrs=done_flags,
             timeout_ms=self.timeout_ms, grid=self.grid, encoder=enc, interleave=self._interleave(remote),
+            desc_group=True if self._group_by_destination() else None, group_cost={d: LOCAL_BYTE_COST for d in local},
         )
         self.bytes_out, self.bytes_in, self.n_desc = enc.bytes_out, enc.bytes_in, int(table.shape[0])
         # bytes that cross NVLink (destinations on other GPUs) and bytes that stay in this GPU's memory
@@ -326,10 +334,15 @@ class PeerStoreSender:
 
     @classmethod
     def _interleave(cls, remote) -> bool:
-        forced = os.environ.get("AWEX_XFER_INTERLEAVE")
-        if forced in ("0", "1"):
-            return forced == "1"
-        return len(remote) == 0 or cls._stripe_bytes() > 0
+        """Round-robin chunks (default) or, with ``AWEX_XFER_INTERLEAVE=0``, one
+        contiguous tile range per CTA."""
+        return os.environ.get("AWEX_XFER_INTERLEAVE", "1") != "0"
+
+    @classmethod
+    def _group_by_destination(cls) -> bool:
+        """One CTA group per destination (default); ``AWEX_XFER_DEST_GROUPS=0`` or a
+        striped table order deal the whole table to all CTAs as one group."""
+        return os.environ.get("AWEX_XFER_DEST_GROUPS", "1") != "0" and cls._stripe_bytes() == 0
 
     def _follow_moves(self, epoch: int) -> None:
         """Wait until every destination that may move has named the address book

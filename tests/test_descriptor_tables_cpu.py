@@ -176,3 +176,51 @@ def test_striped_order_does_the_same_work(arch, train, infer, dtype):
     for table, n_tiles, enc in encoded.values():
         assert run_chunked(table, n_tiles, mem, grid=7, chunk_shift=2, row_offsets=enc.row_offsets)
     assert job.mismatches() == []
+
+
+def test_no_alloc_entry_refuses_malformed_tables_before_any_cuda_call():
+    """The allocation-free entry point checks the structure of a caller-built table
+    on the host first (tile numbering, geometry, bulk alignment, stage size), so a
+    malformed table is refused even on a machine without a GPU."""
+    import ctypes
+
+    from awex_b200.ops import native
+    from awex_b200.transfer.descriptors import FLAG_BULK, OP_FP8_BLOCK, TensorAddr, encode_items
+    from awex_b200.transfer.lowering import CopyItem
+
+    fn = native.load().awex_fused_transfer_no_alloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, ctypes.c_void_p,
+                   ctypes.POINTER(ctypes.c_int32), ctypes.c_char_p, ctypes.c_size_t]
+    src = torch.zeros(300, 512, dtype=torch.bfloat16)
+    dst = torch.zeros(300, 512, dtype=torch.bfloat16)
+    items = [CopyItem("a", 0, (0, 0), (300, 256), 0, "a", (0, 256), torch.bfloat16, torch.bfloat16),
+             CopyItem("a", 0, (0, 256), (300, 256), 0, "a", (0, 0), torch.bfloat16, torch.bfloat16)]
+    table, n_tiles, _ = encode_items(items, {("a", 0): TensorAddr.of(src)}, {0: {"a": TensorAddr.of(dst)}})
+    assert len(table) == 2 and int(table["flags"][0]) & FLAG_BULK
+    err = ctypes.create_string_buffer(256)
+
+    def refused(t, tiles):
+        t = np.ascontiguousarray(t)
+        rc = fn(t.ctypes.data, len(t), tiles, 1000, 0, None, None, err, len(err))
+        assert rc == 1, "cudaErrorInvalidValue expected"
+        return err.value.decode()
+
+    assert "n_tiles does not match" in refused(table, n_tiles + 1)
+    t = table.copy(); t["tile_begin"][0] = 3
+    assert "descriptor 0" in refused(t, n_tiles) and "must be 0" in err.value.decode()
+    t = table.copy(); t["tile_begin"][1] += 1
+    assert "descriptor 1: tile_begin must continue" in refused(t, n_tiles)
+    for field in ("tile_rows", "tile_cols", "col_tiles"):
+        t = table.copy(); t[field][1] = 0
+        assert "non-zero" in refused(t, n_tiles)
+    t = table.copy(); t["col_tiles"][0] = 7
+    assert "col_tiles does not match" in refused(t, n_tiles)
+    t = table.copy(); t["tile_rows"][0] = 4096; t["tile_begin"][1] = 1  # 4096 rows x 512 bytes do not fit a 32 KiB stage
+    assert "exceeds one pipeline stage" in refused(t, 1 + int(n_tiles - table["tile_begin"][1]))
+    t = table.copy(); t["src"][0] += 2
+    assert "bulk source rule" in refused(t, n_tiles)
+    t = table.copy(); t["op"][0] = OP_FP8_BLOCK + 1
+    assert "unknown op" in refused(t, n_tiles)
+    t = table.copy(); t["rows"][1] = 0
+    assert "empty slab" in refused(t, n_tiles)

@@ -45,6 +45,24 @@ def test_block_quant_special_values():
         assert _same_fp8(q.cpu(), q_ref)
 
 
+@pytest.mark.parametrize("ue8m0", [False, True])
+def test_scale_rule_is_exact_for_every_16_bit_amax(ue8m0):
+    """Every block maximum a bf16 or fp16 tensor can have (all non-negative bit
+    patterns, infinity and NaN included) through the kernels' scale rule, against
+    PyTorch's fp32 statement on the CPU."""
+    from awex_b200.ops.fp8 import quant_scales
+
+    bf16 = (torch.arange(0, 0x8000, dtype=torch.int32) << 16).view(torch.float32)
+    fp16 = torch.arange(0, 0x8000, dtype=torch.int32).to(torch.int16).view(torch.float16).float()
+    for amax in (bf16, fp16):
+        want = amax.clamp(min=1e-4) / 448.0
+        if ue8m0:
+            want = want.clamp(min=1e-10).log2().ceil().exp2()
+        got = quant_scales(amax.cuda(), ue8m0).cpu()
+        assert torch.equal(torch.isnan(got), torch.isnan(want))
+        assert torch.equal(torch.nan_to_num(got, nan=0.0), torch.nan_to_num(want, nan=0.0))
+
+
 def test_unaligned_rows_take_the_transfer_kernel_path():
     from awex_b200.ops.fp8 import block_quant
 

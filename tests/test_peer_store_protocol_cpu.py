@@ -75,17 +75,26 @@ class FakeImporter:
 class FakeProgram:
     built = 0
 
-    def __init__(self, table, n_tiles, device, ready_pad=None, ready_slots=(), done_flag_addrs=(), timeout_ms=0, grid=0, encoder=None, interleave=True):
+    def __init__(self, table, n_tiles, device, ready_pad=None, ready_slots=(), done_flag_addrs=(), timeout_ms=0, grid=0, encoder=None, interleave=True,
+                 desc_group=None, group_cost=None):
+        from awex_b200.transfer.descriptors import build_cta_plan, plan_tile_order
+
         FakeProgram.built += 1
         self.table, self.n_tiles, self.encoder = table, n_tiles, encoder
         self.ready_slots, self.interleave, self.launches = list(ready_slots), interleave, []
         self.status = SimpleNamespace(raise_if_failed=lambda: None)
+        self.grouped, self.group_cost = desc_group is not None, dict(group_cost or {})
+        self.order = None
+        if interleave and n_tiles:  # the order in which 16 CTAs would visit the tiles
+            plan, index = build_cta_plan(table, n_tiles, min(16, n_tiles), 1, encoder.desc_dst if desc_group is True else desc_group, group_cost)
+            self.plan, self.order = plan, plan_tile_order(plan, 1)
+            assert sorted(self.order) == list(range(n_tiles)), "the CTA plan must visit every tile exactly once"
 
     def launch(self, epoch):
         self.launches.append(epoch)
         with DONE:  # what the kernel's first wait does: every peer destination must have announced this epoch
             assert DONE.wait_for(lambda: DONE.ready.get(epoch, 0) >= len(self.ready_slots), timeout=30), f"no ready flags for epoch {epoch}"
-        assert run_table(self.table, self.n_tiles, HostMemory(MEMORY), self.encoder.row_offsets) == self.n_tiles
+        assert run_table(self.table, self.n_tiles, HostMemory(MEMORY), self.encoder.row_offsets, tile_order=self.order) == self.n_tiles
         with DONE:  # what the kernel's last CTA does with the receivers' done flags
             DONE.count[epoch] = DONE.count.get(epoch, 0) + 1
             DONE.notify_all()
@@ -191,7 +200,8 @@ def test_two_processes_exchange_through_books_manifests_and_handshakes(fakes, gp
         sender, receiver = make_sides(job, items, local, views, meta)
         assert sender.host_destinations == ([0] if host_pair else []) and receiver.host_senders == ([0] if host_pair else [])
         assert sender.program.ready_slots == ([] if host_pair else [0])  # a peer GPU announces readiness through a device flag
-        assert sender.program.interleave == host_pair  # round-robin chunks only while nothing crosses NVLink
+        assert sender.program.interleave and sender.program.grouped  # round-robin chunks inside one CTA group per destination
+        assert sender.program.group_cost == ({0: 0.25} if host_pair else {})  # bytes that stay on the GPU are cheap
         assert receiver.bytes_in == sender.bytes_out and sender.bytes_remote == (0 if host_pair else sender.bytes_out)
         update(sender, receiver, 1)
         assert job.mismatches() == [] and sender.program.launches == [1]
@@ -285,7 +295,9 @@ def test_two_senders_four_receivers_on_six_gpus(fakes, monkeypatch, stripe_mb):
             with acting_as(f"train{r}"):
                 tx.connect()
             assert len(tx.destinations) >= 2 and tx.program.ready_slots == tx.destinations  # one per engine at least, all on peer GPUs
-            assert tx.program.interleave == (stripe_mb != "0")
+            assert tx.program.interleave and tx.program.grouped == (stripe_mb == "0")
+            if tx.program.grouped:  # one group of CTAs per destination, CTAs shared out by bytes
+                assert len({(int(e["tile_begin"]), int(e["tile_end"])) for e in tx.program.plan}) == len(tx.destinations)
         for i, rx in receivers.items():
             with acting_as(f"infer{i}"):
                 rx.begin(1)

@@ -92,3 +92,31 @@ def test_no_alloc_entry_refuses_oversized_tables():
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
     assert torch.ones(8, device="cuda").sum().item() == 8
+
+
+def test_no_alloc_entry_refuses_raw_encoder_tables_with_gathered_rows_and_bad_addresses():
+    """A table whose `row_table` still holds the encoder's index, or whose
+    addresses are not device memory, is refused on the host: nothing is queued,
+    so nothing can fault."""
+    fn = _symbol()
+    err = ctypes.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+    src = torch.randn(256, 256, device="cuda").to(torch.bfloat16)
+    dst = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
+    from awex_b200.transfer.lowering import CopyItem
+
+    table, n_tiles, _ = _table([CopyItem("a", 0, (0, 0), (256, 256), 0, "a", (0, 0), torch.bfloat16, torch.bfloat16)], {"a": src}, {"a": dst})
+    cases = []
+    t = table.copy(); t["row_table"][0] = 1; cases.append((t, b"row_table"))          # an index, not an address
+    t = table.copy(); t["tensor_map"][0] = 4096; cases.append((t, b"tensor_map"))
+    host = np.zeros(256 * 256, dtype=np.uint16)
+    t = table.copy(); t["src"][0] = (host.ctypes.data + 15) & ~15; cases.append((t, b"src is not a device address"))
+    t = table.copy(); t["dst"][0] = (host.ctypes.data + 15) & ~15; cases.append((t, b"dst is not a device address"))
+    for bad, needle in cases:
+        rc = fn(np.ascontiguousarray(bad).ctypes.data, len(bad), n_tiles, 1_000_000, 0, stream, None, err, len(err))
+        assert rc == 1 and needle in err.value, (needle, err.value)
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(dst).item() == 0  # nothing ran
+    status = (ctypes.c_int32 * 4)()
+    assert fn(table.ctypes.data, len(table), n_tiles, 2_000_000_000, 0, stream, status, err, len(err)) == 0, err.value
+    assert list(status) == [0, 0, 0, 0] and torch.equal(dst, src)  # the context is intact and the good table runs
