@@ -44,6 +44,15 @@ __device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
 __device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// CTA-scope publication of a counter in shared memory
+__device__ __forceinline__ void st_release_cta_shared(uint32_t addr, uint64_t v) {
+  asm volatile("st.release.cta.shared::cta.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_acquire_cta_shared(uint32_t addr) {
+  uint64_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -121,8 +130,14 @@ struct Tile {
 };
 __device__ __forceinline__ Tile tile_of(const XferDesc& d, uint64_t k) {
   Tile t;
-  t.band = static_cast<uint32_t>(k / d.col_tiles);
-  t.ct = static_cast<uint32_t>(k % d.col_tiles);
+  if (k <= 0xFFFFFFFFull) {  // the common case: a 32-bit division
+    const uint32_t k32 = static_cast<uint32_t>(k);
+    t.band = k32 / d.col_tiles;
+    t.ct = k32 - t.band * d.col_tiles;
+  } else {
+    t.band = static_cast<uint32_t>(k / d.col_tiles);
+    t.ct = static_cast<uint32_t>(k % d.col_tiles);
+  }
   t.row0 = static_cast<uint64_t>(t.band) * d.tile_rows;
   t.col0 = static_cast<uint64_t>(t.ct) * d.tile_cols;
   uint64_t r = d.rows - t.row0;
@@ -409,7 +424,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 // Ring of kS stages.  Warp 0 is the copy engine's driver: it issues every load
-// and, for pure copies, the stores; all warps work on computed tiles.  The stage
+// and, for pure copies, the stores; all warps work on computed tiles.  Only warp
+// 0 watches the stages' mbarriers (the other warps skip copied tiles and may be
+// many tiles ahead of the loads, where a phase parity means nothing); it
+// publishes the number of the newest computed tile whose data has landed in
+// `ready_tile`, which the other warps acquire before they read the stage.  The stage
 // of a computed tile is free once its barrier has been passed, the stage of a
 // copied tile once its store group has finished reading shared memory; warp 0
 // keeps as many loads in flight as that rule allows (kS - 1 ahead of a computed
@@ -420,9 +439,13 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kS];
   __shared__ uint32_t red[2][kT / 32];
+  __shared__ __align__(8) unsigned long long ready_tile;  // 1 + newest computed tile seen complete by warp 0; all ones: give up
+  constexpr uint64_t kGiveUp = ~uint64_t{0};
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ready_addr = smem_addr(&ready_tile);
   if (threadIdx.x == 0) {
+    ready_tile = 0;
     for (int s = 0; s < kS; ++s) mbar_init(smem_addr(&full_bar[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -527,9 +550,14 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
 
     bool prev_copy = false;  // warp 0: was the previous tile a pure copy?
     uint32_t n_computed = 0; // selects the half of `red` (two consecutive computed tiles never share one)
+    XferDesc d;              // descriptor of the tile in use
+    uint32_t d_index = 0xFFFFFFFFu;
     for (uint64_t i = 0; i < n; ++i) {
       const uint64_t tile_no = cursor_to(use_cur, i);
-      const XferDesc d = p.descs[use_cur.di];
+      if (use_cur.di != d_index) {  // most tiles continue the previous tile's slab
+        d = p.descs[use_cur.di];
+        d_index = use_cur.di;
+      }
       const Tile t = tile_of(d, tile_no - use_cur.begin);
       const uint32_t stage = static_cast<uint32_t>(i % kS);
       const uint32_t parity = static_cast<uint32_t>((i / kS) & 1);
@@ -555,6 +583,7 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
           if (__any_sync(0xffffffffu, !arrived)) {
             if (lane == 0 && atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
             my_abort = 1;  // warp 0 stops moving data; it keeps meeting the other warps at their barriers
+            if (lane == 0) st_release_cta_shared(ready_addr, kGiveUp);
           } else {
             waited = i + 1;
             const uint32_t pitch = stage_pitch(d);
@@ -570,13 +599,31 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
       if (warp == 0 && !my_abort) bulk_commit();  // an empty group keeps "one group per tile"
 
       if (staged && !my_abort) {
-        // every thread observes the completed phase itself, which orders the
-        // staged bytes before its reads
-        if (!mbar_wait_bounded(bar, parity, p.timeout_ns)) {
-          if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
-          my_abort = 1;
-        } else if (warp == 0) {
-          waited = i + 1;
+        if (warp == 0) {
+          // every lane observes the completed phase itself; lane 0 then hands the
+          // observation on to the other warps (release / acquire on `ready_tile`)
+          const bool arrived = mbar_wait_bounded(bar, parity, p.timeout_ns);
+          if (__any_sync(0xffffffffu, !arrived)) {
+            if (lane == 0 && atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
+            my_abort = 1;
+            if (lane == 0) st_release_cta_shared(ready_addr, kGiveUp);
+          } else {
+            waited = i + 1;
+            if (lane == 0) st_release_cta_shared(ready_addr, i + 1);
+          }
+        } else {
+          uint64_t seen = ld_acquire_cta_shared(ready_addr);
+          if (seen < i + 1) {
+            const uint64_t t0 = globaltimer_ns();
+            while ((seen = ld_acquire_cta_shared(ready_addr)) < i + 1) {
+              if (globaltimer_ns() - t0 > 2 * p.timeout_ns) {  // warp 0 gives up first and says so
+                if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
+                seen = kGiveUp;
+                break;
+              }
+            }
+          }
+          if (seen == kGiveUp) my_abort = 1;
         }
       } else if (!staged && warp == 0 && !my_abort) {
         waited = i + 1;

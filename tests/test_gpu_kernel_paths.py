@@ -1,0 +1,188 @@
+"""Every tile body and launch shape of the fused transfer kernel against the
+plain PyTorch statement of the same op (fp32 math on the CPU for quantisation)."""
+
+import numpy as np
+import pytest
+import torch
+
+from awex_b200.converter.weights_converter import per_block_cast_to_fp8
+
+pytestmark = pytest.mark.gpu
+
+F = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
+
+
+def _run(items, srcs, dsts, **program_kwargs):
+    from awex_b200.ops.fused_transfer import TransferProgram
+    from awex_b200.transfer.descriptors import TensorAddr, encode_items, validate_table
+
+    src_addrs = {(n, 0): TensorAddr.of(t) for n, t in srcs.items()}
+    dst_addrs = {rank: {n: TensorAddr.of(t) for n, t in views.items()} for rank, views in dsts.items()}
+    table, n_tiles, enc = encode_items(items, src_addrs, dst_addrs)
+    spans = [a.byte_span() for views in dst_addrs.values() for a in views.values()]
+    assert validate_table(table, n_tiles, [a.byte_span() for a in src_addrs.values()], spans) == []
+    prog = TransferProgram(table, n_tiles, "cuda", encoder=enc, **program_kwargs)
+    prog.launch(1)
+    torch.cuda.synchronize()
+    prog.check()
+    return prog, table
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("src_dt,dst_dt", [("bf16", "f32"), ("f32", "bf16"), ("f16", "bf16"), ("bf16", "f16"), ("f32", "f16"), ("f16", "f32")])
+def test_vector_cast_and_add_paths(src_dt, dst_dt, variant):
+    """16-byte chunks from the stage, packed converts, vector stores: many short
+    rows, a few long rows (tiles of one row), and a column slab with a pitch."""
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.transfer.lowering import CopyItem
+
+    s, d = F[src_dt], F[dst_dt]
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = (torch.randn(333, 1024, generator=g, device="cuda") * 3).to(s)
+    b = (torch.randn(3, 40000, generator=g, device="cuda") * 3).to(s)
+    out_a = torch.zeros(333, 1024, dtype=d, device="cuda")
+    out_b = torch.zeros(3, 40000, dtype=d, device="cuda")
+    out_c = torch.zeros(333, 2048, dtype=d, device="cuda")
+    items = [
+        CopyItem("a", 0, (0, 0), (333, 1024), 0, "a", (0, 0), s, d, ValueOp("cast", dtype=d)),
+        CopyItem("b", 0, (0, 0), (3, 40000), 0, "b", (0, 0), s, d, ValueOp("cast", dtype=d)),
+        CopyItem("a", 0, (0, 512), (333, 512), 0, "c", (0, 1024), s, d, ValueOp("cast", dtype=d)),
+    ]
+    _run(items, {"a": a, "b": b}, {0: {"a": out_a, "b": out_b, "c": out_c}}, variant=variant)
+    assert torch.equal(out_a, a.float().to(d))
+    assert torch.equal(out_b, b.float().to(d))
+    want_c = torch.zeros_like(out_c)
+    want_c[:, 1024:1536] = a[:, 512:].float().to(d)
+    assert torch.equal(out_c, want_c)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+def test_constant_add_rides_along(variant):
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.transfer.lowering import CopyItem
+
+    g = torch.Generator(device="cuda").manual_seed(12)
+    a = torch.randn(200, 4096, generator=g, device="cuda").to(torch.bfloat16)
+    out = torch.zeros_like(a)
+    _run([CopyItem("a", 0, (0, 0), (200, 4096), 0, "a", (0, 0), torch.bfloat16, torch.bfloat16, ValueOp("add", const=1.0))],
+         {"a": a}, {0: {"a": out}}, variant=variant)
+    assert torch.equal(out, (a.float() + 1.0).to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(512, 1024), (130, 136), (257, 384)])
+@pytest.mark.parametrize("ue8m0", [False, True])
+def test_fused_block_fp8_matches_cpu_statement(shape, dtype, variant, ue8m0):
+    """Block quantisation inside the transfer kernel: whole blocks, edge blocks in
+    both directions, both thread counts (8 and 4 chunks per thread)."""
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.transfer.lowering import CopyItem
+
+    g = torch.Generator(device="cuda").manual_seed(13)
+    x = (torch.randn(shape, generator=g, device="cuda") * 0.05).to(dtype)
+    x[0, 0] = 3.0
+    x[shape[0] - 1, shape[1] - 1] = -7.0
+    q = torch.zeros(shape, dtype=torch.float8_e4m3fn, device="cuda")
+    s = torch.zeros(-(-shape[0] // 128), -(-shape[1] // 128), dtype=torch.float32, device="cuda")
+    item = CopyItem("x", 0, (0, 0), shape, 0, "q", (0, 0), dtype, torch.float8_e4m3fn,
+                    ValueOp("fp8_block", dtype=torch.float8_e4m3fn, ue8m0=ue8m0), scale_name="s", scale_start=(0, 0))
+    _run([item], {"x": x}, {0: {"q": q, "s": s}}, variant=variant)
+    q_ref, s_ref = per_block_cast_to_fp8(x.cpu(), ue8m0)
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+def test_fused_block_fp8_with_gathered_rows():
+    """Blocks whose rows are collected through the per-row offset table (row by
+    row bulk copies into the stage; rows past the block's edge are not loaded and
+    must not leak from the stage's previous contents)."""
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.transfer.lowering import CopyItem
+
+    g = torch.Generator(device="cuda").manual_seed(14)
+    x = (torch.randn(600, 256, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+    # destination rows 0..199 come from source rows 400..499 then 100..199
+    runs = ((0, 400, 100), (100, 100, 100))
+    q = torch.zeros(200, 256, dtype=torch.float8_e4m3fn, device="cuda")
+    s = torch.zeros(2, 2, dtype=torch.float32, device="cuda")
+    item = CopyItem("x", 0, (0, 0), (200, 256), 0, "q", (0, 0), torch.bfloat16, torch.float8_e4m3fn,
+                    ValueOp("fp8_block", dtype=torch.float8_e4m3fn), scale_name="s", scale_start=(0, 0), src_rows=runs)
+    # a plain copy of large values first, so that stale stage contents would show in the maxima
+    big = torch.full((512, 4096), 100.0, dtype=torch.bfloat16, device="cuda")
+    big_out = torch.zeros_like(big)
+    items = [CopyItem("big", 0, (0, 0), (512, 4096), 0, "big", (0, 0), torch.bfloat16, torch.bfloat16), item]
+    for variant in (0, 1):
+        q.zero_(), s.zero_(), big_out.zero_()
+        _run(items, {"x": x, "big": big}, {0: {"q": q, "s": s, "big": big_out}}, variant=variant, grid=3)
+        gathered = torch.cat([x[400:500], x[100:200]]).cpu()
+        q_ref, s_ref = per_block_cast_to_fp8(gathered, False)
+        assert torch.equal(s.cpu(), s_ref) and torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+        assert torch.equal(big_out, big)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("interleave", [False, True])
+def test_destination_groups_and_mixed_tiles(variant, interleave):
+    """Three destinations of very different sizes and tile kinds (copies, strided
+    copies, casts, quantised blocks): one CTA group per destination, chunks dealt
+    round-robin inside a group; every tile is done exactly once."""
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.transfer.descriptors import plan_tile_order
+    from awex_b200.transfer.lowering import CopyItem
+
+    g = torch.Generator(device="cuda").manual_seed(15)
+    w = torch.randn(1024, 2048, generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn(96, 512, generator=g, device="cuda").to(torch.bfloat16)
+    d0 = {"w": torch.zeros(1024, 2048, dtype=torch.bfloat16, device="cuda"), "v32": torch.zeros(96, 512, dtype=torch.float32, device="cuda")}
+    d1 = {"wq": torch.zeros(1024, 2048, dtype=torch.float8_e4m3fn, device="cuda"), "ws": torch.zeros(8, 16, dtype=torch.float32, device="cuda")}
+    d2 = {"wt": torch.zeros(1024, 4096, dtype=torch.bfloat16, device="cuda")}
+    items = [
+        CopyItem("w", 0, (0, 0), (1024, 2048), 0, "w", (0, 0), torch.bfloat16, torch.bfloat16),
+        CopyItem("v", 0, (0, 0), (96, 512), 0, "v32", (0, 0), torch.bfloat16, torch.float32, ValueOp("cast", dtype=torch.float32)),
+        CopyItem("w", 0, (0, 0), (1024, 2048), 1, "wq", (0, 0), torch.bfloat16, torch.float8_e4m3fn,
+                 ValueOp("fp8_block", dtype=torch.float8_e4m3fn), scale_name="ws", scale_start=(0, 0)),
+        CopyItem("w", 0, (0, 0), (1024, 1024), 2, "wt", (0, 3072), torch.bfloat16, torch.bfloat16),
+        CopyItem("w", 0, (0, 1024), (1024, 1024), 2, "wt", (0, 0), torch.bfloat16, torch.bfloat16),
+    ]
+    prog, table = _run(items, {"w": w, "v": v}, {0: d0, 1: d1, 2: d2}, variant=variant, interleave=interleave, desc_group=True,
+                       group_cost={0: 0.25}, grid=37)
+    if interleave:
+        groups = sorted({(int(e["tile_begin"]), int(e["tile_end"]), int(e["size"])) for e in prog.plan_host})
+        assert len(groups) == 3 and sum(size for _, _, size in groups) == 37
+        assert sorted(plan_tile_order(prog.plan_host, prog.chunk_shift)) == list(range(prog.n_tiles))
+    else:
+        assert prog.plan_host is None
+    assert torch.equal(d0["w"], w) and torch.equal(d0["v32"], v.float())
+    q_ref, s_ref = per_block_cast_to_fp8(w.cpu(), False)
+    assert torch.equal(d1["ws"].cpu(), s_ref) and torch.equal(d1["wq"].cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    want = torch.zeros_like(d2["wt"])
+    want[:, 3072:], want[:, :1024] = w[:, :1024], w[:, 1024:]
+    assert torch.equal(d2["wt"], want)
+
+
+def test_a_launch_that_timed_out_leaves_the_program_reusable():
+    """Many CTAs give up waiting for a destination that never announces itself:
+    no byte is written, no flag raised, and the arrival counter is back at zero, so
+    the very next launch (without any host-side reset but the status) completes."""
+    from awex_b200.ops.fused_transfer import FlagPad, TransferError, TransferProgram
+    from awex_b200.transfer.descriptors import TensorAddr, encode_items
+    from awex_b200.transfer.lowering import CopyItem
+
+    src = torch.randn(2048, 4096, device="cuda").to(torch.bfloat16)
+    dst = torch.zeros_like(src)
+    table, n_tiles, enc = encode_items([CopyItem("w", 0, (0, 0), (2048, 4096), 0, "w", (0, 0), torch.bfloat16, torch.bfloat16)],
+                                       {("w", 0): TensorAddr.of(src)}, {0: {"w": TensorAddr.of(dst)}})
+    ready, done = FlagPad(1, "cuda"), FlagPad(1, "cuda")
+    prog = TransferProgram(table, n_tiles, "cuda", ready_pad=ready, ready_slots=[0], done_flag_addrs=[done.slot_addr(0)], timeout_ms=30, encoder=enc)
+    prog.launch(epoch=7)
+    torch.cuda.synchronize()
+    with pytest.raises(TransferError) as err:
+        prog.status.raise_if_failed()  # resets the status only
+    assert err.value.code == 1 and int(prog.counter.item()) == 0
+    assert torch.count_nonzero(dst).item() == 0 and done.t.item() == 0
+    ready.t.fill_(7)
+    prog.launch(epoch=7)
+    torch.cuda.synchronize()
+    prog.status.raise_if_failed()
+    assert torch.equal(dst, src) and done.t.item() == 7
