@@ -35,7 +35,7 @@ import signal
 import threading
 import time
 import traceback
-from typing import Any, Dict, Optional, Tuple, Union
+from typing import Any, Dict, List, Optional, Tuple, Union
 
 import requests
 from aiohttp import web
@@ -57,11 +57,18 @@ def _fail(status: int, error: str) -> web.Response:
     return web.json_response({"success": False, "error": error}, status=status)
 
 
+MAX_SERVER_WAIT_S = 20.0  # longest a single wait_counters request sleeps inside the server; clients re-issue
+
+
 class MetaServer:
     def __init__(self, host: str = "localhost", port: int = 8080):
         self.host = host
         self.port = port
         self.storage: Dict[str, Any] = {}
+        # named counters with server-side waiting (`put_counter` / `wait_counters`): each holds a list of
+        # integers whose first element only grows in normal use; a waiter sleeps on the condition instead of polling
+        self.counters: Dict[str, List[int]] = {}
+        self._counter_cond: Optional[asyncio.Condition] = None
         self.id_counter = 0
         self._loop: Optional[asyncio.AbstractEventLoop] = None
         self._thread: Optional[threading.Thread] = None
@@ -80,6 +87,8 @@ class MetaServer:
         r.add_get("/v1/keys", self._h_keys)
         r.add_get("/v1/has_key/{key:.*}", self._h_has_key)
         r.add_post("/v1/allocate_auto_grow_id", self._h_alloc_id)
+        r.add_put("/v1/put_counter/{key:.*}", self._h_put_counter)
+        r.add_get("/v1/wait_counters", self._h_wait_counters)
 
     # ---- in-process store API --------------------------------------------------------
     def get_binary(self, key: str) -> bytes:
@@ -231,6 +240,53 @@ class MetaServer:
         new_id = self.id_counter
         self.id_counter += 1
         return _ok(id=new_id)
+
+    def _cond(self) -> asyncio.Condition:
+        if self._counter_cond is None:  # created inside the server's loop
+            self._counter_cond = asyncio.Condition()
+        return self._counter_cond
+
+    async def _h_put_counter(self, request):
+        """Body: a JSON list of integers (or one integer).  Wakes every waiter."""
+        key = request.match_info["key"]
+        try:
+            value = await request.json()
+            value = [int(v) for v in value] if isinstance(value, list) else [int(value)]
+        except Exception as exc:
+            return _fail(400, f"counter value must be an integer or a list of integers: {exc}")
+        cond = self._cond()
+        async with cond:
+            self.counters[key] = value
+            cond.notify_all()
+        return _ok(value=value)
+
+    async def _h_wait_counters(self, request):
+        """``?keys=a,b&min=N&timeout=S``: answers when the first element of every
+        listed counter is at least N, or after S seconds; the answer holds the
+        counters as they are then (``null`` for one that was never put) and
+        ``reached``.  The wait sleeps on a condition inside the server: a waiter
+        learns of a put in the time of one reply, without polling."""
+        try:
+            keys = [k for k in request.query.get("keys", "").split(",") if k]
+            least = int(request.query.get("min", "0"))
+            timeout = min(max(float(request.query.get("timeout", "0")), 0.0), MAX_SERVER_WAIT_S)
+        except ValueError as exc:
+            return _fail(400, f"bad wait_counters query: {exc}")
+
+        def reached() -> bool:
+            return all(k in self.counters and self.counters[k][0] >= least for k in keys)
+
+        cond = self._cond()
+        async with cond:
+            ok = reached()
+            if not ok and timeout > 0:
+                try:
+                    await asyncio.wait_for(cond.wait_for(reached), timeout)
+                    ok = True
+                except asyncio.TimeoutError:
+                    ok = reached()
+            values = {k: self.counters.get(k) for k in keys}
+        return _ok(reached=ok, values=values)
 
 
 # ---- subprocess hosting -------------------------------------------------------------------
@@ -509,6 +565,44 @@ class MetaServerClient:
         resp = self._retry(lambda: self._session.post(self._url("allocate_auto_grow_id"), timeout=self.timeout))
         resp.raise_for_status()
         return int(resp.json()["id"])
+
+    # ---- counters with server-side waiting ----------------------------------------------------------
+    def put_counter(self, key: str, value) -> None:
+        """Set counter ``key`` to an integer or a list of integers and wake its waiters."""
+        from urllib.parse import quote
+
+        resp = self._retry(lambda: self._session.put(self._url("put_counter", quote(key, safe="")), json=value, timeout=self.timeout))
+        resp.raise_for_status()
+
+    def get_counter(self, key: str):
+        """The counter's list of integers, or ``None`` when it was never put."""
+        return self.wait_counters([key], 0, 0.0, must_reach=False).get(key)
+
+    def wait_counters(self, keys, at_least: int, timeout: float, must_reach: bool = True) -> Dict[str, Any]:
+        """Block until the first element of every counter in ``keys`` is at least
+        ``at_least``; returns ``{key: list}``.  The server holds each request for up
+        to 20 s and answers the moment the last counter arrives, so a waiter sees a
+        put within one round trip.  ``TimeoutError`` after ``timeout`` seconds (with
+        ``must_reach``)."""
+        from urllib.parse import quote
+
+        keys = list(keys)
+        if not keys:
+            return {}
+        deadline = time.time() + timeout
+        query = "keys=" + ",".join(quote(k, safe="") for k in keys) + f"&min={int(at_least)}"
+        while True:
+            remaining = max(0.0, deadline - time.time())
+            hold = min(remaining, MAX_SERVER_WAIT_S)
+            url = f"{self._base_url}/v1/wait_counters?{query}&timeout={hold:.3f}"
+            resp = self._retry(lambda: self._session.get(url, timeout=hold + self.timeout))
+            resp.raise_for_status()
+            body = resp.json()
+            if body.get("reached") or not must_reach:
+                return body.get("values", {})
+            if time.time() >= deadline:
+                missing = [k for k, v in body.get("values", {}).items() if v is None or v[0] < at_least]
+                raise TimeoutError(f"counters {missing} did not reach {at_least} within {timeout:.1f}s")
 
     def close(self) -> None:
         self._session.close()

@@ -221,6 +221,46 @@ __global__ void __launch_bounds__(256) fp8_block_dequant_kernel(const unsigned c
   }
 }
 
+// Exhaustive check of the division-free quotient used for 16-bit sources: every
+// non-negative amax bit pattern of the type (one per blockIdx.x) against every
+// value bit pattern of the type (threads stride over all 65536), for plain and
+// power-of-two scales.  A value takes part when it can occur in a block with
+// that maximum (|x| <= amax, or NaN / infinity, which make the scale non-finite
+// and take the division anyway).  Counts the pairs whose e4m3 byte differs from
+// the one the true division gives (must be none), and those whose fp32 quotient
+// differs in its last bits (allowed: they never change the byte).
+template <bool kBf16>
+__global__ void fp8_quotient_check_kernel(unsigned long long* out) {
+  const uint32_t amax_bits = blockIdx.x;  // 0 .. 0x7FFF
+  const float amax = kBf16 ? __uint_as_float(amax_bits << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(amax_bits)));
+  unsigned long long bad_bytes = 0, bad_quotients = 0, checked = 0;
+  for (int ue8m0 = 0; ue8m0 < 2; ++ue8m0) {
+    const QuantScale qs = make_quant_scale(amax, ue8m0 != 0);
+    for (uint32_t xb = threadIdx.x; xb < 65536u; xb += blockDim.x) {
+      const float x = kBf16 ? __uint_as_float(xb << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(xb)));
+      if (!(fabsf(x) <= amax) && amax == amax && !isinf(amax)) continue;  // cannot occur in a block with this maximum
+      const uint32_t want = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x, qs.s), 0.f), __NV_SATFINITE, __NV_E4M3) & 0xFFu;
+      // through the very function the kernels call, the value in each of the eight positions of a chunk in turn
+      const uint32_t pos = xb & 7u;
+      uint32_t words[4] = {0u, 0u, 0u, 0u};
+      words[pos >> 1] = xb << (16 * (pos & 1u));
+      const uint2 bytes = quant_chunk16<kBf16>(make_uint4(words[0], words[1], words[2], words[3]), qs);
+      const uint32_t got = ((pos < 4 ? bytes.x : bytes.y) >> (8 * (pos & 3u))) & 0xFFu;
+      ++checked;
+      if (want != got) {
+        ++bad_bytes;
+        // remember one example: amax bits, value bits, scale kind, wanted and produced byte
+        atomicCAS(&out[3], 0ull, 1ull | (static_cast<unsigned long long>(amax_bits) << 48) | (static_cast<unsigned long long>(xb) << 32) |
+                                      (static_cast<unsigned long long>(ue8m0) << 24) | (want << 8) | got << 16);
+      }
+      if (qs.finite && __float_as_uint(quotient_corrected(x, qs)) != __float_as_uint(__fdiv_rn(x, qs.s))) ++bad_quotients;
+    }
+  }
+  atomicAdd(&out[0], bad_bytes);
+  atomicAdd(&out[1], bad_quotients);
+  atomicAdd(&out[2], checked);
+}
+
 // scale[i] = the scale the quantisation kernels derive from a block maximum amax[i].
 __global__ void fp8_scale_table_kernel(const float* __restrict__ amax, float* __restrict__ scale, uint32_t n, int ue8m0) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -339,6 +379,16 @@ int awex_launch_fp8_block_quant(const void* x, void* q, void* scales, uint64_t r
     case 3: return launch_quant<float>(x, q, scales, rows, cols, x_stride, q_stride, scale_stride, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, ue8m0, status, s);
     default: return -3;
   }
+}
+
+// out[4] (zeroed by the caller): e4m3 bytes that differ from the true division, fp32 quotients
+// that differ, pairs checked, one packed example of a differing byte.  src_dtype 1: bf16, 2: fp16.
+int awex_launch_fp8_quotient_check(int src_dtype, void* out, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (src_dtype == 1) awex::fp8_quotient_check_kernel<true><<<0x8000, 256, 0, s>>>(static_cast<unsigned long long*>(out));
+  else if (src_dtype == 2) awex::fp8_quotient_check_kernel<false><<<0x8000, 256, 0, s>>>(static_cast<unsigned long long*>(out));
+  else return -3;
+  return cudaGetLastError();
 }
 
 // The scale rule alone, for exhaustive checks of its rounding: scale[i] from amax[i].

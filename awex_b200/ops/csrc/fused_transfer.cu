@@ -44,15 +44,6 @@ __device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
 __device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-// CTA-scope publication of a counter in shared memory
-__device__ __forceinline__ void st_release_cta_shared(uint32_t addr, uint64_t v) {
-  asm volatile("st.release.cta.shared::cta.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
-}
-__device__ __forceinline__ uint64_t ld_acquire_cta_shared(uint32_t addr) {
-  uint64_t v;
-  asm volatile("ld.acquire.cta.shared::cta.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
-  return v;
-}
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -426,9 +417,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 // Ring of kS stages.  Warp 0 is the copy engine's driver: it issues every load
 // and, for pure copies, the stores; all warps work on computed tiles.  Only warp
 // 0 watches the stages' mbarriers (the other warps skip copied tiles and may be
-// many tiles ahead of the loads, where a phase parity means nothing); it
-// publishes the number of the newest computed tile whose data has landed in
-// `ready_tile`, which the other warps acquire before they read the stage.  The stage
+// many tiles ahead of the loads, where a stage's phase parity means nothing).
+// For a computed tile it then arrives on `ready_bar`, whose phases count staged
+// computed tiles only and which the other warps wait on (suspended by the
+// hardware, not polling) before they read the stage: between two of its phases
+// lies the tile's CTA-wide barrier, so no warp is ever more than one phase away.
+// A warp that has passed the barrier of a computed tile less than one ring
+// round ago knows that warp 0 has consumed the previous phase of every stage, so
+// the stage's parity is unambiguous for it: it then waits on the stage's own
+// mbarrier directly and saves the hand-over.  The stage
 // of a computed tile is free once its barrier has been passed, the stage of a
 // copied tile once its store group has finished reading shared memory; warp 0
 // keeps as many loads in flight as that rule allows (kS - 1 ahead of a computed
@@ -439,13 +436,14 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kS];
   __shared__ uint32_t red[2][kT / 32];
-  __shared__ __align__(8) unsigned long long ready_tile;  // 1 + newest computed tile seen complete by warp 0; all ones: give up
-  constexpr uint64_t kGiveUp = ~uint64_t{0};
+  __shared__ __align__(8) uint64_t ready_bar;  // one phase per staged computed tile: warp 0 has seen its data (or gave up)
+  __shared__ volatile int give_up;             // written by warp 0 before it arrives on ready_bar
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t ready_addr = smem_addr(&ready_tile);
+  const uint32_t ready_addr = smem_addr(&ready_bar);
   if (threadIdx.x == 0) {
-    ready_tile = 0;
+    give_up = 0;
+    mbar_init(ready_addr, 1);
     for (int s = 0; s < kS; ++s) mbar_init(smem_addr(&full_bar[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -550,6 +548,8 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
 
     bool prev_copy = false;  // warp 0: was the previous tile a pure copy?
     uint32_t n_computed = 0; // selects the half of `red` (two consecutive computed tiles never share one)
+    uint32_t n_staged = 0;   // staged computed tiles so far: the phase of `ready_bar`
+    uint64_t last_barrier = ~uint64_t{0} >> 1;  // the newest tile at whose barrier all warps met (none yet: far away)
     XferDesc d;              // descriptor of the tile in use
     uint32_t d_index = 0xFFFFFFFFu;
     for (uint64_t i = 0; i < n; ++i) {
@@ -583,7 +583,6 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
           if (__any_sync(0xffffffffu, !arrived)) {
             if (lane == 0 && atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
             my_abort = 1;  // warp 0 stops moving data; it keeps meeting the other warps at their barriers
-            if (lane == 0) st_release_cta_shared(ready_addr, kGiveUp);
           } else {
             waited = i + 1;
             const uint32_t pitch = stage_pitch(d);
@@ -598,36 +597,42 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
       }
       if (warp == 0 && !my_abort) bulk_commit();  // an empty group keeps "one group per tile"
 
-      if (staged && !my_abort) {
+      if (staged) {
+        const uint32_t ready_parity = n_staged & 1;
+        ++n_staged;
+        // Is the previous phase of this stage's mbarrier known to be over?  Yes in the ring's first
+        // round, and when this thread met warp 0 at a computed tile's barrier less than a round ago
+        // (warp 0 had consumed every earlier tile by then).
+        const bool direct = i < kS || i - last_barrier < kS;
         if (warp == 0) {
           // every lane observes the completed phase itself; lane 0 then hands the
-          // observation on to the other warps (release / acquire on `ready_tile`)
-          const bool arrived = mbar_wait_bounded(bar, parity, p.timeout_ns);
-          if (__any_sync(0xffffffffu, !arrived)) {
-            if (lane == 0 && atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
-            my_abort = 1;
-            if (lane == 0) st_release_cta_shared(ready_addr, kGiveUp);
-          } else {
-            waited = i + 1;
-            if (lane == 0) st_release_cta_shared(ready_addr, i + 1);
-          }
-        } else {
-          uint64_t seen = ld_acquire_cta_shared(ready_addr);
-          if (seen < i + 1) {
-            const uint64_t t0 = globaltimer_ns();
-            while ((seen = ld_acquire_cta_shared(ready_addr)) < i + 1) {
-              if (globaltimer_ns() - t0 > 2 * p.timeout_ns) {  // warp 0 gives up first and says so
-                if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
-                seen = kGiveUp;
-                break;
-              }
+          // observation on to the other warps (arrive releases, their wait acquires)
+          if (!my_abort) {
+            const bool arrived = mbar_wait_bounded(bar, parity, p.timeout_ns);
+            if (__any_sync(0xffffffffu, !arrived)) {
+              if (lane == 0 && atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
+              my_abort = 1;
+            } else {
+              waited = i + 1;
             }
           }
-          if (seen == kGiveUp) my_abort = 1;
+          if (lane == 0) {
+            if (my_abort) give_up = 1;
+            mbar_arrive(ready_addr);
+          }
+        } else if (!my_abort) {
+          const bool arrived = direct ? mbar_wait_bounded(bar, parity, 2 * p.timeout_ns) : mbar_wait_bounded(ready_addr, ready_parity, 2 * p.timeout_ns);
+          if (!arrived) {  // warp 0 gives up first and says so
+            if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(use_cur.di);
+            my_abort = 1;
+          } else if (!direct && give_up) {
+            my_abort = 1;
+          }
         }
-      } else if (!staged && warp == 0 && !my_abort) {
+      } else if (warp == 0 && !my_abort) {
         waited = i + 1;
       }
+      last_barrier = i;
       uint32_t* red_now = red[n_computed & 1];
       ++n_computed;
       bool stop;

@@ -97,3 +97,20 @@ def quant_scales(amax: torch.Tensor, scale_ue8m0: bool = False) -> torch.Tensor:
     code = native.load().awex_launch_fp8_scale_table(amax.data_ptr(), out.data_ptr(), amax.numel(), int(scale_ue8m0), native.current_stream_ptr())
     native.check(code, "fp8_scale_table launch")
     return out
+
+
+def quotient_check(dtype: torch.dtype) -> Tuple[int, int, int]:
+    """Run the exhaustive device check of the division-free quotient for a 16-bit
+    source type: ``(e4m3 bytes that differ from the true division, fp32 quotients
+    that differ, pairs checked)`` over every (value, block maximum, scale kind)."""
+    from awex_b200.ops import native
+
+    out = torch.zeros(4, dtype=torch.int64, device="cuda")
+    code = native.load().awex_launch_fp8_quotient_check(_DT[dtype], out.data_ptr(), native.current_stream_ptr())
+    native.check(code, "fp8_quotient_check launch")
+    bad_bytes, bad_quotients, checked, example = (int(v) for v in out.tolist())
+    if example:
+        e = example & 0xFFFFFFFFFFFFFFFF
+        quotient_check.example = dict(amax_bits=hex((e >> 48) & 0xFFFF), value_bits=hex((e >> 32) & 0xFFFF), ue8m0=(e >> 24) & 1,
+                                      got=hex((e >> 16) & 0xFF), want=hex((e >> 8) & 0xFF))
+    return bad_bytes, bad_quotients, checked

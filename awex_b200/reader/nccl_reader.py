@@ -225,9 +225,14 @@ class NCCLWorkerWeightsReader(WorkerWeightsReader):
 
             self.transport = GlooReceiver(exchange_timeout_s=self.exchange_timeout_s, **common)
         self.transport.connect()
+        # epochs only grow, also across a reader that replaces an earlier one of the same rank
+        self.epoch = max(self.epoch, int(getattr(self.transport, "epoch_base", 0)))
         logger.info(f"Rank[{self.transfer_rank}] reader ready in {time.time() - t0:.2f}s, {len(self.parameters)} canonical views")
 
     def begin_update(self, step_id) -> None:
+        # Every attempt gets a new epoch, also one that fails below: flags of an abandoned attempt can then
+        # never satisfy a later wait.  Senders take the epoch from this side's announcement, so their own
+        # count cannot fall out of step with it.
         self.epoch += 1
         moved = self.parameters_moved()
         if moved and getattr(self.transport, "may_move", False):

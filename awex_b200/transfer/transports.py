@@ -20,15 +20,29 @@ inside one NCCL group, staging copies for strided views and a barrier per step
 (`awex/transfer/nccl_comm.py:378-624`, `awex/writer/nccl_writer.py:197-304`,
 `awex/reader/nccl_reader.py:329-398`).
 
+Every update between different processes opens with a rendezvous on the host,
+through counters of the MetaServer that a waiter sleeps on (no polling): a
+receiver announces the update's epoch (``p2p_ready_<dst>``) once its engine is
+paused; a sender launches only after all its destinations have announced, takes
+the epoch from their announcements, and announces its launch
+(``p2p_launched_<src>``); a receiver queues its flag wait only then.  The device
+flags therefore only ever bridge launch latencies, and their bounded waits can
+stay short however far the two sides' schedules drift apart (the reference blocks
+in NCCL receives for as long as it takes, `awex/reader/nccl_reader.py:329-398`).
+A receiver whose wait runs out all the same withdraws its announcement before
+it reports, so that a late sender cannot write into an engine that has resumed.
+
 A sender and a receiver that are different processes on the SAME GPU (the
 reference's co-located deployment) never wait for each other on the device: two
 kernels of different processes are time-sliced, and one that spins on a flag the
-other has yet to write can starve it.  Such pairs shake hands on the host
-instead (``p2p_host_ready_<dst>_<epoch>`` / ``p2p_host_done_<src>_<epoch>``).
+other has yet to write can starve it.  Such pairs also learn of completion on the
+host (``p2p_done_<src>``).  Roles that share one process are ordered by their
+stream and skip the rendezvous.
 
 MetaServer keys used here: ``p2p_addr_<infer transfer rank>`` (address book),
 ``p2p_manifest_<train transfer rank>`` (what that rank writes where, plus the
-address of its ready-flag pad), ``master_info`` (exchange group rendezvous).
+address of its ready-flag pad), the three counters above, ``master_info``
+(exchange group rendezvous).
 """
 
 from __future__ import annotations
@@ -62,12 +76,19 @@ def manifest_key(train_transfer_rank: int) -> str:
     return f"p2p_manifest_{train_transfer_rank}"
 
 
-def host_ready_key(infer_transfer_rank: int, epoch: int) -> str:
-    return f"p2p_host_ready_{infer_transfer_rank}_{epoch}"
+def ready_key(infer_transfer_rank: int) -> str:
+    """Counter ``[epoch, address book epoch]``: this receiver may be written now."""
+    return f"p2p_ready_{infer_transfer_rank}"
 
 
-def host_done_key(train_transfer_rank: int, epoch: int) -> str:
-    return f"p2p_host_done_{train_transfer_rank}_{epoch}"
+def launched_key(train_transfer_rank: int) -> str:
+    """Counter ``[epoch]``: this sender's kernel for the epoch is on its stream."""
+    return f"p2p_launched_{train_transfer_rank}"
+
+
+def done_key(train_transfer_rank: int) -> str:
+    """Counter ``[epoch]``: this sender's writes for the epoch are complete (same-GPU pairs)."""
+    return f"p2p_done_{train_transfer_rank}"
 
 
 class CoverageError(RuntimeError):
@@ -78,14 +99,11 @@ class HostHandshakeTimeout(TimeoutError):
     pass
 
 
-def poll_key(meta, key: str, timeout_s: float, poll_s: float = 0.002) -> None:
-    """Tight poll for a key that the other side of a same-GPU pair posts once per
-    update (the client's own ``wait_key`` backs off from 0.2 s)."""
-    deadline = time.time() + timeout_s
-    while not meta.has_key(key):
-        if time.time() > deadline:
-            raise HostHandshakeTimeout(f"no '{key}' on the meta server after {timeout_s:.1f}s")
-        time.sleep(poll_s)
+def wait_counters(meta, keys, epoch: int, timeout_s: float):
+    try:
+        return meta.wait_counters(list(keys), epoch, timeout_s)
+    except TimeoutError as exc:
+        raise HostHandshakeTimeout(str(exc)) from exc
 
 
 def shares_gpu(book_or_record, my_uuid: str, me: Tuple[str, int]) -> bool:
@@ -135,11 +153,17 @@ class PeerStoreReceiver:
         self.timeout_ms, self.wait_timeout_s = timeout_ms, wait_timeout_s
         self.host_wait_timeout_s = wait_timeout_s if host_wait_timeout_s is None else host_wait_timeout_s
         self.host_senders: List[int] = []
-        self._last_host_epoch: Optional[int] = None
+        # senders in other processes: every update opens with the host rendezvous
+        self.foreign_senders: List[int] = []
+        # CUDA events around this side's GPU work of each update, when a list is put here (benchmarks)
+        self.gpu_events: Optional[list] = None
         self.done_pad = FlagPad(train_world, self.device)
         self.exporter = PeerMemoryExporter(self.device.index)
         self.waiter = None
         self.poster = None
+        # a receiver that replaces an earlier one of the same rank continues its epochs: flags and counters only grow
+        earlier = self.meta.get_counter(ready_key(self.rank)) if hasattr(self.meta, "get_counter") else None
+        self.epoch_base = int(earlier[0]) if earlier else 0
         self.publish()
 
     def _named(self):
@@ -177,6 +201,8 @@ class PeerStoreReceiver:
         my_uuid, me = _device_uuid(self.exporter.device_index), process_identity()
         self.host_senders = [r for r in self.senders if "owner" in records[r] and shares_gpu(records[r], my_uuid, me)]
         device_senders = [r for r in self.senders if r not in self.host_senders]
+        self.foreign_senders = [r for r in self.senders if "owner" not in records[r] or tuple(records[r]["owner"]) != tuple(me)]
+        self.foreign_device_senders = [r for r in device_senders if r in self.foreign_senders]
         ready_addrs = []
         for r in device_senders:
             pad = self.importer.resolve(records[r]["ready_pad"])[READY_PAD]
@@ -190,26 +216,52 @@ class PeerStoreReceiver:
         logger.info(f"inference rank {self.rank}: {len(self.senders)} senders {self.senders}, {self.bytes_in} bytes per update")
 
     def begin(self, epoch: int) -> None:
-        """Tell every sender that parameters may be overwritten now."""
+        """Tell every sender that parameters may be overwritten now: device flags
+        for the kernels, the ready counter for the hosts that launch them."""
         if self.may_move:
             self.republish_if_moved()
         self.poster.launch(epoch)
         if self.host_senders or self.may_move:
             # work queued on this GPU before the update must not read half-written weights
             torch.cuda.current_stream(self.device).synchronize()
-            # the value is the epoch of the address book that is valid for this update
-            self.meta.put_object(host_ready_key(self.rank, epoch), self.exporter.epoch)
-            if self._last_host_epoch is not None and self._last_host_epoch != epoch:
-                self.meta.delete_if_exists(host_ready_key(self.rank, self._last_host_epoch))
-            self._last_host_epoch = epoch
+        if self.foreign_senders:
+            # the second value is the epoch of the address book that is valid for this update
+            self.meta.put_counter(ready_key(self.rank), [epoch, self.exporter.epoch])
 
     def finish(self, epoch: int, synchronize: bool = True) -> None:
-        self.waiter.launch(epoch)
-        for r in self.host_senders:
-            poll_key(self.meta, host_done_key(self.infer_world + r, epoch), self.host_wait_timeout_s)
+        if self.foreign_device_senders:
+            # queue the device wait only once every sender's kernel is on its stream: the wait's
+            # deadline then covers a transfer, not the drift between the two sides' schedules
+            wait_counters(self.meta, [launched_key(self.infer_world + r) for r in self.foreign_device_senders], epoch, self.host_wait_timeout_s)
+        if self.gpu_events is not None:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            self.waiter.launch(epoch)
+            stop.record()
+            self.gpu_events.append((start, stop))
+        else:
+            self.waiter.launch(epoch)
+        if self.host_senders:
+            wait_counters(self.meta, [done_key(self.infer_world + r) for r in self.host_senders], epoch, self.host_wait_timeout_s)
         if synchronize:
             torch.cuda.current_stream(self.device).synchronize()
-            self.waiter.status.raise_if_failed()
+            try:
+                self.waiter.status.raise_if_failed()
+            except Exception:
+                self.withdraw(epoch)
+                raise
+
+    def withdraw(self, epoch: int) -> None:
+        """Take back the announcement of ``epoch`` (the update failed on this side):
+        a sender that has not started yet then finds the destination not ready and
+        gives up without writing, instead of writing into an engine that resumed."""
+        try:
+            self.poster.launch(epoch - 1)
+            if self.foreign_senders:
+                self.meta.put_counter(ready_key(self.rank), [epoch - 1, self.exporter.epoch])
+            torch.cuda.current_stream(self.device).synchronize()
+        except Exception as exc:  # the original failure is what the caller must see
+            logger.error(f"inference rank {self.rank}: could not withdraw the announcement of epoch {epoch}: {exc!r}")
 
     def gpu_launches_per_update(self) -> int:
         return (1 if self.poster and self.poster.n else 0) + (1 if self.waiter and self.waiter.n else 0)
@@ -237,7 +289,10 @@ class PeerStoreSender:
         self.moving_destinations: List[int] = []
         self._book_epochs: Dict[int, int] = {}
         self.rebuilds = 0
-        self._last_host_epoch: Optional[int] = None
+        # destinations owned by other processes (the rendezvous partners) and the last epoch sent
+        self.foreign_destinations: List[int] = []
+        self.last_epoch = 0
+        self.gpu_events: Optional[list] = None  # CUDA events around each kernel launch, when a list is put here
         self.ready_pad = FlagPad(infer_world, self.device)
         self.exporter = PeerMemoryExporter(self.device.index)
         self.manifest = manifest_by_destination(self.items)
@@ -266,8 +321,10 @@ class PeerStoreSender:
             self._book_epochs[d] = book.epoch
             if getattr(book, "may_move", False) and tuple(book.owner) != me:
                 self.moving_destinations.append(d)
+            if tuple(book.owner) != me:
+                self.foreign_destinations.append(d)
             if shares_gpu(book, my_uuid, me):
-                self.host_destinations.append(d)  # same GPU, other process: host handshake
+                self.host_destinations.append(d)  # same GPU, other process: completion is announced on the host
             elif tuple(book.owner) != me or book.device_uuid != my_uuid:
                 # another process, or this process on another GPU (no stream orders the two devices): device flags
                 remote.append(d)
@@ -344,24 +401,32 @@ class PeerStoreSender:
         striped table order deal the whole table to all CTAs as one group."""
         return os.environ.get("AWEX_XFER_DEST_GROUPS", "1") != "0" and cls._stripe_bytes() == 0
 
-    def _follow_moves(self, epoch: int) -> None:
-        """Wait until every destination that may move has named the address book
-        that is valid for this update; when one of them is newer than the book the
-        table was built from, unmap everything, fetch the books again and rebuild
-        the table."""
-        stale = False
-        for d in self.moving_destinations:
-            key = host_ready_key(d, epoch)
-            poll_key(self.meta, key, self.host_wait_timeout_s)
-            stale = stale or int(self.meta.get_object(key, timeout=self.host_wait_timeout_s)) != self._book_epochs.get(d)
+    def _rendezvous(self, epoch: int) -> int:
+        """Wait until every destination in another process has announced an update
+        newer than the last one sent; returns its epoch.  The announcement also names
+        the address book that is valid for the update: when a destination that may
+        move names a newer book than the table was built from, everything is unmapped,
+        the books are fetched again and the table is rebuilt."""
+        if not self.foreign_destinations:
+            return epoch
+        values = wait_counters(self.meta, [ready_key(d) for d in self.foreign_destinations], self.last_epoch + 1, self.host_wait_timeout_s)
+        announced = {d: int(values[ready_key(d)][0]) for d in self.foreign_destinations}
+        if len(set(announced.values())) > 1:
+            raise RuntimeError(f"training rank {self.train_rank}: destinations announce different update epochs {announced}; "
+                               "an update failed on some of them: start the next update on all inference workers")
+        agreed = next(iter(announced.values()))
+        if agreed != epoch:
+            logger.info(f"training rank {self.train_rank}: following the inference side's epoch {agreed} (own count {epoch})")
+        stale = any(int(values[ready_key(d)][1]) != self._book_epochs.get(d) for d in self.moving_destinations)
         if stale:
             self._rebuild("destinations moved")
+        return agreed
 
     def _rebuild(self, why: str) -> None:
         """Unmap everything, fetch the address books again and encode a new table
         from the current source and destination addresses."""
         self.importer.close_all()
-        self.host_destinations, self.moving_destinations, self._book_epochs = [], [], {}
+        self.host_destinations, self.moving_destinations, self.foreign_destinations, self._book_epochs = [], [], [], {}
         self.connect()
         self.rebuilds += 1
         logger.info(f"training rank {self.train_rank}: {why}, table rebuilt ({self.rebuilds} so far)")
@@ -371,24 +436,31 @@ class PeerStoreSender:
         the table holds their old addresses and must be encoded again."""
         self._rebuild("training tensors moved")
 
-    def send(self, epoch: int, synchronize: bool = True) -> None:
-        if self.moving_destinations:
-            self._follow_moves(epoch)
-        for d in self.host_destinations:
-            poll_key(self.meta, host_ready_key(d, epoch), self.host_wait_timeout_s)
+    def send(self, epoch: Optional[int] = None, synchronize: bool = True) -> int:
+        """One update; returns the epoch it carried (the inference side's, when
+        destinations live in other processes)."""
+        epoch = self._rendezvous(self.last_epoch + 1 if epoch is None else epoch)
         if env.flag("AWEX_P2P_TRACE"):
             per_dst = {d: sum(entry_nbytes(e) for e in es) for d, es in self.manifest.items()}
             logger.info(f"[p2p] train rank {self.train_rank} epoch {epoch}: {self.n_desc} descriptors, {self.program.n_tiles} tiles, "
                         f"bytes per destination {per_dst}, host-synchronised {self.host_destinations}")
-        self.program.launch(epoch)
+        if self.gpu_events is not None:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            self.program.launch(epoch)
+            stop.record()
+            self.gpu_events.append((start, stop))
+        else:
+            self.program.launch(epoch)
+        self.last_epoch = epoch
+        if self.foreign_destinations:
+            self.meta.put_counter(launched_key(self.transfer_rank), [epoch])
         if synchronize or self.host_destinations:
             torch.cuda.current_stream(self.device).synchronize()
             self.program.check()
         if self.host_destinations:
-            self.meta.put_object(host_done_key(self.transfer_rank, epoch), 1)
-            if self._last_host_epoch is not None and self._last_host_epoch != epoch:
-                self.meta.delete_if_exists(host_done_key(self.transfer_rank, self._last_host_epoch))
-            self._last_host_epoch = epoch
+            self.meta.put_counter(done_key(self.transfer_rank), [epoch])
+        return epoch
 
     def gpu_launches_per_update(self) -> int:
         return 1
@@ -472,6 +544,7 @@ class GlooSender:
                     works.append((work, msg))
         for w, _keepalive in works:
             w.wait()
+        return epoch
 
     def gpu_launches_per_update(self) -> int:
         return 0

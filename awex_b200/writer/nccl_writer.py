@@ -111,13 +111,14 @@ class NCCLWeightsWriter(WeightsExchangeShardingWriter):
 
     def _write_weights(self, step_id, **kwargs) -> None:
         t0 = time.time()
-        self.epoch += 1
         self._follow_moved_sources()
         if self.derived:
             with phase("derive_tensors"):
                 refresh_derived(self.derived, self._local, self._gather_tp_shards)  # same stream as the transfer: ordered before it
         with phase("send_weights"):
-            self.transport.send(self.epoch, synchronize=kwargs.get("synchronize", True))
+            # the count moves only when an update went out; across processes the transport follows the epoch the
+            # inference side announces, so a failed or repeated update on either side cannot put the two out of step
+            self.epoch = self.transport.send(self.epoch + 1, synchronize=kwargs.get("synchronize", True))
         compute_statistics(self._history, step_id, time.time() - t0, "Send weights")
 
     def close(self) -> None:

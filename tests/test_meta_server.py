@@ -137,17 +137,36 @@ def test_client_gives_up_when_the_server_is_gone():
     c.delete_if_exists("x")  # swallowed
 
 
-def test_host_handshake_poll_times_out_quickly(served):
-    from awex_b200.transfer.transports import HostHandshakeTimeout, host_done_key, host_ready_key, poll_key
+def test_counters_wake_waiters_without_polling(served):
+    """`put_counter` / `wait_counters`: a waiter sleeps inside the server and is
+    answered when the last counter it names reaches the value; a wait that cannot
+    be satisfied ends with the host-handshake timeout of the data plane."""
+    import threading
+
+    from awex_b200.transfer.transports import HostHandshakeTimeout, done_key, launched_key, ready_key, wait_counters
 
     _, c = served
-    assert host_ready_key(3, 7) == "p2p_host_ready_3_7" and host_done_key(9, 7) == "p2p_host_done_9_7"
+    assert ready_key(3) == "p2p_ready_3" and launched_key(9) == "p2p_launched_9" and done_key(9) == "p2p_done_9"
+    assert c.get_counter(ready_key(0)) is None
     started = time.time()
     with pytest.raises(HostHandshakeTimeout):
-        poll_key(c, host_ready_key(0, 1), timeout_s=0.2)
+        wait_counters(c, [ready_key(0)], 1, timeout_s=0.2)
     assert time.time() - started < 2
-    c.put_object(host_ready_key(0, 1), 1)
-    poll_key(c, host_ready_key(0, 1), timeout_s=0.2)
+    c.put_counter(ready_key(0), [1, 5])
+    assert wait_counters(c, [ready_key(0)], 1, timeout_s=0.2) == {ready_key(0): [1, 5]}
+    with pytest.raises(HostHandshakeTimeout):  # epoch 1 is there, epoch 2 is not
+        wait_counters(c, [ready_key(0)], 2, timeout_s=0.2)
+    # two counters, the second arrives while the request sleeps in the server
+    other = MetaServerClient("127.0.0.1", c._port)
+    timer = threading.Timer(0.3, lambda: other.put_counter(ready_key(1), 4))
+    timer.start()
+    started = time.time()
+    got = wait_counters(c, [ready_key(0), ready_key(1)], 1, timeout_s=10)
+    waited = time.time() - started
+    timer.join()
+    assert got == {ready_key(0): [1, 5], ready_key(1): [4]} and 0.2 < waited < 3
+    c.put_counter("odd/key with spaces", 7)  # keys are quoted on the wire
+    assert c.get_counter("odd/key with spaces") == [7]
 
 
 @pytest.mark.timeout(180)

@@ -93,7 +93,7 @@ class FakeProgram:
     def launch(self, epoch):
         self.launches.append(epoch)
         with DONE:  # what the kernel's first wait does: every peer destination must have announced this epoch
-            assert DONE.wait_for(lambda: DONE.ready.get(epoch, 0) >= len(self.ready_slots), timeout=30), f"no ready flags for epoch {epoch}"
+            assert DONE.wait_for(lambda: DONE.ready.get(epoch, 0) >= len(self.ready_slots), timeout=DEVICE_WAIT_S[0]), f"no ready flags for epoch {epoch}"
         assert run_table(self.table, self.n_tiles, HostMemory(MEMORY), self.encoder.row_offsets, tile_order=self.order) == self.n_tiles
         with DONE:  # what the kernel's last CTA does with the receivers' done flags
             DONE.count[epoch] = DONE.count.get(epoch, 0) + 1
@@ -105,6 +105,7 @@ class FakeProgram:
 
 DONE = threading.Condition()
 DONE.count, DONE.ready = {}, {}
+DEVICE_WAIT_S = [30.0]  # how long the stand-in kernels wait for a flag (the real ones: two seconds)
 
 
 class FakePoster:
@@ -128,7 +129,7 @@ class FakeWaiter:
     def launch(self, epoch, stream_ptr=None):
         self.launches.append(epoch)
         with DONE:
-            assert DONE.wait_for(lambda: DONE.count.get(epoch, 0) >= self.n, timeout=30), f"flags of epoch {epoch} never came"
+            assert DONE.wait_for(lambda: DONE.count.get(epoch, 0) >= self.n, timeout=DEVICE_WAIT_S[0]), f"flags of epoch {epoch} never came"
 
 
 @pytest.fixture
@@ -143,6 +144,7 @@ def fakes(monkeypatch):
     monkeypatch.setattr(fused_transfer, "FlagPoster", FakePoster)
     monkeypatch.setattr(fused_transfer, "FlagWaiter", FakeWaiter)
     DONE.count, DONE.ready = {}, {}
+    monkeypatch.setitem(DEVICE_WAIT_S, 0, 30.0)
     monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: SimpleNamespace(synchronize=lambda: None))
     FakeImporter.opened = FakeImporter.closed = FakeProgram.built = 0
     MEMORY.clear()
@@ -205,13 +207,92 @@ def test_two_processes_exchange_through_books_manifests_and_handshakes(fakes, gp
         assert receiver.bytes_in == sender.bytes_out and sender.bytes_remote == (0 if host_pair else sender.bytes_out)
         update(sender, receiver, 1)
         assert job.mismatches() == [] and sender.program.launches == [1]
-        if host_pair:  # same GPU, two processes: the sides met on the host
-            from awex_b200.transfer.transports import host_done_key, host_ready_key
+        # two processes: the update opened with the rendezvous on the host, whatever GPUs they sit on
+        from awex_b200.transfer.transports import done_key, launched_key, ready_key
 
-            assert meta.has_key(host_ready_key(0, 1)) and meta.has_key(host_done_key(1, 1))
-            update(sender, receiver, 2)
-            assert not meta.has_key(host_ready_key(0, 1)) and meta.has_key(host_ready_key(0, 2))  # old epochs are cleaned up
+        assert meta.get_counter(ready_key(0)) == [1, 1] and meta.get_counter(launched_key(1)) == [1]
+        assert meta.get_counter(done_key(1)) == ([1] if host_pair else None)  # completion on the host only for a same-GPU pair
+        update(sender, receiver, 2)
+        assert meta.get_counter(ready_key(0)) == [2, 1] and meta.get_counter(launched_key(1)) == [2]
         assert FakeProgram.built == 1 and FakeImporter.opened == 2  # planned and mapped once, whatever the number of updates
+    finally:
+        server.stop()
+
+
+@pytest.mark.parametrize("late", ["sender", "receiver"])
+def test_sides_that_reach_the_update_seconds_apart_meet_on_the_host(fakes, late):
+    """Trainer and inference side on different GPUs reach an update three seconds
+    apart (normal in an RL loop) while the device waits last one second: neither
+    kernel is launched before its partner is there, so no device wait runs out,
+    and the sender follows the epoch the receiver announces."""
+    import time
+
+    job, items, local, views, server, meta = build_pair(("GPU-a", "GPU-b"))
+    try:
+        sender, receiver = make_sides(job, items, local, views, meta)
+        DEVICE_WAIT_S[0] = 1.0
+        failures, order = [], []
+
+        def inference_side(delay):
+            try:
+                time.sleep(delay)
+                with acting_as("infer0"):
+                    receiver.begin(5)  # the receiver's own epoch; the sender has counted nothing yet
+                    order.append("announced")
+                    receiver.finish(5)
+            except BaseException as exc:  # noqa: BLE001
+                failures.append(exc)
+
+        def training_side(delay):
+            try:
+                time.sleep(delay)
+                with acting_as("train0"):
+                    order.append(("sent", sender.send()))
+            except BaseException as exc:  # noqa: BLE001
+                failures.append(exc)
+
+        threads = [threading.Thread(target=inference_side, args=(3.0 if late == "receiver" else 0.0,)),
+                   threading.Thread(target=training_side, args=(3.0 if late == "sender" else 0.0,))]
+        started = time.time()
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(60)
+        assert not failures, failures
+        assert time.time() - started >= 3.0 and order == ["announced", ("sent", 5)]
+        assert sender.program.launches == [5] and sender.last_epoch == 5 and job.mismatches() == []
+    finally:
+        server.stop()
+
+
+def test_a_receiver_that_gives_up_withdraws_its_announcement(fakes):
+    """The receiver's device wait runs out (its sender never launched a kernel that
+    completes): before it reports, it takes its announcement back, on the device
+    flags and on the host counter, so that a sender arriving later finds the
+    destination not ready."""
+    from awex_b200.ops.fused_transfer import TransferError
+    from awex_b200.transfer.transports import HostHandshakeTimeout, ready_key
+
+    job, items, local, views, server, meta = build_pair(("GPU-a", "GPU-b"))
+    try:
+        sender, receiver = make_sides(job, items, local, views, meta)
+        sender.host_wait_timeout_s = 0.3
+
+        def failed():
+            raise TransferError(3, (0, 0, 0))
+
+        receiver.waiter.status = SimpleNamespace(raise_if_failed=failed)
+        receiver.foreign_device_senders = []  # skip the wait for the launch announcement: the device wait is what fails here
+        receiver.waiter.launch = lambda epoch, stream_ptr=None: None
+        with acting_as("infer0"):
+            receiver.begin(1)
+            assert meta.get_counter(ready_key(0)) == [1, 1]
+            with pytest.raises(TransferError):
+                receiver.finish(1)
+        assert meta.get_counter(ready_key(0)) == [0, 1] and receiver.poster.launches == [1, 0]
+        with acting_as("train0"), pytest.raises(HostHandshakeTimeout):
+            sender.send()  # nothing to write into: the announcement is gone
+        assert sender.program.launches == []
     finally:
         server.stop()
 
@@ -222,7 +303,7 @@ def test_a_receiver_whose_parameters_move_is_followed_by_its_senders(fakes, gpus
     the receiver publishes a new address book before it announces the update, the
     announcement names the book's epoch, and a sender that built its table from
     an older book unmaps, fetches and rebuilds before it writes."""
-    from awex_b200.transfer.transports import addr_key, host_ready_key
+    from awex_b200.transfer.transports import addr_key, ready_key
 
     job, items, local, views, server, meta = build_pair(gpus)
     try:
@@ -230,7 +311,7 @@ def test_a_receiver_whose_parameters_move_is_followed_by_its_senders(fakes, gpus
         assert sender.moving_destinations == [0] and meta.get_object(addr_key(0), timeout=5).may_move
         update(sender, receiver, 1)
         assert job.mismatches() == [] and sender.rebuilds == 0
-        assert meta.get_object(host_ready_key(0, 1), timeout=5) == 1  # the announcement carries the epoch of the valid book
+        assert meta.get_counter(ready_key(0)) == [1, 1]  # the announcement carries the epoch of the valid book
         update(sender, receiver, 2)
         assert sender.rebuilds == 0 and FakeProgram.built == 1  # nothing moved: one extra host round trip, nothing else
 
@@ -246,7 +327,7 @@ def test_a_receiver_whose_parameters_move_is_followed_by_its_senders(fakes, gpus
             receiver.rebind(job.destination_views()[0])
         update(sender, receiver, 3)
         assert sender.rebuilds == 1 and FakeProgram.built == 2 and FakeImporter.closed == 1
-        assert meta.get_object(addr_key(0), timeout=5).epoch == 2 and meta.get_object(host_ready_key(0, 3), timeout=5) == 2
+        assert meta.get_object(addr_key(0), timeout=5).epoch == 2 and meta.get_counter(ready_key(0)) == [3, 2]
         assert job.mismatches() == []                                 # the new tensors hold the weights
         assert all(bool((t == 7.0).all()) for t in old.values())      # and nobody wrote through the stale addresses
         update(sender, receiver, 4)
