@@ -229,6 +229,15 @@ class PeerStoreReceiver:
             self.meta.put_counter(ready_key(self.rank), [epoch, self.exporter.epoch])
 
     def finish(self, epoch: int, synchronize: bool = True) -> None:
+        try:
+            self._finish(epoch, synchronize)
+        except Exception:
+            # whatever went wrong (no sender announced its launch, a flag never came): this side gives the update
+            # up, so nobody may write here any more
+            self.withdraw(epoch)
+            raise
+
+    def _finish(self, epoch: int, synchronize: bool) -> None:
         if self.foreign_device_senders:
             # queue the device wait only once every sender's kernel is on its stream: the wait's
             # deadline then covers a transfer, not the drift between the two sides' schedules
@@ -245,11 +254,7 @@ class PeerStoreReceiver:
             wait_counters(self.meta, [done_key(self.infer_world + r) for r in self.host_senders], epoch, self.host_wait_timeout_s)
         if synchronize:
             torch.cuda.current_stream(self.device).synchronize()
-            try:
-                self.waiter.status.raise_if_failed()
-            except Exception:
-                self.withdraw(epoch)
-                raise
+            self.waiter.status.raise_if_failed()
 
     def withdraw(self, epoch: int) -> None:
         """Take back the announcement of ``epoch`` (the update failed on this side):

@@ -28,7 +28,6 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-PUBLISHED_10B_SECONDS = 0.8  # the reference's published NCCL-mode time for a 10B / 31 GB model
 
 
 def parse_args():
@@ -167,15 +166,14 @@ def run_single_gpu(args):
         "warmup": args.warmup,
         "ms_per_step": ms,
         "higher_is_better": False,
-        "scaling": "strong",
-        "vs_baseline": seconds / PUBLISHED_10B_SECONDS,
+        "scaling": "per-N layouts (not a scaling series)",
+        "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic random-init N(0,0.02) weights from per-name seeds",
         "impl": "ours",
         "config": {
             "model": arch.name, "params": arch.param_count(), "bytes_per_update": bytes_out, "parallelism": label,
             "mode": "colocated", "l2": "inputs (>=16 GB) exceed L2; no flush needed", "validated_bitwise": valid,
-            "vs_baseline_note": "reference publishes only 10B/31GB in 0.8 s on an unnamed cluster; ratio is ours / 0.8 s",
         },
         "aggregate_GBps": bytes_out / seconds / 1e9,
         "hbm_GBps_read_plus_write": 2 * bytes_out / seconds / 1e9,
@@ -196,15 +194,18 @@ def run_single_gpu(args):
 def main():
     args = parse_args()
     if args.impl == "reference":
+        from baseline.reference_bench import run_reference, run_reference_colocated
+
+        if args.config == "colocated" or (args.config == "separated" and args.gpus == 1):
+            # co-located deployment (and the one-GPU point of the default series, where both roles share the GPU)
+            args.model = args.model or ("llama3-8b" if args.config == "separated" else "qwen2.5-32b")
+            return run_reference_colocated(args)
         if args.config != "separated":
-            # the reference's co-located writer reads attributes nothing assigns
-            # (`awex/writer/nccl_writer.py:175,182`): only its separated mode runs unmodified
             if int(os.environ.get("RANK", "0")) != 0:
                 return None
-            return emit({"impl": "reference", "unavailable": "the unmodified reference cannot run its co-located mode (nccl_writer.py:175,182 read unset attributes)"})
+            return emit({"impl": "reference", "unavailable": f"the reference harness does not build the '{args.config}' configuration "
+                         "(co-located MoE / fp8 layouts: see BASELINE.md for why the reference cannot express them)"})
         args.model = args.model or "llama3-8b"
-        from baseline.reference_bench import run_reference
-
         return run_reference(args)
     if args.emulate:
         args.model = args.model or "llama3-8b"

@@ -93,7 +93,7 @@ class FakeProgram:
     def launch(self, epoch):
         self.launches.append(epoch)
         with DONE:  # what the kernel's first wait does: every peer destination must have announced this epoch
-            assert DONE.wait_for(lambda: DONE.ready.get(epoch, 0) >= len(self.ready_slots), timeout=DEVICE_WAIT_S[0]), f"no ready flags for epoch {epoch}"
+            assert DONE.wait_for(lambda: DONE.ready.get(epoch, 0) >= len(self.ready_slots), timeout=DEVICE_WAIT_S["s"]), f"no ready flags for epoch {epoch}"
         assert run_table(self.table, self.n_tiles, HostMemory(MEMORY), self.encoder.row_offsets, tile_order=self.order) == self.n_tiles
         with DONE:  # what the kernel's last CTA does with the receivers' done flags
             DONE.count[epoch] = DONE.count.get(epoch, 0) + 1
@@ -105,7 +105,7 @@ class FakeProgram:
 
 DONE = threading.Condition()
 DONE.count, DONE.ready = {}, {}
-DEVICE_WAIT_S = [30.0]  # how long the stand-in kernels wait for a flag (the real ones: two seconds)
+DEVICE_WAIT_S = {"s": 30.0}  # how long the stand-in kernels wait for a flag (the real ones: two seconds)
 
 
 class FakePoster:
@@ -129,7 +129,7 @@ class FakeWaiter:
     def launch(self, epoch, stream_ptr=None):
         self.launches.append(epoch)
         with DONE:
-            assert DONE.wait_for(lambda: DONE.count.get(epoch, 0) >= self.n, timeout=DEVICE_WAIT_S[0]), f"flags of epoch {epoch} never came"
+            assert DONE.wait_for(lambda: DONE.count.get(epoch, 0) >= self.n, timeout=DEVICE_WAIT_S["s"]), f"flags of epoch {epoch} never came"
 
 
 @pytest.fixture
@@ -144,7 +144,7 @@ def fakes(monkeypatch):
     monkeypatch.setattr(fused_transfer, "FlagPoster", FakePoster)
     monkeypatch.setattr(fused_transfer, "FlagWaiter", FakeWaiter)
     DONE.count, DONE.ready = {}, {}
-    monkeypatch.setitem(DEVICE_WAIT_S, 0, 30.0)
+    monkeypatch.setitem(DEVICE_WAIT_S, "s", 30.0)
     monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: SimpleNamespace(synchronize=lambda: None))
     FakeImporter.opened = FakeImporter.closed = FakeProgram.built = 0
     MEMORY.clear()
@@ -230,7 +230,7 @@ def test_sides_that_reach_the_update_seconds_apart_meet_on_the_host(fakes, late)
     job, items, local, views, server, meta = build_pair(("GPU-a", "GPU-b"))
     try:
         sender, receiver = make_sides(job, items, local, views, meta)
-        DEVICE_WAIT_S[0] = 1.0
+        DEVICE_WAIT_S["s"] = 1.0
         failures, order = [], []
 
         def inference_side(delay):
