@@ -3,8 +3,10 @@ timing:  ``python -m awex_b200.ops.profile_cases <case> [--mb N] [--iters K]``.
 
 Cases: ``transfer_copy`` (contiguous slabs, bulk path), ``transfer_strided``
 (column slabs with 2 KiB runs), ``transfer_cast`` (bf16 -> fp32 elementwise),
-``transfer_fp8`` (fused block quantisation), ``fp8_quant`` / ``fp8_dequant``
-(stand-alone kernels), ``checksum``.  Every case holds a few hundred MB (more
+``transfer_fp8`` (fused block quantisation), ``transfer_peer`` (contiguous
+slabs stored into the memory of a second GPU of this process over NVLink; needs
+two devices), ``fp8_quant`` / ``fp8_dequant`` (stand-alone kernels),
+``checksum``.  Every case holds a few hundred MB (more
 than L2) and prints achieved GB/s from CUDA-event timings.
 """
 
@@ -40,7 +42,19 @@ def _transfer_case(kind: str, mb: int):
     g = torch.Generator(device="cuda").manual_seed(0)
     src = torch.randn(rows, cols, generator=g, device="cuda").to(torch.bfloat16)
     views = {}
-    if kind == "transfer_copy":
+    if kind == "transfer_peer":
+        if torch.cuda.device_count() < 2:
+            raise SystemExit("transfer_peer needs two GPUs")
+        from awex_b200.ops import native
+
+        code = native.load().awex_enable_peer_access(0, 1)
+        if code != 0:
+            raise SystemExit(f"no peer access from device 0 to device 1 (code {code})")
+        dst = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda:1")
+        items = [CopyItem("w", 0, (0, 0), (rows, cols), 0, "w", (0, 0), torch.bfloat16, torch.bfloat16)]
+        views["w"] = dst
+        moved = src.numel() * 2  # bytes that cross the link, one direction
+    elif kind == "transfer_copy":
         dst = torch.zeros_like(src)
         items = [CopyItem("w", 0, (0, 0), (rows, cols), 0, "w", (0, 0), torch.bfloat16, torch.bfloat16)]
         views["w"] = dst
@@ -79,7 +93,13 @@ def _transfer_case(kind: str, mb: int):
         epoch[0] += 1
         prog.launch(epoch[0])
 
-    return run, moved, lambda: prog.status.raise_if_failed()
+    def check():
+        prog.status.raise_if_failed()
+        if kind == "transfer_peer":
+            torch.cuda.synchronize(1)
+            assert torch.equal(views["w"].to("cuda:0"), src), "peer destination differs from the source"
+
+    return run, moved, check
 
 
 def main():

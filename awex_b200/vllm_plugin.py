@@ -187,12 +187,38 @@ def execute_task_on_worker(worker, groups, task_module: str, task_qualname: str,
 
 
 # ---- worker patches (need vLLM) -----------------------------------------------------------------
+def reload_load_config(load_config, load_format: Optional[str] = None):
+    """The load configuration for re-reading weights from a checkpoint directory:
+    the engine's own, with ``load_format`` when the caller names one, and never the
+    ``dummy`` format (a server started with random weights would otherwise answer a
+    reload with fresh random weights instead of the checkpoint's)."""
+    import copy
+
+    current = str(getattr(load_config, "load_format", "auto"))
+    current = current.rsplit(".", 1)[-1].lower()  # enum members print as LoadFormat.DUMMY on older releases
+    wanted = load_format or ("auto" if current == "dummy" else None)
+    if not wanted or wanted == current:
+        return load_config
+    changed = copy.copy(load_config)
+    object.__setattr__(changed, "load_format", wanted)  # the config may be a frozen dataclass
+    return changed
+
+
 def worker_update_weights_from_disk(self, model_path: str, load_format: Optional[str] = None):
     from vllm.model_executor.model_loader import get_model_loader
 
     self.model_runner.model_config.model = model_path
-    loader = get_model_loader(self.model_runner.vllm_config.load_config)
-    loader.load_weights(self.model_runner.model, model_config=self.model_runner.model_config)
+    vllm_config = self.model_runner.vllm_config
+    loader = get_model_loader(reload_load_config(vllm_config.load_config, load_format))
+    try:  # newer loaders read the engine configuration from a context that is only set while the engine builds its model
+        from vllm.config import set_current_vllm_config
+    except Exception:
+        set_current_vllm_config = None
+    if set_current_vllm_config is None:
+        loader.load_weights(self.model_runner.model, model_config=self.model_runner.model_config)
+    else:
+        with set_current_vllm_config(vllm_config):
+            loader.load_weights(self.model_runner.model, model_config=self.model_runner.model_config)
     return True
 
 

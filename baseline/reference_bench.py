@@ -119,6 +119,8 @@ class _ColocatedTrainEngine(_TrainEngine):
     def __init__(self, model, hf_config, meta_server_addr):
         super().__init__(model, hf_config, meta_server_addr)
         self._backup = {name: p.detach().clone() for name, p in model.named_parameters()}
+        # a parameter may be a view at an offset into a larger storage (a row slice of a full tensor)
+        self._storage_bytes = {name: p.untyped_storage().size() for name, p in model.named_parameters()}
 
     def resume_memory_occupation(self, tags=None):
         import torch
@@ -129,8 +131,8 @@ class _ColocatedTrainEngine(_TrainEngine):
             for name, p in self.model.named_parameters():
                 keep = self._backup[name]
                 storage = p.untyped_storage()
-                if storage.size() < keep.numel() * keep.element_size():
-                    storage.resize_(keep.untyped_storage().size())
+                if storage.size() < self._storage_bytes[name]:
+                    storage.resize_(self._storage_bytes[name])
                     p.copy_(keep)
 
 
@@ -188,12 +190,16 @@ def colocated_child(rank, world, store_addr, store_port, meta_addr, arch, steps,
             torch.cuda.synchronize()
             wall_ms.append((time.perf_counter() - t0) * 1e3)
             times_ms.append(start.elapsed_time(stop))
-        valid = True
+        valid, bad = True, []
         if validate:
             want = synth.vllm_module(arch, world, rank, torch.bfloat16, device, hf_config)
-            valid = all(torch.equal(a, b) for (_, a), (_, b) in zip(model.named_parameters(), want.named_parameters()))
+            for (name, a), (_, b) in zip(model.named_parameters(), want.named_parameters()):
+                if not torch.equal(a, b):
+                    bad.append((name, "all zero" if not bool(a.any()) else f"{int((a != b).sum())} of {a.numel()} differ"))
+            valid = not bad
         local_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
-        store.set(f"result_infer{rank}", json.dumps({"ms": times_ms[warmup:], "wall": wall_ms[warmup:], "bytes": local_bytes, "valid": valid}))
+        store.set(f"result_infer{rank}", json.dumps({"ms": times_ms[warmup:], "wall": wall_ms[warmup:], "bytes": local_bytes, "valid": valid,
+                                                     "mismatching": bad[:6], "n_mismatching": len(bad)}))
     except BaseException:
         import traceback
 
@@ -333,6 +339,7 @@ def run_reference_colocated(args):
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "per-N layouts (not a scaling series)",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic random-init N(0,0.02) weights from per-name seeds",
                 "impl": "reference", "instance_attrs_set": ["asystem_train_config = {}", "backend = 'nccl'"],
+                "mismatching_parameters": [r.get("mismatching") for r in results if r.get("n_mismatching")],
                 "config": bench_config(arch, total_bytes, f"colocated-tp{world}->tp{world}", "colocated",
                                        all(r.get("valid", True) for r in results), extra={
                     "processes": "one training and one inference process per GPU (CUDA IPC hand-over, NCCL among the inference processes)",

@@ -76,3 +76,18 @@ def test_routes_are_added_by_the_real_build_app_and_drive_the_adapter(patched):
     failed = client.post("/areal_awex_update", json={"step_id": -1})
     assert failed.status_code == 500 and "no such step" in failed.json()["message"]
     assert calls == [("new", engine_client, "127.0.0.1:9", "nccl", 2), ("initialize",), ("update", 7, {"path": "/x"})]
+
+
+def test_a_reload_from_disk_never_uses_the_dummy_loader(patched):
+    """A server started with `--load-format dummy` must read the checkpoint when it
+    is asked to reload from disk, and a caller's `load_format` wins."""
+    from vllm.config import LoadConfig
+    from vllm.model_executor.model_loader import get_model_loader
+
+    dummy = LoadConfig(load_format="dummy")
+    picked = patched.reload_load_config(dummy)
+    assert str(picked.load_format).rsplit(".", 1)[-1].lower() == "auto" and str(dummy.load_format).rsplit(".", 1)[-1].lower() == "dummy"
+    assert type(get_model_loader(picked)).__name__ != type(get_model_loader(dummy)).__name__
+    auto = LoadConfig(load_format="auto")
+    assert patched.reload_load_config(auto) is auto
+    assert str(patched.reload_load_config(auto, "safetensors").load_format).rsplit(".", 1)[-1].lower() == "safetensors"

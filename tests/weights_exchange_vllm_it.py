@@ -162,21 +162,22 @@ class VLLMWeightsExchange:
             self.writer.write_weights(step_id=self.step, path=path)
             self.awex_update(path)
             return time.time() - started
-        # the reader first, so that it is waiting when the writer sends
+        # The writer runs beside the HTTP call (it waits until the server's workers announce the update).  The
+        # server's answer decides: when the update fails there, this side must not go on waiting for it.
         failure: List[BaseException] = []
 
-        def update():
+        def write():
             try:
-                self.awex_update(path)
+                self.writer.write_weights(step_id=self.step, **({"path": path} if path else {}))
             except BaseException as exc:  # surfaced after the join
                 failure.append(exc)
 
-        thread = threading.Thread(target=update, daemon=True)
+        thread = threading.Thread(target=write, daemon=True)
         thread.start()
-        self.writer.write_weights(step_id=self.step, **({"path": path} if path else {}))
-        thread.join(timeout=900)
+        self.awex_update(path)  # raises when the server reports a failure; the daemon thread ends with the process
+        thread.join(timeout=300)
         if thread.is_alive():
-            raise RuntimeError("the server did not answer /areal_awex_update within 900 s")
+            raise RuntimeError("the server finished the update but the writer did not return within 300 s")
         if failure:
             raise failure[0]
         return time.time() - started
