@@ -143,7 +143,8 @@ class WorkerWeightsReader:
     def _after_update(self) -> None:
         """Caches computed with the old weights are stale."""
         if self.scheduler is not None and hasattr(self.scheduler, "flush_cache"):
-            self.scheduler.flush_cache()
+            flushed = self.scheduler.flush_cache()
+            logger.info(f"Rank[{self.transfer_rank}] flushed the engine's caches after the update (flush_cache returned {flushed!r})")
 
     def dump_parameters(self, step_id, names, directory: str) -> List[str]:
         """Save the received canonical tensors named in ``names`` (as
@@ -163,6 +164,31 @@ class WorkerWeightsReader:
             written.append(path)
             logger.info(f"[Reader] saved parameter {name} to {path}")
         return written
+
+    # ---- validation detail: what differs in parameters that failed ----------------------------------
+    def stash_received(self, names) -> int:
+        """Copy the current (received) values of ``names`` to the host."""
+        self._stash = {n: self.parameters[n].detach().to("cpu", copy=True) for n in names if n in self.parameters}
+        return len(self._stash)
+
+    def diff_against_stash(self) -> Dict[str, bool]:
+        """The parameters now hold the oracle again (the checkpoint was re-loaded):
+        log how the stashed, received values differ from it, then put the received
+        values back."""
+        from awex_b200.utils.tensor_util import compare_and_log_tensor_differences
+
+        stash, self._stash = getattr(self, "_stash", {}) or {}, {}
+        verdicts = {}
+        with torch.no_grad():
+            for name, received in stash.items():
+                live = self.parameters[name]
+                oracle = live.detach().to("cpu", copy=True)
+                if received.dtype.itemsize == 1 and received.is_floating_point():  # 8-bit floats: compare what they decode to
+                    verdicts[name] = compare_and_log_tensor_differences(received.float(), oracle.float(), name, exact_match=True)
+                else:
+                    verdicts[name] = compare_and_log_tensor_differences(received, oracle, name, exact_match=True)
+                live.copy_(received.to(live.device))
+        return verdicts
 
     # ---- validation: record, clear, compare ----------------------------------------------------------
     def _validation_tensors(self):

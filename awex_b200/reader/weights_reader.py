@@ -258,6 +258,14 @@ class WeightsReader(WeightExchangeReader):
             worker.dump_parameters(step_id, dump_weights_list_for_validation, dump_weights_dir_for_validation or os.getcwd())
         return worker.verify_against_snapshot()
 
+    @staticmethod
+    def _stash_for_diff_on_tp_worker(names=None, **kwargs):
+        return _worker_reader(kwargs).stash_received(names or [])
+
+    @staticmethod
+    def _diff_against_stash_on_tp_worker(**kwargs):
+        return _worker_reader(kwargs).diff_against_stash()
+
     # ---- per step -------------------------------------------------------------------------------------
     def _ensure_initialized(self) -> None:
         if not self.initialized:
@@ -278,6 +286,7 @@ class WeightsReader(WeightExchangeReader):
             self.inference_engine.release_memory_occupation()
             self._pre_update_weights()
         self._validating = self._should_validate(step_id)
+        self._validation_path = (kwargs.get("path"), kwargs.get("load_format")) if self._validating else (None, None)
         if self._validating:
             self._pre_validate_weights(step_id, **kwargs)
         self.inference_engine.execute_task_in_model_worker(self._begin_update_in_tp_worker, step_id=step_id)
@@ -351,9 +360,39 @@ class WeightsReader(WeightExchangeReader):
         verdict = "PASSED" if not failed else "FAILED"
         logger.info(f"[Validation] step {step_id} {verdict}" + (f": {len(failed)} mismatching parameters, e.g. {failed[:8]}" if failed else ""))
         self.last_validation_failed = failed
+        if failed:
+            self._log_detailed_differences(step_id, failed)
         if failed and self.raise_on_validation_fail:
             raise RuntimeError(f"weights validation failed at step {step_id}: {failed[:8]}")
         return not failed
+
+
+def _attach_detail_logger():
+    def _log_detailed_differences(self, step_id, failed) -> None:
+        """What differs in the parameters that failed (the reference logs max / mean
+        absolute and relative differences and the first differing positions for each,
+        `awex/reader/weights_reader.py:510-587`).  On CUDA the comparison itself only
+        moves checksums, so the values it was made against are gone: when the update
+        was validated against a checkpoint, the workers set the received values of the
+        failed parameters aside on the host, the engine loads the checkpoint once more,
+        the workers log the differences, and the received values are put back.  Only
+        the failed parameters are copied."""
+        path, load_format = getattr(self, "_validation_path", (None, None))
+        if not path:
+            logger.info(f"[Validation] step {step_id}: no checkpoint to compare with; per-element differences are not available "
+                        "(validate with a path, or on CPU, to get them)")
+            return
+        try:
+            self.inference_engine.execute_task_in_model_worker(self._stash_for_diff_on_tp_worker, names=list(failed))
+            self.inference_engine.update_weights_from_disk(path, load_format)
+            self.inference_engine.execute_task_in_model_worker(self._diff_against_stash_on_tp_worker)
+        except Exception as exc:  # the verdict stands; the detail is best effort
+            logger.warning(f"[Validation] step {step_id}: could not produce per-element differences: {exc!r}")
+
+    WeightsReader._log_detailed_differences = _log_detailed_differences
+
+
+_attach_detail_logger()
 
 
 def get_weights_exchange_reader(inference_engine):

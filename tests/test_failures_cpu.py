@@ -226,3 +226,46 @@ def test_poison_fill_catches_an_unwritten_tensor_whose_values_are_zero():
         result = w.verify_against_snapshot()
         assert result["w"] and result["q"] and result["ids"]
         assert result["bias"] == bias_passes
+
+
+def test_failed_validation_logs_differences_against_the_reloaded_checkpoint():
+    """Where validation only moves checksums, a parameter that fails gets its
+    per-element differences from a second load of the checkpoint: received values
+    are set aside, the oracle is loaded again, the differences are logged, and the
+    received values are put back.  Only the failed parameters are touched."""
+    import torch
+
+    from awex_b200.reader.nccl_reader import WorkerWeightsReader
+    from awex_b200.reader.weights_reader import WeightsReader
+
+    oracle = {"a.weight": torch.arange(12, dtype=torch.float32).view(3, 4), "b.weight": torch.ones(5)}
+    received = {"a.weight": oracle["a.weight"].clone(), "b.weight": torch.ones(5)}
+    received["a.weight"][1, 2] = -7.0
+    worker = WorkerWeightsReader.__new__(WorkerWeightsReader)
+    worker.parameters = {n: t.clone() for n, t in received.items()}
+    loads = []
+
+    class Engine:
+        def execute_task_in_model_worker(self, fn, **kwargs):
+            return [fn(model=None, model_context={"scheduler": type("S", (), {"awes_weights_reader": worker})()}, **kwargs)]
+
+        def update_weights_from_disk(self, path, load_format=None):
+            loads.append((path, load_format))
+            for n, t in oracle.items():
+                worker.parameters[n].copy_(t)
+
+    reader = WeightsReader.__new__(WeightsReader)
+    reader.inference_engine = Engine()
+    reader._validation_path = ("/ckpt", None)
+    reader._log_detailed_differences(3, ["a.weight"])
+    assert loads == [("/ckpt", None)]
+    assert torch.equal(worker.parameters["a.weight"], received["a.weight"])  # the received values are back
+    assert worker._stash == {}
+    # without a checkpoint there is nothing to compare with, and nothing is loaded
+    reader._validation_path = (None, None)
+    reader._log_detailed_differences(4, ["a.weight"])
+    assert len(loads) == 1
+    # the worker-side pieces on their own
+    assert worker.stash_received(["a.weight", "missing"]) == 1
+    worker.parameters["a.weight"].copy_(oracle["a.weight"])
+    assert worker.diff_against_stash() == {"a.weight": False}
