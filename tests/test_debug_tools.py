@@ -144,37 +144,6 @@ def test_plan_study_reports_bytes_and_bounds():
     assert main(["--model", "tiny-llama", "--train", "tp2", "--infer", "tp1", "--placement", "separated"]) == 0
 
 
-def test_contention_model_two_senders_meeting_at_one_receiver():
-    """Two senders with equal tables (first receiver A, then receiver B): with
-    contiguous CTA ranges both receivers are fed all the time and the update
-    takes bytes / link rate; with all CTAs in one window both senders sit on the
-    same receiver and take twice as long.  A local destination is bounded by
-    memory bandwidth instead."""
-    import numpy as np
-
-    from awex_b200.debug.contention_model import CTA_RATE, simulate
-
-    link, mb = 770e9, 1e6
-    table = np.array([[2, 50 * mb, 1.0, CTA_RATE["copy"]], [3, 50 * mb, 1.0, CTA_RATE["copy"]]])
-    ideal_ms = 100 * mb / link * 1e3
-    spread = simulate({0: table, 1: table.copy()}, "contiguous", 4, dt=2e-6)
-    convoy = simulate({0: table, 1: table.copy()}, "chunks", 4, dt=2e-6, chunk_bytes=16384)  # a window much smaller than the table
-    assert abs(spread["ms"] - ideal_ms) < 0.05 * ideal_ms
-    assert abs(convoy["ms"] - 2 * ideal_ms) < 0.08 * 2 * ideal_ms
-    assert max(convoy["peak_ingress_GBps"]) <= 770.0 + 1e-6
-    local = simulate({0: np.array([[0, 100 * mb, 1.0, CTA_RATE["copy"]]])}, "contiguous", 1, dt=1e-6)
-    assert abs(local["ms"] - 100 * mb / (6.42e12 / 2) * 1e3) < 0.1 * local["ms"]  # 148 CTAs at the copy rate
-
-
-def test_contention_model_cli_on_a_tiny_layout(capsys):
-    from awex_b200.debug import contention_model
-
-    assert contention_model.main(["--model", "tiny-llama", "--train", "tp2", "--infer", "tp1,engines2", "--placement", "separated",
-                                  "--orders", "contiguous,chunks,striped,rotated", "--stripe-mb", "0.0625"]) == 0
-    lines = [l for l in capsys.readouterr().out.splitlines() if " ms " in l]
-    assert [l.split(":")[0].strip() for l in lines] == ["contiguous", "chunks", "striped", "rotated"]
-
-
 def test_plan_study_finds_a_placement_that_keeps_more_bytes_local():
     from awex_b200.debug.plan_study import parse_layout, study
 
