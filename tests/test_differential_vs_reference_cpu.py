@@ -254,3 +254,101 @@ def test_serving_side_converter_of_a_registered_family_agrees():
         }
         for name, tensor in cases.items():
             _same(ours, theirs, name, tensor)
+
+
+# ---- multimodal, hybrid and MLA families ----------------------------------------------------------------
+M = "module.module."
+
+
+def _both_infer_converters(arch, hf, cfg=None, **rank_kw):
+    import awex.models.registry as ref_registry
+    import awex.sharding.rank_info as ref_rank
+
+    import awex_b200.models.registry as our_registry
+    import awex_b200.sharding.rank_info as our_rank
+
+    cfg = cfg or SimpleNamespace(tp_size=1, ep_size=1, device_backend="cpu")
+    rank_kw = dict(is_infer=True, **rank_kw)
+    return (our_registry.get_infer_weights_converter("sglang", arch, hf, _rank(our_rank, **rank_kw), cfg),
+            ref_registry.get_infer_weights_converter("sglang", arch, hf, _rank(ref_rank, **rank_kw), cfg))
+
+
+@pytest.mark.parametrize("arch", ["Qwen3VLForConditionalGeneration", "Qwen3VLMoeForConditionalGeneration"])
+def test_qwen3_vl_converters_agree_on_decoder_tower_and_experts(arch):
+    text = SimpleNamespace(hidden_size=8, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=2,
+                           num_experts=4, tie_word_embeddings=False)
+    hf = SimpleNamespace(architectures=[arch], text_config=text, vision_config=SimpleNamespace(num_heads=2, hidden_size=4))
+    tf = SimpleNamespace(hidden_size=8, num_attention_heads=4, num_query_groups=2, kv_channels=2, num_layers=2)
+    for infer_tp in (1, 2):
+        conf = {"infer_atten_tp_size": infer_tp, "router_dtype": "fp32", "infer_engine_config": SimpleNamespace(tp_size=infer_tp, ep_size=1)}
+        ours, theirs = _both_train_converters(arch, hf, tf, conf)
+        cases = {
+            M + "language_model.decoder.layers.0.self_attention.linear_qkv.weight": _seq(16, 8),
+            M + "language_model.decoder.layers.1.self_attention.linear_proj.weight": _seq(8, 8),
+            M + "language_model.embedding.word_embeddings.weight": _seq(4, 8),
+            M + "vision_model.decoder.layers.1.self_attention.linear_qkv.weight": _seq(12, 4),
+            M + "vision_model.decoder.layers.1.self_attention.linear_qkv.bias": _seq(12),
+            M + "vision_model.patch_embed.proj.weight": _seq(8),
+            M + "vision_model.decoder.layers.1.mlp.linear_fc1.weight": _seq(8, 4),
+            M + "vision_model.merger.linear_fc2.weight": _seq(8, 4),
+            M + "vision_model.decoder.deepstack_merger_list.2.patch_norm.weight": _seq(8),
+        }
+        for name, tensor in cases.items():
+            _same(ours, theirs, name, tensor)
+    ours, theirs = _both_train_converters(arch, hf, tf, {"infer_atten_tp_size": 1, "infer_engine_config": SimpleNamespace(tp_size=1, ep_size=2)},
+                                          ep_rank=1, ep_size=2)
+    _same(ours, theirs, M + "language_model.decoder.layers.0.mlp.experts.linear_fc2.weight0", _seq(8, 6))
+    ours, theirs = _both_infer_converters(arch, hf)
+    for name, tensor in {"model.layers.0.self_attn.qkv_proj.weight": _seq(16, 8), "model.embed_tokens.weight": _seq(4, 8),
+                         "visual.patch_embed.proj.weight": _seq(8), "visual.blocks.1.mlp.linear_fc1.weight": _seq(8, 4),
+                         "visual.deepstack_merger_list.2.norm.weight": _seq(8)}.items():
+        _same(ours, theirs, name, tensor)
+
+
+def test_qwen3_5_converters_agree_on_gated_attention_and_delta_net():
+    text = SimpleNamespace(model_type="qwen3_5_moe_text", architectures=["Qwen3_5MoeForCausalLM"], hidden_size=8, num_hidden_layers=4,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=2, linear_num_key_heads=2, linear_key_head_dim=2,
+                           linear_num_value_heads=4, linear_value_head_dim=2, num_experts=4, tie_word_embeddings=False)
+    hf = SimpleNamespace(architectures=["Qwen3_5MoeForConditionalGeneration"], text_config=text,
+                         vision_config=SimpleNamespace(num_heads=2, hidden_size=4), tie_word_embeddings=False)
+    tf = SimpleNamespace(hidden_size=8, num_attention_heads=4, num_query_groups=2, kv_channels=2, num_layers=4)
+    for infer_tp in (1, 2):
+        conf = {"infer_atten_tp_size": infer_tp, "infer_engine_config": SimpleNamespace(tp_size=infer_tp, ep_size=1)}
+        ours, theirs = _both_train_converters(hf.architectures[0], hf, tf, conf)
+        cases = {
+            M + "language_model.decoder.layers.0.self_attention.linear_qkv.weight": _seq(24, 8),  # [Q, gate, K, V] per KV group
+            M + "language_model.decoder.layers.0.self_attention.in_proj.weight": _seq(32, 8),     # Q 4, K 4, V 8, Z 8, B 4, A 4
+            M + "language_model.decoder.layers.1.self_attention.linear_proj.weight": _seq(8, 8),
+            M + "language_model.embedding.word_embeddings.weight": _seq(4, 8),
+        }
+        for name, tensor in cases.items():
+            _same(ours, theirs, name, tensor)
+        for skipped in ("language_model.mtp.layers.0.eh_proj.weight", "mtp.layers.0.mtp_model_layer.mlp.linear_fc1.weight"):
+            _same(ours, theirs, M + skipped, _seq(8, 8))  # multi-token-prediction weights are not sent by either
+    ours, theirs = _both_infer_converters(hf.architectures[0], hf)
+    for name, tensor in {"model.layers.0.qkv_proj.weight": _seq(24, 8), "model.layers.0.linear_attn.A_log": _seq(4),
+                         "mtp.norm.weight": _seq(8)}.items():
+        _same(ours, theirs, name, tensor)
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4])
+def test_mla_down_projection_packing_agrees(tp):
+    from awex.converter.mcore_converter import pack_fused_qkv_a_proj_for_tp as ref_pack
+
+    from awex_b200.converter.mcore_converter import pack_fused_qkv_a_proj_for_tp as our_pack
+
+    q, kv = _seq(8, 3), -_seq(4, 3)
+    assert torch.equal(our_pack(q, kv, tp), ref_pack(q, kv, tp))
+
+
+@pytest.mark.parametrize("arch", ["BailingMoeForCausalLM", "BailingMoeV2ForCausalLM", "BailingMoeV2_5ForCausalLM"])
+def test_bailing_families_resolve_to_the_same_kind_of_converters_and_sharding(arch):
+    import awex.models.registry as ref_registry
+
+    import awex_b200.models.registry as our_registry
+
+    hf = SimpleNamespace(architectures=[arch], quantization_config={})
+    tf = SimpleNamespace(layer_group_size=4)
+    ours, theirs = _both_train_converters(arch, hf, tf, {"infer_atten_tp_size": 1})
+    assert type(ours).__name__ == type(theirs).__name__
+    assert our_registry.get_sharding_strategy(arch).__name__ == ref_registry.get_sharding_strategy(arch).__name__
