@@ -102,6 +102,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "awex_launch_fp8_block_dequant": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i64_t(), i32, vp], i32),
         "awex_launch_fp8_scale_table": ([vp, vp, u32, i32, vp], i32),
         "awex_launch_fp8_quotient_check": ([i32, vp, vp], i32),
+        "awex_col_normalize_scratch_floats": ([u64, u64], u64),
+        "awex_launch_col_l2_normalize": ([vp, vp, vp, u64, u64, i64_t(), i64_t(), i32, ctypes.c_float, vp], i32),
         "awex_vmm_available": ([], i32),
         "awex_vmm_export_fd": ([u64, ctypes.POINTER(i32)], i32),
         "awex_vmm_reserve": ([u64, u64, ctypes.POINTER(u64)], i32),

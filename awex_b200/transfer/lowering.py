@@ -128,6 +128,20 @@ class DerivedTensor:
         value = self.spec.rows.gather(fetch)
         return self.spec.value_op.apply(value) if self.spec.value_op.kind in WHOLE_TENSOR_OPS else value
 
+    def compute_into(self, buffer: Optional[torch.Tensor], local: Dict[Tuple[str, int], torch.Tensor],
+                     gather_fn: Optional[Callable] = None) -> Optional[torch.Tensor]:
+        """Refresh ``buffer`` in place with the device kernel where there is one
+        (column normalisation of a 2-D CUDA tensor: no temporary of the tensor's
+        size); returns ``None`` when the general path must be taken."""
+        if buffer is None or self.gathers or self.spec.value_op.kind != "l2norm_dim0":
+            return None
+        value = self.spec.rows.gather(lambda src: local[(src[0], self.key[1])])
+        if not value.is_cuda or value.dim() != 2 or value.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            return None
+        from awex_b200.ops.normalize import col_l2_normalize
+
+        return col_l2_normalize(value, out=buffer, eps=1e-7)
+
 
 def refresh_derived(derived: Iterable[DerivedTensor], local: Dict[Tuple[str, int], torch.Tensor],
                     gather_fn: Optional[Callable] = None) -> int:
@@ -141,6 +155,9 @@ def refresh_derived(derived: Iterable[DerivedTensor], local: Dict[Tuple[str, int
     n = 0
     with torch.no_grad():
         for d in sorted(derived, key=lambda d: d.key):
+            if d.compute_into(local.get(d.key), local, gather_fn) is not None:
+                n += 1
+                continue
             value = d.compute(local, gather_fn)
             if d.key not in local:
                 local[d.key] = torch.empty_like(value, memory_format=torch.contiguous_format)

@@ -186,3 +186,42 @@ def test_a_launch_that_timed_out_leaves_the_program_reusable():
     torch.cuda.synchronize()
     prog.status.raise_if_failed()
     assert torch.equal(dst, src) and done.t.item() == 7
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(1000, 512), (257, 1030), (19008, 2048)])
+def test_column_normalisation_matches_the_pytorch_statement(shape, dtype):
+    """``F.normalize(x, dim=0)``: everything but the summation order is the same
+    arithmetic, so elements agree exactly except where a column's norm lands on
+    the other side of a rounding boundary of the dtype (then by one unit in the
+    last place)."""
+    from awex_b200.ops.normalize import col_l2_normalize
+
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = (torch.randn(shape, generator=g, device="cuda") * 0.02).to(dtype)
+    x[:, 3] = 0  # an all-zero column: divided by eps, stays zero
+    got = col_l2_normalize(x)
+    want = torch.nn.functional.normalize(x.cpu(), dim=0, p=2, eps=1e-7)
+    same = (got.cpu() == want)
+    assert same.float().mean().item() > 0.98
+    ulp = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10, torch.float32: 2.0 ** -22}[dtype]
+    assert torch.allclose(got.cpu().float(), want.float(), rtol=2 * ulp, atol=1e-30)
+    assert bool((got[:, 3] == 0).all())
+    # in place, and into a buffer with a pitch
+    wide = torch.zeros(shape[0], shape[1] + 8, dtype=dtype, device="cuda")
+    col_l2_normalize(x, out=wide[:, : shape[1]])
+    assert torch.equal(wide[:, : shape[1]], got) and bool((wide[:, shape[1]:] == 0).all())
+    again = x.clone()
+    col_l2_normalize(again, out=again)
+    assert torch.equal(again, got)
+
+
+def test_column_normalisation_is_exact_where_the_norm_is_exact():
+    from awex_b200.ops.normalize import col_l2_normalize
+
+    x = torch.zeros(300, 64, dtype=torch.bfloat16, device="cuda")
+    rows = torch.arange(64, device="cuda") * 3
+    x[rows, torch.arange(64, device="cuda")] = torch.linspace(-4, 4, 64, device="cuda").to(torch.bfloat16)  # one value per column
+    got = col_l2_normalize(x)
+    want = torch.nn.functional.normalize(x.cpu(), dim=0, p=2, eps=1e-7)
+    assert torch.equal(got.cpu(), want)

@@ -33,7 +33,13 @@ def _writer(meta_addr, q):
         raise
 
 
-def _reader(meta_addr, q):
+def _reader(meta_addr, q, expandable=False):
+    import os
+
+    if expandable:
+        # the engine's weights then live in virtual-memory allocations (cuMemCreate), which CUDA IPC refuses:
+        # the address book must hand them over as file descriptors instead
+        os.environ["PYTORCH_CUDA_ALLOC_CONF"] = "expandable_segments:True"
     from awex_b200 import WeightsReader
     from awex_b200.synthetic.arch import get_arch
     from awex_b200.synthetic.harness import SyntheticInferenceEngine
@@ -51,14 +57,15 @@ def _reader(meta_addr, q):
         reader.update_weights(step_id=2)
         bad2 = engine.mismatches(step=2)
         worker = engine.schedulers[0].awes_weights_reader
-        q.put(("reader", list(worker.transport.host_senders), (bad1, bad2)))
+        book = worker.meta_server_client.get_object("p2p_addr_0", timeout=30)
+        q.put(("reader", list(worker.transport.host_senders), (bad1, bad2, len(book.vmm))))
     except BaseException as exc:
         q.put(("reader-error", repr(exc), None))
         raise
 
 
-@pytest.mark.timeout(600)
-def test_two_processes_one_gpu_host_handshake():
+@pytest.mark.parametrize("expandable", [False, True])
+def test_two_processes_one_gpu_host_handshake(expandable):
     from awex_b200.meta.meta_server import MetaServer
 
     server = MetaServer("127.0.0.1", 0)
@@ -66,19 +73,26 @@ def test_two_processes_one_gpu_host_handshake():
     addr = f"127.0.0.1:{server.port}"
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_reader, args=(addr, q)), ctx.Process(target=_writer, args=(addr, q))]
+    procs = [ctx.Process(target=_reader, args=(addr, q, expandable)), ctx.Process(target=_writer, args=(addr, q))]
     for p in procs:
         p.start()
     got = {}
-    for _ in procs:
-        kind, a, b = q.get(timeout=500)
-        assert not kind.endswith("error"), (kind, a)
-        got[kind] = (a, b)
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
-    server.stop()
+    try:
+        for _ in procs:
+            kind, a, b = q.get(timeout=500)
+            assert not kind.endswith("error"), (kind, a)
+            got[kind] = (a, b)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:  # a child that neither reported nor left is not left behind
+            if p.is_alive():
+                p.kill()
+        server.stop()
     assert got["writer"][0] == [0], "the sender must have recognised a same-GPU destination in another process"
     assert got["reader"][0] == [0]
-    assert got["reader"][1] == ([], [])
+    assert got["reader"][1][:2] == ([], [])
+    # with expandable segments the parameters were handed over as virtual-memory allocations, otherwise as CUDA IPC handles
+    assert (got["reader"][1][2] > 0) == expandable
     assert got["writer"][1][0] == 0
