@@ -85,6 +85,27 @@ def bench_config(model: str, bytes_per_update: int, parallelism: str, mode: str,
             "validated_bitwise": bool(validated), "details": dict(extra or {})}
 
 
+def _spawn_inference_process(args):
+    """Two processes per GPU: this process (a rank of the launcher, or the only
+    process) becomes the training process of its GPU and starts a second
+    interpreter on the same benchmark as the GPU's inference process.  All 2 n
+    processes then form one host-side group on a port of their own; the training
+    processes are its ranks 0 .. n-1, the inference processes n .. 2n-1."""
+    import subprocess
+
+    n = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 23
+    env = dict(os.environ, AWEX_BENCH_ROLE="inference", WORLD_SIZE=str(2 * n), RANK=str(n + rank), LOCAL_RANK=os.environ.get("LOCAL_RANK", "0"),
+               MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    for name in ("TORCHELASTIC_USE_AGENT_STORE", "TORCHELASTIC_RUN_ID", "GROUP_RANK", "ROLE_RANK", "LOCAL_WORLD_SIZE", "GROUP_WORLD_SIZE"):
+        env.pop(name, None)  # the second group is not the launcher's
+    os.environ.update(AWEX_BENCH_ROLE="training", WORLD_SIZE=str(2 * n), RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return subprocess.Popen([sys.executable, os.path.join(root, "bench.py"), *sys.argv[1:]], env=env)
+
+
 def _max_over_ranks(value: float, group=None) -> float:
     t = torch.tensor([value], dtype=torch.float64)
     if dist.is_initialized() and dist.get_world_size() > 1:
@@ -166,10 +187,15 @@ def run_distributed(args):
     from awex_b200.utils.gpu import ClockSampler
 
     logging.setLevel(os.environ.get("AWEX_LOG_LEVEL", "WARNING"))
+    two_processes = int(getattr(args, "processes", 1) or 1) == 2
+    child = None
+    if two_processes and os.environ.get("AWEX_BENCH_ROLE") is None:
+        child = _spawn_inference_process(args)  # re-runs this benchmark as the inference process of this GPU
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
+    gpus = world // 2 if two_processes else world
+    if gpus != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     # "--device cpu" runs the same flow over gloo on CPU tensors: a functional check of
     # this harness and of the public API, not a measurement
@@ -190,11 +216,23 @@ def run_distributed(args):
         sync = torch.cuda.synchronize
         if world > 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=device)
+            if two_processes:  # two processes share each GPU: host-side groups only (a NCCL communicator cannot hold both)
+                dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+            else:
+                dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=device)
     ctl = dist.new_group(list(range(world)), backend="gloo") if world > 1 else None  # host-side control traffic
 
     config = getattr(args, "config", "separated")
-    train_layout, infer_layout, train_ranks, engines, label = role_table(world, config, getattr(args, "placement", "blocked"))
+    if two_processes:
+        from awex_b200.synthetic.simulate import InferLayout, TrainLayout
+
+        if config != "colocated":
+            raise SystemExit("--processes 2 is the co-located deployment with trainer and engine in separate processes: use --config colocated")
+        # ranks 0 .. n-1 train on GPUs 0 .. n-1, ranks n .. 2n-1 serve on the same GPUs
+        train_layout, infer_layout = TrainLayout(tp=gpus), InferLayout(tp=gpus)
+        train_ranks, engines, label = list(range(gpus)), [list(range(gpus, 2 * gpus))], f"colocated-tp{gpus}->tp{gpus}-two-processes-per-gpu"
+    else:
+        train_layout, infer_layout, train_ranks, engines, label = role_table(world, config, getattr(args, "placement", "blocked"))
     arch = get_arch(args.model or CONFIG_MODELS[config])
     if infer_layout.fp8:
         # a CPU oracle would take hours at this size; the stand-alone quantisation
@@ -241,7 +279,7 @@ def run_distributed(args):
         writer.initialize()
         note("training shard built")
     if is_infer:
-        ri = infer_rank_infos(infer_layout.tp, infer_layout.ep, engine_rank=my_engine, first_local_rank=engines[my_engine][0])[
+        ri = infer_rank_infos(infer_layout.tp, infer_layout.ep, engine_rank=my_engine, first_local_rank=engines[my_engine][0] % gpus)[
             engines[my_engine].index(rank)
         ]
         infer_engine = SyntheticInferenceEngine(arch, infer_layout, ri, meta_addr, dtype=torch.bfloat16, device=device,
@@ -421,10 +459,10 @@ def run_distributed(args):
     if rank == 0:
         if not valid:
             raise SystemExit("validation failed: inference weights differ from the oracle")
-        remote = world > 1
-        colocated = world == 1 or config != "separated"
+        remote = gpus > 1
+        colocated = gpus == 1 or config != "separated"
         result = {
-            "metric": "weight_sync_seconds_per_update", "value": seconds, "unit": "s", "n_gpus": world,
+            "metric": "weight_sync_seconds_per_update", "value": seconds, "unit": "s", "n_gpus": gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
             # every GPU count runs the layout BASELINE names for it (one GPU: both roles on it, no link; 2 and 4: one
             # NVLink stream per sender; 8: two), so the per-N figure to compare is the fraction of that layout's roofline
@@ -465,3 +503,5 @@ def run_distributed(args):
         dist.destroy_process_group()
     if server is not None:
         server.stop()
+    if child is not None:
+        child.wait(timeout=120)

@@ -432,7 +432,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 // tile, kS - 2 ahead of a copied one).
 template <int kT, int kS>
 __device__ __forceinline__ void transfer_body(const XferParams& p) {
-  static_assert(kS >= 3, "a copied tile's stage is released two tiles later");
+  static_assert(kS >= 2, "a ring needs two stages; pure copies overlap loads with stores only from three stages on");
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kS];
   __shared__ uint32_t red[2][kT / 32];
@@ -698,6 +698,17 @@ __global__ void __launch_bounds__(kThreadsX2, 2) fused_transfer_kernel_x2(const 
   transfer_body<kThreadsX2, kStagesX2>(p);
 }
 
+// Three CTAs of 256 threads per SM with a 2-stage ring each: the variant for
+// tables that are almost only quantised blocks.  A computed tile frees its stage
+// at its barrier, so two stages still keep one load in flight per CTA, and the
+// third resident CTA hides more of each tile's latency.  Pure copies are correct
+// in this shape but do not overlap their loads with their stores.
+constexpr int kThreadsX3 = 256;
+constexpr int kStagesX3 = 2;
+__global__ void __launch_bounds__(kThreadsX3, 3) fused_transfer_kernel_x3(const __grid_constant__ XferParams p) {
+  transfer_body<kThreadsX3, kStagesX3>(p);
+}
+
 // Receiver side: wait (bounded) until every listed sender has raised `epoch`.
 __global__ void wait_flags_kernel(const uint64_t* pad, const uint32_t* slots, uint32_t n, uint64_t epoch, uint64_t timeout_ns,
                                   int32_t* status) {
@@ -734,7 +745,7 @@ int awex_xfer_smem_bytes() { return awex::kStages * awex::kStageBytes; }
 int awex_xfer_stage_bytes() { return awex::kStageBytes; }
 
 // Returns a cudaError_t.  `variant` 0: one CTA of 512 threads per SM; 1: two
-// CTAs of 256 threads per SM.  `grid` == 0 fills the device for the variant.
+// CTAs of 256 threads per SM; 2: three CTAs of 256 threads per SM.  `grid` == 0 fills the device for the variant.
 // With `cta_plan` (one CtaPlan per CTA, plus `chunk_desc`) `grid` is the number
 // of plan entries and is used as given.
 int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_tiles, uint64_t epoch, uint64_t timeout_ns,
@@ -742,16 +753,18 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
                                uint32_t n_done, void* cta_counter, void* status, int grid, void* stream,
                                const void* chunk_desc, uint32_t chunk_shift, uint32_t variant, const void* cta_plan) {
   // the shared-memory attribute is set once per (variant, device)
-  static std::atomic<uint64_t> configured[2];
-  if (variant > 1) return cudaErrorInvalidValue;
+  static std::atomic<uint64_t> configured[3];
+  if (variant > 2) return cudaErrorInvalidValue;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  const int smem = (variant ? awex::kStagesX2 : awex::kStages) * awex::kStageBytes;
+  const int stages = variant == 0 ? awex::kStages : variant == 1 ? awex::kStagesX2 : awex::kStagesX3;
+  const int smem = stages * awex::kStageBytes;
   const uint64_t bit = (dev >= 0 && dev < 64) ? (uint64_t{1} << dev) : 0;
   if (bit == 0 || !(configured[variant].load(std::memory_order_acquire) & bit)) {
-    err = variant ? cudaFuncSetAttribute(awex::fused_transfer_kernel_x2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
-                  : cudaFuncSetAttribute(awex::fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = variant == 0   ? cudaFuncSetAttribute(awex::fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+          : variant == 1 ? cudaFuncSetAttribute(awex::fused_transfer_kernel_x2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                         : cudaFuncSetAttribute(awex::fused_transfer_kernel_x3, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
     configured[variant].fetch_or(bit, std::memory_order_release);
   }
@@ -759,7 +772,7 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
   if (grid <= 0) {
     err = cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
-    if (variant) grid *= 2;
+    grid *= static_cast<int>(variant) + 1;
   }
   if (cta_plan == nullptr && n_tiles > 0 && static_cast<uint64_t>(grid) > n_tiles) grid = static_cast<int>(n_tiles);
   if (grid < 1) grid = 1;
@@ -779,7 +792,9 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
   p.cta_plan = static_cast<const awex::CtaPlan*>(cta_plan);
   p.chunk_desc = static_cast<const uint32_t*>(chunk_desc);
   p.chunk_shift = cta_plan ? chunk_shift : 0;
-  if (variant)
+  if (variant == 2)
+    awex::fused_transfer_kernel_x3<<<grid, awex::kThreadsX3, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  else if (variant == 1)
     awex::fused_transfer_kernel_x2<<<grid, awex::kThreadsX2, smem, static_cast<cudaStream_t>(stream)>>>(p);
   else
     awex::fused_transfer_kernel<<<grid, awex::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);

@@ -75,7 +75,7 @@ def _pick_variant(table: np.ndarray, n_tiles: int) -> int:
     from awex_b200.transfer.descriptors import OP_COPY
 
     forced = os.environ.get("AWEX_XFER_VARIANT")
-    if forced in ("0", "1"):
+    if forced in ("0", "1", "2"):
         return int(forced)
     if not len(table) or not n_tiles:
         return 0
@@ -179,7 +179,7 @@ class TransferProgram:
         if interleave and self.n_desc and self.n_tiles:
             from awex_b200.transfer.descriptors import build_cta_plan
 
-            ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count * (2 if self.variant else 1)
+            ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count * (self.variant + 1)
             ctas = max(1, min(ctas, self.n_tiles))
             shift = _max_chunk_shift(table, self.n_tiles)
             while shift > 0 and (self.n_tiles >> shift) < 4 * ctas:

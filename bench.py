@@ -43,6 +43,9 @@ def parse_args():
                     help="moe configuration: which GPUs the two inference instances sit on (see role_table)")
     ap.add_argument("--pairing", default=None, choices=["spread", "round_robin", "local"],
                     help="replica pairing of the planner (default: the writer's own, least-loaded); 'local' prefers the replica on the same GPU")
+    ap.add_argument("--processes", type=int, default=1, choices=[1, 2],
+                    help="2 (with --config colocated): trainer and inference engine of every GPU in separate processes, as the "
+                         "reference deploys its co-located mode (CUDA IPC for the same-GPU pair, completion announced on the host)")
     ap.add_argument("--model", default=None, help="architecture preset; default is the one the configuration names")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model to this many layers (result is then not a valid benchmark)")
     ap.add_argument("--no-validate", action="store_true")

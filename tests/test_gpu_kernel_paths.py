@@ -69,7 +69,7 @@ def test_constant_add_rides_along(variant):
     assert torch.equal(out, (a.float() + 1.0).to(torch.bfloat16))
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(512, 1024), (130, 136), (257, 384)])
 @pytest.mark.parametrize("ue8m0", [False, True])
@@ -112,7 +112,7 @@ def test_fused_block_fp8_with_gathered_rows():
     big = torch.full((512, 4096), 100.0, dtype=torch.bfloat16, device="cuda")
     big_out = torch.zeros_like(big)
     items = [CopyItem("big", 0, (0, 0), (512, 4096), 0, "big", (0, 0), torch.bfloat16, torch.bfloat16), item]
-    for variant in (0, 1):
+    for variant in (0, 1, 2):
         q.zero_(), s.zero_(), big_out.zero_()
         _run(items, {"x": x, "big": big}, {0: {"q": q, "s": s, "big": big_out}}, variant=variant, grid=3)
         gathered = torch.cat([x[400:500], x[100:200]]).cpu()
@@ -121,7 +121,7 @@ def test_fused_block_fp8_with_gathered_rows():
         assert torch.equal(big_out, big)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("interleave", [False, True])
 def test_destination_groups_and_mixed_tiles(variant, interleave):
     """Three destinations of very different sizes and tile kinds (copies, strided
