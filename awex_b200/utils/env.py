@@ -27,11 +27,12 @@ KNOBS: Dict[str, Tuple[str, str]] = {
     "AWEX_META_SERVER_TOKEN": ("", "shared secret: a MetaServer started with it refuses requests that do not carry it, clients send it (set it on every process)"),
     "AWEX_DATA_PLANE": ("", "peer_stores (fused kernel through CUDA IPC, one machine) or messages (NCCL / gloo messages, any topology); default by device"),
     "AWEX_XFER_CHUNK_MB": ("", "size in MiB of the chunks of tiles dealt to CTAs by the fused transfer kernel (default by op mix)"),
-    "AWEX_XFER_VARIANT": ("", "0 | 1: force the launch shape of the fused transfer kernel (one 512-thread or two 256-thread CTAs per SM)"),
+    "AWEX_XFER_VARIANT": ("", "0 | 1 | 2: force the launch shape of the fused transfer kernel (one 512-thread, two or three 256-thread CTAs per SM)"),
     "AWEX_XFER_INTERLEAVE": ("1", "0: one contiguous tile range per CTA instead of round-robin chunks"),
     "AWEX_XFER_DEST_GROUPS": ("1", "0: deal the whole table to all CTAs as one group instead of one CTA group per destination"),
     "AWEX_XFER_DEST_STRIPE_MB": ("0", "cut items into stripes of this many MiB and merge the destinations' stripes in proportion to their bytes, with round-robin chunks (experimental)"),
     "AWEX_XFER_DEST_ROTATE": ("0", "1: each sender starts its table at a different destination (experimental, with AWEX_XFER_INTERLEAVE=1; only helps when all senders have the same destination set)"),
+    "AWEX_BENCH_ROLE": ("", "set by the benchmark for its two-processes-per-GPU mode: training | inference (which half of a GPU's pair this process is)"),
     "AWEX_USE_BATCH_SEND_RECV": ("1", "message transport only: 0 sends one message at a time and waits for each"),
     "AWEX_SYNTH_FP8_ORACLE": ("cpu", "synthetic models: 'kernel' builds fp8 oracles with the quantisation kernel instead of the CPU"),
     # accepted, no effect here
