@@ -316,6 +316,11 @@ __device__ __forceinline__ void store_scale(const XferDesc& d, const Tile& t, fl
   if (threadIdx.x == 0) reinterpret_cast<float*>(d.aux_ptr)[static_cast<int64_t>(t.band) * d.aux_stride + t.ct] = scale;
 }
 
+// Does a quantised tile leave through shared memory and bulk-async stores?
+__device__ __forceinline__ bool fp8_leaves_through_stage(const XferDesc& d, const Tile& t) {
+  return (d.flags & FLAG_OUT_BULK) != 0 && (d.flags & FLAG_BULK) != 0 && (t.cols & 15u) == 0;
+}
+
 // Fast form: 2-byte source staged in shared memory with a 256-byte pitch
 // (tile_cols == 128), destination rows 8-byte aligned.  One pass over the stage:
 // a thread keeps its 16-byte chunks in registers from the maximum search, the
@@ -346,6 +351,20 @@ __device__ __forceinline__ bool tile_fp8_staged(const XferDesc& d, const Tile& t
   const float amax = kBf16 ? __uint_as_float(all << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(all)));
   const QuantScale q = make_quant_scale(amax, (d.flags & FLAG_UE8M0) != 0);
   store_scale(d, t, q.s);
+  if (fp8_leaves_through_stage(d, t)) {
+    // Every thread holds its part of the tile in registers (the barrier above), so the stage can take the
+    // result: 128 bytes per row, which warp 0 then sends with one bulk-async store per row.
+    unsigned char* out_stage = const_cast<unsigned char*>(stage) + chunk * 8u;
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const uint32_t row = row0 + p * kRowStep;
+      if (!col_ok || row >= t.rows) continue;
+      *reinterpret_cast<uint2*>(out_stage + row * kFp8Block) = quant_chunk16<kBf16>(raw[p], q);
+    }
+    fence_proxy_async();  // these generic-proxy writes before the bulk stores' async-proxy reads
+    __syncthreads();
+    return false;
+  }
   unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0 + chunk * 8u;
   const bool vec = (d.flags & FLAG_DST_VEC16) != 0;
 #pragma unroll
@@ -565,6 +584,8 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
       unsigned char* stage_ptr = smem + static_cast<size_t>(stage) * kStageBytes;
       const bool staged = wants_stage(d);
       const bool is_copy = d.op == OP_COPY && staged;
+      // a quantised tile that leaves through its stage keeps the stage busy like a copy does
+      const bool out_bulk = d.op == OP_FP8_BLOCK && fp8_leaves_through_stage(d, t);
 
       if (warp == 0 && !my_abort) {
         // Of the store groups committed so far (one per tile) only the most recent
@@ -575,7 +596,7 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
         const uint64_t limit = i + kS - (prev_copy ? 1 : 0);
         while (next_load < limit && next_load < n) issue_load(next_load++);
       }
-      prev_copy = is_copy;
+      prev_copy = is_copy || out_bulk;
 
       if (is_copy) {
         if (warp == 0 && !my_abort) {
@@ -595,7 +616,6 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
         }
         continue;  // other warps have nothing to do for pure copies
       }
-      if (warp == 0 && !my_abort) bulk_commit();  // an empty group keeps "one group per tile"
 
       if (staged) {
         const uint32_t ready_parity = n_staged & 1;
@@ -648,6 +668,14 @@ __device__ __forceinline__ void transfer_body(const XferParams& p) {
       if (stop) {  // the same for every thread of the CTA
         my_abort = 1;
         break;
+      }
+      if (warp == 0 && !my_abort) {
+        if (out_bulk) {
+          unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst) + t.row0 * d.dst_stride + t.col0;
+          const uint32_t base = smem_addr(stage_ptr);
+          for (uint32_t r = lane; r < t.rows; r += 32) bulk_store(dst + static_cast<int64_t>(r) * d.dst_stride, base + r * kFp8Block, t.cols);
+        }
+        bulk_commit();  // one group per tile, empty unless the tile left through its stage
       }
     }
   }

@@ -31,6 +31,9 @@ enum XferFlags : uint32_t {
   FLAG_BULK = 1u << 0,      // every row chunk is 16-byte aligned and sized on the source side
   FLAG_DST_VEC16 = 1u << 1, // ... and on the destination side
   FLAG_UE8M0 = 1u << 2,     // OP_FP8_BLOCK: round scales up to a power of two
+  FLAG_OUT_BULK = 1u << 3,  // OP_FP8_BLOCK, staged, destination rows 16-byte aligned: leave through shared memory and
+                            // bulk-async stores (destinations across NVLink, where per-thread stores are limited by
+                            // the SM's outstanding writes)
 };
 
 struct alignas(16) XferDesc {

@@ -5,7 +5,9 @@ Cases: ``transfer_copy`` (contiguous slabs, bulk path), ``transfer_strided``
 (column slabs with 2 KiB runs), ``transfer_cast`` (bf16 -> fp32 elementwise),
 ``transfer_fp8`` (fused block quantisation), ``transfer_peer`` (contiguous
 slabs stored into the memory of a second GPU of this process over NVLink; needs
-two devices), ``fp8_quant`` / ``fp8_dequant`` (stand-alone kernels),
+two devices), ``transfer_peer_fp8`` (block quantisation into the second GPU's
+memory; ``AWEX_XFER_OUT_BULK=0`` stores per thread instead of through shared
+memory and bulk stores), ``fp8_quant`` / ``fp8_dequant`` (stand-alone kernels),
 ``checksum``.  Every case holds a few hundred MB (more
 than L2) and prints achieved GB/s from CUDA-event timings.
 """
@@ -42,7 +44,7 @@ def _transfer_case(kind: str, mb: int):
     g = torch.Generator(device="cuda").manual_seed(0)
     src = torch.randn(rows, cols, generator=g, device="cuda").to(torch.bfloat16)
     views = {}
-    if kind == "transfer_peer":
+    if kind in ("transfer_peer", "transfer_peer_fp8"):
         if torch.cuda.device_count() < 2:
             raise SystemExit("transfer_peer needs two GPUs")
         from awex_b200.ops import native
@@ -50,10 +52,18 @@ def _transfer_case(kind: str, mb: int):
         code = native.load().awex_enable_peer_access(0, 1)
         if code != 0:
             raise SystemExit(f"no peer access from device 0 to device 1 (code {code})")
-        dst = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda:1")
-        items = [CopyItem("w", 0, (0, 0), (rows, cols), 0, "w", (0, 0), torch.bfloat16, torch.bfloat16)]
-        views["w"] = dst
-        moved = src.numel() * 2  # bytes that cross the link, one direction
+        if kind == "transfer_peer_fp8":
+            dst = torch.zeros(rows, cols, dtype=torch.float8_e4m3fn, device="cuda:1")
+            scale = torch.zeros(-(-rows // 128), cols // 128, dtype=torch.float32, device="cuda:1")
+            items = [CopyItem("w", 0, (0, 0), (rows, cols), 0, "w", (0, 0), torch.bfloat16, torch.float8_e4m3fn,
+                              ValueOp("fp8_block", dtype=torch.float8_e4m3fn), scale_name="w_scale_inv", scale_start=(0, 0))]
+            views["w"], views["w_scale_inv"] = dst, scale
+            moved = src.numel()  # fp8 bytes that cross the link
+        else:
+            dst = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda:1")
+            items = [CopyItem("w", 0, (0, 0), (rows, cols), 0, "w", (0, 0), torch.bfloat16, torch.bfloat16)]
+            views["w"] = dst
+            moved = src.numel() * 2  # bytes that cross the link, one direction
     elif kind == "transfer_copy":
         dst = torch.zeros_like(src)
         items = [CopyItem("w", 0, (0, 0), (rows, cols), 0, "w", (0, 0), torch.bfloat16, torch.bfloat16)]
@@ -84,6 +94,13 @@ def _transfer_case(kind: str, mb: int):
     srcs = {("w", 0): TensorAddr.of(src)}
     dsts = {0: {n: TensorAddr.of(t) for n, t in views.items()}}
     table, n_tiles, enc = encode_items(items, srcs, dsts)
+    if kind == "transfer_peer_fp8":
+        import os
+
+        from awex_b200.transfer.descriptors import mark_bulk_output
+
+        if os.environ.get("AWEX_XFER_OUT_BULK", "1") != "0":
+            mark_bulk_output(table, enc.desc_dst, [0])
     problems = validate_table(table, n_tiles, [a.byte_span() for a in srcs.values()], [a.byte_span() for a in dsts[0].values()])
     assert not problems, problems
     prog = TransferProgram(table, n_tiles, "cuda", encoder=enc)
@@ -98,6 +115,12 @@ def _transfer_case(kind: str, mb: int):
         if kind == "transfer_peer":
             torch.cuda.synchronize(1)
             assert torch.equal(views["w"].to("cuda:0"), src), "peer destination differs from the source"
+        if kind == "transfer_peer_fp8":
+            from awex_b200.ops.fp8 import block_quant
+
+            torch.cuda.synchronize(1)
+            q_ref, s_ref = block_quant(src)
+            assert torch.equal(views["w"].to("cuda:0").view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(views["w_scale_inv"].to("cuda:0"), s_ref)
 
     return run, moved, check
 

@@ -28,7 +28,7 @@ from awex_b200.transfer.lowering import CopyItem
 
 OP_COPY, OP_CAST, OP_ADD, OP_FP8_BLOCK = 0, 1, 2, 3
 DT_BYTES, DT_BF16, DT_F16, DT_F32, DT_FP8_E4M3 = 0, 1, 2, 3, 4
-FLAG_BULK, FLAG_DST_VEC16, FLAG_UE8M0 = 1, 2, 4
+FLAG_BULK, FLAG_DST_VEC16, FLAG_UE8M0, FLAG_OUT_BULK = 1, 2, 4, 8
 STAGE_BYTES = 32 * 1024
 MAX_TX_BYTES = (1 << 20) - 1
 
@@ -251,6 +251,22 @@ def encode_items(items: Iterable[CopyItem], src_addrs: Dict[Tuple[str, int], Ten
         scale = dst_book.get(it.scale_name) if it.scale_name else None
         enc.add_item(it, src_addrs[(it.src_param, it.vp_stage)], dst_book[it.dst_name], scale)
     return enc.table(), enc.n_tiles, enc
+
+
+def mark_bulk_output(table: np.ndarray, desc_dst: Sequence[int], remote_ranks: Iterable[int]) -> int:
+    """Let the quantised tiles of destinations across NVLink leave through shared
+    memory and bulk-async stores (``FLAG_OUT_BULK``): per-thread stores to a peer
+    are limited by the writes an SM can have outstanding, bulk stores are not
+    (measured on 8 GPUs: 261 GB/s per sender with per-thread stores against 640
+    GB/s for copies, which use bulk stores).  Needs staged tiles and 16-byte
+    aligned destination rows.  Returns the number of descriptors marked."""
+    remote = np.isin(np.asarray(desc_dst, dtype=np.int64), np.fromiter(remote_ranks, dtype=np.int64))
+    if not len(table) or not remote.any():
+        return 0
+    need = FLAG_BULK | FLAG_DST_VEC16
+    mask = remote & (table["op"] == OP_FP8_BLOCK) & ((table["flags"] & need) == need) & (table["dst_stride"] % 16 == 0)
+    table["flags"][mask] |= FLAG_OUT_BULK
+    return int(mask.sum())
 
 
 def table_dst_bytes(table: np.ndarray) -> np.ndarray:

@@ -335,6 +335,10 @@ class PeerStoreSender:
                 remote.append(d)
         src_addrs = {key: TensorAddr.of(t) for key, t in self.local.items()}
         table, n_tiles, enc = encode_items(self._ordered_items(), src_addrs, dst_addrs)
+        if os.environ.get("AWEX_XFER_OUT_BULK", "1") != "0":
+            from awex_b200.transfer.descriptors import mark_bulk_output
+
+            mark_bulk_output(table, enc.desc_dst, remote)
         if self.validate:
             dst_spans = [a.byte_span() for book in dst_addrs.values() for n, a in book.items() if n != DONE_PAD]
             problems = validate_table(table, n_tiles, [a.byte_span() for a in src_addrs.values()], dst_spans, check_overlap=False)

@@ -19,6 +19,10 @@ def _run(items, srcs, dsts, **program_kwargs):
     src_addrs = {(n, 0): TensorAddr.of(t) for n, t in srcs.items()}
     dst_addrs = {rank: {n: TensorAddr.of(t) for n, t in views.items()} for rank, views in dsts.items()}
     table, n_tiles, enc = encode_items(items, src_addrs, dst_addrs)
+    if program_kwargs.pop("out_bulk", False):  # as for destinations across NVLink: quantised tiles leave through shared memory
+        from awex_b200.transfer.descriptors import mark_bulk_output
+
+        assert mark_bulk_output(table, enc.desc_dst, list(dst_addrs)) > 0
     spans = [a.byte_span() for views in dst_addrs.values() for a in views.values()]
     assert validate_table(table, n_tiles, [a.byte_span() for a in src_addrs.values()], spans) == []
     prog = TransferProgram(table, n_tiles, "cuda", encoder=enc, **program_kwargs)
@@ -73,7 +77,8 @@ def test_constant_add_rides_along(variant):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(512, 1024), (130, 136), (257, 384)])
 @pytest.mark.parametrize("ue8m0", [False, True])
-def test_fused_block_fp8_matches_cpu_statement(shape, dtype, variant, ue8m0):
+@pytest.mark.parametrize("out_bulk", [False, True])
+def test_fused_block_fp8_matches_cpu_statement(shape, dtype, variant, ue8m0, out_bulk):
     """Block quantisation inside the transfer kernel: whole blocks, edge blocks in
     both directions, both thread counts (8 and 4 chunks per thread)."""
     from awex_b200.converter.rows import ValueOp
@@ -87,7 +92,9 @@ def test_fused_block_fp8_matches_cpu_statement(shape, dtype, variant, ue8m0):
     s = torch.zeros(-(-shape[0] // 128), -(-shape[1] // 128), dtype=torch.float32, device="cuda")
     item = CopyItem("x", 0, (0, 0), shape, 0, "q", (0, 0), dtype, torch.float8_e4m3fn,
                     ValueOp("fp8_block", dtype=torch.float8_e4m3fn, ue8m0=ue8m0), scale_name="s", scale_start=(0, 0))
-    _run([item], {"x": x}, {0: {"q": q, "s": s}}, variant=variant)
+    if out_bulk and shape[1] % 16:
+        pytest.skip("rows of the destination are not 16-byte aligned: such slabs never take the bulk-store exit")
+    _run([item], {"x": x}, {0: {"q": q, "s": s}}, variant=variant, out_bulk=out_bulk)
     q_ref, s_ref = per_block_cast_to_fp8(x.cpu(), ue8m0)
     assert torch.equal(s.cpu(), s_ref)
     assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
@@ -146,7 +153,7 @@ def test_destination_groups_and_mixed_tiles(variant, interleave):
         CopyItem("w", 0, (0, 1024), (1024, 1024), 2, "wt", (0, 0), torch.bfloat16, torch.bfloat16),
     ]
     prog, table = _run(items, {"w": w, "v": v}, {0: d0, 1: d1, 2: d2}, variant=variant, interleave=interleave, desc_group=True,
-                       group_cost={0: 0.25}, grid=37)
+                       group_cost={0: 0.25}, grid=37, out_bulk=True)
     if interleave:
         groups = sorted({(int(e["tile_begin"]), int(e["tile_end"]), int(e["size"])) for e in prog.plan_host})
         assert len(groups) == 3 and sum(size for _, _, size in groups) == 37
