@@ -6,8 +6,8 @@ Cases: ``transfer_copy`` (contiguous slabs, bulk path), ``transfer_strided``
 ``transfer_fp8`` (fused block quantisation), ``transfer_peer`` (contiguous
 slabs stored into the memory of a second GPU of this process over NVLink; needs
 two devices), ``transfer_peer_fp8`` (block quantisation into the second GPU's
-memory; ``AWEX_XFER_OUT_BULK=0`` stores per thread instead of through shared
-memory and bulk stores), ``fp8_quant`` / ``fp8_dequant`` (stand-alone kernels),
+memory; ``AWEX_XFER_OUT_BULK=1`` sends the result through shared memory and
+bulk stores instead of per-thread stores), ``fp8_quant`` / ``fp8_dequant`` (stand-alone kernels),
 ``checksum``.  Every case holds a few hundred MB (more
 than L2) and prints achieved GB/s from CUDA-event timings.
 """
@@ -99,7 +99,7 @@ def _transfer_case(kind: str, mb: int):
 
         from awex_b200.transfer.descriptors import mark_bulk_output
 
-        if os.environ.get("AWEX_XFER_OUT_BULK", "1") != "0":
+        if os.environ.get("AWEX_XFER_OUT_BULK", "0") == "1":
             mark_bulk_output(table, enc.desc_dst, [0])
     problems = validate_table(table, n_tiles, [a.byte_span() for a in srcs.values()], [a.byte_span() for a in dsts[0].values()])
     assert not problems, problems

@@ -255,11 +255,12 @@ def encode_items(items: Iterable[CopyItem], src_addrs: Dict[Tuple[str, int], Ten
 
 def mark_bulk_output(table: np.ndarray, desc_dst: Sequence[int], remote_ranks: Iterable[int]) -> int:
     """Let the quantised tiles of destinations across NVLink leave through shared
-    memory and bulk-async stores (``FLAG_OUT_BULK``): per-thread stores to a peer
-    are limited by the writes an SM can have outstanding, bulk stores are not
-    (measured on 8 GPUs: 261 GB/s per sender with per-thread stores against 640
-    GB/s for copies, which use bulk stores).  Needs staged tiles and 16-byte
-    aligned destination rows.  Returns the number of descriptors marked."""
+    memory and bulk-async stores (``FLAG_OUT_BULK``) instead of per-thread
+    stores.  An option, off by default: one sender to one receiver it measured
+    slower (526 against 631 GB/s of fp8 payload; the second barrier per tile and
+    the shorter load lookahead cost more than the store path gains).  Needs staged
+    tiles and 16-byte aligned destination rows.  Returns the number of descriptors
+    marked."""
     remote = np.isin(np.asarray(desc_dst, dtype=np.int64), np.fromiter(remote_ranks, dtype=np.int64))
     if not len(table) or not remote.any():
         return 0
@@ -280,9 +281,14 @@ def build_cta_plan(table: np.ndarray, n_tiles: int, n_ctas: int, chunk_shift: in
     """The per-CTA plan (``PLAN_DTYPE``) and the chunk index of the fused kernel.
 
     Descriptors with the same group id that follow one another form a group; a
-    group gets CTAs in proportion to ``bytes written x cost per byte`` (at least
-    one) and its tiles are dealt to them in round-robin chunks of
-    ``2**chunk_shift`` tiles.  Without group ids, or when the table alternates
+    group gets CTAs in proportion to the time its tiles take (at least one) and its
+    tiles are dealt to them in round-robin chunks of ``2**chunk_shift`` tiles.  The
+    estimate: bytes written, times ``group_cost`` for plain copies (a copy that
+    stays in this GPU's memory is several times faster per byte than one across
+    NVLink), times one for tiles that are computed on (quantised, cast): those
+    take a CTA the same time wherever they go.  (With the copy discount applied to
+    quantised tiles, the group of the local destination of a block-fp8 layout got
+    a quarter of its share of CTAs and finished three times later than the rest.)  Without group ids, or when the table alternates
     between groups more often than there are CTAs to share out, all CTAs form one
     group over the whole table.  The chunk index holds, group after group, the
     descriptor of every chunk's first tile."""
@@ -295,13 +301,18 @@ def build_cta_plan(table: np.ndarray, n_tiles: int, n_ctas: int, chunk_shift: in
         cuts = np.flatnonzero(np.diff(ids)) + 1
         first = np.concatenate(([0], cuts))
         last = np.concatenate((cuts, [n_desc]))
-        nbytes = table_dst_bytes(table)
-        csum = np.concatenate(([0], np.cumsum(nbytes)))
+        per_byte = np.array([float((group_cost or {}).get(int(g), 1.0)) for g in ids])
+        per_byte[table["op"] != OP_COPY] = 1.0
+        # a computed tile reads its source too; count what it moves in and out
+        es = np.array([_DT_SIZE[c] for c in range(5)], dtype=np.int64)
+        moved = table_dst_bytes(table).astype(np.float64)
+        moved[table["op"] != OP_COPY] += (table["rows"].astype(np.int64) * table["row_elems"].astype(np.int64)
+                                          * es[table["src_dtype"].astype(np.int64)])[table["op"] != OP_COPY]
+        csum = np.concatenate(([0.0], np.cumsum(moved * per_byte)))
         for a, b in zip(first.tolist(), last.tolist()):
             tb, te = int(begins[a]), int(begins[b]) if b < n_desc else int(n_tiles)
-            cost = float((group_cost or {}).get(int(ids[a]), 1.0))
             if te > tb:
-                runs.append((tb, te, float(csum[b] - csum[a]) * cost))
+                runs.append((tb, te, float(csum[b] - csum[a])))
     if not runs or len(runs) > max(1, n_ctas // 2):
         runs = [(0, int(n_tiles), 1.0)]
     # apportion the CTAs: at least one each, the rest by largest remainder

@@ -335,7 +335,7 @@ class PeerStoreSender:
                 remote.append(d)
         src_addrs = {key: TensorAddr.of(t) for key, t in self.local.items()}
         table, n_tiles, enc = encode_items(self._ordered_items(), src_addrs, dst_addrs)
-        if os.environ.get("AWEX_XFER_OUT_BULK", "1") != "0":
+        if os.environ.get("AWEX_XFER_OUT_BULK", "0") == "1":
             from awex_b200.transfer.descriptors import mark_bulk_output
 
             mark_bulk_output(table, enc.desc_dst, remote)
