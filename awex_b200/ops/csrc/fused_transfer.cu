@@ -737,6 +737,219 @@ __global__ void __launch_bounds__(kThreadsX3, 3) fused_transfer_kernel_x3(const 
   transfer_body<kThreadsX3, kStagesX3>(p);
 }
 
+// ---------------------------------------------------------------- the lean block-fp8 kernel
+// Tables of nothing but quantised blocks fetched by tiled TMA loads (the expert
+// weights of a block-fp8 serving layout: nine tenths of its bytes) do not need
+// the general kernel's machinery, whose registers hold it at two CTAs per SM.
+// This kernel keeps the table walk out of the threads that compute: a producer
+// warp walks the CTA's tiles, and for each one issues the TMA load and leaves a
+// small record (where the block goes, its extent, where its scale goes) beside
+// the stage; eight consumer warps wait for the stage's mbarrier, read the
+// record, quantise from registers and store.  A consumed stage is handed back
+// through an "empty" mbarrier.  72 registers, three CTAs per SM, two 32 KiB stages
+// each.  Same plans, same flags, same status words and the same self-resetting
+// arrival counter as the general kernel; the host launches it on the part of a
+// table that qualifies and the general kernel on the rest.
+constexpr int kLeanConsumers = 256;
+constexpr int kLeanThreads = kLeanConsumers + 32;
+constexpr int kLeanStages = 2;
+
+struct alignas(16) Fp8Rec {
+  uint64_t dst;         // first byte of the block in the destination
+  int64_t dst_stride;   // bytes
+  uint64_t scale_addr;  // where the block's scale goes
+  uint32_t rows;        // rows of the block that exist
+  uint32_t chunks;      // 16-byte source chunks per row that exist (8 values each)
+  uint32_t flags;       // XferFlags of the descriptor
+  uint32_t src_bf16;    // 1: bf16 source, 0: fp16
+};
+
+// CTA-wide OR over the consumer threads only (named barrier 1).
+__device__ __forceinline__ bool consumers_or(bool mine) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "barrier.cta.red.or.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(mine)), "r"(kLeanConsumers)
+      : "memory");
+  return out != 0;
+}
+
+__global__ void __launch_bounds__(kLeanThreads, 3) fp8_table_kernel(const __grid_constant__ XferParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[kLeanStages];
+  __shared__ __align__(8) uint64_t empty_bar[kLeanStages];
+  __shared__ Fp8Rec recs[kLeanStages];
+  __shared__ uint32_t red[2][kLeanConsumers / 32];
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kLeanStages; ++s) {
+      mbar_init(smem_addr(&full_bar[s]), 1);
+      mbar_init(smem_addr(&empty_bar[s]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // wait until every destination has announced this epoch (as in the general kernel)
+  uint32_t my_abort = 0;
+  if (p.n_ready) {
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = threadIdx.x; i < p.n_ready && !my_abort; i += blockDim.x) {
+      const uint64_t* flag = p.ready_pad + p.ready_slots[i];
+      while (ld_acquire_sys(flag) < p.epoch) {
+        if (globaltimer_ns() - t0 > p.timeout_ns) {
+          if (atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_READY_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(p.ready_slots[i]);
+          my_abort = 1;
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    my_abort = __syncthreads_or(static_cast<int>(my_abort)) != 0;
+  }
+
+  // this CTA's tiles: its plan entry, or an even contiguous share
+  const bool planned = p.cta_plan != nullptr;
+  const uint32_t cs = planned ? p.chunk_shift : 0;
+  const uint64_t cmask = (uint64_t{1} << cs) - 1;
+  uint64_t t_begin, n = 0;
+  uint32_t g_rank = 0, g_size = 1, chunk_off = 0;
+  if (planned) {
+    const CtaPlan plan = p.cta_plan[blockIdx.x];
+    t_begin = plan.tile_begin;
+    g_rank = plan.rank;
+    g_size = plan.size;
+    chunk_off = plan.chunk_off;
+    const uint64_t range = plan.tile_end - plan.tile_begin;
+    const uint64_t n_chunks = (range + cmask) >> cs;
+    if (g_rank < n_chunks) {
+      const uint64_t mine = (n_chunks - g_rank + g_size - 1) / g_size;
+      n = mine << cs;
+      if (g_rank + (mine - 1) * g_size == n_chunks - 1) n -= (n_chunks << cs) - range;
+    }
+  } else {
+    t_begin = p.n_tiles * blockIdx.x / gridDim.x;
+    n = p.n_tiles * (blockIdx.x + 1) / gridDim.x - t_begin;
+  }
+  if (my_abort) n = 0;
+
+  if (warp == kLeanConsumers / 32) {
+    // ---- producer: one lane walks the table, issues the loads, writes the records
+    if (lane == 0 && n > 0) {
+      Cursor cur;
+      if (planned) cursor_jump(cur, p, chunk_off + g_rank);
+      else cursor_seek(cur, p, t_begin);
+      uint64_t issued = 0;
+      bool failed = false;
+      for (uint64_t j = 0; j < n; ++j) {
+        const uint32_t stage = static_cast<uint32_t>(j & 1);
+        if (j >= kLeanStages) {  // the stage's previous block has been taken into registers by every consumer
+          if (!mbar_wait_bounded(smem_addr(&empty_bar[stage]), static_cast<uint32_t>(((j >> 1) - 1) & 1), 2 * p.timeout_ns)) {
+            failed = true;  // the consumers stopped (they have reported why)
+            break;
+          }
+        }
+        const uint64_t chunk = (j >> cs) * g_size + g_rank;
+        const uint64_t tile = t_begin + (chunk << cs) + (j & cmask);
+        if (planned && (j & cmask) == 0) cursor_jump(cur, p, chunk_off + chunk);
+        cursor_advance_to(cur, p, tile);
+        const XferDesc* d = &p.descs[cur.di];
+        const uint32_t col_tiles = d->col_tiles;
+        const uint32_t k = static_cast<uint32_t>(tile - cur.begin);
+        const uint32_t band = k / col_tiles, ct = k - band * col_tiles;
+        const uint64_t row0 = static_cast<uint64_t>(band) * kFp8Block, col0 = static_cast<uint64_t>(ct) * kFp8Block;
+        const uint64_t rows_left = d->rows - row0, cols_left = d->row_elems - col0;
+        Fp8Rec& rec = recs[stage];
+        rec.dst = d->dst + row0 * d->dst_stride + col0;
+        rec.dst_stride = d->dst_stride;
+        rec.scale_addr = d->aux_ptr + (static_cast<int64_t>(band) * d->aux_stride + ct) * 4;
+        rec.rows = rows_left < kFp8Block ? static_cast<uint32_t>(rows_left) : kFp8Block;
+        rec.chunks = (cols_left < kFp8Block ? static_cast<uint32_t>(cols_left) : kFp8Block) >> 3;
+        rec.flags = d->flags;
+        rec.src_bf16 = d->src_dtype == DT_BF16;
+        const uint32_t bar = smem_addr(&full_bar[stage]);
+        mbar_arrive_expect_tx(bar, kStageBytes);  // releases the record; the whole 128 x 128 box counts, zero-filled past the slab's edge
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                smem_addr(smem + static_cast<size_t>(stage) * kStageBytes)),
+            "l"(d->tensor_map), "r"(static_cast<int32_t>(col0)), "r"(static_cast<int32_t>(row0)), "r"(bar)
+            : "memory");
+        issued = j + 1;
+      }
+      if (failed || my_abort) {
+        // nothing of this CTA may be in flight when it returns: the last loads issued get one more deadline
+        for (uint64_t j = issued > kLeanStages ? issued - kLeanStages : 0; j < issued; ++j)
+          if (!mbar_wait_bounded(smem_addr(&full_bar[j & 1]), static_cast<uint32_t>((j >> 1) & 1), p.timeout_ns)) break;
+      }
+    }
+  } else {
+    // ---- consumers
+    const uint32_t chunk = threadIdx.x & 15u, row0 = threadIdx.x >> 4;
+    constexpr int kPasses = (kFp8Block * kFp8Block * 2 / 16) / kLeanConsumers;  // 8 chunks per thread
+    constexpr uint32_t kRowStep = kLeanConsumers / 16;
+    for (uint64_t i = 0; i < n; ++i) {
+      const uint32_t stage = static_cast<uint32_t>(i & 1);
+      const bool arrived = mbar_wait_bounded(smem_addr(&full_bar[stage]), static_cast<uint32_t>((i >> 1) & 1), p.timeout_ns);
+      if (!arrived && atomicCAS(reinterpret_cast<int*>(p.status), ST_OK, ST_LOAD_TIMEOUT) == ST_OK) p.status[1] = static_cast<int>(i);
+      const Fp8Rec rec = recs[stage];
+      const unsigned char* stage_ptr = smem + static_cast<size_t>(stage) * kStageBytes;
+      const bool col_ok = arrived && chunk < rec.chunks;
+      uint4 raw[kPasses];
+      uint32_t m = 0;
+#pragma unroll
+      for (int q = 0; q < kPasses; ++q) {
+        const uint32_t row = row0 + q * kRowStep;
+        raw[q] = (col_ok && row < rec.rows) ? *reinterpret_cast<const uint4*>(stage_ptr + row * 256u + chunk * 16u) : make_uint4(0, 0, 0, 0);
+        m = amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(amax_bits_bf16x2(m, raw[q].x), raw[q].y), raw[q].z), raw[q].w);
+      }
+      m = __reduce_max_sync(0xffffffffu, max(m & 0xFFFFu, m >> 16));
+      if (lane == 0) red[i & 1][warp] = m;
+      if (consumers_or(!arrived)) break;  // the same verdict for every consumer
+      if (threadIdx.x == 0) mbar_arrive(smem_addr(&empty_bar[stage]));  // every consumer holds its part in registers
+      uint32_t all = red[i & 1][0];
+#pragma unroll
+      for (int w = 1; w < kLeanConsumers / 32; ++w) all = max(all, red[i & 1][w]);
+      const float amax = rec.src_bf16 ? __uint_as_float(all << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(all)));
+      const QuantScale qs = make_quant_scale(amax, (rec.flags & FLAG_UE8M0) != 0);
+      if (threadIdx.x == 0) *reinterpret_cast<float*>(rec.scale_addr) = qs.s;
+      unsigned char* dst = reinterpret_cast<unsigned char*>(rec.dst) + chunk * 8u;
+      const bool vec = (rec.flags & FLAG_DST_VEC16) != 0;
+#pragma unroll
+      for (int q = 0; q < kPasses; ++q) {
+        const uint32_t row = row0 + q * kRowStep;
+        if (!col_ok || row >= rec.rows) continue;
+        const uint2 out = rec.src_bf16 ? quant_chunk16<true>(raw[q], qs) : quant_chunk16<false>(raw[q], qs);
+        unsigned char* o = dst + static_cast<int64_t>(row) * rec.dst_stride;
+        if (vec) {
+          *reinterpret_cast<uint2*>(o) = out;
+        } else {
+          const unsigned char* b = reinterpret_cast<const unsigned char*>(&out);
+          for (int j = 0; j < 8; ++j) o[j] = b[j];
+        }
+      }
+    }
+  }
+
+  // Drain: this CTA's writes must be visible system-wide before it counts itself in.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int arrived = atomicAdd(p.cta_counter, 1u) + 1u;
+    if (arrived == gridDim.x) {
+      __threadfence_system();
+      const bool ok = *reinterpret_cast<volatile int32_t*>(p.status) == ST_OK;
+      if (ok)
+        for (uint32_t i = 0; i < p.n_done; ++i) st_release_sys(p.done_flags[i], p.epoch);
+      *p.cta_counter = 0;
+    }
+  }
+}
+
 // Receiver side: wait (bounded) until every listed sender has raised `epoch`.
 __global__ void wait_flags_kernel(const uint64_t* pad, const uint32_t* slots, uint32_t n, uint64_t epoch, uint64_t timeout_ns,
                                   int32_t* status) {
@@ -773,7 +986,9 @@ int awex_xfer_smem_bytes() { return awex::kStages * awex::kStageBytes; }
 int awex_xfer_stage_bytes() { return awex::kStageBytes; }
 
 // Returns a cudaError_t.  `variant` 0: one CTA of 512 threads per SM; 1: two
-// CTAs of 256 threads per SM; 2: three CTAs of 256 threads per SM.  `grid` == 0 fills the device for the variant.
+// CTAs of 256 threads per SM; 2: three CTAs of 256 threads per SM; 3: the lean
+// block-fp8 kernel (every descriptor must be a staged OP_FP8_BLOCK slab of a
+// 2-byte type with a tensor map; the caller checks).  `grid` == 0 fills the device for the variant.
 // With `cta_plan` (one CtaPlan per CTA, plus `chunk_desc`) `grid` is the number
 // of plan entries and is used as given.
 int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_tiles, uint64_t epoch, uint64_t timeout_ns,
@@ -781,18 +996,19 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
                                uint32_t n_done, void* cta_counter, void* status, int grid, void* stream,
                                const void* chunk_desc, uint32_t chunk_shift, uint32_t variant, const void* cta_plan) {
   // the shared-memory attribute is set once per (variant, device)
-  static std::atomic<uint64_t> configured[3];
-  if (variant > 2) return cudaErrorInvalidValue;
+  static std::atomic<uint64_t> configured[4];
+  if (variant > 3) return cudaErrorInvalidValue;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  const int stages = variant == 0 ? awex::kStages : variant == 1 ? awex::kStagesX2 : awex::kStagesX3;
+  const int stages = variant == 0 ? awex::kStages : variant == 1 ? awex::kStagesX2 : variant == 2 ? awex::kStagesX3 : awex::kLeanStages;
   const int smem = stages * awex::kStageBytes;
   const uint64_t bit = (dev >= 0 && dev < 64) ? (uint64_t{1} << dev) : 0;
   if (bit == 0 || !(configured[variant].load(std::memory_order_acquire) & bit)) {
     err = variant == 0   ? cudaFuncSetAttribute(awex::fused_transfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
           : variant == 1 ? cudaFuncSetAttribute(awex::fused_transfer_kernel_x2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
-                         : cudaFuncSetAttribute(awex::fused_transfer_kernel_x3, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+          : variant == 2 ? cudaFuncSetAttribute(awex::fused_transfer_kernel_x3, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                         : cudaFuncSetAttribute(awex::fp8_table_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return err;
     configured[variant].fetch_or(bit, std::memory_order_release);
   }
@@ -800,7 +1016,7 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
   if (grid <= 0) {
     err = cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
-    grid *= static_cast<int>(variant) + 1;
+    grid *= variant == 3 ? 3 : static_cast<int>(variant) + 1;
   }
   if (cta_plan == nullptr && n_tiles > 0 && static_cast<uint64_t>(grid) > n_tiles) grid = static_cast<int>(n_tiles);
   if (grid < 1) grid = 1;
@@ -820,7 +1036,9 @@ int awex_launch_fused_transfer(const void* descs, uint32_t n_desc, uint64_t n_ti
   p.cta_plan = static_cast<const awex::CtaPlan*>(cta_plan);
   p.chunk_desc = static_cast<const uint32_t*>(chunk_desc);
   p.chunk_shift = cta_plan ? chunk_shift : 0;
-  if (variant == 2)
+  if (variant == 3)
+    awex::fp8_table_kernel<<<grid, awex::kLeanThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  else if (variant == 2)
     awex::fused_transfer_kernel_x3<<<grid, awex::kThreadsX3, smem, static_cast<cudaStream_t>(stream)>>>(p);
   else if (variant == 1)
     awex::fused_transfer_kernel_x2<<<grid, awex::kThreadsX2, smem, static_cast<cudaStream_t>(stream)>>>(p);

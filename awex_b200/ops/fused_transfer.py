@@ -59,8 +59,13 @@ def _max_chunk_shift(table: np.ndarray, n_tiles: int) -> int:
             pass
     begins = table["tile_begin"].astype(np.int64)
     counts = np.diff(np.append(begins, n_tiles))
-    fp8_tiles = int(counts[table["op"] == OP_FP8_BLOCK].sum())
-    return 4 if 2 * fp8_tiles > n_tiles else 2
+    is_fp8 = table["op"] == OP_FP8_BLOCK
+    fp8_tiles = int(counts[is_fp8].sum())
+    if 2 * fp8_tiles <= n_tiles:
+        return 2
+    # small slabs (an expert's shard: 64 blocks): a chunk per slab, so that a CTA stays with one tensor map
+    # (slabs of 192 x 4096 ran at 2.50 TB/s with chunks of 16 blocks and at 2.87 TB/s with chunks of 64)
+    return 6 if float(np.median(counts[is_fp8])) <= 256 else 4
 
 
 def _pick_variant(table: np.ndarray, n_tiles: int) -> int:
@@ -134,12 +139,18 @@ class TransferProgram:
                  ready_slots: Sequence[int] = (), done_flag_addrs: Sequence[int] = (), timeout_ms: int = 2000,
                  grid: int = 0, row_offsets: Sequence[int] = (), tensor_map_descs: Sequence[int] = (), encoder=None,
                  interleave: bool = True, variant: Optional[int] = None, desc_group: Optional[Sequence[int]] = None,
-                 group_cost: Optional[Dict[int, float]] = None):
+                 group_cost: Optional[Dict[int, float]] = None, _resolved: bool = False, _status: Optional["StatusWord"] = None):
         """``interleave``: deal tiles to CTAs in round-robin chunks instead of one
         contiguous range per CTA.  ``desc_group`` (one id per descriptor, e.g. the
         destination rank; taken from ``encoder`` when it is given and this is
         ``True``) makes one group of CTAs per run of equal ids, sized by the bytes it
-        writes times ``group_cost[id]`` (relative time per byte, default 1)."""
+        writes times ``group_cost[id]`` (relative time per byte, default 1).
+
+        When no launch shape is forced and a worthwhile part of the table is
+        quantised blocks fetched by tiled TMA loads, that part is split off and run
+        by the lean block-fp8 kernel (``self.lean``, launched first on the same
+        stream); the general kernel then runs the rest and raises the completion
+        flags.  ``AWEX_XFER_LEAN_FP8=0`` keeps everything in the general kernel."""
         if encoder is not None:  # side tables produced while encoding
             row_offsets, tensor_map_descs = encoder.row_offsets, encoder.tensor_map_descs
             if desc_group is True:
@@ -154,17 +165,24 @@ class TransferProgram:
         self.n_desc = int(table.shape[0])
         self.n_tiles = int(n_tiles)
         self.row_table_dev = None
+        self.lean: Optional["TransferProgram"] = None
+        if _resolved:
+            row_offsets, tensor_map_descs = (), ()
         if len(row_offsets):
             # descriptors refer to the gathered-row offsets by index + 1; give them addresses
             self.row_table_dev = _device_array(list(row_offsets), np.int64, self.device)
             table = table.copy()
             has = table["row_table"] != 0
             table["row_table"][has] = self.row_table_dev.data_ptr() + (table["row_table"][has] - 1) * 8
-        elif self.n_desc and bool((table["row_table"] != 0).any()):
+        elif not _resolved and self.n_desc and bool((table["row_table"] != 0).any()):
             raise ValueError("descriptor table uses gathered rows but no row offsets were given")
         self.tensor_maps_dev = None
         if len(tensor_map_descs):
             table = self._attach_tensor_maps(table, tensor_map_descs)
+        self.status = _status if _status is not None else StatusWord(self.device)
+        self.total_tiles = self.n_tiles
+        if variant is None and not _resolved:
+            table, desc_group = self._split_off_lean_part(table, desc_group, group_cost, ready_pad, ready_slots, timeout_ms, interleave)
         self.table_host = table
         self.table_dev = torch.from_numpy(table.view(np.uint8).reshape(-1).copy()).to(self.device) if self.n_desc else torch.empty(0, dtype=torch.uint8, device=self.device)
         self.ready_pad = ready_pad
@@ -179,7 +197,8 @@ class TransferProgram:
         if interleave and self.n_desc and self.n_tiles:
             from awex_b200.transfer.descriptors import build_cta_plan
 
-            ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count * (self.variant + 1)
+            per_sm = 3 if self.variant == 3 else self.variant + 1
+            ctas = grid if grid > 0 else torch.cuda.get_device_properties(self.device).multi_processor_count * per_sm
             ctas = max(1, min(ctas, self.n_tiles))
             shift = _max_chunk_shift(table, self.n_tiles)
             while shift > 0 and (self.n_tiles >> shift) < 4 * ctas:
@@ -190,10 +209,42 @@ class TransferProgram:
             self.chunk_shift = shift
             grid = ctas
         self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.status = StatusWord(self.device)
         self.timeout_ns = int(timeout_ms) * 1_000_000
         self.grid = grid
         self.launches = 0
+
+    def _split_off_lean_part(self, table, desc_group, group_cost, ready_pad, ready_slots, timeout_ms, interleave):
+        """Move the descriptors the lean block-fp8 kernel can run (staged
+        ``OP_FP8_BLOCK`` slabs of a 2-byte type with a tensor map) into a program of
+        their own when they are worth a launch; returns what stays here."""
+        import os
+
+        from awex_b200.transfer.descriptors import DT_BF16, DT_F16, FLAG_BULK, FLAG_OUT_BULK, OP_FP8_BLOCK
+
+        if os.environ.get("AWEX_XFER_LEAN_FP8", "1") == "0" or os.environ.get("AWEX_XFER_VARIANT") or not self.n_desc:
+            return table, desc_group
+        lean = ((table["op"] == OP_FP8_BLOCK) & (table["tensor_map"] != 0) & ((table["flags"] & FLAG_BULK) != 0)
+                & ((table["flags"] & FLAG_OUT_BULK) == 0) & np.isin(table["src_dtype"], (DT_BF16, DT_F16)))
+        begins = table["tile_begin"].astype(np.int64)
+        counts = np.diff(np.append(begins, self.n_tiles))
+        lean_tiles = int(counts[lean].sum())
+        if lean_tiles < 4096 and 2 * lean_tiles < self.n_tiles:
+            return table, desc_group
+
+        def part(mask):
+            sub = table[mask].copy()
+            sub_counts = counts[mask]
+            sub["tile_begin"] = np.concatenate(([0], np.cumsum(sub_counts)[:-1])) if len(sub) else sub["tile_begin"]
+            groups = None if desc_group is None else [g for g, m in zip(desc_group, mask) if m]
+            return sub, int(sub_counts.sum()), groups
+
+        lean_table, lean_n, lean_groups = part(lean)
+        rest_table, rest_n, rest_groups = part(~lean)
+        self.lean = TransferProgram(lean_table, lean_n, self.device, ready_pad=ready_pad, ready_slots=ready_slots, done_flag_addrs=(),
+                                    timeout_ms=timeout_ms, interleave=interleave, variant=3, desc_group=lean_groups, group_cost=group_cost,
+                                    _resolved=True, _status=self.status)
+        self.n_desc, self.n_tiles = int(rest_table.shape[0]), rest_n
+        return rest_table, rest_groups
 
     def _attach_tensor_maps(self, table: np.ndarray, indices: Sequence[int]) -> np.ndarray:
         """Encode one CUtensorMap per listed descriptor (its tiles are then fetched
@@ -229,10 +280,14 @@ class TransferProgram:
             self.status.raise_if_failed()
         except TransferError:
             self.counter.zero_()
+            if self.lean is not None:
+                self.lean.counter.zero_()
             raise
 
     def launch(self, epoch: int, stream_ptr: Optional[int] = None) -> None:
         stream = native.current_stream_ptr() if stream_ptr is None else stream_ptr
+        if self.lean is not None:
+            self.lean.launch(epoch, stream)  # same stream: finished before the launch below raises the completion flags
         code = self.lib.awex_launch_fused_transfer(
             self.table_dev.data_ptr() if self.n_desc else None, self.n_desc, self.n_tiles, epoch, self.timeout_ns,
             self.ready_pad.ptr if (self.ready_pad is not None and self.n_ready) else None,

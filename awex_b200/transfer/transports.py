@@ -451,7 +451,7 @@ class PeerStoreSender:
         epoch = self._rendezvous(self.last_epoch + 1 if epoch is None else epoch)
         if env.flag("AWEX_P2P_TRACE"):
             per_dst = {d: sum(entry_nbytes(e) for e in es) for d, es in self.manifest.items()}
-            logger.info(f"[p2p] train rank {self.train_rank} epoch {epoch}: {self.n_desc} descriptors, {self.program.n_tiles} tiles, "
+            logger.info(f"[p2p] train rank {self.train_rank} epoch {epoch}: {self.n_desc} descriptors, {getattr(self.program, 'total_tiles', self.program.n_tiles)} tiles, "
                         f"bytes per destination {per_dst}, host-synchronised {self.host_destinations}")
         if self.gpu_events is not None:
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -30,6 +30,7 @@ KNOBS: Dict[str, Tuple[str, str]] = {
     "AWEX_XFER_VARIANT": ("", "0 | 1 | 2: force the launch shape of the fused transfer kernel (one 512-thread, two or three 256-thread CTAs per SM)"),
     "AWEX_XFER_INTERLEAVE": ("1", "0: one contiguous tile range per CTA instead of round-robin chunks"),
     "AWEX_XFER_DEST_GROUPS": ("1", "0: deal the whole table to all CTAs as one group instead of one CTA group per destination"),
+    "AWEX_XFER_LEAN_FP8": ("1", "0: quantised blocks stay in the general transfer kernel instead of being split off to the lean block-fp8 kernel"),
     "AWEX_XFER_OUT_BULK": ("0", "1: quantised tiles for destinations across NVLink leave through shared memory and bulk stores instead of per-thread stores (measured slower one to one: 526 against 631 GB/s of fp8 payload)"),
     "AWEX_XFER_DEST_STRIPE_MB": ("0", "cut items into stripes of this many MiB and merge the destinations' stripes in proportion to their bytes, with round-robin chunks (experimental)"),
     "AWEX_XFER_DEST_ROTATE": ("0", "1: each sender starts its table at a different destination (experimental, with AWEX_XFER_INTERLEAVE=1; only helps when all senders have the same destination set)"),

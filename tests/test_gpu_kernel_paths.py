@@ -232,3 +232,92 @@ def test_column_normalisation_is_exact_where_the_norm_is_exact():
     got = col_l2_normalize(x)
     want = torch.nn.functional.normalize(x.cpu(), dim=0, p=2, eps=1e-7)
     assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("ue8m0", [False, True])
+def test_lean_block_fp8_kernel_on_many_small_slabs_with_copies_beside_them(dtype, ue8m0):
+    """A table like a block-fp8 serving layout: many expert-sized slabs (row and
+    column slices with half-filled edge blocks) plus plain copies.  With no launch
+    shape forced, the quantised slabs run in the lean kernel and the rest in the
+    general one; one completion flag is raised, after both."""
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.ops.fused_transfer import FlagPad
+    from awex_b200.transfer.lowering import CopyItem
+
+    g = torch.Generator(device="cuda").manual_seed(31)
+    experts, hid, ffn, tp = 6, 1024, 384, 2
+    w13 = (torch.randn(experts, 2 * ffn, hid, generator=g, device="cuda") * 0.05).to(dtype)
+    w2 = (torch.randn(experts, hid, ffn, generator=g, device="cuda") * 0.05).to(dtype)
+    emb = torch.randn(4096, hid, generator=g, device="cuda").to(dtype)
+    srcs, dsts, items = {"emb": emb}, {0: {"emb": torch.zeros_like(emb)}}, []
+    items.append(CopyItem("emb", 0, (0, 0), (4096, hid), 0, "emb", (0, 0), dtype, dtype))
+    part = ffn // tp  # 192 rows / columns per shard: one and a half blocks
+    for e in range(experts):
+        srcs[f"w13_{e}"], srcs[f"w2_{e}"] = w13[e], w2[e]
+        for j in range(tp):
+            for kind, base in (("gate", 0), ("up", ffn)):
+                name = f"{kind}{e}_{j}"
+                dsts[0][name] = torch.zeros(part, hid, dtype=torch.float8_e4m3fn, device="cuda")
+                dsts[0][name + "_s"] = torch.zeros(2, hid // 128, dtype=torch.float32, device="cuda")
+                items.append(CopyItem(f"w13_{e}", 0, (base + part * j, 0), (part, hid), 0, name, (0, 0), dtype, torch.float8_e4m3fn,
+                                      ValueOp("fp8_block", dtype=torch.float8_e4m3fn, ue8m0=ue8m0), scale_name=name + "_s", scale_start=(0, 0)))
+            name = f"down{e}_{j}"
+            dsts[0][name] = torch.zeros(hid, part, dtype=torch.float8_e4m3fn, device="cuda")
+            dsts[0][name + "_s"] = torch.zeros(hid // 128, 2, dtype=torch.float32, device="cuda")
+            items.append(CopyItem(f"w2_{e}", 0, (0, part * j), (hid, part), 0, name, (0, 0), dtype, torch.float8_e4m3fn,
+                                  ValueOp("fp8_block", dtype=torch.float8_e4m3fn, ue8m0=ue8m0), scale_name=name + "_s", scale_start=(0, 0)))
+    done = FlagPad(1, "cuda")
+    prog, _ = _run(items, srcs, dsts, done_flag_addrs=[done.slot_addr(0)])
+    assert prog.lean is not None and prog.lean.variant == 3 and prog.lean.n_tiles > 0 and prog.n_tiles > 0
+    assert prog.lean.n_tiles + prog.n_tiles == prog.total_tiles
+    assert done.t.item() == 1 and int(prog.counter.item()) == 0 and int(prog.lean.counter.item()) == 0
+    assert torch.equal(dsts[0]["emb"], emb)
+    for e in range(experts):
+        for j in range(tp):
+            for kind, base in (("gate", 0), ("up", ffn)):
+                q_ref, s_ref = per_block_cast_to_fp8(w13[e, base + part * j: base + part * (j + 1)].cpu(), ue8m0)
+                name = f"{kind}{e}_{j}"
+                assert torch.equal(dsts[0][name + "_s"].cpu(), s_ref), name
+                assert torch.equal(dsts[0][name].cpu().view(torch.uint8), q_ref.view(torch.uint8)), name
+            q_ref, s_ref = per_block_cast_to_fp8(w2[e, :, part * j: part * (j + 1)].cpu().contiguous(), ue8m0)
+            assert torch.equal(dsts[0][f"down{e}_{j}_s"].cpu(), s_ref)
+            assert torch.equal(dsts[0][f"down{e}_{j}"].cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    # a second launch of the same programs (the counters reset themselves)
+    for t in dsts[0].values():
+        t.zero_()
+    prog.launch(2)
+    torch.cuda.synchronize()
+    prog.check()
+    assert done.t.item() == 2 and torch.equal(dsts[0]["emb"], emb)
+    q_ref, _ = per_block_cast_to_fp8(w2[0, :, :part].cpu().contiguous(), ue8m0)
+    assert torch.equal(dsts[0]["down0_0"].cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+def test_lean_kernel_gives_up_cleanly_when_a_destination_never_announces():
+    from awex_b200.converter.rows import ValueOp
+    from awex_b200.ops.fused_transfer import FlagPad, TransferError, TransferProgram
+    from awex_b200.transfer.descriptors import TensorAddr, encode_items
+    from awex_b200.transfer.lowering import CopyItem
+
+    x = (torch.randn(4096, 1024, device="cuda") * 0.05).to(torch.bfloat16)
+    q = torch.zeros(4096, 1024, dtype=torch.float8_e4m3fn, device="cuda")
+    s = torch.zeros(32, 8, dtype=torch.float32, device="cuda")
+    item = CopyItem("x", 0, (0, 0), (4096, 1024), 0, "q", (0, 0), torch.bfloat16, torch.float8_e4m3fn,
+                    ValueOp("fp8_block", dtype=torch.float8_e4m3fn), scale_name="s", scale_start=(0, 0))
+    table, n_tiles, enc = encode_items([item], {("x", 0): TensorAddr.of(x)}, {0: {"q": TensorAddr.of(q), "s": TensorAddr.of(s)}})
+    ready, done = FlagPad(1, "cuda"), FlagPad(1, "cuda")
+    prog = TransferProgram(table, n_tiles, "cuda", ready_pad=ready, ready_slots=[0], done_flag_addrs=[done.slot_addr(0)], timeout_ms=30, encoder=enc)
+    assert prog.lean is not None
+    prog.launch(3)
+    torch.cuda.synchronize()
+    with pytest.raises(TransferError) as err:
+        prog.status.raise_if_failed()
+    assert err.value.code == 1 and int(prog.lean.counter.item()) == 0 and int(prog.counter.item()) == 0
+    assert torch.count_nonzero(q.view(torch.uint8)).item() == 0 and done.t.item() == 0
+    ready.t.fill_(3)
+    prog.launch(3)
+    torch.cuda.synchronize()
+    prog.status.raise_if_failed()
+    q_ref, s_ref = per_block_cast_to_fp8(x.cpu(), False)
+    assert done.t.item() == 3 and torch.equal(s.cpu(), s_ref) and torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
