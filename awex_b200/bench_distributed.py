@@ -77,12 +77,14 @@ def role_table(n: int, config: str = "separated", placement: str = "blocked"):
     return TrainLayout(tp=4), InferLayout(tp=2, num_engines=2), [0, 1, 2, 3], [[4, 5], [6, 7]], "tp4->2xtp2"
 
 
-def bench_config(model: str, bytes_per_update: int, parallelism: str, mode: str, validated: bool, extra=None) -> dict:
+def bench_config(model: str, bytes_per_update: int, parallelism: str, mode: str, validated: bool) -> dict:
     """The ``config`` record of a benchmark line.  Both arms (this framework and
-    the reference harness) build it here, so that they carry the same keys; what
-    only one arm knows goes under ``details``."""
+    the reference harness) build it here, so that the same job gives the same
+    record in both; what only one arm knows goes into the line's
+    ``config_details``."""
     return {"model": model, "bytes_per_update": int(bytes_per_update), "parallelism": parallelism, "mode": mode,
-            "validated_bitwise": bool(validated), "details": dict(extra or {})}
+            "validated_bitwise": bool(validated),
+            "l2": "every update moves far more than L2 holds (>= 8 GB per GPU at full size); no flush between steps"}
 
 
 def _spawn_inference_process(args):
@@ -473,15 +475,15 @@ def run_distributed(args):
             "vs_baseline": None, "dtype": "bf16",
             "device": "cpu (functional check, not a measurement)" if cpu else "cuda",
             "data": "synthetic random-init N(0,0.02) weights from per-name seeds", "impl": "ours",
-            "config": bench_config(arch.name, int(bytes_out), label, "colocated" if colocated else "separated", bool(valid), extra={
+            "config": bench_config(arch.name, int(bytes_out), label, "colocated" if colocated else "separated", bool(valid)),
+            "config_details": {
                 "params": arch.param_count(), "config": config,
                 "infer_dtype": "fp8_e4m3 128x128 blocks, fp32 scales" if infer_layout.fp8 else "bf16",
                 "fp8_oracle": os.environ.get("AWEX_SYNTH_FP8_ORACLE") if infer_layout.fp8 else None,
-                "l2": "inputs (>=8 GB per GPU) exceed L2; no flush needed",
                 "placement": getattr(args, "placement", "blocked"), "replica_pairing": getattr(args, "pairing", None) or "spread (writer default)",
                 "timing": "CUDA events around each rank's GPU work of the update (transfer kernel incl. its wait for the destinations' device "
                           "flags; readers' flag wait), max over ranks; ms_per_step_with_host_rendezvous brackets the whole step",
-            }),
+            },
             "ms_per_step_with_host_rendezvous": ms_with_host,
             "aggregate_GBps": bytes_out / seconds / 1e9,
             "nvlink_GBps_per_gpu": (egress / seconds / 1e9) if remote else 0.0,

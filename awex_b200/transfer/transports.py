@@ -372,8 +372,9 @@ class PeerStoreSender:
     def _ordered_items(self) -> List[CopyItem]:
         """Items arrive grouped by destination in ascending rank order.  With
         ``AWEX_XFER_DEST_ROTATE=1`` every sender starts its walk at a different
-        destination (rotation by its own rank), so that senders which work on one
-        destination at a time (round-robin chunks) take turns at each receiver
+        destination (:meth:`turn_order`), so that senders which work on one
+        destination at a time (round-robin chunks over the whole table, i.e.
+        together with ``AWEX_XFER_DEST_GROUPS=0``) take turns at each receiver
         instead of meeting there.  With ``AWEX_XFER_DEST_STRIPE_MB=<MiB>`` the items
         are cut into stripes of that size and the destinations' stripes are merged
         in proportion to their bytes (:func:`stripe_by_destination`), and tiles are
@@ -387,9 +388,23 @@ class PeerStoreSender:
             return stripe_by_destination(self.items, stripe)
         if os.environ.get("AWEX_XFER_DEST_ROTATE", "0") != "1" or len(self.destinations) < 2:
             return self.items
-        shift = self.train_rank % len(self.destinations)
-        order = {d: (i - shift) % len(self.destinations) for i, d in enumerate(self.destinations)}
-        return sorted(self.items, key=lambda it: order[it.dst_rank])  # stable: keeps the order inside a destination
+        position = {d: i for i, d in enumerate(self.turn_order(self.train_rank, {d: sum(entry_nbytes(e) for e in es) for d, es in self.manifest.items()}))}
+        return sorted(self.items, key=lambda it: position[it.dst_rank])  # stable: keeps the order inside a destination
+
+    @staticmethod
+    def turn_order(train_rank: int, bytes_to: Dict[int, int]) -> List[int]:
+        """The order in which a sender that works on one destination at a time
+        visits its destinations.  Destinations that take a sizeable share of the
+        bytes (a tenth of the largest or more) come first, in ascending order
+        rotated by the sender's rank; the small rest follows.  Senders that share
+        their large destinations (training TP peers that feed the same inference
+        shard of several instances; expert-parallel ranks that feed every
+        inference rank) then start at different receivers and take turns."""
+        large_from = max(bytes_to.values()) / 10
+        large = sorted(d for d, n in bytes_to.items() if n >= large_from)
+        small = sorted(d for d in bytes_to if d not in large)
+        shift = train_rank % len(large)
+        return large[shift:] + large[:shift] + small
 
     @staticmethod
     def _stripe_bytes() -> int:

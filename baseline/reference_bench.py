@@ -341,10 +341,11 @@ def run_reference_colocated(args):
                 "impl": "reference", "instance_attrs_set": ["asystem_train_config = {}", "backend = 'nccl'"],
                 "mismatching_parameters": [r.get("mismatching") for r in results if r.get("n_mismatching")],
                 "config": bench_config(arch, total_bytes, f"colocated-tp{world}->tp{world}", "colocated",
-                                       all(r.get("valid", True) for r in results), extra={
+                                       all(r.get("valid", True) for r in results)),
+                "config_details": {
                     "processes": "one training and one inference process per GPU (CUDA IPC hand-over, NCCL among the inference processes)",
                     "train_engine": "weights restored from a second device copy at the start of every update (the reference frees them after each)",
-                    "timing": "CUDA events around NCCLWeightsWriter.write_weights / WeightsReader.update_weights in every process, max over all"}),
+                    "timing": "CUDA events around NCCLWeightsWriter.write_weights / WeightsReader.update_weights in every process, max over all"},
                 "aggregate_GBps": total_bytes / (ms / 1e3) / 1e9, "nvlink_GBps_per_gpu": 0.0,
                 "e2e": {"value": wall / 1e3, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                         "what": "wall clock of the blocking reference calls, max over all processes"},
@@ -501,8 +502,8 @@ def run_reference(args):
             "scaling": "per-N layouts (not a scaling series)",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic random-init N(0,0.02) weights from per-name seeds",
             "impl": "reference",
-            "config": bench_config(arch, total_bytes, label, "separated", all(r["valid"] for r in results), extra={
-                "timing": "CUDA events around NCCLWeightsWriter.write_weights / WeightsReader.update_weights, max over ranks"}),
+            "config": bench_config(arch, total_bytes, label, "separated", all(r["valid"] for r in results)),
+            "config_details": {"timing": "CUDA events around NCCLWeightsWriter.write_weights / WeightsReader.update_weights, max over ranks"},
             "aggregate_GBps": total_bytes / (ms / 1e3) / 1e9, "nvlink_GBps_per_gpu": egress / (ms / 1e3) / 1e9,
             "e2e": {"value": wall / 1e3, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "what": "wall clock of the blocking reference calls, max over ranks"},

@@ -207,7 +207,8 @@ def main():
             if int(os.environ.get("RANK", "0")) != 0:
                 return None
             return emit({"impl": "reference", "unavailable": f"the reference harness does not build the '{args.config}' configuration "
-                         "(co-located MoE / fp8 layouts: see BASELINE.md for why the reference cannot express them)"})
+                         "(its registry gives vLLM-named Qwen3-MoE engines a converter whose names do not match its training converter, and it "
+                         "quantises on the training side only for Bailing architectures)"})
         args.model = args.model or "llama3-8b"
         return run_reference(args)
     if args.emulate:

@@ -338,18 +338,37 @@ def test_a_receiver_whose_parameters_move_is_followed_by_its_senders(fakes, gpus
         server.stop()
 
 
-@pytest.mark.parametrize("stripe_mb", ["0", "0.0625"])
-def test_two_senders_four_receivers_on_six_gpus(fakes, monkeypatch, stripe_mb):
+def test_senders_that_share_their_large_destinations_start_at_different_ones():
+    from awex_b200.transfer.transports import PeerStoreSender
+
+    giga = 10**9
+    # training TP4 -> two instances of inference TP2: ranks 0, 1 feed shards 0 and 2, ranks 2, 3 feed 1 and 3 (plus crumbs elsewhere)
+    tables = {0: {0: 4 * giga, 2: 4 * giga}, 1: {0: 4 * giga, 1: 1000, 2: 4 * giga}, 2: {0: 1000, 1: 4 * giga, 3: 4 * giga}, 3: {1: 4 * giga, 3: 4 * giga}}
+    orders = {r: PeerStoreSender.turn_order(r, t) for r, t in tables.items()}
+    assert orders == {0: [0, 2], 1: [2, 0, 1], 2: [1, 3, 0], 3: [3, 1]}
+    for turn in range(2):  # at every turn each receiver has one writer
+        assert sorted(o[turn] for o in orders.values()) == [0, 1, 2, 3]
+    # expert-parallel ranks that feed every inference rank: a Latin square
+    orders = [PeerStoreSender.turn_order(r, {d: giga for d in range(8)}) for r in range(8)]
+    assert all(sorted(o[turn] for o in orders) == list(range(8)) for turn in range(8))
+
+
+@pytest.mark.parametrize("stripe_mb,turns", [("0", False), ("0.0625", False), ("0", True)])
+def test_two_senders_four_receivers_on_six_gpus(fakes, monkeypatch, stripe_mb, turns):
     """Training TP2 -> two engines of inference TP2, every process on a GPU of its
     own: every receiver checks that the senders' manifests tile its views exactly
     once, every sender writes to receivers of both engines; with striping switched on the senders'
-    tables are re-ordered and dealt in chunks, and move the same bytes."""
+    tables are re-ordered and dealt in chunks, and move the same bytes; so do senders that
+    take turns at their destinations."""
     from awex_b200.meta.meta_server import MetaServer, MetaServerClient
     from awex_b200.synthetic.arch import get_arch
     from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
     from awex_b200.transfer.transports import PeerStoreReceiver, PeerStoreSender
 
     monkeypatch.setenv("AWEX_XFER_DEST_STRIPE_MB", stripe_mb)
+    if turns:
+        monkeypatch.setenv("AWEX_XFER_DEST_GROUPS", "0")
+        monkeypatch.setenv("AWEX_XFER_DEST_ROTATE", "1")
     job = SimulatedJob(get_arch("tiny-qwen2"), TrainLayout(tp=2), InferLayout(tp=2, num_engines=2), dtype=torch.bfloat16)
     programs = job.compile_all()
     views = job.destination_views()
@@ -376,9 +395,12 @@ def test_two_senders_four_receivers_on_six_gpus(fakes, monkeypatch, stripe_mb):
             with acting_as(f"train{r}"):
                 tx.connect()
             assert len(tx.destinations) >= 2 and tx.program.ready_slots == tx.destinations  # one per engine at least, all on peer GPUs
-            assert tx.program.interleave and tx.program.grouped == (stripe_mb == "0")
+            assert tx.program.interleave and tx.program.grouped == (stripe_mb == "0" and not turns)
             if tx.program.grouped:  # one group of CTAs per destination, CTAs shared out by bytes
                 assert len({(int(e["tile_begin"]), int(e["tile_end"])) for e in tx.program.plan}) == len(tx.destinations)
+        if turns:  # the table of each sender opens with another destination
+            first = {r: tx.program.encoder.desc_dst[0] for r, tx in senders.items()}
+            assert len(set(first.values())) == len(senders), first
         for i, rx in receivers.items():
             with acting_as(f"infer{i}"):
                 rx.begin(1)

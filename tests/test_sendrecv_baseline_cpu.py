@@ -11,6 +11,9 @@ WORLD = 3  # transfer rank 0: inference; 1, 2: training
 
 
 def _rank_main(rank, port, q):
+    import faulthandler
+
+    faulthandler.dump_traceback_later(150, exit=True)  # a rank that is stuck says where, and leaves
     try:
         _rank_body(rank, port, q)
     except BaseException as exc:  # the parent must not wait for a rank that died
