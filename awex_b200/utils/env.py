@@ -33,7 +33,7 @@ KNOBS: Dict[str, Tuple[str, str]] = {
     "AWEX_XFER_LEAN_FP8": ("1", "0: quantised blocks stay in the general transfer kernel instead of being split off to the lean block-fp8 kernel"),
     "AWEX_XFER_OUT_BULK": ("0", "1: quantised tiles for destinations across NVLink leave through shared memory and bulk stores instead of per-thread stores (measured slower one to one: 526 against 631 GB/s of fp8 payload)"),
     "AWEX_XFER_DEST_STRIPE_MB": ("0", "cut items into stripes of this many MiB and merge the destinations' stripes in proportion to their bytes, with round-robin chunks (experimental)"),
-    "AWEX_XFER_DEST_ROTATE": ("0", "1: each sender starts its table at a different destination (experimental, with AWEX_XFER_INTERLEAVE=1; only helps when all senders have the same destination set)"),
+    "AWEX_XFER_DEST_ROTATE": ("0", "1, with AWEX_XFER_DEST_GROUPS=0: senders work on one destination at a time and take turns at their large destinations (experimental; measured equal to destination groups on 8 GPUs)"),
     "AWEX_BENCH_ROLE": ("", "set by the benchmark for its two-processes-per-GPU mode: training | inference (which half of a GPU's pair this process is)"),
     "AWEX_USE_BATCH_SEND_RECV": ("1", "message transport only: 0 sends one message at a time and waits for each"),
     "AWEX_SYNTH_FP8_ORACLE": ("cpu", "synthetic models: 'kernel' builds fp8 oracles with the quantisation kernel instead of the CPU"),
