@@ -24,7 +24,7 @@ reference, `mcore_converter.py:475-690,1055-1352`):
 from __future__ import annotations
 
 import os
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

@@ -70,9 +70,6 @@ class Rows:
             seen.setdefault(src)
         return list(seen)
 
-    def is_identity_of(self, source: Source, n_rows: int) -> bool:
-        return self.runs == [(source, 0, n_rows)]
-
     # ---- algebra -------------------------------------------------------------
     def narrow(self, start: int, length: int) -> "Rows":
         if start < 0 or length < 0 or start + length > self._n:
@@ -105,9 +102,6 @@ class Rows:
 
     def blocks(self, block_rows: int) -> List["Rows"]:
         return self.chunk(self._n // block_rows) if self._n else []
-
-    def rebase(self, mapping: Callable[[Source], Source]) -> "Rows":
-        return Rows((mapping(src), s, n) for src, s, n in self.runs)
 
     # ---- realisation -----------------------------------------------------------
     def gather(self, fetch: Callable[[Source], torch.Tensor]) -> torch.Tensor:

@@ -4,7 +4,6 @@ from __future__ import annotations
 
 import os
 import time
-from typing import Optional
 
 from awex_b200 import logging
 from awex_b200.engine.core import TrainingEngine

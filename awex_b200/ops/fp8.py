@@ -13,7 +13,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from awex_b200.converter.weights_converter import FP8_BLOCK, block_scale_shape, per_block_cast_to_fp8, per_block_dequant_from_fp8
+from awex_b200.converter.weights_converter import block_scale_shape, per_block_cast_to_fp8, per_block_dequant_from_fp8
 
 _DT = {torch.bfloat16: 1, torch.float16: 2, torch.float32: 3}
 

@@ -55,9 +55,6 @@ class AddressBook:
     # every update, for the epoch of the book that is valid for it
     may_move: bool = False
 
-    def dtype_of(self, name: str) -> torch.dtype:
-        return getattr(torch, self.tensors[name][4])
-
 
 def _device_uuid(index: int) -> str:
     try:

@@ -15,7 +15,7 @@ and the send/recv baseline.
 from __future__ import annotations
 
 from datetime import timedelta
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist

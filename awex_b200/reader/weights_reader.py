@@ -30,8 +30,6 @@ from awex_b200 import logging
 from awex_b200.meta.infer_meta_resolver import InferParamMetaResolver, canonical_named_views
 from awex_b200.meta.meta_server import MetaServerClient
 from awex_b200.meta.weight_meta import ParameterMeta
-from awex_b200.models.registry import get_infer_weights_converter
-from awex_b200.sharding.param_sharding import get_rank_info_extractor
 from awex_b200.utils import device as device_util
 from awex_b200.utils.common import check_train_infer_params_meta, compute_statistics, simple_hf_config
 

@@ -10,8 +10,6 @@ share the device.
 
 from __future__ import annotations
 
-from typing import Optional, Sequence
-
 import torch
 
 from awex_b200.engine.mcore import MegatronEngine

@@ -20,8 +20,7 @@ from __future__ import annotations
 import hashlib
 import os
 from collections import OrderedDict
-from types import SimpleNamespace
-from typing import Callable, Dict, Iterator, List, Optional, Tuple
+from typing import Dict, Iterator, List, Optional, Tuple
 
 import torch
 

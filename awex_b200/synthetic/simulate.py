@@ -11,7 +11,6 @@ one kernel launch over all ranks' data.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from types import SimpleNamespace
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

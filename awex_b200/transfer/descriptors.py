@@ -16,7 +16,6 @@ fails is never launched.
 
 from __future__ import annotations
 
-import itertools
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
@@ -64,9 +63,6 @@ class TensorAddr:
     @staticmethod
     def of(t: torch.Tensor, ptr: Optional[int] = None) -> "TensorAddr":
         return TensorAddr(t.data_ptr() if ptr is None else ptr, tuple(t.shape), tuple(t.stride()), t.dtype)
-
-    def rebased(self, delta: int) -> "TensorAddr":
-        return TensorAddr(self.ptr + delta, self.shape, self.strides, self.dtype)
 
     def byte_span(self) -> Tuple[int, int]:
         """[low, high) addresses the view can touch."""

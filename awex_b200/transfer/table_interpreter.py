@@ -13,7 +13,7 @@ instead of corrupting memory.
 from __future__ import annotations
 
 import ctypes
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Iterable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch

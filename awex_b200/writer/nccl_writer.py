@@ -14,7 +14,6 @@ from __future__ import annotations
 
 import os
 import time
-from typing import List
 
 import torch
 

@@ -95,11 +95,6 @@ class WeightsExchangeShardingWriter(WeightExchangeWriter):
         self.process_group = getattr(train_engine, "process_group", None)
 
     # ---- helpers ---------------------------------------------------------------------------
-    def _train_world_rank(self):
-        if dist.is_initialized():
-            return dist.get_rank(self.process_group), dist.get_world_size(self.process_group)
-        return self.rank_info.global_rank, self.rank_info.world_size
-
     def _train_barrier(self) -> None:
         if dist.is_initialized() and dist.get_world_size(self.process_group) > 1:
             dist.barrier(group=self.process_group)

@@ -78,7 +78,6 @@ def run_single_gpu(args):
     import torch
 
     from awex_b200 import logging
-    from awex_b200.ops.fused_transfer import FlagPad, FlagPoster
     from awex_b200.synthetic.arch import get_arch
     from awex_b200.synthetic.simulate import SimulatedJob
     from awex_b200.utils.gpu import ClockSampler

@@ -307,3 +307,46 @@ def test_data_plane_choice(monkeypatch):
         choose_data_plane("cuda", "rdma")
     monkeypatch.setenv("AWEX_DATA_PLANE", "messages")
     assert choose_data_plane("cuda", "peer_stores") == "messages"  # the environment wins
+
+
+def test_device_helpers_without_a_gpu(monkeypatch):
+    """The device helpers answer for the CPU when it is forced (the reference's
+    `awex/util/device.py` surface, CUDA and CPU only)."""
+    from awex_b200.utils import device
+
+    monkeypatch.setenv("AWEX_DEVICE_TYPE", "cpu")
+    assert device.get_device_type() == "cpu" and device.device_count() == 0 and device.current_device() == 0
+    device.set_device(0), device.synchronize(), device.empty_cache()  # no-ops
+    assert device.get_device_name() == "cpu" and device.get_torch_device() == torch.device("cpu")
+    assert device.memory_stats() == {"allocated": 0, "reserved": 0, "free": 0, "total": 0}
+    assert device.current_stream() is None and device.get_dist_backend() == "gloo"
+    with device.stream_context(None):
+        pass
+    with pytest.raises(RuntimeError, match="CUDA"):
+        device.get_device_properties()
+    assert device.visible_devices_env_names() == ["CUDA_VISIBLE_DEVICES"]
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "3,4")
+    assert device.visible_devices_env_value() == "3,4"
+    assert device.is_cuda_available() == torch.cuda.is_available()
+    monkeypatch.setenv("AWEX_DEVICE_TYPE", "npu")
+    with pytest.raises(ValueError, match="not supported"):
+        device.get_device_type()
+
+
+def test_config_from_an_sglang_engine_and_small_helpers(monkeypatch):
+    from awex_b200.config import InferenceConfig
+    from awex_b200.ops.checksum import checksum_reference, tensor_checksums
+    from awex_b200.utils.common import stripped_env_vars
+
+    server_args = SimpleNamespace(tp_size=4, pp_size=1, dp_size=2, ep_size=2, enable_dp_attention=True, unknown_to_us=7, nnodes=None)
+    cfg = InferenceConfig.from_sgl_engine(SimpleNamespace(server_args=server_args), comm_backend="nccl", meta_server_addr="10.0.0.1:8080")
+    assert (cfg.tp_size, cfg.dp_size, cfg.ep_size, cfg.enable_dp_attention, cfg.comm_backend) == (4, 2, 2, True, "nccl")
+    assert not hasattr(cfg, "unknown_to_us")
+    monkeypatch.setenv("MY_SECRET_TOKEN", "x")
+    monkeypatch.setenv("PLAIN_SETTING", "y")
+    env = stripped_env_vars()
+    assert "MY_SECRET_TOKEN" not in env and env["PLAIN_SETTING"] == "y" and "LS_COLORS" not in env
+    a, b = torch.arange(64, dtype=torch.float32), torch.tensor([1.0, float("nan"), 3.0, float("nan")])
+    sums, nans = tensor_checksums([a, b])
+    assert sums == [checksum_reference(a), checksum_reference(b)] and nans == [0, 2]
+    assert tensor_checksums([]) == ([], [])

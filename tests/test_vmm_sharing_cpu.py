@@ -3,7 +3,6 @@ travel between real processes over a unix socket, and the exporter / importer
 drive the native calls in the right order (checked against a fake of the
 library; the driver calls themselves need a GPU)."""
 
-import ctypes
 import os
 
 import pytest
