@@ -56,12 +56,16 @@ def set_train_tp_group(group, size: int) -> None:
 
 
 def _train_tp_group():
+    """(group, size) of the training tensor-parallel group: the one the host
+    program registered, else Megatron's."""
+    if _TRAIN_TP_GROUP["group"] is not None or _TRAIN_TP_GROUP["size"] != 1:
+        return _TRAIN_TP_GROUP["group"], _TRAIN_TP_GROUP["size"]
     try:
         from megatron.core import parallel_state as mpu
 
         return mpu.get_tensor_model_parallel_group(), mpu.get_tensor_model_parallel_world_size()
     except Exception:
-        return _TRAIN_TP_GROUP["group"], _TRAIN_TP_GROUP["size"]
+        return None, 1
 
 
 def get_full_tensor(weight: torch.Tensor, dim: int = 0) -> torch.Tensor:

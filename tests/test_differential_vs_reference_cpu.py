@@ -23,13 +23,25 @@ STUBS = os.path.join(ROOT, "baseline", "stubs")
 
 if not os.path.isdir(os.path.join(REF, "awex", "transfer")):
     pytest.skip("no copy of the reference package under baseline/_ref", allow_module_level=True)
-for path in (STUBS, REF):
-    if path not in sys.path:
+
+
+@pytest.fixture(scope="module", autouse=True)
+def reference_on_the_path():
+    """The reference package and the stand-in for Megatron are importable while
+    this module's tests run, and only then: processes that later tests spawn
+    inherit ``sys.path``, and a ``megatron`` that imports changes what the
+    training-side converter takes for its tensor-parallel group."""
+    added = [path for path in (STUBS, REF) if path not in sys.path]
+    for path in added:
         sys.path.insert(0, path)
+    import awex.logging as ref_logging
 
-import awex.logging as _ref_logging  # noqa: E402
-
-_ref_logging.setLevel("ERROR")
+    ref_logging.setLevel("ERROR")
+    yield
+    for path in added:
+        sys.path.remove(path)
+    for name in [n for n in sys.modules if n == "awex" or n.startswith("awex.") or n == "megatron" or n.startswith("megatron.")]:
+        del sys.modules[name]
 
 
 # ---- block fp8 --------------------------------------------------------------------------------------
