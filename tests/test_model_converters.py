@@ -224,3 +224,33 @@ def test_bailing_linear_serves_lm_head_in_fp32_and_quantises_routed_experts_only
     strat = get_sharding_strategy("BailingMoeV2ForCausalLM")("sglang", False, False, None, 2, 1, 1, ri(tp_size=2))
     assert strat.get_sharding_strategy("model.layers.3.attention.q_a_proj.weight")[0] == ShardingType.NO_SHARDING
     assert strat.get_sharding_strategy("model.layers.0.attention.g_norm.weight") == (ShardingType.TP_SHARDING, 0, 2)
+
+
+def test_a_registered_training_tp_group_wins_over_an_importable_megatron(monkeypatch):
+    """A host program that registers its training TP group gets that group, even
+    where a ``megatron`` package imports and answers something else."""
+    import sys
+    from types import ModuleType
+
+    from awex_b200.converter import mcore_converter as mc
+
+    state = ModuleType("megatron.core.parallel_state")
+    state.get_tensor_model_parallel_group = lambda: "megatron-group"
+    state.get_tensor_model_parallel_world_size = lambda: 4
+    core = ModuleType("megatron.core")
+    core.parallel_state = state
+    top = ModuleType("megatron")
+    top.core = core
+    for name, module in (("megatron", top), ("megatron.core", core), ("megatron.core.parallel_state", state)):
+        monkeypatch.setitem(sys.modules, name, module)
+    monkeypatch.setitem(mc._TRAIN_TP_GROUP, "group", None)
+    monkeypatch.setitem(mc._TRAIN_TP_GROUP, "size", 1)
+    assert mc._train_tp_group() == ("megatron-group", 4)  # nothing registered: Megatron's
+    mc.set_train_tp_group("registered", 2)
+    assert mc._train_tp_group() == ("registered", 2)
+    monkeypatch.delitem(sys.modules, "megatron.core.parallel_state")
+    monkeypatch.delitem(sys.modules, "megatron.core")
+    monkeypatch.delitem(sys.modules, "megatron")
+    monkeypatch.setitem(mc._TRAIN_TP_GROUP, "group", None)
+    monkeypatch.setitem(mc._TRAIN_TP_GROUP, "size", 1)
+    assert mc._train_tp_group() == (None, 1)  # neither: a single rank

@@ -60,9 +60,8 @@ def _rank_body(rank, port, q):
     dist.destroy_process_group()
 
 
-def _exchange_once(rank_timeout_s):
-    """One run of the three ranks; None when a rank did not report in time (the
-    stuck rank has then printed where it stood and left)."""
+@pytest.mark.timeout(400)
+def test_per_operation_send_recv_over_gloo():
     import queue
 
     from awex_b200.utils.common import get_free_port
@@ -74,26 +73,16 @@ def _exchange_once(rank_timeout_s):
     for p in procs:
         p.start()
     try:
-        results = {r[0]: r[1:] for r in (q.get(timeout=rank_timeout_s) for _ in procs)}
+        results = {r[0]: r[1:] for r in (q.get(timeout=240) for _ in procs)}
         for p in procs:
             p.join(timeout=60)
             assert p.exitcode == 0
-        return results
     except queue.Empty:
-        return None
+        pytest.fail("a rank did not report (a stuck rank prints where it stands after 150 s and leaves)")
     finally:
         for p in procs:
             if p.is_alive():
                 p.kill()
-
-
-@pytest.mark.timeout(600)
-def test_per_operation_send_recv_over_gloo():
-    # Rarely, and so far only inside a run of the whole suite on a loaded machine, the receiving rank has stayed in
-    # its batch of receives (cause unknown; forty runs under load alone passed).  Every rank prints where it stands
-    # when it is stuck and leaves; a second run then decides.
-    results = _exchange_once(180) or _exchange_once(180)
-    assert results is not None, "the ranks did not finish in two runs"
     bad, stats, staged = results[0]
     assert bad == []
     assert stats == {"op_count": 29, "numel": 1705216, "bytes": 6820864}  # the plan of BASELINE configuration 1
