@@ -364,3 +364,138 @@ def test_bailing_families_resolve_to_the_same_kind_of_converters_and_sharding(ar
     ours, theirs = _both_train_converters(arch, hf, tf, {"infer_atten_tp_size": 1})
     assert type(ours).__name__ == type(theirs).__name__
     assert our_registry.get_sharding_strategy(arch).__name__ == ref_registry.get_sharding_strategy(arch).__name__
+
+
+# ---- the control plane on the wire --------------------------------------------------------------------
+def _exercise_meta_client(client, other_client):
+    """The calls the exchange makes, written by ``client`` and read back by
+    ``other_client`` (and the other way round), both talking to one server."""
+    client.put_object("infer_conf", {"tp_size": 2, "names": ["a", "b"], "nested": (1, 2.5, None)})
+    assert other_client.get_object("infer_conf") == {"tp_size": 2, "names": ["a", "b"], "nested": (1, 2.5, None)}
+    other_client.put_binary("blob/with/slashes", bytes(range(256)) * 40)
+    assert client.get_binary("blob/with/slashes") == bytes(range(256)) * 40
+    client.put_json("json_key", {"step": 3, "ok": True})
+    assert other_client.get_json("json_key") == {"step": 3, "ok": True}
+    for member, who in ((0, client), (1, other_client), (1, client)):
+        who.add_object_to_set("ready_engines", member)
+    assert client.get_set("ready_engines") == {0, 1} == other_client.get_set("ready_engines")
+    other_client.wait_set_until_size("ready_engines", 2, timeout=5)
+    assert client.has_key("json_key") and other_client.has_key("json_key") and not other_client.has_key("absent")
+    assert {"infer_conf", "json_key", "ready_engines"} <= set(client.list_keys()) and set(client.list_keys()) == set(other_client.list_keys())
+    ids = [client.allocate_auto_grow_id(), other_client.allocate_auto_grow_id(), client.allocate_auto_grow_id()]
+    assert ids == sorted(ids) and len(set(ids)) == 3
+    other_client.delete("json_key")
+    assert not client.has_key("json_key")
+    client.delete_if_exists("json_key")  # absent: no error
+    assert other_client.get_object("absent", default_value="fallback") == "fallback"
+    assert client.health_check() and other_client.health_check()
+
+
+def test_both_clients_speak_to_both_servers():
+    """The reference's client against this server, this client against the
+    reference's server, each mixed with the other client on the same keys: the
+    REST routes and the payload encoding are the same."""
+    from awex.meta.meta_server import MetaServer as RefServer, MetaServerClient as RefClient
+
+    from awex_b200.meta.meta_server import MetaServer, MetaServerClient
+    from awex_b200.utils.common import get_free_port
+
+    ours = MetaServer("127.0.0.1", 0)
+    ours.start()
+    try:
+        _exercise_meta_client(RefClient("127.0.0.1", ours.port), MetaServerClient("127.0.0.1", ours.port))
+    finally:
+        ours.stop()
+    theirs = RefServer("127.0.0.1", get_free_port())
+    theirs.start()
+    try:
+        _exercise_meta_client(MetaServerClient("127.0.0.1", theirs.port), RefClient("127.0.0.1", theirs.port))
+    finally:
+        theirs.stop()
+
+
+# ---- the inference-side metadata resolver ---------------------------------------------------------------
+def _meta_key(metas):
+    """ParameterMeta lists of either implementation as plain comparable data."""
+    out = {}
+    for p in metas:
+        out[p.name] = (
+            tuple(p.global_shape), str(p.dtype), p.global_numel,
+            tuple(tuple((s.name, tuple(s.shape), tuple(s.global_offset), s.sharding_type.name, s.num_shards, s.sharding_dim,
+                         s.tp_rank, s.attn_tp_rank, s.pp_rank, s.ep_rank, s.global_rank, s.world_size, s.engine_rank)
+                        for s in replica.shards) for replica in p.replicas),
+        )
+    return out
+
+
+class _CannedEngine:
+    """An inference engine whose workers answer the metadata task with reports made beforehand."""
+
+    def __init__(self, engine_name, hf_config, config, reports):
+        self.engine_name, self.hf_config, self.config, self.reports = engine_name, hf_config, config, reports
+
+    def execute_task_in_model_worker(self, fn, **kwargs):
+        return self.reports
+
+
+def _both_inference_resolvers(arch, infer):
+    from awex.meta.infer_meta_resolver import InferParamMetaResolver as RefResolver
+
+    from awex_b200.meta.infer_meta_resolver import InferParamMetaResolver, collect_worker_param_info
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+
+    job = SimulatedJob(get_arch(arch), TrainLayout(tp=1), InferLayout(**infer), dtype=torch.bfloat16)
+    engine = job.engines[0]
+    reports = engine.execute_task_in_model_worker(collect_worker_param_info, engine_name=engine.engine_name,
+                                                  infer_engine_config=engine.config, engine_rank=0, convert_params=True)
+    for report in reports:  # what an RPC layer hands back; both resolvers restore it to their own class
+        report["rank_info"] = dataclasses.asdict(report["rank_info"])
+    aliases = set(job.aliases)
+    for report in reports:  # second names of one memory are this framework's addition: the reference has no such entry
+        report["params_meta"] = [m for m in report["params_meta"] if m["name"] not in aliases]
+        report.pop("aliases", None)
+
+    def canned():
+        return _CannedEngine(engine.engine_name, engine.hf_config, engine.config, [dict(r) for r in reports])
+
+    ours = InferParamMetaResolver(canned(), convert_params=True, num_engines=job.infer.num_engines, engine_rank=0)
+    theirs = RefResolver(canned(), convert_params=True, num_engines=job.infer.num_engines, engine_rank=0)
+    return ours, theirs, job
+
+
+@pytest.mark.parametrize("arch,infer", [
+    ("tiny-llama", dict(tp=2)),
+    ("tiny-qwen2", dict(tp=2, num_engines=2)),
+    ("tiny-qwen3-moe", dict(tp=2, ep=2, engine_name="sglang")),
+    ("tiny-llama", dict(tp=4, attn_tp=2, engine_name="sglang")),  # data-parallel attention
+])
+def test_inference_resolver_builds_the_same_metadata_from_the_same_worker_reports(arch, infer):
+    """Per-worker reports (canonical names, local shapes, rank descriptions) of a
+    synthetic engine go through the reference's resolver and through this one:
+    global shapes, shard offsets, sharding kinds and replicas must agree."""
+    ours, theirs, _job = _both_inference_resolvers(arch, infer)
+    got, want = _meta_key(ours.get_parameters_meta()), _meta_key(theirs.get_parameters_meta())
+    assert set(got) == set(want)
+    differing = [name for name in want if got[name] != want[name]]
+    assert not differing, (differing[:5], got[differing[0]], want[differing[0]])
+    assert (ours.total_numel, ours.total_size, ours.get_model_arch_name()) == (theirs.total_numel, theirs.total_size, theirs.get_model_arch_name())
+
+
+def test_data_parallel_attention_with_split_projection_names_is_where_the_two_part():
+    """Known difference.  The reference recognises attention weights by the
+    substring ``attention`` (`awex/sharding/param_sharding.py:289`), so the
+    ``self_attn.q_proj`` names of the Qwen3 families fall through to plain tensor
+    parallelism over the whole TP group and, under data-parallel attention, get a
+    global shape twice too large.  Here they are attention weights: two replicas
+    of attention-TP shards and the true global shape."""
+    ours, theirs, job = _both_inference_resolvers("tiny-qwen3-moe", dict(tp=4, ep=4, attn_tp=2, engine_name="sglang"))
+    name = "model.layers.0.self_attn.q_proj.weight"
+    got = {p.name: p for p in ours.get_parameters_meta()}[name]
+    want = {p.name: p for p in theirs.get_parameters_meta()}[name]
+    true_rows = job.arch.num_heads * job.arch.head_dim
+    assert got.global_shape[0] == true_rows and len(got.replicas) == 2 and got.shards[0].sharding_type.name == "DP_TP_SHARDING"
+    assert want.global_shape[0] == 2 * true_rows and want.shards[0].sharding_type.name == "TP_SHARDING"
+    # everything that is not attention agrees
+    a, b = _meta_key(ours.get_parameters_meta()), _meta_key(theirs.get_parameters_meta())
+    assert all(a[n] == b[n] for n in a if "self_attn" not in n)
