@@ -499,3 +499,86 @@ def test_data_parallel_attention_with_split_projection_names_is_where_the_two_pa
     # everything that is not attention agrees
     a, b = _meta_key(ours.get_parameters_meta()), _meta_key(theirs.get_parameters_meta())
     assert all(a[n] == b[n] for n in a if "self_attn" not in n)
+
+
+# ---- the training-side metadata resolver (two tensor-parallel ranks over gloo) ----------------------------------
+def _train_resolver_rank(rank, world, port, arch, q):
+    """One training rank: the reference's resolver and this one on the same
+    Megatron-layout shard, with the stand-in for Megatron's parallel state
+    (tensor-parallel group = all ranks)."""
+    import faulthandler
+
+    faulthandler.dump_traceback_later(200, exit=True)
+    try:
+        for path in (STUBS, REF):
+            if path not in sys.path:
+                sys.path.insert(0, path)
+        os.environ["AWEX_DEVICE_TYPE"] = "cpu"
+        import torch.distributed as dist
+
+        import awex.logging as ref_logging
+        from awex.meta.train_meta_resolver import McoreParamMetaResolver as RefResolver
+
+        from awex_b200 import logging as our_logging
+        from awex_b200.config import InferenceConfig
+        from awex_b200.meta.train_meta_resolver import McoreParamMetaResolver
+        from baseline import synth
+        from baseline.reference_bench import _TrainEngine
+
+        ref_logging.setLevel("ERROR")
+        our_logging.setLevel("ERROR")
+        # the reference takes the local rank modulo the number of accelerators, which is zero on a CPU-only
+        # machine; tell both sides (in this process only) that the node has eight
+        import awex.util.device as ref_device
+
+        import awex_b200.utils.device as our_device
+
+        ref_device.device_count = our_device.device_count = lambda: 8
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        hf_config = synth.hf_config_for(arch)
+        model = synth.megatron_module(arch, world, rank, torch.float32, "cpu")
+        infer_conf = {"hf_config": hf_config, "engine_name": "vllm", "infer_atten_tp_size": 1, "router_dtype": "bf16",
+                      "infer_engine_config": InferenceConfig(tp_size=1, comm_backend="nccl"), "infer_world_size": 1}
+        theirs = RefResolver(_TrainEngine(model, hf_config, "unused"), hf_config, dict(infer_conf))
+        ours = McoreParamMetaResolver(_TrainEngine(model, hf_config, "unused"), hf_config, dict(infer_conf))
+        got, want = _meta_key(ours.get_parameters_meta()), _meta_key(theirs.get_parameters_meta())
+        problems = sorted(set(got) ^ set(want)) + [n for n in want if n in got and got[n] != want[n]]
+        if (ours.total_numel, ours.total_size) != (theirs.total_numel, theirs.total_size):
+            problems.append(f"totals {ours.total_numel, ours.total_size} != {theirs.total_numel, theirs.total_size}")
+        if ours.get_pp_stage_layer_id_map() != theirs.get_pp_stage_layer_id_map():
+            problems.append("pipeline stage maps differ")
+        q.put((rank, problems[:5], len(want)))
+        dist.barrier()
+        dist.destroy_process_group()
+    except BaseException as exc:
+        q.put((rank, [f"rank {rank} failed: {exc!r}"], 0))
+        raise
+
+
+@pytest.mark.timeout(400)
+@pytest.mark.parametrize("arch", ["tiny-llama", "tiny-qwen2"])
+def test_training_resolver_builds_the_same_metadata_on_two_tensor_parallel_ranks(arch):
+    import queue
+
+    import torch.multiprocessing as mp
+
+    from awex_b200.utils.common import get_free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = get_free_port()
+    procs = [ctx.Process(target=_train_resolver_rank, args=(r, 2, port, arch, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        results = [q.get(timeout=240) for _ in procs]
+        for p in procs:
+            p.join(timeout=60)
+    except queue.Empty:
+        pytest.fail("a rank did not report")
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+    for rank, problems, count in results:
+        assert problems == [] and count > 0, (rank, problems)
