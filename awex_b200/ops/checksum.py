@@ -5,6 +5,10 @@ the same function in numpy as its oracle.
 ``mix(w) = w ^ (w >> 32)`` over the 8-byte words of each row (last word
 zero-padded), ``i = row * words_per_row + j``.
 Contiguous tensors are hashed as one long row.
+
+Validation of an update compares these sums with the sums of a file-loaded
+copy; the reference compares the tensors themselves, parameter by parameter
+(`awex/reader/weights_reader.py:457-587`, `awex/util/tensor_util.py:431-537`).
 """
 
 from __future__ import annotations

@@ -1,6 +1,7 @@
 // Shared device math of the block-fp8 kernels.
 //
-// Bit-exact contract (per_block_cast_to_fp8 run by PyTorch on the CPU):
+// Bit-exact contract (per_block_cast_to_fp8 of the reference, awex/converter/weights_converter.py:42-61,
+// run by PyTorch on the CPU):
 //   amax  = max |x| over the 128x128 block, NaN-propagating
 //   scale = max(amax, 1e-4) / 448                    (fp32, true division)
 //   q     = e4m3( fp32(x / scale) )                  (true division, round to nearest even)

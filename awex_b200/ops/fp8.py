@@ -5,6 +5,9 @@
 (16-byte aligned base, row pitch a multiple of 16 bytes) are quantised by the
 fused transfer kernel's element path instead, so there is no PyTorch fallback
 on a GPU.  On CPU tensors the plain-PyTorch oracle runs.
+
+The arithmetic is that of the reference's ``per_block_cast_to_fp8``
+(`awex/converter/weights_converter.py:42-61`), bit for bit.
 """
 
 from __future__ import annotations

@@ -6,6 +6,11 @@ destination, raised by the reader when its engine is paused) and the flags it
 raises when its writes are complete.  :meth:`TransferProgram.launch` is a single
 kernel launch on the current stream; nothing is allocated and nothing
 synchronises with the host.
+
+One launch stands where the reference slices and converts every parameter,
+builds one send per planned operation and issues them as batched NCCL
+point-to-point calls (`awex/transfer/nccl_comm.py:379-447,544-624`,
+`awex/writer/nccl_writer.py:198-340`).
 """
 
 from __future__ import annotations

@@ -1,7 +1,9 @@
 """Column-wise L2 normalisation on the device (``csrc/col_normalize.cu``):
 ``out[r, c] = x[r, c] / max(||x[:, c]||_2, eps)``, i.e.
 ``torch.nn.functional.normalize(x, dim=0, p=2, eps=eps)`` without its
-temporaries.  On CPU tensors the PyTorch function runs."""
+temporaries.  On CPU tensors the PyTorch function runs.  It produces the head
+with unit-norm columns that the reference computes with that PyTorch call while
+converting the output layer (`awex/converter/mcore_converter.py:668-675`)."""
 
 from __future__ import annotations
 

@@ -4,6 +4,8 @@ It is the oracle for the fused CUDA kernel and the data plane of the CPU
 (gloo) backend: the same items, executed with ``copy_`` semantics.  Messages
 between processes are flat byte buffers in item order, so that both ends
 derive offsets from the published manifest and nothing but payload travels.
+The reference states the same semantics in its CPU simulation of a plan
+(`awex/tests/test_transfer_plan_cpu_sim.py:94-168`).
 """
 
 from __future__ import annotations

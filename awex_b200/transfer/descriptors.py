@@ -12,6 +12,9 @@ proves, from addresses and extents alone, that every slab stays inside the
 tensors it names, that no two slabs write the same destination byte, and that
 every bulk copy meets the alignment rules of ``cp.async.bulk``; a table that
 fails is never launched.
+
+The table takes the place of the per-operation send and receive lists the
+reference builds from a plan (`awex/transfer/nccl_comm.py:379-541`).
 """
 
 from __future__ import annotations

@@ -1,6 +1,8 @@
 """Hugging Face style checkpoint directories: ``model-XXXXX-of-YYYYY.safetensors``
 shards plus ``model.safetensors.index.json``.  Used by the ``file`` backend and
-as the file-loaded reference of weight validation."""
+as the file-loaded reference of weight validation (the reference writes such
+directories from its file-mode writer, `awex/writer/weights_writer.py:374-410`,
+and loads them through the engine, `awex/reader/weights_reader.py:380-400`)."""
 
 from __future__ import annotations
 
