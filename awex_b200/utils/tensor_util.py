@@ -176,6 +176,55 @@ def ipc_deserialize(data: bytes):
 cuda_ipc_serialize = ipc_serialize
 cuda_ipc_deserialize = ipc_deserialize
 
+# Position of the device index among the arguments torch's reduction of a CUDA
+# tensor hands to ``rebuild_cuda_tensor``.
+_REBUILD_DEVICE_ARG = 6
+
+
+def device_to_uuid(index: int) -> str:
+    return str(torch.cuda.get_device_properties(index).uuid)
+
+
+def device_from_uuid(device: Union[int, str]) -> int:
+    """The local index of the GPU with this UUID (an index passes through)."""
+    if isinstance(device, int):
+        return device
+    for index in range(torch.cuda.device_count()):
+        if device_to_uuid(index) == device:
+            return index
+    raise RuntimeError(f"no visible GPU has UUID {device}: the process that pickled the tensor sees a GPU this one does not")
+
+
+def monkey_patch_torch_reductions() -> None:
+    """Make pickled CUDA-IPC tensors name their GPU by UUID instead of by index,
+    so that two processes whose ``CUDA_VISIBLE_DEVICES`` differ open a handle on
+    the right device (`awex/util/tensor_util.py:35-106` in the reference; the
+    address books of the fused path carry the UUID themselves).  Idempotent."""
+    from torch.multiprocessing import reductions
+
+    if hasattr(reductions, "_awex_reduce_tensor"):
+        return
+    reductions._awex_reduce_tensor = reductions.reduce_tensor
+    reductions._awex_rebuild_cuda_tensor = reductions.rebuild_cuda_tensor
+
+    def rebuild_by_uuid(*args):
+        args = list(args)
+        args[_REBUILD_DEVICE_ARG] = device_from_uuid(args[_REBUILD_DEVICE_ARG])
+        return reductions._awex_rebuild_cuda_tensor(*args)
+
+    def reduce_by_uuid(*args, **kwargs):
+        rebuild, rebuild_args = reductions._awex_reduce_tensor(*args, **kwargs)
+        # torch's reducer names the module's current ``rebuild_cuda_tensor``, which is the patched one from here on
+        if rebuild is rebuild_by_uuid or rebuild is reductions._awex_rebuild_cuda_tensor:
+            rebuild_args = list(rebuild_args)
+            rebuild_args[_REBUILD_DEVICE_ARG] = device_to_uuid(rebuild_args[_REBUILD_DEVICE_ARG])
+            return rebuild_by_uuid, tuple(rebuild_args)
+        return rebuild, rebuild_args
+
+    reductions.reduce_tensor = reduce_by_uuid
+    reductions.rebuild_cuda_tensor = rebuild_by_uuid
+    reductions.init_reductions()  # register the patched reducer for tensors and parameters
+
 
 def reconstruct_ipc_weights(payload: bytes) -> Dict[str, torch.Tensor]:
     """Inverse of ``ipc_serialize((groups, metadata, names))``: name -> view."""

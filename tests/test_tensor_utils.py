@@ -177,3 +177,50 @@ def test_difference_report_names_elements_and_statistics():
     many = torch.ones(10, 10)
     ok, text = logged(compare_and_log_tensor_differences, torch.zeros(10, 10), many, "many", 1e-8, 1e-5, 5)
     assert not ok and "differs in 100 of 100" in text and text.count("  many[") == 5  # the list of positions is bounded
+
+
+def test_pickled_cuda_tensors_name_their_gpu_by_uuid(monkeypatch):
+    """The reduction patch swaps the device index for the GPU's UUID on the
+    pickling side and finds the local index of that UUID on the other side,
+    where the visible devices may be numbered differently."""
+    from types import SimpleNamespace
+
+    from torch.multiprocessing import reductions
+
+    from awex_b200.utils import tensor_util
+
+    uuids = ["GPU-aaaa", "GPU-bbbb", "GPU-cccc"]
+    monkeypatch.setattr(torch.cuda, "get_device_properties", lambda index: SimpleNamespace(uuid=uuids[index]))
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: len(uuids))
+    rebuilt = []
+
+    def fake_rebuild(*args):
+        rebuilt.append(args)
+        return "tensor"
+
+    def fake_reduce(tensor):
+        if tensor == "cpu tensor":
+            return "rebuild_cpu", ("shared memory",)
+        return reductions.rebuild_cuda_tensor, ("cls", (2,), (1,), 0, "storage_cls", torch.float32, 1, b"handle", 8, 0, False, b"ref", 0, b"event", True)
+
+    monkeypatch.setattr(reductions, "rebuild_cuda_tensor", fake_rebuild)
+    monkeypatch.setattr(reductions, "reduce_tensor", fake_reduce)
+    monkeypatch.setattr(reductions, "init_reductions", lambda: None)
+    try:
+        tensor_util.monkey_patch_torch_reductions()
+        patched = reductions.reduce_tensor
+        tensor_util.monkey_patch_torch_reductions()  # a second call changes nothing
+        assert reductions.reduce_tensor is patched
+        rebuild, args = reductions.reduce_tensor("cuda tensor")
+        assert args[6] == "GPU-bbbb" and args[7] == b"handle"
+        assert reductions.reduce_tensor("cpu tensor") == ("rebuild_cpu", ("shared memory",))  # other reductions pass through
+        # the receiving process numbers the same GPUs in another order
+        uuids[:] = ["GPU-cccc", "GPU-bbbb", "GPU-aaaa"][::-1][1:] + ["GPU-aaaa"]  # bbbb is device 0 there
+        assert rebuild(*args) == "tensor" and rebuilt[-1][6] == 0
+        assert tensor_util.device_from_uuid(2) == 2  # plain indices pass through
+        with pytest.raises(RuntimeError, match="no visible GPU"):
+            tensor_util.device_from_uuid("GPU-zzzz")
+    finally:
+        for name in ("_awex_reduce_tensor", "_awex_rebuild_cuda_tensor"):
+            if hasattr(reductions, name):
+                delattr(reductions, name)
