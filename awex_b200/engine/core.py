@@ -19,9 +19,14 @@ from typing import Any, List, Optional
 
 class Engine(ABC):
     hf_config: Any = None
+    global_step: int = 0
 
     def initialize(self) -> None:
         pass
+
+    def set_global_step(self, global_step: int) -> None:
+        """The training step the engine's weights belong to (`awex/engine/core.py:44-46`)."""
+        self.global_step = global_step
 
     def release_memory_occupation(self, tags: Optional[List[str]] = None) -> None:
         raise NotImplementedError

@@ -14,8 +14,21 @@ import os
 import sys
 import time
 import traceback
+from enum import IntEnum
 
-DEBUG, INFO, WARNING, ERROR, CRITICAL = 10, 20, 30, 40, 50
+
+class LogLevel(IntEnum):
+    """The levels as an enumeration (`awex/logging.py:25-30`); the module
+    constants below are the same numbers."""
+
+    DEBUG = 10
+    INFO = 20
+    WARNING = 30
+    ERROR = 40
+    CRITICAL = 50
+
+
+DEBUG, INFO, WARNING, ERROR, CRITICAL = (int(level) for level in LogLevel)
 _NAMES = {DEBUG: "DEBUG", INFO: "INFO", WARNING: "WARNING", ERROR: "ERROR", CRITICAL: "CRITICAL"}
 _BY_NAME = {v: k for k, v in _NAMES.items()}
 _BY_NAME["WARN"] = WARNING

@@ -38,6 +38,19 @@ def is_allowed_infer_only_alias(extra_key: str, infer_keys: set, train_keys: set
 _is_allowed_infer_only_alias = is_allowed_infer_only_alias
 
 
+def configure_logging(level=None, force: bool = True) -> None:
+    """Configure the standard library's root logger with the line format of this
+    package's own logger (`awex/util/common.py:53-58`), for host programs that log
+    through ``logging``."""
+    import logging as std_logging
+
+    std_logging.basicConfig(
+        level=std_logging.INFO if level is None else level,
+        format="%(asctime)s\t%(levelname)s %(filename)s:%(lineno)s -- %(process)d -- %(message)s",
+        force=force,
+    )
+
+
 def ensure_divisibility(numerator: int, denominator: int) -> None:
     if numerator % denominator != 0:
         raise AssertionError(f"{numerator} is not divisible by {denominator}")

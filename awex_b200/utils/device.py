@@ -85,6 +85,23 @@ def current_stream():
     return torch.cuda.current_stream() if get_device_type() == "cuda" else None
 
 
+def get_stream_class():
+    """``torch.cuda.Stream`` on CUDA, ``None`` on the CPU (`awex/util/device.py:169-176`)."""
+    return torch.cuda.Stream if get_device_type() == "cuda" else None
+
+
+def create_stream(device_id: int | None = None):
+    cls = get_stream_class()
+    if cls is None:
+        return None
+    return cls() if device_id is None else cls(device=device_id)
+
+
+def is_npu_available() -> bool:
+    """Always false: Ascend devices are not supported."""
+    return False
+
+
 @contextmanager
 def stream_context(stream):
     if stream is None or get_device_type() != "cuda":

@@ -37,6 +37,26 @@ def get_gpu_status() -> str:
         return f"nvidia-smi failed: {exc}"
 
 
+def print_gpu_status(stage: str) -> None:
+    logger.info(f"GPU status for {stage}:\n{get_gpu_status()}")
+
+
+def print_current_gpu_status(stage: str) -> None:
+    """What torch and the driver say about this process's GPU memory
+    (`awex/util/gpu.py:57-78`)."""
+    from awex_b200.utils.common import pretty_bytes
+
+    if not torch.cuda.is_available():
+        logger.info(f"Device cpu memory status for [{stage}]: no GPU")
+        return
+    free, total = torch.cuda.mem_get_info()
+    logger.info(
+        f"Device cuda memory status for [{stage}]: torch allocated {pretty_bytes(torch.cuda.memory_allocated())}, "
+        f"torch reserved {pretty_bytes(torch.cuda.memory_reserved())} device mem_free {pretty_bytes(free)}, "
+        f"device occupy {pretty_bytes(total - free)}"
+    )
+
+
 def memory_snapshot(tag: str = "") -> Dict[str, int]:
     if not torch.cuda.is_available():
         return {}

@@ -195,6 +195,12 @@ def device_from_uuid(device: Union[int, str]) -> int:
     raise RuntimeError(f"no visible GPU has UUID {device}: the process that pickled the tensor sees a GPU this one does not")
 
 
+def monkey_patch_torch_compile() -> None:
+    """Nothing to do: the reference marks two higher-order ops as cacheable for
+    ``torch.compile`` on PyTorch older than 2.8 (`awex/util/tensor_util.py:109-116`);
+    this package requires a newer PyTorch, where they are."""
+
+
 def monkey_patch_torch_reductions() -> None:
     """Make pickled CUDA-IPC tensors name their GPU by UUID instead of by index,
     so that two processes whose ``CUDA_VISIBLE_DEVICES`` differ open a handle on

@@ -350,3 +350,47 @@ def test_config_from_an_sglang_engine_and_small_helpers(monkeypatch):
     sums, nans = tensor_checksums([a, b])
     assert sums == [checksum_reference(a), checksum_reference(b)] and nans == [0, 2]
     assert tensor_checksums([]) == ([], [])
+
+
+def test_small_public_helpers_of_the_reference_surface(monkeypatch, capsys):
+    import logging as std_logging
+
+    from awex_b200 import logging as awex_logging
+    from awex_b200.engine.core import Engine
+    from awex_b200.logging import LogLevel
+    from awex_b200.utils import device, gpu
+    from awex_b200.utils.common import configure_logging
+    from awex_b200.utils.tensor_util import monkey_patch_torch_compile
+
+    assert [int(level) for level in LogLevel] == [awex_logging.DEBUG, awex_logging.INFO, awex_logging.WARNING, awex_logging.ERROR, awex_logging.CRITICAL]
+    log = awex_logging.getLogger("levels")
+    log.level = LogLevel.ERROR
+    assert not log.isEnabledFor(awex_logging.WARNING) and log.isEnabledFor(LogLevel.CRITICAL)
+
+    class Plain(Engine):
+        pass
+
+    engine = Plain()
+    assert engine.global_step == 0
+    engine.set_global_step(7)
+    assert engine.global_step == 7
+
+    monkeypatch.setenv("AWEX_DEVICE_TYPE", "cpu")
+    assert device.get_stream_class() is None and device.create_stream(0) is None and device.is_npu_available() is False
+    monkeypatch.setattr(awex_logging.getLogger("awex_b200.utils.gpu"), "level", awex_logging.INFO)
+    gpu.print_gpu_status("before")
+    gpu.print_current_gpu_status("before")
+    out = capsys.readouterr().out
+    assert "GPU status for before" in out and "memory status for [before]" in out
+    root = std_logging.getLogger()
+    handlers, level = list(root.handlers), root.level
+    try:
+        configure_logging(level=std_logging.WARNING)
+        assert root.level == std_logging.WARNING and "%(process)d" in root.handlers[0].formatter._fmt
+    finally:  # the test runner's own handlers come back
+        for handler in list(root.handlers):
+            root.removeHandler(handler)
+        for handler in handlers:
+            root.addHandler(handler)
+        root.setLevel(level)
+    assert monkey_patch_torch_compile() is None
