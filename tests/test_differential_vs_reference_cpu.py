@@ -123,10 +123,18 @@ def test_planner_agrees_with_the_reference_operation_by_operation(arch, train, i
         ref_train = [m for m in ref_train if m.name not in job.aliases]
     theirs = RefBuilder(infer_world, train_world, len(job.infer_ranks), False)
     total = 0
+    from awex.transfer.transfer_plan import compute_transfer_plan_hash as ref_hash, compute_transfer_plan_stats as ref_stats
+
+    from awex_b200.transfer.transfer_plan import compute_transfer_plan_hash, compute_transfer_plan_stats
+
     for rank in range(infer_world + train_world):
-        mine = _ops_key(ours.build_local_transfer_plan(job.infer_meta, job.train_meta, rank))
-        want = _ops_key(theirs.build_local_transfer_plan(ref_infer, ref_train, rank))
+        our_plan = ours.build_local_transfer_plan(job.infer_meta, job.train_meta, rank)
+        ref_plan = theirs.build_local_transfer_plan(ref_infer, ref_train, rank)
+        mine, want = _ops_key(our_plan), _ops_key(ref_plan)
         assert mine == want, f"transfer rank {rank}"
+        # the digest both sides log to compare their plans, and the per-peer statistics
+        assert compute_transfer_plan_hash(our_plan) == ref_hash(ref_plan), f"plan hash of transfer rank {rank}"
+        assert compute_transfer_plan_stats(our_plan) == ref_stats(ref_plan), f"plan statistics of transfer rank {rank}"
         total += len(mine)
     assert total > 0
 
