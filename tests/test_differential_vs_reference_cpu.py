@@ -590,3 +590,118 @@ def test_training_resolver_builds_the_same_metadata_on_two_tensor_parallel_ranks
                 p.kill()
     for rank, problems, count in results:
         assert problems == [] and count > 0, (rank, problems)
+
+
+# ---- sharding rules and rank descriptions ---------------------------------------------------------------
+SHARDING_NAMES = [
+    "model.embed_tokens.weight", "lm_head.weight", "model.norm.weight",
+    "model.layers.0.input_layernorm.weight", "model.layers.0.post_attention_layernorm.weight",
+    "model.layers.0.attention.query_key_value_proj.weight", "model.layers.0.attention.query_key_value_proj.bias",
+    "model.layers.0.attention.dense.weight", "model.layers.0.attention.q_norm.weight",
+    "model.layers.3.mlp.gate_proj.weight", "model.layers.3.mlp.up_proj.weight", "model.layers.3.mlp.down_proj.weight",
+    "model.layers.3.mlp.gate_up_proj.weight", "model.layers.3.mlp.gate.weight", "model.layers.3.mlp.router.weight",
+    "model.layers.3.mlp.gate.expert_bias", "model.layers.3.mlp.experts.7.gate_proj.weight",
+    "model.layers.3.mlp.experts.7.down_proj.weight", "model.layers.3.mlp.shared_experts.gate_proj.weight",
+    "model.layers.3.mlp.shared_experts.down_proj.weight", "model.layers.1.attention.kv_a_proj_with_mqa.weight",
+    "model.layers.1.attention.fused_qkv_a_proj_with_mqa.weight", "model.layers.1.attention.q_a_layernorm.weight",
+    "model.layers.1.attention.kv_b_proj.weight", "model.layers.1.attention.g_norm.weight", "model.layers.1.attention.g_proj.weight",
+    "model.layers.2.self_attn.o_proj.weight", "model.layers.2.linear_attn.in_proj_qkvz.weight", "model.layers.2.linear_attn.out_proj.weight",
+    "model.layers.2.linear_attn.conv1d.weight", "model.layers.2.linear_attn.A_log", "model.layers.2.linear_attn.dt_bias",
+    "model.layers.2.linear_attn.norm.weight", "model.visual.blocks.0.attn.qkv.weight", "model.visual.blocks.0.mlp.linear_fc1.weight",
+    "model.visual.merger.linear_fc2.weight", "model.visual.patch_embed.proj.weight", "model.language_model.layers.0.mlp.experts.gate_up_proj",
+    "model.language_model.layers.0.mlp.experts.down_proj", "something.unrecognised.weight",
+]
+SHARDING_ARCHS = ["LlamaForCausalLM", "Qwen3MoeForCausalLM", "BailingMoeV2ForCausalLM", "BailingMoeLinearV2ForCausalLM",
+                  "Qwen3VLMoeForConditionalGeneration", "Qwen3_5MoeForConditionalGeneration"]
+
+
+def _rank_kwargs(tp, ep=1, etp=1, attn_tp=None, infer=True):
+    attn_tp = attn_tp or tp
+    return dict(tp_rank=0, tp_size=tp, pp_rank=0, pp_size=1, dp_size=1, dp_rank=0, ep_rank=0, ep_size=ep, ep_tp_rank=0, ep_tp_size=etp,
+                attn_tp_rank=0, attn_tp_size=attn_tp, attn_dp_rank=0, world_size=tp, global_rank=0, local_rank=0, engine_rank=0, is_infer=infer)
+
+
+@pytest.mark.parametrize("arch", SHARDING_ARCHS)
+def test_sharding_rules_agree_name_by_name(arch):
+    """(kind, dimension, number of shards) of every kind of parameter name, for
+    the training side and both serving engines, over several parallel layouts.
+    Names that hold ``self_attn`` are left out under data-parallel attention (the
+    known difference above)."""
+    import awex.sharding.param_sharding as ref_sharding
+    import awex.sharding.rank_info as ref_rank
+    from awex.sharding.mcore_sharding import get_mcore_sharding_strategy as ref_mcore
+
+    import awex_b200.sharding.param_sharding as our_sharding
+    import awex_b200.sharding.rank_info as our_rank
+    from awex_b200.config import InferenceConfig
+    from awex_b200.sharding.extractors import get_mcore_sharding_strategy
+
+    layouts = [dict(tp=1), dict(tp=4), dict(tp=4, ep=4), dict(tp=8, ep=4, etp=2), dict(tp=4, ep=2, attn_tp=2)]
+    checked = 0
+    for layout in layouts:
+        kw = _rank_kwargs(**layout)
+        dp_attention = kw["attn_tp_size"] != kw["tp_size"]
+        config = InferenceConfig(tp_size=kw["tp_size"], ep_size=kw["ep_size"], dp_size=kw["tp_size"] // kw["attn_tp_size"],
+                                 enable_dp_attention=dp_attention, enable_dp_lm_head=dp_attention, comm_backend="nccl")
+        pairs = [(get_mcore_sharding_strategy(arch, our_rank.RankInfo(**dict(kw, is_infer=False))),
+                  ref_mcore(arch, ref_rank.RankInfo(**dict(kw, is_infer=False))))] if not dp_attention else []
+        for engine in ("sglang", "vllm"):
+            pairs.append((our_sharding.get_sharding_strategy_builder(engine)(arch, config, our_rank.RankInfo(**kw)),
+                          ref_sharding.get_sharding_strategy_builder(engine)(arch, config, ref_rank.RankInfo(**kw))))
+        for ours, theirs in pairs:
+            for name in SHARDING_NAMES:
+                if dp_attention and "self_attn" in name:
+                    continue
+                kind, dim, shards = ours.get_sharding_strategy(name)
+                ref_kind, ref_dim, ref_shards = theirs.get_sharding_strategy(name)
+                assert (kind.name, dim, shards) == (ref_kind.name, ref_dim, ref_shards), (arch, layout, ours.engine_name, name)
+                checked += 1
+    assert checked > 300
+    for name in SHARDING_NAMES:
+        assert our_sharding.get_default_sharding_dim(name) == ref_sharding.get_default_sharding_dim(name), name
+
+
+def test_rank_descriptions_from_worker_contexts_agree():
+    """What a serving worker's context says about its place in the engine, as
+    both implementations read it (SGLang and vLLM flavours, expert parallelism
+    inside and outside the TP group, context parallelism, data-parallel attention)."""
+    from awex.sharding.sglang_sharding import get_sglang_rank_info as ref_sglang
+    from awex.sharding.vllm_sharding import get_vllm_rank_info as ref_vllm
+
+    from awex_b200.sharding.extractors import get_sglang_rank_info, get_vllm_rank_info
+
+    def context(tp_rank, tp_size, server_args=None, **extra):
+        ctx = dict(tp_rank=tp_rank, tp_size=tp_size, pp_rank=0, pp_size=1, dp_rank=0, dp_size=1, attn_tp_rank=tp_rank,
+                   attn_tp_size=tp_size, attn_dp_rank=0, world_size=tp_size, global_rank=tp_rank, local_rank=tp_rank,
+                   scheduler=SimpleNamespace(server_args=server_args))
+        ctx.update(extra)
+        return ctx
+
+    def args(**kw):
+        base = dict(dp_size=1, enable_dp_attention=False, ep_size=1)
+        base.update(kw)
+        return SimpleNamespace(**base)
+
+    sglang_cases = [
+        context(3, 8, args()),
+        context(5, 8, args(ep_size=4)),                                    # expert TP of two inside each expert group
+        context(2, 4, args(ep_size=4)),
+        context(1, 4, args(dp_size=2, enable_dp_attention=True), attn_tp_rank=1, attn_tp_size=2, attn_dp_rank=0, dp_size=2),
+        context(0, 2, args(context_parallel_size=2, context_parallel_mode="ulysses"), cp_rank=1),
+        context(0, 2, args(), cp_size=2, cp_rank=1),                       # mode left to the default of a ring
+    ]
+    for ctx in sglang_cases:
+        assert dataclasses.asdict(get_sglang_rank_info(ctx, 1)) == dataclasses.asdict(ref_sglang(ctx, 1)), ctx
+    with pytest.raises(ValueError):
+        get_sglang_rank_info(context(0, 2, args(dp_size=2)), 0)
+    with pytest.raises(ValueError):
+        ref_sglang(context(0, 2, args(dp_size=2)), 0)
+    vllm_cases = [
+        context(1, 2),
+        context(1, 2, ep_size=4, ep_rank=3),
+        context(1, 2, ep_size=4, ep_rank=3, ep_tp_size=2, ep_tp_rank=1),
+        context(0, 1, ep_size=1, ep_rank=5, ep_tp_size=4, ep_tp_rank=2),      # no expert parallelism: the EP fields are reset
+        context(0, 4, dp_size=2, dp_rank=1, cp_size=2, cp_rank=1, cp_mode="ulysses"),
+    ]
+    for ctx in vllm_cases:
+        assert dataclasses.asdict(get_vllm_rank_info(ctx, 2)) == dataclasses.asdict(ref_vllm(ctx, 2)), ctx
