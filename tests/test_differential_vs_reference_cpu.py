@@ -705,3 +705,62 @@ def test_rank_descriptions_from_worker_contexts_agree():
     ]
     for ctx in vllm_cases:
         assert dataclasses.asdict(get_vllm_rank_info(ctx, 2)) == dataclasses.asdict(ref_vllm(ctx, 2)), ctx
+
+
+# ---- which decoder layers a pipeline stage holds ---------------------------------------------------------------
+def _outcome(fn, *args, **kwargs):
+    try:
+        return ("ok", fn(*args, **kwargs))
+    except (ValueError, AssertionError, ZeroDivisionError) as exc:
+        return ("error", type(exc).__name__)
+
+
+def test_pipeline_stage_layer_ids_agree_over_a_grid_of_split_settings():
+    """Even and uneven splits, first/last stage sizes, embedding / loss counted as
+    layers, virtual stages, explicit layouts: for every (pipeline rank, virtual
+    stage) both implementations name the same global layers, and settings one
+    refuses the other refuses too."""
+    import itertools
+
+    import awex.sharding.rank_info as ref_rank
+    from awex.converter.mcore_converter import _process_mcore_pp_name as ref_name, _resolve_pp_stage_global_layer_ids as ref_ids
+
+    import awex_b200.sharding.rank_info as our_rank
+    from awex_b200.converter.pp_layout import process_mcore_pp_name, resolve_pp_stage_global_layer_ids
+
+    checked = refused = 0
+    grid = itertools.product([8, 12, 14], [1, 2, 4], [None, 2], [None, 1, 3], [None, 2, 3], [False, True], [False, True])
+    for layers, pp, vp, first, last, embed, loss in grid:
+        tf = SimpleNamespace(num_layers=layers, num_layers_in_first_pipeline_stage=first, num_layers_in_last_pipeline_stage=last,
+                             account_for_embedding_in_pipeline_split=embed, account_for_loss_in_pipeline_split=loss,
+                             virtual_pipeline_model_parallel_size=vp, pipeline_model_parallel_layout=None)
+        hf = SimpleNamespace(num_hidden_layers=layers)
+        for pp_rank in range(pp):
+            for vp_stage in range(vp or 1):
+                kw = dict(_rank_kwargs(tp=1, infer=False), pp_rank=pp_rank, pp_size=pp, world_size=pp, global_rank=pp_rank)
+                got = _outcome(resolve_pp_stage_global_layer_ids, our_rank.RankInfo(**kw), hf, tf, vp_stage)
+                want = _outcome(ref_ids, ref_rank.RankInfo(**kw), hf, tf, vp_stage)
+                assert got[0] == want[0] and (got[0] == "error" or got[1] == want[1]), ((layers, pp, vp, first, last, embed, loss), pp_rank, vp_stage, got, want)
+                checked += 1
+                refused += got[0] == "error"
+    assert checked > 1500 and 0 < refused < checked
+    # explicit layouts: a list of stages, each a list of layer kinds ("E" embedding, "t" decoder, "L" loss)
+    for layout, pp in (([["embedding", "decoder", "decoder"], ["decoder"], ["decoder", "decoder", "decoder"], ["decoder", "loss"]], 4),
+                       ([["embedding", "decoder"], ["decoder", "decoder"], ["decoder", "decoder"], ["decoder", "decoder", "loss"]], 2)):
+        tf = SimpleNamespace(num_layers=7, pipeline_model_parallel_layout=layout, virtual_pipeline_model_parallel_size=None)
+        hf = SimpleNamespace(num_hidden_layers=7)
+        vp_size = len(layout) // pp
+        for pp_rank in range(pp):
+            for vp_stage in range(vp_size):
+                kw = dict(_rank_kwargs(tp=1, infer=False), pp_rank=pp_rank, pp_size=pp, world_size=pp, global_rank=pp_rank)
+                got = _outcome(resolve_pp_stage_global_layer_ids, our_rank.RankInfo(**kw), hf, tf, vp_stage)
+                want = _outcome(ref_ids, ref_rank.RankInfo(**kw), hf, tf, vp_stage)
+                assert got == want and got[0] == "ok", (layout, pp_rank, vp_stage, got, want)
+    # renaming a stage-local layer index
+    stage_map = {(1, 0): {0: 4, 1: 5}, (1, 1): {0: 12}}
+    kw = dict(_rank_kwargs(tp=1, infer=False), pp_rank=1, pp_size=2)
+    for name, vp_stage in (("decoder.layers.1.mlp.linear_fc1.weight", 0), ("decoder.layers.0.self_attention.linear_qkv.weight", 1),
+                           ("embedding.word_embeddings.weight", 0), ("decoder.layers.7.mlp.linear_fc2.weight", 0)):
+        got = _outcome(process_mcore_pp_name, name, our_rank.RankInfo(**kw), None, None, vp_stage, stage_map)
+        want = _outcome(ref_name, name, ref_rank.RankInfo(**kw), None, None, vp_stage, stage_map)
+        assert got == want, (name, got, want)
