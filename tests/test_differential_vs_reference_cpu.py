@@ -764,3 +764,77 @@ def test_pipeline_stage_layer_ids_agree_over_a_grid_of_split_settings():
         got = _outcome(process_mcore_pp_name, name, our_rank.RankInfo(**kw), None, None, vp_stage, stage_map)
         want = _outcome(ref_name, name, ref_rank.RankInfo(**kw), None, None, vp_stage, stage_map)
         assert got == want, (name, got, want)
+
+
+# ---- the alignment contract, the configuration schema, packed tensors ---------------------------------------------
+def test_metadata_alignment_contract_refuses_the_same_pairs():
+    """Training and inference metadata that both implementations accept, and
+    seeded mismatches (a missing name, an extra name that is no alias, another
+    element count, shape or dtype) that both refuse."""
+    import copy
+
+    import awex.meta.weight_meta as ref_meta
+    from awex.util.common import check_train_infer_params_meta as ref_check
+
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.simulate import InferLayout, SimulatedJob, TrainLayout
+    from awex_b200.utils.common import check_train_infer_params_meta
+
+    job = SimulatedJob(get_arch("tiny-llama"), TrainLayout(tp=2), InferLayout(tp=1), dtype=torch.float32, device="meta")
+
+    def verdicts(train, infer, strict=False):
+        ours = _outcome(check_train_infer_params_meta, train, infer, raise_exception=True, strict_key_match=strict)[0]
+        theirs = _outcome(ref_check, _to_reference(train, ref_meta), _to_reference(infer, ref_meta), raise_exception=True, strict_key_match=strict)[0]
+        return ours, theirs
+
+    train, infer = job.train_meta, job.infer_meta
+    assert verdicts(train, infer) == ("ok", "ok") and verdicts(train, infer, strict=True) == ("ok", "ok")
+    assert verdicts(train, infer[1:]) == ("error", "error")                       # a trained parameter nobody serves
+    extra = copy.deepcopy(infer[3])
+    extra.name = "model.layers.0.something_else.weight"
+    assert verdicts(train, infer + [extra]) == ("error", "error")                 # an extra name that is no alias
+    tied = copy.deepcopy(next(m for m in infer if m.name == "model.embed_tokens.weight"))
+    tied.name = "lm_head.weight"
+    no_head = [m for m in train if m.name != "lm_head.weight"]
+    assert verdicts(no_head, infer) == ("ok", "ok")                               # the tied head is an allowed infer-only name
+    assert verdicts(no_head, infer, strict=True) == ("error", "error")
+    for field, value in (("global_numel", 7), ("global_shape", (3, 5)), ("dtype", torch.float16)):
+        changed = copy.deepcopy(infer)
+        setattr(changed[2], field, value)
+        assert verdicts(train, changed) == ("error", "error"), field
+
+
+def test_configuration_schema_has_every_field_of_the_reference_with_its_default():
+    from awex.config import InferenceConfig as RefConfig
+
+    from awex_b200.config import InferenceConfig
+
+    ours = {f.name: f for f in dataclasses.fields(InferenceConfig)}
+    for field in dataclasses.fields(RefConfig):
+        assert field.name in ours, field.name
+        if field.default is not dataclasses.MISSING:
+            assert ours[field.name].default == field.default, field.name
+    server_args = SimpleNamespace(tp_size=2, pp_size=1, dp_size=1, ep_size=1, enable_dp_attention=False, nnodes=1, node_rank=0, something_else=1)
+    mine = InferenceConfig.from_sgl_server_args(server_args, comm_backend="file")
+    theirs = RefConfig.from_sgl_server_args(server_args, comm_backend="file")
+    for field in dataclasses.fields(RefConfig):
+        assert getattr(mine, field.name) == getattr(theirs, field.name), field.name
+
+
+def test_packed_tensor_groups_cross_between_the_two_implementations():
+    """Tensors packed by dtype by one implementation are taken apart by the
+    other: the metadata that travels with the groups means the same."""
+    from awex.util.tensor_util import group_tensors_by_shape_and_dtype as ref_group, reconstruct_tensors_from_groups as ref_rebuild
+
+    from awex_b200.utils.tensor_util import group_tensors_by_shape_and_dtype, reconstruct_tensors_from_groups
+
+    g = torch.Generator().manual_seed(3)
+    tensors = [torch.randn(4, 6, generator=g), torch.randn(7, generator=g).to(torch.bfloat16), torch.randn(2, 3, 5, generator=g),
+               torch.arange(11, dtype=torch.int32), torch.randn(1, 9, generator=g).to(torch.bfloat16), torch.randn(5, 5, generator=g)[:, 1:3]]
+    for pack, unpack in ((group_tensors_by_shape_and_dtype, ref_rebuild), (ref_group, reconstruct_tensors_from_groups)):
+        for limit in (5 * 1024**3, 64):  # one group per dtype, and groups cut at a small size bound
+            groups, metadata = pack(tensors, max_tensor_size=limit)
+            back = unpack(groups, metadata)
+            assert len(back) == len(tensors)
+            for a, b in zip(back, tensors):
+                assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
