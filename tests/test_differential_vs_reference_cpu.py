@@ -838,3 +838,29 @@ def test_packed_tensor_groups_cross_between_the_two_implementations():
             assert len(back) == len(tensors)
             for a, b in zip(back, tensors):
                 assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
+
+
+def test_nan_scans_and_difference_reports_reach_the_same_verdicts():
+    from awex.util.tensor_util import check_and_log_nan_values as ref_nan, compare_and_log_tensor_differences as ref_compare
+
+    from awex_b200.utils.tensor_util import check_and_log_nan_values, compare_and_log_tensor_differences
+
+    g = torch.Generator().manual_seed(9)
+    base = torch.randn(6, 7, generator=g)
+    with_nan = base.clone()
+    with_nan[2, 3] = float("nan")
+    for tensor in (base, with_nan, torch.full((3,), float("inf")), torch.full((2, 2), float("nan")), torch.zeros(0), base.to(torch.bfloat16)):
+        assert check_and_log_nan_values(tensor, "t", " after update") == ref_nan(tensor, "t", " after update")
+    near = base + 1e-7
+    far = base.clone()
+    far[1, 1] += 0.5
+    cases = [(base, base.clone(), {}), (base, near, {}), (base, near, dict(exact_match=True)), (base, far, {}), (base, far, dict(atol=1.0)),
+             (base, base[:, :3], {}), (base, near, dict(atol=0.0, rtol=0.0)), (base.to(torch.bfloat16), base.to(torch.bfloat16), dict(exact_match=True))]
+    for a, b, kw in cases:
+        ours, theirs = compare_and_log_tensor_differences(a, b, "t", **kw), ref_compare(a, b, "t", **kw)
+        if kw.get("exact_match") and not torch.equal(a, b):
+            # Known difference: after a failed bitwise comparison the reference looks for elements outside the
+            # tolerances, finds none and reports agreement (`awex/util/tensor_util.py:467-537`); exact means exact here.
+            assert (ours, theirs) == (False, True)
+            continue
+        assert ours == theirs, kw
