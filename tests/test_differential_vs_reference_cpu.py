@@ -864,3 +864,50 @@ def test_nan_scans_and_difference_reports_reach_the_same_verdicts():
             assert (ours, theirs) == (False, True)
             continue
         assert ours == theirs, kw
+
+
+def test_mbridge_loaders_fill_a_model_with_the_same_values():
+    """A bridge that maps Megatron names to one or several checkpoint names
+    (fused QKV = q + k + v along the rows, fused gate/up), a critic whose output
+    layer stays untouched, a reader that serves tensors by name."""
+    from awex.mbridge_loader import load_weights_from_hf_with_mbridge as ref_load
+
+    from awex_b200.mbridge_loader import load_weights_from_hf_with_mbridge
+
+    g = torch.Generator().manual_seed(21)
+    checkpoint = {name: torch.randn(shape, generator=g) for name, shape in {
+        "q": (8, 6), "k": (4, 6), "v": (4, 6), "gate": (10, 6), "up": (10, 6), "down": (6, 10), "norm": (6,), "head": (12, 6)}.items()}
+    hf_names = {"decoder.qkv.weight": ["q", "k", "v"], "decoder.fc1.weight": ["gate", "up"], "decoder.fc2.weight": "down",
+                "decoder.norm.weight": "norm", "output_layer.weight": "head"}
+
+    class Bridge:
+        def _get_actual_hf_path(self, path):
+            return path + "/resolved"
+
+        def _weight_name_mapping_mcore_local_to_global(self, model):
+            return {name: name for name in model.state_dict()} | {"decoder.absent.weight": "decoder.absent.weight"}
+
+        def _weight_name_mapping_mcore_to_hf(self, name):
+            return hf_names[name]
+
+    def reader(path, name):
+        assert path == "ckpt/resolved"
+        return checkpoint[name].to(torch.bfloat16)  # the loader casts to the parameter's dtype
+
+    def model():
+        m = torch.nn.Module()
+        m.register_parameter("placeholder", None)
+        for name, shape in {"decoder.qkv.weight": (16, 6), "decoder.fc1.weight": (20, 6), "decoder.fc2.weight": (6, 10),
+                            "decoder.norm.weight": (6,), "output_layer.weight": (12, 6)}.items():
+            m.register_buffer(name.replace(".", "_"), torch.zeros(shape))
+        m.state_dict = lambda: {name: getattr(m, name.replace(".", "_")) for name in hf_names}
+        return m
+
+    for critic in (False, True):
+        ours, theirs = model(), model()
+        load_weights_from_hf_with_mbridge(Bridge(), [ours], "ckpt", reader=reader, is_critic=critic)
+        ref_load(Bridge(), [theirs], "ckpt", reader=reader, is_critic=critic)
+        for name in hf_names:
+            assert torch.equal(ours.state_dict()[name], theirs.state_dict()[name]), (critic, name)
+        assert bool(ours.state_dict()["output_layer.weight"].any()) == (not critic)
+        assert torch.equal(ours.state_dict()["decoder.qkv.weight"], torch.cat([checkpoint[n] for n in "qkv"]).to(torch.bfloat16).float())
