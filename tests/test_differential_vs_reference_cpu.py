@@ -911,3 +911,36 @@ def test_mbridge_loaders_fill_a_model_with_the_same_values():
             assert torch.equal(ours.state_dict()[name], theirs.state_dict()[name]), (critic, name)
         assert bool(ours.state_dict()["output_layer.weight"].any()) == (not critic)
         assert torch.equal(ours.state_dict()["decoder.qkv.weight"], torch.cat([checkpoint[n] for n in "qkv"]).to(torch.bfloat16).float())
+
+
+def test_vllm_plugin_request_schema_and_rpc_envelope_agree():
+    """The two HTTP request bodies (field names and defaults), what may cross
+    vLLM's engine-core RPC (dtypes and devices as strings, tuples as lists) and
+    which keyword arguments reach a worker method."""
+    pytest.importorskip("vllm")
+    import awex.vllm_plugin as ref_plugin
+
+    from awex_b200 import vllm_plugin
+
+    for ours, theirs in ((vllm_plugin.AwexInitRequest, ref_plugin.AwexInitRequest), (vllm_plugin.AwexUpdateRequest, ref_plugin.AwexUpdateRequest)):
+        assert list(ours.model_fields) == list(theirs.model_fields)
+        for name, field in theirs.model_fields.items():
+            assert ours.model_fields[name].default == field.default and ours.model_fields[name].is_required() == field.is_required(), name
+    payload = {"dtype": torch.bfloat16, "device": torch.device("cpu"), "shape": (2, 3), "nested": [{"d": torch.float8_e4m3fn, "n": None, "x": 1.5}], "s": "text"}
+    assert vllm_plugin.sanitize_for_ipc(payload) == ref_plugin._sanitize_for_ipc(payload)
+    # worker methods this framework keeps from the reference's table accept the same keyword arguments
+    for method, signature in ref_plugin._AWEX_WORKER_SIGNATURES.items():
+        if method not in vllm_plugin.AWEX_WORKER_SIGNATURES:
+            continue
+        kwargs = {name: 1 for name in signature["required"] + signature["optional"]}
+        kwargs["not_for_the_worker"] = 2
+        ours = _outcome(vllm_plugin.filter_awex_kwargs, method, dict(kwargs))
+        theirs = _outcome(ref_plugin._filter_awex_kwargs, method, dict(kwargs))
+        assert ours[0] == theirs[0] == "ok" and set(theirs[1]) <= set(ours[1]) and "not_for_the_worker" not in ours[1], method
+        # what this framework requires, the reference requires too (the validation calls take their step as an option here)
+        assert set(vllm_plugin.AWEX_WORKER_SIGNATURES[method]["required"]) <= set(signature["required"]), method
+        without_required = {name: 1 for name in signature["optional"]}
+        if vllm_plugin.AWEX_WORKER_SIGNATURES[method]["required"]:
+            assert _outcome(vllm_plugin.filter_awex_kwargs, method, without_required)[0] == "error"
+            assert _outcome(ref_plugin._filter_awex_kwargs, method, without_required)[0] == "error"
+    assert set(ref_plugin._AWEX_WORKER_METHODS) & set(vllm_plugin.AWEX_WORKER_METHODS)
