@@ -36,11 +36,13 @@ class SyntheticTrainEngine(MegatronEngine):
         if self.rank_info.global_rank == 0:
             from awex_b200.utils.safetensors_io import save_checkpoint
 
-            save_checkpoint(path, canonical_state_dict(self.arch, CanonicalWeights(self.arch, self.dtype, self.device, self.seed)))
+            weights = CanonicalWeights(self.arch, self.dtype, self.device, self.seed, getattr(self, "step", 0))
+            save_checkpoint(path, canonical_state_dict(self.arch, weights))
 
     def regenerate(self, step: int) -> None:
         """Overwrite the shards in place with the weights of ``step`` (a stand-in
         for an optimizer step; addresses do not change)."""
+        self.step = step  # a checkpoint written from now on holds these weights
         fresh = build_megatron_model(self.arch, self.rank_info, self.dtype, self.device, self.seed, step=step)
         for (_, old), (_, new) in zip(self.model.named_parameters(), fresh.named_parameters()):
             old.copy_(new)

@@ -465,3 +465,80 @@ def test_vllm_integration_script_speaks_the_plugin_protocol(monkeypatch, tmp_pat
     import shutil
 
     shutil.rmtree(run.workdir)
+
+
+def test_sglang_integration_script_runs_against_a_stand_in_engine(monkeypatch, tmp_path):
+    """``tests/weights_exchange_it.py`` end to end on the CPU with the file
+    backend: a stand-in ``sglang`` package whose ``Engine`` keeps what it loads
+    from disk, wrapped in :class:`SGLangEngine` by the script; every exchange's
+    checkpoint must hold the weights the training side had at that step."""
+    import dataclasses
+    import importlib.util
+    import os
+    import sys
+
+    import torch
+
+    from awex_b200.synthetic.arch import get_arch
+    from awex_b200.synthetic.models import CanonicalWeights, canonical_state_dict
+    from awex_b200.utils.safetensors_io import load_checkpoint
+
+    @dataclasses.dataclass
+    class ServerArgs:
+        model_path: str = ""
+        skip_tokenizer_init: bool = False
+        load_format: str = "auto"
+        dtype: str = "auto"
+        device: str = "cuda"
+        mem_fraction_static: float = 0.9
+        tp_size: int = 1
+        pp_size: int = 1
+        dp_size: int = 1
+        ep_size: int = 1
+        random_seed: int = 0
+        log_level: str = "info"
+
+    engines = []
+
+    class Engine:
+        def __init__(self, **kwargs):
+            self.server_args = ServerArgs(**kwargs)  # refuses what the real dataclass would not know
+            self.tokenizer_manager = types.SimpleNamespace(model_config=types.SimpleNamespace(architectures=["LlamaForCausalLM"]))
+            self.loaded, self.down = [], False
+            engines.append(self)
+
+        def update_weights_from_disk(self, model_path, load_format=None):
+            self.loaded.append(load_checkpoint(model_path))
+
+        def release_memory_occupation(self, tags=None):
+            pass
+
+        def resume_memory_occupation(self, tags=None):
+            pass
+
+        def execute_task_in_model_worker(self, fn, **kwargs):
+            return [fn(**kwargs)]
+
+        def shutdown(self):
+            self.down = True
+
+    package, srt, server_args = types.ModuleType("sglang"), types.ModuleType("sglang.srt"), types.ModuleType("sglang.srt.server_args")
+    package.Engine, package.srt, srt.server_args, server_args.ServerArgs = Engine, srt, server_args, ServerArgs
+    for name, module in (("sglang", package), ("sglang.srt", srt), ("sglang.srt.server_args", server_args)):
+        monkeypatch.setitem(sys.modules, name, module)
+    monkeypatch.setenv("AWEX_DEVICE_TYPE", "cpu")
+    monkeypatch.setattr("tempfile.mkdtemp", lambda prefix="": str(tmp_path))
+    spec = importlib.util.spec_from_file_location("weights_exchange_it", os.path.join(os.path.dirname(__file__), "weights_exchange_it.py"))
+    script = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(script)
+    args = types.SimpleNamespace(comm_backend="file", arch="tiny-llama", layers=0, tp=1, steps=2, mem_fraction_static=0.5, debug=False)
+    assert script.main(args) == 0
+    (engine,) = engines
+    assert engine.down and engine.server_args.load_format == "dummy" and engine.server_args.device == "cpu"
+    assert not hasattr(engine.server_args, "attention_backend")  # settings the engine's arguments do not know were dropped
+    arch = get_arch("tiny-llama")
+    assert len(engine.loaded) == 3  # the first exchange and two more, each after an "optimizer step"
+    for step, got in zip((0, 2, 3), engine.loaded):
+        want = canonical_state_dict(arch, CanonicalWeights(arch, torch.bfloat16, "cpu", 0, step))
+        assert set(got) == set(want)
+        assert all(torch.equal(got[name], want[name]) for name in want), step

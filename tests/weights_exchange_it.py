@@ -68,14 +68,16 @@ class WeightsExchangeIT:
         from awex_b200.meta.meta_server import MetaServer
         from awex_b200.synthetic.harness import SyntheticTrainEngine
         from awex_b200.synthetic.topology import train_rank_infos
+        from awex_b200.utils import device as device_util
         from awex_b200.writer.weights_writer import get_weights_exchange_writer
 
+        on_gpu = device_util.get_device_type() == "cuda"
         self.meta_server = MetaServer("127.0.0.1", 0)
         self.meta_server.start()
         meta_addr = f"127.0.0.1:{self.meta_server.port}"
         model_dir = arch.write_model_dir(os.path.join(self.workdir, "model"))
         settings = {
-            "model_path": model_dir, "skip_tokenizer_init": True, "load_format": "dummy", "dtype": "bfloat16", "device": "cuda",
+            "model_path": model_dir, "skip_tokenizer_init": True, "load_format": "dummy", "dtype": "bfloat16", "device": "cuda" if on_gpu else "cpu",
             "mem_fraction_static": self.args.mem_fraction_static, "tp_size": self.args.tp, "pp_size": 1, "dp_size": 1, "ep_size": 1,
             "random_seed": 47, "log_level": "info", "attention_backend": "torch_native",
         }
@@ -87,8 +89,9 @@ class WeightsExchangeIT:
         self.inference = SGLangEngine(config, self.sgl)
         self.inference.initialize()
         # the training shard lives on the GPU after the engine's
-        device = f"cuda:{self.args.tp}"
-        torch.cuda.set_device(self.args.tp)
+        device = f"cuda:{self.args.tp}" if on_gpu else "cpu"
+        if on_gpu:
+            torch.cuda.set_device(self.args.tp)
         self.training = SyntheticTrainEngine(arch, train_rank_infos(tp=1)[0], meta_addr, dtype=torch.bfloat16, device=device,
                                              comm_backend=self.args.comm_backend, enable_debug_mode=self.args.debug)
         self.writer = get_weights_exchange_writer(self.training)
@@ -182,4 +185,8 @@ if __name__ == "__main__":
     parser.add_argument("--steps", type=int, default=10, help="exchanges after the first")
     parser.add_argument("--mem-fraction-static", type=float, default=0.5)
     parser.add_argument("--debug", action="store_true", help="enable_debug_mode on both sides (metadata and plan dumps)")
-    sys.exit(main(parser.parse_args()))
+    parser.add_argument("--device-backend", choices=["auto", "cuda", "cpu"], default="auto", help="device of both sides (auto: CUDA when there is one)")
+    cli = parser.parse_args()
+    if cli.device_backend != "auto":
+        os.environ["AWEX_DEVICE_TYPE"] = cli.device_backend
+    sys.exit(main(cli))
