@@ -23,3 +23,17 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _interpreter_paths_are_left_alone():
+    """Ranks that later tests start with ``spawn`` inherit ``sys.path``: a test
+    module that leaves one of this repository's directories behind (the stand-in
+    packages under ``baseline/``, say) changes what those ranks import."""
+
+    def ours():
+        return [p for p in sys.path if os.path.abspath(p).startswith(ROOT)]
+
+    before = ours()
+    yield
+    assert ours() == before, f"a test module left sys.path changed: {before} -> {ours()}"
