@@ -452,7 +452,7 @@ def run_distributed(args):
     # the busiest sender's bytes that cross NVLink (destinations on its own GPU do not)
     egress = _max_over_ranks(float(getattr(writer.transport, "bytes_remote", writer.transport.bytes_out)) if writer is not None else 0.0, ctl)
     n_desc = _sum_over_ranks(float(getattr(writer.transport, "n_desc", 0)) if writer is not None else 0.0, ctl)
-    launches = (1 if writer is not None else 0) + (infer_engine.schedulers[0].awes_weights_reader.transport.gpu_launches_per_update() if reader is not None else 0)
+    launches = (getattr(writer.transport, "gpu_launches_per_update", lambda: 1)() if writer is not None else 0) + (infer_engine.schedulers[0].awes_weights_reader.transport.gpu_launches_per_update() if reader is not None else 0)
     launches_total = _sum_over_ranks(float(launches), ctl)
     roofline = _roofline(writer, reader, infer_engine, ms, ctl)
     clock_summary = clocks.summary() if clocks is not None else {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["cpu run"], "samples": 0}

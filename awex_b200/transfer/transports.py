@@ -487,7 +487,9 @@ class PeerStoreSender:
         return epoch
 
     def gpu_launches_per_update(self) -> int:
-        return 1
+        """The transfer kernel, plus the lean block-fp8 kernel where the table has a part for it."""
+        program = getattr(self, "program", None)
+        return 1 + (1 if getattr(program, "lean", None) is not None else 0)
 
     def close(self) -> None:
         if getattr(self, "importer", None) is not None:
