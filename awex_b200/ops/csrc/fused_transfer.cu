@@ -1,10 +1,13 @@
 // Fused resharding transfer for sm_100a.
 //
 // One persistent launch per (update, source GPU) walks a descriptor table
-// (xfer_desc.h).  Each CTA owns a contiguous range of tiles.  A tile is staged
-// from this GPU's HBM into shared memory with bulk-async copies
-// (cp.async.bulk global->shared, completion on an mbarrier) through a 6-deep
-// ring, then leaves either
+// (xfer_desc.h).  Which tiles a CTA works on comes from its entry of a per-CTA
+// plan the host builds (one group of CTAs per destination GPU, round-robin
+// chunks of tiles inside a group), or, without a plan, from an even split of
+// the tile range.  A tile is staged from this GPU's HBM into shared memory with
+// bulk-async copies (cp.async.bulk global->shared, or one tiled
+// cp.async.bulk.tensor load where the slab has a tensor map; completion on an
+// mbarrier) through a ring of 32 KiB stages, then leaves either
 //   * unchanged, by bulk-async copies shared->global whose destination may be a
 //     peer GPU's memory mapped over NVLink (pure layout moves: slices, row
 //     permutations, column slabs), or
